@@ -1,0 +1,83 @@
+// Shared declarations of the CUDA sources: dtype codes, conversions, reductions
+// with a fixed order, and the error convention of the C entry points.
+//
+// Every entry point is `extern "C" int lp_*(...)`: 0 on success, a positive
+// cudaError_t when a launch failed, -1 when the arguments were refused; the
+// text of the last refusal or failure is kept per library (lp_last_error).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define LP_F32 0
+#define LP_BF16 1
+
+#ifndef LP_ERROR_DEFINED
+#define LP_ERROR_DEFINED
+static char lp_error_text[512] = "";
+extern "C" const char* lp_last_error() { return lp_error_text; }
+#endif
+
+#define LP_REFUSE(...)                                            \
+    do {                                                          \
+        snprintf(lp_error_text, sizeof(lp_error_text), __VA_ARGS__); \
+        return -1;                                                \
+    } while (0)
+
+static inline int lp_check_launch(const char* what) {
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) {
+        snprintf(lp_error_text, sizeof(lp_error_text), "%s: %s", what, cudaGetErrorString(err));
+        return (int)err;
+    }
+    return 0;
+}
+
+__device__ __forceinline__ float lp_to_float(float v) { return v; }
+__device__ __forceinline__ float lp_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T lp_from_float(float v);
+template <> __device__ __forceinline__ float lp_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 lp_from_float<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// Sum over a warp: a butterfly, so every lane ends with the same value and the
+// order of additions does not depend on anything but the lane count.
+__device__ __forceinline__ float lp_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float lp_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats. Warp sums
+// are added in warp order by every thread, so all threads get the same value.
+__device__ __forceinline__ float lp_block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = lp_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < nwarps; ++w) total += scratch[w];
+    return total;
+}
+__device__ __forceinline__ float lp_block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = lp_warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = -INFINITY;
+    for (int w = 0; w < nwarps; ++w) total = fmaxf(total, scratch[w]);
+    return total;
+}

@@ -1,0 +1,154 @@
+// Small memory-bound kernels of the step: embedding rows, RMS norm, and the
+// rotation of queries and keys together with the write of keys and values into
+// the paged cache. All arithmetic is float32; only loads and stores convert.
+//
+// Counterparts in the reference (src/main/resources/kernels/cuda/): rmsnorm.cu:6-46,
+// rope.cu:11-52, attention.cu:114-128 (kv_cache_update); the embedding row is
+// gathered on the host there (inference/InferenceEngine.java:199-201).
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int d) {
+    const int t = blockIdx.x;
+    const long long row = tokens[t];
+    const TW* src = table + row * d;
+    float* dst = out + (long long)t * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = lp_to_float(src[i]);
+}
+
+extern "C" int lp_embed(const void* table, int table_dtype, const int* tokens, float* out, int T, int d,
+                        cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d <= 0) LP_REFUSE("embed: width %d", d);
+    const int threads = d >= 1024 ? 256 : 128;
+    if (table_dtype == LP_F32)
+        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, d);
+    else if (table_dtype == LP_BF16)
+        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, d);
+    else
+        LP_REFUSE("embed: table dtype code %d", table_dtype);
+    return lp_check_launch("embed");
+}
+
+// ---------------------------------------------------------------- RMS norm
+// out[r, i] = x[row(r), i] * (1 / sqrt(sum_i x^2 / d + eps)) * w[i]; one block per row.
+// When `add` is given, x[row] += add[row] first (in float32) and the sum is stored back:
+// the residual sum and the norm that follows it in one pass.
+template <typename TOut, typename TAdd>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const TAdd* __restrict__ add,
+                               const int* __restrict__ rows, const float* __restrict__ w,
+                               TOut* __restrict__ out, int d, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long long src = rows ? rows[r] : r;
+    float* xr = x + src * d;
+    float ss = 0.f;
+    if (add) {
+        const TAdd* ar = add + src * d;
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = xr[i] + lp_to_float(ar[i]);
+            xr[i] = v;
+            ss += v * v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = xr[i];
+            ss += v * v;
+        }
+    }
+    ss = lp_block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    TOut* o = out + (long long)r * d;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = lp_from_float<TOut>(xr[i] * scale * w[i]);
+}
+
+extern "C" int lp_rmsnorm(float* x, const void* add, int add_dtype, const int* rows, const float* w, void* out,
+                          int out_dtype, int R, int d, float eps, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (d <= 0) LP_REFUSE("rmsnorm: width %d", d);
+    if (add && rows) LP_REFUSE("rmsnorm: a fused residual add cannot be combined with a row selection");
+    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
+#define LP_LAUNCH_NORM(TOUT, TADD) \
+    rmsnorm_kernel<TOUT, TADD><<<R, threads, 0, stream>>>(x, (const TADD*)add, rows, w, (TOUT*)out, d, eps)
+    if (out_dtype == LP_F32 && add_dtype == LP_F32) LP_LAUNCH_NORM(float, float);
+    else if (out_dtype == LP_F32 && add_dtype == LP_BF16) LP_LAUNCH_NORM(float, __nv_bfloat16);
+    else if (out_dtype == LP_BF16 && add_dtype == LP_F32) LP_LAUNCH_NORM(__nv_bfloat16, float);
+    else if (out_dtype == LP_BF16 && add_dtype == LP_BF16) LP_LAUNCH_NORM(__nv_bfloat16, __nv_bfloat16);
+    else LP_REFUSE("rmsnorm: dtype codes out=%d add=%d", out_dtype, add_dtype);
+#undef LP_LAUNCH_NORM
+    return lp_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------- rotation + cache write
+// One block per (token, head) of the fused projection output
+//   qkv[t] = [ H query heads | G key heads | G value heads ] x head_dim   (float32).
+// Queries and keys: the first `rd` features of a head are rotated by
+// angle = float(position) * inv_freq[pair]; the rest pass through. Queries go to
+// q_out[t, h, :]; keys and values go to the page of the token's sequence that holds
+// its position:  pages[page][0|1][g][position % page_size][:].
+template <typename TQ, typename TKV>
+__global__ void rope_cache_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ inv_freq,
+                                  const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                                  const int* __restrict__ page_table, int pt_stride, TQ* __restrict__ q_out,
+                                  TKV* __restrict__ pages, int H, int G, int hd, int rd, int interleaved,
+                                  int page_size) {
+    const int t = blockIdx.x;
+    const int head = blockIdx.y;             // 0..H-1 queries, then G keys, then G values
+    const int pos = positions[t];
+    const float* src = qkv + (long long)t * ld + (long long)head * hd;
+    const bool is_q = head < H;
+    const bool is_v = head >= H + G;
+    long long dst_off = 0;
+    if (!is_q) {
+        const int g = is_v ? head - H - G : head - H;
+        const int page = page_table[(long long)seq_ids[t] * pt_stride + pos / page_size];
+        dst_off = ((((long long)page * 2 + (is_v ? 1 : 0)) * G + g) * page_size + (pos % page_size)) * hd;
+    }
+    const int half = rd >> 1;
+    for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+        float val = src[e];
+        if (!is_v && e < rd) {
+            int pair, partner;
+            bool first;
+            if (interleaved) { pair = e >> 1; first = (e & 1) == 0; partner = e ^ 1; }
+            else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
+            const float angle = (float)pos * inv_freq[pair];
+            float sn, cs;
+            sincosf(angle, &sn, &cs);
+            const float other = src[partner];
+            val = first ? val * cs - other * sn : other * sn + val * cs;
+        }
+        if (is_q) q_out[((long long)t * H + head) * hd + e] = lp_from_float<TQ>(val);
+        else pages[dst_off + e] = lp_from_float<TKV>(val);
+    }
+}
+
+extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_freq, const int* positions,
+                                   const int* seq_ids, const int* page_table, int pt_stride, void* q_out,
+                                   int q_dtype, void* pages, int kv_dtype, int T, int H, int G, int hd, int rd,
+                                   int interleaved, int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hd <= 0 || H <= 0 || G < 0) LP_REFUSE("rope_cache_write: heads %d/%d of %d", H, G, hd);
+    if (rd < 0 || rd > hd || (rd & 1)) LP_REFUSE("rope_cache_write: rotary width %d of a head of %d", rd, hd);
+    if (rd > 0 && !inv_freq) LP_REFUSE("rope_cache_write: rotation without frequencies");
+    const int heads = pages ? H + 2 * G : H;
+    if (ld < heads * hd) LP_REFUSE("rope_cache_write: row of %d values for %d heads of %d", ld, heads, hd);
+    if (pages && page_size <= 0) LP_REFUSE("rope_cache_write: page size %d", page_size);
+    if (heads > 65535) LP_REFUSE("rope_cache_write: %d heads exceed the grid", heads);
+    dim3 grid(T, heads);
+    const int threads = hd <= 64 ? 64 : (hd <= 128 ? 128 : 256);
+#define LP_LAUNCH_ROPE(TQ, TKV)                                                                          \
+    rope_cache_kernel<TQ, TKV><<<grid, threads, 0, stream>>>(qkv, ld, inv_freq, positions, seq_ids,       \
+                                                             page_table, pt_stride, (TQ*)q_out,           \
+                                                             (TKV*)pages, H, G, hd, rd, interleaved,     \
+                                                             page_size)
+    if (q_dtype == LP_F32 && kv_dtype == LP_F32) LP_LAUNCH_ROPE(float, float);
+    else if (q_dtype == LP_BF16 && kv_dtype == LP_BF16) LP_LAUNCH_ROPE(__nv_bfloat16, __nv_bfloat16);
+    else if (q_dtype == LP_F32 && kv_dtype == LP_BF16) LP_LAUNCH_ROPE(float, __nv_bfloat16);
+    else if (q_dtype == LP_BF16 && kv_dtype == LP_F32) LP_LAUNCH_ROPE(__nv_bfloat16, float);
+    else LP_REFUSE("rope_cache_write: dtype codes q=%d kv=%d", q_dtype, kv_dtype);
+#undef LP_LAUNCH_ROPE
+    return lp_check_launch("rope_cache_write");
+}

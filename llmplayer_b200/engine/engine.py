@@ -1,0 +1,140 @@
+"""The engine: a loaded model, its cache, and the one step function everything uses.
+
+Reference: api/LLMEngine.java:233-350 (``load(path, contextLength)``), :941-1033
+(``forwardSingleToken`` / ``forwardBatch``: logits for given tokens), and
+inference/InferenceEngine.java:180-191 (one token of one sequence per call). Here
+one call runs the new tokens of a whole batch: all prompts of a batch in one step,
+then one token for each sequence, always from the cache that earlier steps left.
+"""
+from __future__ import annotations
+
+import os
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.pages import PAGE_SIZE
+from ..cache.sequence_cache import SequenceCache
+from ..config.registry import ArchitectureConfig, load_config
+from ..errors import RequestError
+from ..kernels import ops
+from ..parts.base import Runtime
+from ..weights.loader import load_tensors
+from .model import Model
+from .step import SequenceStep, StepContext, Workspace
+
+
+def _round_up(n: int, m: int) -> int:
+    return -(-n // m) * m
+
+
+class Engine:
+    def __init__(self, config: ArchitectureConfig, model: Model, runtime: Runtime, *, max_tokens: int,
+                 max_slots: Optional[int] = None, context_length: Optional[int] = None):
+        self.config = config
+        self.model = model
+        self.runtime = runtime
+        self.vocab_size = model.layout.head.vocab_size
+        self.context_length = context_length if context_length is not None else config.max_positions()
+        self.cache = SequenceCache(model.cache_requests(), max_tokens=max_tokens, max_slots=max_slots,
+                                   kv_dtype=runtime.kv_dtype, device=runtime.device)
+        self.workspace = Workspace(runtime.device)
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def load(cls, model_dir: str, *, dtype: str = "bfloat16", context_length: Optional[int] = None,
+             max_batch: int = 1, max_tokens: Optional[int] = None, max_slots: Optional[int] = None,
+             device: str = "cuda:0", kernels: str = "fast") -> "Engine":
+        """Load ``config.json`` and ``model.safetensors`` from ``model_dir``.
+
+        ``context_length`` caps each sequence (default and upper bound: the model's
+        ``max_position_embeddings``, as api/LLMEngine.java:348 takes the smaller of
+        the two); the cache holds ``max_tokens`` positions in all, by default
+        ``max_batch`` sequences of that length.
+        """
+        ops.require_gpu()
+        config = load_config(model_dir)
+        dev = torch.device(device)
+        torch.cuda.set_device(dev)
+        runtime = Runtime(device=dev, dtype=dtype, kernels=kernels)
+        model = Model(config.layout())
+        tensors = load_tensors(model_dir, model.tensor_specs())
+        model.load(tensors, runtime)
+        del tensors
+        limit = config.max_positions()
+        ctx_len = limit if context_length is None else min(int(context_length), limit)
+        if max_tokens is None:
+            max_tokens = max(1, max_batch) * _round_up(ctx_len, PAGE_SIZE)
+        return cls(config, model, runtime, max_tokens=max_tokens, max_slots=max_slots, context_length=ctx_len)
+
+    def close(self) -> None:
+        self.cache = None
+        self.model = None
+        self.workspace = None
+
+    # ------------------------------------------------------------------ slots
+    def acquire(self) -> int:
+        """A slot for a new sequence (``createState`` in inference/InferenceEngine.java:172-174)."""
+        return self.cache.acquire()
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ------------------------------------------------------------------ the step
+    def plan(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Sequence[Sequence[int]]) -> StepContext:
+        """Check a step, reserve its pages and describe it to the device."""
+        if len(entries) != len(want):
+            raise RequestError(f"{len(entries)} entries but {len(want)} lists of wanted places")
+        if not entries:
+            raise RequestError("a step needs at least one sequence")
+        sequences: List[SequenceStep] = []
+        tokens: List[int] = []
+        rows: List[int] = []
+        for (slot, toks), places in zip(entries, want):
+            toks = [int(t) for t in toks]
+            if not toks:
+                raise RequestError(f"slot {slot}: a step must bring at least one token")
+            bad = [t for t in toks if not 0 <= t < self.vocab_size]
+            if bad:
+                raise RequestError(f"slot {slot}: token id {bad[0]} lies outside the vocabulary of {self.vocab_size}")
+            have = self.cache.length(slot)
+            if have + len(toks) > self.context_length:
+                raise RequestError(
+                    f"slot {slot}: {have} cached + {len(toks)} new tokens exceed the context length "
+                    f"of {self.context_length}")
+            for p in places:
+                if not 0 <= int(p) < len(toks):
+                    raise RequestError(f"slot {slot}: wanted place {p} is not among its {len(toks)} new tokens")
+                rows.append(len(tokens) + int(p))
+            sequences.append(SequenceStep(slot, len(tokens), len(toks), have))
+            tokens.extend(toks)
+        slots = [s.slot for s in sequences]
+        counts = [s.num_new for s in sequences]
+        self.cache.reserve(slots, counts)
+        return StepContext(self.workspace, sequences, tokens, self.cache.page_tables(slots), rows)
+
+    def run(self, ctx: StepContext) -> torch.Tensor:
+        """Run a planned step; returns float32 logits [wanted, vocab] (valid until the next step)."""
+        logits = self.workspace.get("logits", (ctx.num_wanted, self.vocab_size), torch.float32)
+        self.model.forward(ctx, self.cache, ctx.rows, logits)
+        self.cache.commit([s.slot for s in ctx.sequences], [s.num_new for s in ctx.sequences])
+        return logits
+
+    def step(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Sequence[Sequence[int]]) -> torch.Tensor:
+        """Run the given new tokens of each slot, as one batch, from the cache.
+
+        ``entries``: ``(slot, new token ids)`` per sequence; ``want[i]``: the places
+        among sequence i's new tokens whose logits are returned, in order.
+        """
+        return self.run(self.plan(entries, want))
+
+    # ------------------------------------------------------------------ reporting
+    def info(self) -> str:
+        lines = [self.config.describe() if hasattr(self.config, "describe") else repr(self.config)]
+        lines.append(f"dtype: {self.runtime.dtype} ({self.runtime.kernels} kernels), device {self.runtime.device}")
+        lines.append(f"context length: {self.context_length}; cache: {self.cache.num_pages} pages of {PAGE_SIZE} "
+                     f"positions, {self.cache.max_slots} slots, {self.cache.memory_bytes() / 2**20:.1f} MiB")
+        return "\n".join(lines)

@@ -1,0 +1,228 @@
+"""The operations of a step, as calls into the compiled CUDA libraries.
+
+Each function checks the tensors it is given (device, dtype, shape, layout),
+then launches on torch's current stream. There is no other implementation
+behind them: without a GPU and the compiled library they raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Dict, Optional
+
+import torch
+
+from ..errors import ExtensionMissing, KernelError
+from . import build
+
+F32, BF16 = 0, 1
+STORE, ACCUMULATE, SWIGLU = 0, 1, 2
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+_P, _I, _F = c_void_p, c_int, c_float
+_SIGNATURES = {
+    "elementwise": {
+        "lp_embed": [_P, _I, _P, _P, _I, _I, _P],
+        "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P],
+        "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    },
+    "gemm_plain": {
+        "lp_gemm_plain": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    },
+    "attention_plain": {
+        "lp_attention_plain": [_P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    },
+}
+
+_libs: Dict[str, ctypes.CDLL] = {}
+
+
+def library(name: str) -> ctypes.CDLL:
+    """The loaded library ``name``; compiled first if it is missing or stale."""
+    lib = _libs.get(name)
+    if lib is not None:
+        return lib
+    path = build.ensure_built(name)
+    try:
+        lib = ctypes.CDLL(path)
+    except OSError as exc:
+        raise ExtensionMissing(f"cannot load {path}: {exc}") from None
+    for fn, args in _SIGNATURES.get(name, {}).items():
+        f = getattr(lib, fn)
+        f.argtypes = args
+        f.restype = c_int
+    lib.lp_last_error.restype = ctypes.c_char_p
+    _libs[name] = lib
+    return lib
+
+
+def require_gpu() -> None:
+    if not torch.cuda.is_available():
+        raise ExtensionMissing("no CUDA device: this library runs on the GPU only and has no CPU path")
+
+
+def _check(lib: ctypes.CDLL, code: int) -> None:
+    if code != 0:
+        raise KernelError(lib.lp_last_error().decode("utf-8", "replace") or f"kernel call failed with code {code}")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _CODES[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _want(t: torch.Tensor, what: str, dtype=None, ndim: Optional[int] = None) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{what}: expected a CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: expected dtype {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{what}: expected {ndim} dimensions, got shape {tuple(t.shape)}")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: expected a contiguous tensor, got strides {t.stride()}")
+    return t
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# --------------------------------------------------------------------------- embedding
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t, :] = float32(table[tokens[t], :])."""
+    _want(table, "embed table", ndim=2)
+    _want(tokens, "embed tokens", torch.int32, 1)
+    _want(out, "embed out", torch.float32, 2)
+    T, d = out.shape
+    if tokens.numel() != T or table.shape[1] != d:
+        raise KernelError(f"embed: {tokens.numel()} tokens, table {tuple(table.shape)}, out {tuple(out.shape)}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_embed(table.data_ptr(), _code(table, "embed table"), tokens.data_ptr(), out.data_ptr(),
+                             T, d, _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------- norm
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = x[rows[r]] / sqrt(mean(x^2) + eps) * weight, float32 inside.
+
+    ``add`` (same shape as x) is first added into x in place: the residual sum
+    fused with the norm that follows it.
+    """
+    _want(x, "rmsnorm x", torch.float32, 2)
+    _want(weight, "rmsnorm weight", torch.float32, 1)
+    _want(out, "rmsnorm out", ndim=2)
+    d = x.shape[1]
+    R = out.shape[0]
+    if weight.numel() != d or out.shape[1] != d:
+        raise KernelError(f"rmsnorm: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if rows is not None:
+        _want(rows, "rmsnorm rows", torch.int32, 1)
+        if rows.numel() != R:
+            raise KernelError(f"rmsnorm: {rows.numel()} row indices for {R} output rows")
+    elif x.shape[0] != R:
+        raise KernelError(f"rmsnorm: x {tuple(x.shape)} and out {tuple(out.shape)} differ in rows")
+    add_code = F32
+    if add is not None:
+        _want(add, "rmsnorm add", ndim=2)
+        if add.shape != x.shape:
+            raise KernelError(f"rmsnorm: add {tuple(add.shape)} does not match x {tuple(x.shape)}")
+        add_code = _code(add, "rmsnorm add")
+    lib = library("elementwise")
+    _check(lib, lib.lp_rmsnorm(x.data_ptr(), _ptr(add), add_code, _ptr(rows), weight.data_ptr(), out.data_ptr(),
+                               _code(out, "rmsnorm out"), R, d, float(eps), _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------- rotation + cache write
+def rope_cache_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
+                     seq_ids: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor,
+                     pages: Optional[torch.Tensor], *, num_heads: int, num_kv_heads: int, head_dim: int,
+                     rotary_dim: int, interleaved: bool) -> None:
+    """Rotate queries (and keys), write queries to ``q_out`` [T, H*hd] and keys and
+    values into ``pages`` [num_pages, 2, G, page_size, hd]. ``pages=None``: queries only."""
+    _want(qkv, "rope qkv", torch.float32, 2)
+    _want(positions, "rope positions", torch.int32, 1)
+    _want(seq_ids, "rope seq_ids", torch.int32, 1)
+    _want(page_table, "rope page_table", torch.int32, 2)
+    _want(q_out, "rope q_out", ndim=2)
+    T = qkv.shape[0]
+    H, G, hd = num_heads, num_kv_heads, head_dim
+    if positions.numel() != T or seq_ids.numel() != T or q_out.shape != (T, H * hd):
+        raise KernelError(f"rope: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}, {positions.numel()} positions")
+    page_size, kv_code = 0, F32
+    if pages is not None:
+        _want(pages, "rope pages", ndim=5)
+        if pages.shape[1] != 2 or pages.shape[2] != G or pages.shape[4] != hd:
+            raise KernelError(f"rope: pages {tuple(pages.shape)} do not fit {G} key heads of {hd}")
+        page_size, kv_code = pages.shape[3], _code(pages, "rope pages")
+    if rotary_dim > 0:
+        _want(inv_freq, "rope inv_freq", torch.float32, 1)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError(f"rope: {inv_freq.numel()} frequencies for a rotary width of {rotary_dim}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_rope_cache_write(
+        qkv.data_ptr(), qkv.shape[1], _ptr(inv_freq) if rotary_dim > 0 else None, positions.data_ptr(),
+        seq_ids.data_ptr(), page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(), _code(q_out, "rope q_out"),
+        _ptr(pages), kv_code, T, H, G, hd, rotary_dim, 1 if interleaved else 0, page_size, _stream()))
+
+
+# --------------------------------------------------------------------------- matrix products
+def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE) -> torch.Tensor:
+    """out (=|+=) a @ w.T with float32 multiply-adds in increasing k.
+
+    ``SWIGLU``: ``w`` is [2N, K], gate rows then up rows; out = silu(a gate^T) * (a up^T).
+    """
+    _want(a, "gemm a", ndim=2)
+    _want(w, "gemm w", ndim=2)
+    _want(out, "gemm out", ndim=2)
+    M, K = a.shape
+    N = out.shape[1]
+    rows = 2 * N if mode == SWIGLU else N
+    if w.shape != (rows, K) or out.shape[0] != M:
+        raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, mode {mode}")
+    lib = library("gemm_plain")
+    _check(lib, lib.lp_gemm_plain(a.data_ptr(), _code(a, "gemm a"), w.data_ptr(), _code(w, "gemm w"), out.data_ptr(),
+                                  _code(out, "gemm out"), M, N, K, K, K, N, mode, _stream()))
+    return out
+
+
+# --------------------------------------------------------------------------- attention
+def attention_plain(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
+                    seq_ids: torch.Tensor, positions: torch.Tensor, *, num_heads: int, num_kv_heads: int,
+                    head_dim: int, scale: float, window: Optional[int]) -> torch.Tensor:
+    """Each query token attends over the cached keys of its sequence up to its own
+    position (and within ``window``, if given)."""
+    _want(q, "attention q", ndim=2)
+    _want(out, "attention out", q.dtype, 2)
+    _want(pages, "attention pages", ndim=5)
+    _want(page_table, "attention page_table", torch.int32, 2)
+    _want(seq_ids, "attention seq_ids", torch.int32, 1)
+    _want(positions, "attention positions", torch.int32, 1)
+    T = q.shape[0]
+    H, G, hd = num_heads, num_kv_heads, head_dim
+    if q.shape != (T, H * hd) or out.shape != q.shape or seq_ids.numel() != T or positions.numel() != T:
+        raise KernelError(f"attention: q {tuple(q.shape)}, out {tuple(out.shape)} for {H} heads of {hd}")
+    if pages.shape[1] != 2 or pages.shape[2] != G or pages.shape[4] != hd:
+        raise KernelError(f"attention: pages {tuple(pages.shape)} do not fit {G} key heads of {hd}")
+    lib = library("attention_plain")
+    _check(lib, lib.lp_attention_plain(
+        q.data_ptr(), out.data_ptr(), _code(q, "attention q"), pages.data_ptr(), _code(pages, "attention pages"),
+        page_table.data_ptr(), page_table.shape[1], seq_ids.data_ptr(), positions.data_ptr(), T, H, G, hd,
+        pages.shape[3], float(scale), int(window) if window else 0, _stream()))
+    return out
+
+
+def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor, *,
+              num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
+              fast: bool) -> torch.Tensor:
+    """Attention of the step's tokens over the cache; picks the kernel for the step's shape."""
+    return attention_plain(q, out, pages, page_table, ctx.seq_ids, ctx.positions, num_heads=num_heads,
+                           num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window)

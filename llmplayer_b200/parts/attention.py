@@ -1,0 +1,89 @@
+"""Grouped-query softmax attention over the cached keys and values of each sequence.
+
+One fused projection gives queries, keys and values; queries and keys are rotated
+by the mixer's position encoding; keys and values are written to the sequence's
+pages; every new token attends over the cache up to its own position (within the
+window, if the layer has one); the output projection adds into the residual stream.
+
+Reference: inference/Attention.java:76-240 (projections :86-114, rotation :129-131,
+cache write :134-135, scale :138-140, scores/softmax/values :210-230, output
+projection :234-239), GQA head mapping ``kvHead = h / (H/G)`` :212.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..cache.sequence_cache import KVRequest
+from ..errors import ConfigError
+from ..kernels import ops
+from .base import MIXERS, POSITIONS, Part, Runtime
+from .linear import Linear
+from .specs import MATRIX, AttentionSpec, TensorSpec
+
+
+class Attention(Part):
+    def __init__(self, spec: AttentionSpec):
+        s = spec
+        if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
+            raise ConfigError(f"{s.num_heads} query heads cannot share {s.num_kv_heads} key/value heads")
+        if s.head_dim <= 0:
+            raise ConfigError(f"head size {s.head_dim}")
+        if s.window is not None and s.window <= 0:
+            raise ConfigError(f"attention window must be positive or absent, got {s.window}")
+        if not s.shares_kv and (s.k is None or s.v is None):
+            raise ConfigError("an attention layer that keeps its own cache needs key and value projections")
+        self.spec = spec
+        self.position = POSITIONS.build(s.position)
+        self.qkv: Optional[Linear] = None
+        self.out: Optional[Linear] = None
+
+    # ------------------------------------------------------------------ tensors
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        s = self.spec
+        specs = {s.q: TensorSpec((s.num_heads * s.head_dim, s.hidden_size), MATRIX)}
+        if not s.shares_kv:
+            specs[s.k] = TensorSpec((s.num_kv_heads * s.head_dim, s.hidden_size), MATRIX)
+            specs[s.v] = TensorSpec((s.num_kv_heads * s.head_dim, s.hidden_size), MATRIX)
+        specs[s.o] = TensorSpec((s.hidden_size, s.num_heads * s.head_dim), MATRIX)
+        return specs
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        s = self.spec
+        names = [s.q] if s.shares_kv else [s.q, s.k, s.v]
+        self.qkv = Linear([tensors[n] for n in names], runtime)      # rows: queries, keys, values
+        self.out = Linear([tensors[s.o]], runtime)
+        self.position.load(tensors, runtime)
+
+    # ------------------------------------------------------------------ cache
+    def cache_request(self):
+        s = self.spec
+        if s.shares_kv:
+            return None
+        return KVRequest(s.num_kv_heads, s.head_dim, s.window)
+
+    # ------------------------------------------------------------------ step
+    def forward(self, ctx, cache, x: torch.Tensor, residual: torch.Tensor) -> None:
+        s, rt = self.spec, self.runtime
+        if cache is None:
+            raise ConfigError("attention needs a key/value cache (its own or another run's)")
+        T = x.shape[0]
+        H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim
+        table = ctx.page_tables[cache.group_index]
+        qkv = ctx.buffer("qkv", (T, self.qkv.out_features), torch.float32)
+        self.qkv.store(x, qkv)
+        q = ctx.buffer("q", (T, H * hd), rt.act_dtype)
+        ops.rope_cache_write(
+            qkv, self.position.inv_freq, ctx.positions, ctx.seq_ids, table, q,
+            None if s.shares_kv else cache.pages,
+            num_heads=H, num_kv_heads=G, head_dim=hd, rotary_dim=self.position.rotary_dim,
+            interleaved=self.position.interleaved)
+        o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
+        ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd,
+                      scale=s.scale, window=s.window, fast=rt.fast)
+        self.out.accumulate(o, residual)
+
+
+MIXERS.register("attention", Attention)

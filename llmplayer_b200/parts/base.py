@@ -1,0 +1,119 @@
+"""Interfaces of the parts and the registries that resolve a specification's kind.
+
+A part is built from its specification alone, says which tensors it needs
+(``tensor_specs``), takes them (``load``) and then works on the tensors of a
+step. No part knows which model it is in.
+
+* Norm:          ``apply(x[T, d] float32, out[T, d]) -> out`` (optionally on chosen rows)
+* Position:      owned by a mixer; offers what the mixer's kernels need (frequencies)
+* Mixer:         ``cache_request()`` and ``forward(ctx, cache_view, x[T, d], residual[T, d])``:
+                 adds its output into the float32 residual stream
+* Feed-forward:  ``forward(ctx, x[T, d], residual[T, d])``: adds into the residual stream
+* Block:         ``forward(ctx, cache_view, residual[T, d])``: one layer, in place
+
+``ctx`` is the step's :class:`llmplayer_b200.engine.step.StepContext`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, Mapping
+
+import torch
+
+from ..errors import ConfigError
+from .specs import TensorSpec
+
+
+@dataclass
+class Runtime:
+    """Where and in which precision a model runs.
+
+    ``dtype`` is ``"bfloat16"`` (activations and cache in bfloat16, tensor-core
+    kernels) or ``"float32"`` (everything in true float32 through the plain
+    kernels). ``kernels`` is ``"fast"`` or ``"plain"``: the latter forces the
+    plain twins in bfloat16 too. The residual stream and the logits are float32
+    in both.
+    """
+    device: torch.device
+    dtype: str = "bfloat16"
+    kernels: str = "fast"
+
+    def __post_init__(self):
+        if self.dtype not in ("bfloat16", "float32"):
+            raise ConfigError(f"dtype must be 'bfloat16' or 'float32', got {self.dtype!r}")
+        if self.kernels not in ("fast", "plain"):
+            raise ConfigError(f"kernels must be 'fast' or 'plain', got {self.kernels!r}")
+
+    @property
+    def act_dtype(self) -> torch.dtype:
+        return torch.bfloat16 if self.dtype == "bfloat16" else torch.float32
+
+    @property
+    def kv_dtype(self) -> torch.dtype:
+        return self.act_dtype
+
+    @property
+    def fast(self) -> bool:
+        return self.dtype == "bfloat16" and self.kernels == "fast"
+
+    def matrix(self, t: torch.Tensor) -> torch.Tensor:
+        """A weight matrix on the device: widened to float32 in the float32 path,
+        kept as stored (bfloat16, or float32 if the file held 32 bits) otherwise.
+        The same host tensor always yields the same device tensor, so a table that
+        two parts name (a tied head) is held once."""
+        memo = self.__dict__.setdefault("_uploaded", {})
+        hit = memo.get(id(t))
+        if hit is not None and hit[0] is t:
+            return hit[1]
+        if self.dtype == "float32":
+            dev = t.to(device=self.device, dtype=torch.float32).contiguous()
+        else:
+            dev = t.to(device=self.device).contiguous()
+        memo[id(t)] = (t, dev)
+        return dev
+
+    def forget_uploads(self) -> None:
+        """Drop the host tensors remembered by :meth:`matrix` (after a model is loaded)."""
+        self.__dict__.pop("_uploaded", None)
+
+    def gain(self, t: torch.Tensor) -> torch.Tensor:
+        """A norm's gain: float32 always (widening is exact)."""
+        return t.to(device=self.device, dtype=torch.float32).contiguous()
+
+
+class Part:
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        self.runtime = runtime
+
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._kinds: Dict[str, Callable] = {}
+
+    def register(self, kind: str, factory: Callable, *, replace: bool = False) -> None:
+        if kind in self._kinds and not replace and self._kinds[kind] is not factory:
+            raise ConfigError(f"{self.what} kind {kind!r} is already registered")
+        self._kinds[kind] = factory
+
+    def unregister(self, kind: str) -> None:
+        self._kinds.pop(kind, None)
+
+    def build(self, spec):
+        kind = getattr(spec, "kind", None)
+        if kind not in self._kinds:
+            raise ConfigError(f"unknown {self.what} kind {kind!r}; known: {', '.join(sorted(self._kinds))}")
+        return self._kinds[kind](spec)
+
+    def kinds(self):
+        return tuple(sorted(self._kinds))
+
+
+NORMS = Registry("norm")
+POSITIONS = Registry("position encoding")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+BLOCKS = Registry("block")

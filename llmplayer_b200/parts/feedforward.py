@@ -1,0 +1,46 @@
+"""Dense gated feed-forward: residual += down(silu(gate x) * (up x)).
+
+Gate and up are held as one stacked matrix so that one product yields both and
+the activation is applied where the sums are formed.
+
+Reference: inference/SwiGLUFFN.java:36-67, tensor/ScalarOps.java:69-73,
+src/main/resources/kernels/cuda/silu_mul.cu:6-15.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .base import FEED_FORWARDS, Part, Runtime
+from .linear import Linear
+from .specs import MATRIX, SwiGLUSpec, TensorSpec
+
+
+class SwiGLU(Part):
+    def __init__(self, spec: SwiGLUSpec):
+        self.spec = spec
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        s = self.spec
+        return {
+            s.gate: TensorSpec((s.intermediate_size, s.hidden_size), MATRIX),
+            s.up: TensorSpec((s.intermediate_size, s.hidden_size), MATRIX),
+            s.down: TensorSpec((s.hidden_size, s.intermediate_size), MATRIX),
+        }
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        s = self.spec
+        self.gate_up = Linear([tensors[s.gate], tensors[s.up]], runtime)
+        self.down = Linear([tensors[s.down]], runtime)
+
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor) -> None:
+        h = ctx.buffer("ffn_hidden", (x.shape[0], self.spec.intermediate_size), self.runtime.act_dtype)
+        self.gate_up.swiglu(x, h)
+        self.down.accumulate(h, residual)
+
+
+FEED_FORWARDS.register("swiglu", SwiGLU)

@@ -1,0 +1,43 @@
+"""A linear map held as an [out, in] matrix, and the choice of the kernel that applies it.
+
+Reference: tensor/FloatTensor.java:49-67 (row-major [rows, cols], one dot product per
+output row) and the per-dtype kernels src/main/resources/kernels/cuda/matmul_f32.cu,
+matmul_bf16.cu.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from ..kernels import ops
+from .base import Runtime
+
+
+class Linear:
+    """out (=|+=) x @ W^T, or the gated product when W stacks gate rows over up rows."""
+
+    def __init__(self, parts: Sequence[torch.Tensor], runtime: Runtime):
+        mats = [runtime.matrix(p) for p in parts]
+        if len({m.dtype for m in mats}) > 1:        # mixed storage: widen to the widest
+            mats = [m.to(torch.float32) for m in mats]
+        self.weight = mats[0] if len(mats) == 1 else torch.cat(mats, dim=0).contiguous()
+        self.runtime = runtime
+        self.out_features, self.in_features = self.weight.shape
+
+    def _fast(self) -> bool:
+        return self.runtime.fast and self.weight.dtype == torch.bfloat16
+
+    def store(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        return self._run(x, out, ops.STORE)
+
+    def accumulate(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        return self._run(x, out, ops.ACCUMULATE)
+
+    def swiglu(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        return self._run(x, out, ops.SWIGLU)
+
+    def _run(self, x, out, mode):
+        if self._fast():
+            return ops.gemm(x, self.weight, out, mode)
+        return ops.gemm_plain(x, self.weight, out, mode)

@@ -1,0 +1,35 @@
+"""RMS norm: out = x / sqrt(mean(x^2) + eps) * gain, in float32.
+
+Reference: inference/RMSNorm.java:17-35, tensor/ScalarOps.java:26-35,
+src/main/resources/kernels/cuda/rmsnorm.cu:6-46. The gain is used as stored.
+"""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..kernels import ops
+from .base import NORMS, Part, Runtime
+from .specs import GAIN, NormSpec, TensorSpec
+
+
+class RMSNorm(Part):
+    def __init__(self, spec: NormSpec):
+        self.spec = spec
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self.spec.weight: TensorSpec((self.spec.size,), GAIN)}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        self.weight = runtime.gain(tensors[self.spec.weight])
+
+    def apply(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+              add: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``out[r] = norm(x[rows[r]])``; ``add`` is summed into ``x`` first (in place)."""
+        return ops.rmsnorm(x, self.weight, self.spec.eps, out, rows=rows, add=add)
+
+
+NORMS.register("rmsnorm", RMSNorm)

@@ -1,0 +1,69 @@
+"""Rotary position encoding: the per-pair frequencies a mixer's kernels rotate by.
+
+Reference: inference/RoPE.java:80-105. f_i = 1 / theta^(2i / rotary_dim) is
+computed in double and rounded to float32 (:83); a per-pair divisor may follow
+(:85-87), which for "llama3" scaling is what the model file's converter derives
+from the wavelength rule implemented here. The angle position * f_i is a
+float32 product (:101), evaluated inside the kernel that rotates.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ..errors import ConfigError
+from .base import POSITIONS, Part, Runtime
+from .specs import PositionSpec
+
+
+def inverse_frequencies(spec: PositionSpec) -> torch.Tensor:
+    if spec.rotary_dim <= 0 or spec.rotary_dim % 2 or spec.rotary_dim > spec.head_dim:
+        raise ConfigError(f"rotary width {spec.rotary_dim} does not fit a head of {spec.head_dim}")
+    if not spec.theta > 0:
+        raise ConfigError(f"rope theta must be positive, got {spec.theta}")
+    freqs = []
+    s = spec.scaling
+    for i in range(spec.rotary_dim // 2):
+        f = 1.0 / math.pow(spec.theta, 2.0 * i / spec.rotary_dim)
+        if s is not None:
+            wavelength = 2.0 * math.pi / f
+            short = s.original_max_position / s.high_freq_factor
+            long = s.original_max_position / s.low_freq_factor
+            if wavelength > long:
+                f = f / s.factor
+            elif wavelength >= short:
+                blend = (s.original_max_position / wavelength - s.low_freq_factor) / (
+                    s.high_freq_factor - s.low_freq_factor)
+                f = (1.0 - blend) * f / s.factor + blend * f
+        freqs.append(f)
+    return torch.tensor(freqs, dtype=torch.float64).to(torch.float32)
+
+
+class Rotary(Part):
+    def __init__(self, spec: PositionSpec):
+        if spec.pairing not in ("split_half", "interleaved"):
+            raise ConfigError(f"unknown rotary pairing {spec.pairing!r}")
+        self.spec = spec
+        self.rotary_dim = spec.rotary_dim
+        self.interleaved = spec.pairing == "interleaved"
+        self.inv_freq: Optional[torch.Tensor] = None
+
+    def load(self, tensors, runtime: Runtime) -> None:
+        super().load(tensors, runtime)
+        self.inv_freq = inverse_frequencies(self.spec).to(runtime.device)
+
+
+class NoPosition(Part):
+    """Queries and keys are used as projected."""
+
+    def __init__(self, spec: PositionSpec):
+        self.spec = spec
+        self.rotary_dim = 0
+        self.interleaved = False
+        self.inv_freq = None
+
+
+POSITIONS.register("rope", Rotary)
+POSITIONS.register("none", NoPosition)

@@ -1,0 +1,63 @@
+"""Tiny configurations and comparison helpers shared by the tests."""
+import os
+
+import torch
+
+import plain_llama
+
+# Two tiny configurations that differ in every size and option.
+TINY_A = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 16, "intermediate_size": 192, "vocab_size": 256, "rope_theta": 10000.0,
+    "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 128,
+}
+TINY_B = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 3,
+    "num_key_value_heads": 1, "head_dim": 32, "intermediate_size": 320, "vocab_size": 384, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 4.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64},
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 256,
+}
+# A third one for long sequences: heads wider than the width / heads, odd sizes.
+TINY_C = {
+    "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 80, "num_attention_heads": 6,
+    "num_key_value_heads": 3, "head_dim": 48, "intermediate_size": 176, "vocab_size": 301, "rope_theta": 25000.0,
+    "rope_scaling": None, "rms_norm_eps": 3e-6, "tie_word_embeddings": False, "max_position_embeddings": 1024,
+}
+TINY = {"A": (TINY_A, 0, 0.02), "B": (TINY_B, 1, 0.05), "C": (TINY_C, 5, 0.08)}
+
+# Largest |engine - plain| allowed, as a fraction of the largest |plain| logit.
+TOLERANCE = {"float32": 2e-5, "bfloat16": 4e-2}
+
+
+def make_model(tmp_path, name, dtype="bfloat16"):
+    from llmplayer_b200.config import config_from_dict
+    from llmplayer_b200.weights import write_random_model
+    raw, seed, std = TINY[name]
+    out = os.path.join(str(tmp_path), f"tiny{name}_{dtype}")
+    write_random_model(config_from_dict(raw), seed, out, dtype=dtype, std=std)
+    return out
+
+
+def random_tokens(n, vocab, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def plain_logits(model_dir, tokens):
+    cfg, w = plain_llama.read_model(model_dir)
+    return plain_llama.forward(cfg, w, tokens, dtype=torch.float64)
+
+
+def relative_error(got, ref):
+    got = torch.as_tensor(got, dtype=torch.float64).cpu()
+    ref = torch.as_tensor(ref, dtype=torch.float64).cpu()
+    assert got.shape == ref.shape, (got.shape, ref.shape)
+    assert torch.isfinite(got).all(), "engine produced non-finite logits"
+    return float((got - ref).abs().max() / ref.abs().max())
+
+
+def assert_close(got, ref, dtype, what=""):
+    err = relative_error(got, ref)
+    assert err <= TOLERANCE[dtype], f"{what}: relative error {err:.3e} exceeds {TOLERANCE[dtype]:.1e} ({dtype})"
+    return err
