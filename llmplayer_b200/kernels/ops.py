@@ -194,6 +194,10 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = 
     return out
 
 
+def fast_gemm_available() -> bool:
+    return False
+
+
 # --------------------------------------------------------------------------- attention
 def attention_plain(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
                     seq_ids: torch.Tensor, positions: torch.Tensor, *, num_heads: int, num_kv_heads: int,

@@ -26,7 +26,7 @@ class Linear:
         self.out_features, self.in_features = self.weight.shape
 
     def _fast(self) -> bool:
-        return self.runtime.fast and self.weight.dtype == torch.bfloat16
+        return self.runtime.fast and self.weight.dtype == torch.bfloat16 and ops.fast_gemm_available()
 
     def store(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return self._run(x, out, ops.STORE)
