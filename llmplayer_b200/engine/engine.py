@@ -39,6 +39,8 @@ class Engine:
         self.cache = SequenceCache(model.cache_requests(), max_tokens=max_tokens, max_slots=max_slots,
                                    kv_dtype=runtime.kv_dtype, device=runtime.device)
         self.workspace = Workspace(runtime.device)
+        self._sampler = None
+        self.last_generation_stats = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -130,6 +132,48 @@ class Engine:
         among sequence i's new tokens whose logits are returned, in order.
         """
         return self.run(self.plan(entries, want))
+
+    # ------------------------------------------------------------------ generation
+    def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers) -> List[int]:
+        """One token for each sampler from row ``rows[i]`` of ``logits``, drawn on the device."""
+        if self._sampler is None:
+            from ..sampling.sampler import BatchSampler
+            self._sampler = BatchSampler(self.vocab_size, self.runtime.device)
+        return self._sampler.sample(logits, rows, samplers)
+
+    def fits(self, token_counts: Sequence[int]) -> bool:
+        """Whether sequences of these final lengths can be held at once, beside what is held now."""
+        need = sum(-(-int(n) // PAGE_SIZE) for n in token_counts)
+        return (len(token_counts) <= self.cache.slots.num_free
+                and all(need <= free for free in self.cache.free_pages()))
+
+    def generate(self, prompts, sampler_config=None, *, max_tokens: int = 256, stop_token_ids=None,
+                 on_token=None, max_batch: Optional[int] = None):
+        """Generate for a batch of prompts (lists of token ids) or of
+        :class:`GenerationRequest`; returns one :class:`GenerationResponse` each, in order.
+
+        Mirrors ``engine.generate(request[, callback])`` (api/LLMEngine.java:356-468):
+        a prompt, a token budget, sampler options; ``on_token(request_index, token_id)``
+        may return False to stop that request. ``stats`` of the last call are kept in
+        ``last_generation_stats``.
+        """
+        from ..sampling.params import SamplerConfig
+        from .generate import GenerationLoop, GenerationRequest
+        requests = []
+        for p in prompts:
+            if isinstance(p, GenerationRequest):
+                requests.append(p)
+            else:
+                requests.append(GenerationRequest(
+                    prompt_ids=list(p), max_tokens=max_tokens,
+                    sampler_config=sampler_config if sampler_config is not None else SamplerConfig(),
+                    stop_token_ids=stop_token_ids))
+        loop = GenerationLoop(self, max_batch=max_batch or self.cache.max_slots,
+                              context_length=self.context_length,
+                              default_stop_ids=self.config.stop_token_ids())
+        out = loop.run(requests, on_token=on_token)
+        self.last_generation_stats = loop.stats
+        return out
 
     # ------------------------------------------------------------------ reporting
     def info(self) -> str:

@@ -29,6 +29,7 @@ LIBRARIES: Dict[str, str] = {
     "elementwise": "elementwise.cu",
     "gemm_plain": "gemm_plain.cu",
     "attention_plain": "attention_plain.cu",
+    "sampling": "sampling.cu",
 }
 HEADERS = ("common.cuh",)
 

@@ -32,6 +32,10 @@ _SIGNATURES = {
     "attention_plain": {
         "lp_attention_plain": [_P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     },
+    "sampling": {
+        "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
+        "lp_sample_params_size": [],
+    },
 }
 
 _libs: Dict[str, ctypes.CDLL] = {}
@@ -230,3 +234,27 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page
     """Attention of the step's tokens over the cache; picks the kernel for the step's shape."""
     return attention_plain(q, out, pages, page_table, ctx.seq_ids, ctx.positions, num_heads=num_heads,
                            num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window)
+
+
+# --------------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, work: torch.Tensor, params: torch.Tensor, edit_token: torch.Tensor,
+           edit_subtract: torch.Tensor, edit_factor: torch.Tensor, out_token: torch.Tensor,
+           out_prob: torch.Tensor) -> None:
+    """One token per row of ``params`` (packed LpSampleParams records) from the float32 ``logits``."""
+    _want(logits, "sample logits", torch.float32, 2)
+    _want(work, "sample work", torch.float32, 2)
+    _want(params, "sample params", torch.uint8, 1)
+    _want(edit_token, "sample edit tokens", torch.int32, 1)
+    _want(edit_subtract, "sample edit amounts", torch.float32, 1)
+    _want(edit_factor, "sample edit factors", torch.float32, 1)
+    _want(out_token, "sample out tokens", torch.int32, 1)
+    _want(out_prob, "sample out probabilities", torch.float32, 1)
+    lib = library("sampling")
+    record = lib.lp_sample_params_size()
+    B = out_token.numel()
+    V = logits.shape[1]
+    if params.numel() != B * record or work.shape != (B, V) or out_prob.numel() != B:
+        raise KernelError(f"sample: {params.numel()} parameter bytes, work {tuple(work.shape)} for {B} rows of {V}")
+    _check(lib, lib.lp_sample(logits.data_ptr(), V, work.data_ptr(), V, params.data_ptr(), B, edit_token.data_ptr(),
+                              edit_subtract.data_ptr(), edit_factor.data_ptr(), out_token.data_ptr(),
+                              out_prob.data_ptr(), _stream()))

@@ -1,0 +1,129 @@
+"""Per-request sampler state on the host and the batched call of the sampling kernel.
+
+The reference keeps, per request, a random generator, the recently sampled tokens
+(at most max(64, dry range)) and the mirostat threshold mu
+(sampler/CompositeSampler.java:14-31). The same state lives here in
+:class:`SequenceSampler`; what depends on the logits runs on the device, one
+block per sequence (csrc/sampling.cu).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..kernels import ops
+from .java_random import JavaRandom
+from .params import SamplerConfig
+
+PARAMS_DTYPE = np.dtype([
+    ("inv_temperature", "<f4"), ("top_k", "<i4"), ("top_p", "<f4"), ("min_p", "<f4"),
+    ("mirostat_threshold", "<f4"), ("uniform", "<f4"), ("edit_begin", "<i4"), ("edit_count", "<i4"),
+    ("logits_row", "<i4"),
+])
+
+
+class SequenceSampler:
+    def __init__(self, config: SamplerConfig):
+        self.config = config
+        self.rng = JavaRandom(config.seed)
+        self.recent: List[int] = []
+        self.max_recent = max(64, config.dry_range)
+        self.mu = 2.0 * config.mirostat_tau
+
+    # ------------------------------------------------------------------ before a draw
+    def logit_edits(self) -> List[Tuple[int, float, float]]:
+        """(token, amount to subtract, penalty factor) for every token whose logit changes."""
+        c = self.config
+        subtract: Dict[int, float] = {}
+        if c.dry_multiplier > 0:
+            for tok, pen in self._dry_penalties():
+                subtract[tok] = subtract.get(tok, 0.0) + pen
+        factor: Dict[int, float] = {}
+        if c.repetition_penalty != 1.0:
+            for tok in self.recent:            # once per occurrence (sampler/CompositeSampler.java:45-55)
+                factor[tok] = factor.get(tok, 1.0) * c.repetition_penalty
+        return [(tok, subtract.get(tok, 0.0), factor.get(tok, 1.0)) for tok in sorted(set(subtract) | set(factor))]
+
+    def _dry_penalties(self):
+        """sampler/CompositeSampler.java:150-192: for each earlier occurrence of the last token,
+        the length of the repeated suffix ending there; the token that followed it is penalised
+        by multiplier * base^(length - allowed) once the length reaches the allowed one."""
+        c, rec = self.config, self.recent
+        n = len(rec)
+        if n < 2:
+            return
+        start = n - min(n, c.dry_range)
+        last = rec[-1]
+        for p in range(start, n - 1):
+            if rec[p] != last:
+                continue
+            length, pi, ni = 1, p - 1, n - 2
+            while pi >= start and ni > p and rec[pi] == rec[ni]:
+                length, pi, ni = length + 1, pi - 1, ni - 1
+            if length >= c.dry_allowed_length:
+                yield rec[p + 1], c.dry_multiplier * math.pow(c.dry_base, length - c.dry_allowed_length)
+
+    def draw(self) -> float:
+        """One uniform number per sampled token; none for a greedy choice."""
+        return 0.0 if self.config.is_greedy else self.rng.next_float()
+
+    def mirostat_threshold(self) -> float:
+        return math.pow(2.0, -self.mu) if (self.config.mirostat == 2 and not self.config.is_greedy) else -1.0
+
+    # ------------------------------------------------------------------ after a draw
+    def accept(self, token: int, observed_probability: float) -> None:
+        c = self.config
+        if c.mirostat == 2 and not c.is_greedy and observed_probability > 0:
+            surprise = -math.log2(observed_probability)
+            self.mu -= c.mirostat_eta * (surprise - c.mirostat_tau)
+        self.recent.append(int(token))
+        if len(self.recent) > self.max_recent:
+            self.recent.pop(0)
+
+
+class BatchSampler:
+    """Draws one token for each of several sequences from their rows of logits."""
+
+    def __init__(self, vocab_size: int, device):
+        self.vocab_size = vocab_size
+        self.device = device
+        self._work = None
+        self._out = None
+
+    def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers: Sequence[SequenceSampler]) -> List[int]:
+        B = len(samplers)
+        params = np.zeros(B, dtype=PARAMS_DTYPE)
+        tokens, subs, facs = [], [], []
+        for i, (row, s) in enumerate(zip(rows, samplers)):
+            c = s.config
+            edits = s.logit_edits()
+            params[i] = (0.0 if c.is_greedy else 1.0 / np.float32(c.temperature), c.top_k, c.top_p, c.min_p,
+                         s.mirostat_threshold(), s.draw(), len(tokens), len(edits), row)
+            for tok, sub, fac in edits:
+                tokens.append(tok)
+                subs.append(sub)
+                facs.append(fac)
+        dev = self.device
+        params_dev = torch.from_numpy(params.view(np.uint8).copy()).to(dev)
+        n_edits = max(1, len(tokens))
+        edit_tok = torch.zeros(n_edits, dtype=torch.int32)
+        edit_sub = torch.zeros(n_edits, dtype=torch.float32)
+        edit_fac = torch.ones(n_edits, dtype=torch.float32)
+        if tokens:
+            edit_tok[:len(tokens)] = torch.tensor(tokens, dtype=torch.int32)
+            edit_sub[:len(tokens)] = torch.tensor(subs, dtype=torch.float32)
+            edit_fac[:len(tokens)] = torch.tensor(facs, dtype=torch.float32)
+        if self._work is None or self._work.shape[0] < B:
+            self._work = torch.empty((B, self.vocab_size), dtype=torch.float32, device=dev)
+            self._out = (torch.empty(B, dtype=torch.int32, device=dev), torch.empty(B, dtype=torch.float32, device=dev))
+        out_tok, out_prob = self._out[0][:B], self._out[1][:B]
+        ops.sample(logits, self._work[:B], params_dev, edit_tok.to(dev), edit_sub.to(dev), edit_fac.to(dev),
+                   out_tok, out_prob)
+        chosen = out_tok.tolist()
+        probs = out_prob.tolist()
+        for s, tok, pr in zip(samplers, chosen, probs):
+            s.accept(tok, pr)
+        return chosen

@@ -1,0 +1,73 @@
+"""The device sampler against the plain restatement of the reference's sampler."""
+import pytest
+import torch
+
+import plain_llama as P
+from llmplayer_b200.sampling import BatchSampler, SamplerConfig, SequenceSampler
+
+pytestmark = pytest.mark.gpu
+
+CONFIGS = [
+    dict(temperature=0.0, top_k=1, top_p=1.0, repetition_penalty=1.0),
+    dict(temperature=0.0, top_k=40, top_p=0.9, repetition_penalty=1.3),
+    dict(temperature=0.8, top_k=0, top_p=1.0, repetition_penalty=1.0),
+    dict(temperature=0.7, top_k=40, top_p=0.9, repetition_penalty=1.1),          # the reference's defaults
+    dict(temperature=1.3, top_k=0, top_p=0.8, repetition_penalty=1.0),
+    dict(temperature=1.0, top_k=5000, top_p=0.95, repetition_penalty=1.2),       # more survivors than fit on chip
+    dict(temperature=1.0, top_k=0, top_p=1.0, min_p=0.05, repetition_penalty=1.0),
+    dict(temperature=0.9, top_k=50, top_p=1.0, mirostat=2, mirostat_tau=3.0, mirostat_eta=0.2, repetition_penalty=1.0),
+    dict(temperature=1.0, top_k=0, top_p=1.0, mirostat=2, repetition_penalty=1.0),
+    dict(temperature=0.8, top_k=20, top_p=0.9, repetition_penalty=1.1, dry_multiplier=0.8, dry_allowed_length=1,
+         dry_range=16),
+]
+
+
+def make_logits(V, steps, seed, spread):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(steps, V, generator=g) * spread
+    x[:, 7] = x[:, 11]                       # exact ties
+    x[::3, 5] = x[::3].max(dim=1).values     # ... also at the maximum
+    return x
+
+
+@pytest.mark.parametrize("V,spread", [(1000, 3.0), (5003, 1.5), (128256, 2.0)])
+def test_batched_sampler_follows_the_plain_one(V, spread):
+    steps = 24 if V < 100000 else 6
+    dev = torch.device("cuda:0")
+    configs = CONFIGS if V < 100000 else CONFIGS[:8]
+    logits = [make_logits(V, steps, seed=i, spread=spread) for i in range(len(configs))]
+    if V < 100000:
+        for x in logits:                     # a small alphabet in the lead, so that tokens repeat
+            x[:, :6] += 3.0 * spread
+    plain = [P.PlainSampler(seed=100 + i, **c) for i, c in enumerate(configs)]
+    ours = [SequenceSampler(SamplerConfig(seed=100 + i, **c)) for i, c in enumerate(configs)]
+    batch = BatchSampler(V, dev)
+    mismatches = []
+    for t in range(steps):
+        rows = torch.stack([x[t] for x in logits]).to(dev)
+        got = batch.sample(rows, list(range(len(configs))), ours)
+        want = [p.sample(x[t]) for p, x in zip(plain, logits)]
+        for i, (a, b) in enumerate(zip(got, want)):
+            if a != b:
+                mismatches.append((t, i, a, b))
+                # keep both histories alike so that later steps stay comparable
+                ours[i].recent[-1] = b
+    assert not mismatches, mismatches
+
+
+def test_draws_do_not_depend_on_the_batch():
+    dev = torch.device("cuda:0")
+    V = 777
+    x = make_logits(V, 10, seed=5, spread=2.0)
+    cfg = SamplerConfig(temperature=0.9, top_k=30, top_p=0.9, repetition_penalty=1.1, seed=42)
+    alone = SequenceSampler(cfg)
+    batch = BatchSampler(V, dev)
+    a = [batch.sample(x[t:t + 1].to(dev), [0], [alone])[0] for t in range(10)]
+    together = SequenceSampler(cfg)
+    other = SequenceSampler(SamplerConfig(temperature=1.5, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=1))
+    y = make_logits(V, 10, seed=6, spread=2.0)
+    b = []
+    for t in range(10):
+        rows = torch.stack([y[t], x[t]]).to(dev)
+        b.append(batch.sample(rows, [0, 1], [other, together])[1])
+    assert a == b
