@@ -158,6 +158,10 @@ class SequenceCache:
             for s, n in zip(slots, new_tokens):
                 group.pages.extend(s, self._length[s] + n)
 
+    def reserve_up_to(self, slots: Sequence[int], lengths: Sequence[int]) -> None:
+        """Pages for every slot up to the given total length, ahead of the steps that fill them."""
+        self.reserve(slots, [max(0, n - self.length(s)) for s, n in zip(slots, lengths)])
+
     def commit(self, slots: Sequence[int], new_tokens: Sequence[int]) -> None:
         """The step ran: lengths grow, pages behind a window go back."""
         for s, n in zip(slots, new_tokens):

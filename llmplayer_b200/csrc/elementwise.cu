@@ -152,3 +152,24 @@ extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_fr
 #undef LP_LAUNCH_ROPE
     return lp_check_launch("rope_cache_write");
 }
+
+// ---------------------------------------------------------------- advancing a decoding batch on the device
+// After a decode step whose sampler left one token per sequence: that token becomes the next
+// step's input, and every sequence moves on by one position. Lets decode steps follow one
+// another without the host (the reference keeps position and length on the device for the
+// same reason: java21 inference/CudaForwardPass.java:138-141).
+__global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ positions, int* __restrict__ kv_len,
+                               const int* __restrict__ sampled, int B) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < B) {
+        tokens[i] = sampled[i];
+        positions[i] += 1;
+        kv_len[i] += 1;
+    }
+}
+
+extern "C" int lp_advance(int* tokens, int* positions, int* kv_len, const int* sampled, int B, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, positions, kv_len, sampled, B);
+    return lp_check_launch("advance");
+}

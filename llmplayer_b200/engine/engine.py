@@ -41,6 +41,7 @@ class Engine:
         self.workspace = Workspace(runtime.device)
         self._sampler = None
         self.last_generation_stats = None
+        self.last_step_h2d_bytes = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -121,6 +122,7 @@ class Engine:
     def run(self, ctx: StepContext) -> torch.Tensor:
         """Run a planned step; returns float32 logits [wanted, vocab] (valid until the next step)."""
         logits = self.workspace.get("logits", (ctx.num_wanted, self.vocab_size), torch.float32)
+        self.last_step_h2d_bytes = ctx.h2d_bytes
         self.model.forward(ctx, self.cache, ctx.rows, logits)
         self.cache.commit([s.slot for s in ctx.sequences], [s.num_new for s in ctx.sequences])
         return logits

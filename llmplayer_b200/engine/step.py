@@ -61,7 +61,7 @@ class StepContext:
 
     def __init__(self, workspace: Workspace, sequences: List[SequenceStep], tokens: Sequence[int],
                  page_tables: List[List[List[int]]], wanted_rows: Sequence[int], *,
-                 min_table_width: int = 1):
+                 min_table_width: int = 1, meta_name: str = "step_meta"):
         self.workspace = workspace
         self.sequences = sequences
         self.num_tokens = T = len(tokens)
@@ -94,7 +94,8 @@ class StepContext:
                 view[base + i * w:base + i * w + len(table)] = table
         view[o[-1]:o[-1] + W] = wanted_rows
 
-        meta = workspace.get("step_meta", (total,), torch.int32)
+        meta = workspace.get(meta_name, (total,), torch.int32)
+        self.h2d_bytes = total * 4
         meta.copy_(host.pin_memory() if torch.cuda.is_available() else host, non_blocking=False)
         self.meta = meta
         self.tokens = meta[o[0]:o[0] + T]

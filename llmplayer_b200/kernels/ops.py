@@ -25,6 +25,7 @@ _SIGNATURES = {
         "lp_embed": [_P, _I, _P, _P, _I, _I, _P],
         "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P],
         "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+        "lp_advance": [_P, _P, _P, _P, _I, _P],
     },
     "gemm_plain": {
         "lp_gemm_plain": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -65,7 +66,17 @@ def require_gpu() -> None:
         raise ExtensionMissing("no CUDA device: this library runs on the GPU only and has no CPU path")
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels of this library have been launched by this process."""
+    return _launches
+
+
 def _check(lib: ctypes.CDLL, code: int) -> None:
+    global _launches
+    _launches += 1
     if code != 0:
         raise KernelError(lib.lp_last_error().decode("utf-8", "replace") or f"kernel call failed with code {code}")
 
@@ -258,3 +269,15 @@ def sample(logits: torch.Tensor, work: torch.Tensor, params: torch.Tensor, edit_
     _check(lib, lib.lp_sample(logits.data_ptr(), V, work.data_ptr(), V, params.data_ptr(), B, edit_token.data_ptr(),
                               edit_subtract.data_ptr(), edit_factor.data_ptr(), out_token.data_ptr(),
                               out_prob.data_ptr(), _stream()))
+
+
+def advance(tokens: torch.Tensor, positions: torch.Tensor, kv_len: torch.Tensor, sampled: torch.Tensor) -> None:
+    """tokens <- sampled; positions += 1; kv_len += 1 (a decoding batch moves on by one token)."""
+    B = tokens.numel()
+    for t, what in ((tokens, "tokens"), (positions, "positions"), (kv_len, "kv_len"), (sampled, "sampled")):
+        _want(t, f"advance {what}", torch.int32, 1)
+        if t.numel() != B:
+            raise KernelError(f"advance: {what} has {t.numel()} entries, tokens {B}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_advance(tokens.data_ptr(), positions.data_ptr(), kv_len.data_ptr(), sampled.data_ptr(), B,
+                               _stream()))

@@ -104,3 +104,28 @@ def test_prompt_too_long_is_an_error_response(tmp_path):
     out = eng.generate([list(range(15)), [1, 2, 3]], SamplerConfig.greedy(), max_tokens=40, stop_token_ids=())
     assert out[0].finish_reason == "error" and "prompt too long" in out[0].error
     assert out[1].finish_reason == "context" and out[1].token_count == 16 - 1 - 3 + 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_device_resident_decoding_equals_the_generation_loop(tmp_path, dtype):
+    """Decode steps that follow one another on the device (captured once, replayed) must
+    produce the tokens that the host-driven loop produces, across page boundaries."""
+    from llmplayer_b200 import Engine, SamplerConfig
+    from llmplayer_b200.engine.decode import DecodeSession
+    model_dir = make_model(tmp_path, "C", dtype=dtype)
+    prompts = prompts_for("C", [50, 3, 61], seed=80)
+    eng = Engine.load(model_dir, dtype=dtype, context_length=512, max_batch=3)
+    steps = 90
+    ref = eng.generate(prompts, SamplerConfig.greedy(), max_tokens=steps + 1, stop_token_ids=())
+    session = DecodeSession(eng, prompts, reserve=61 + steps + 2)
+    try:
+        session.run(steps, keep_tokens=True)
+        got = session.tokens()
+    finally:
+        session.close()
+    if dtype == "float32":
+        assert got == [r.token_ids for r in ref]
+    else:
+        for p, g in zip(prompts, got):
+            check_greedy_chain(model_dir, p, g, dtype)
+    assert eng.cache.slots.num_held == 0
