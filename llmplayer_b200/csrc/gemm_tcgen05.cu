@@ -1,0 +1,371 @@
+// Tensor-core matrix product for bfloat16 weights stored [out, in]:
+//   C[tokens, features] (=|+=) X[tokens, K] * W[features, K]^T          (float32 accumulation)
+//
+// Blackwell path: TMA (cp.async.bulk.tensor, 128-byte swizzle, no multicast) brings
+// tiles of W and X into a ring of shared-memory stages; one thread issues tcgen05.mma
+// (kind::f16, bf16 in, fp32 out) with the accumulator in tensor memory; four warps read
+// the accumulator back with tcgen05.ld and run the epilogue. The weights are the MMA's
+// 128-row operand and the tokens its N operand (16..256), so the same kernel streams
+// weights for a handful of decoding sequences and tiles a long prompt. A K range can be
+// split over CTAs (grid.z); partial sums then meet in float32 atomics.
+//
+// Epilogues: store (float32 or bfloat16), add into a float32 output (the residual
+// stream, or split-K partial sums), or the gated activation silu(gate) * up for W that
+// stacks the gate rows over the up rows.
+//
+// Counterparts in the reference are its one-warp-per-row SIMT kernels
+// (src/main/resources/kernels/cuda/matmul_bf16.cu:6-37, silu_mul.cu:6-15).
+//
+// Every wait on an mbarrier is bounded: after too many polls the waiting thread records
+// an error code in *status, and the CTA winds down (outstanding copies are awaited,
+// tensor memory is freed) instead of spinning forever.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define LP_GEMM_STORE 0
+#define LP_GEMM_ACCUMULATE 1
+#define LP_GEMM_SWIGLU 2
+
+namespace {
+
+constexpr int BLOCK_FEAT = 128;   // weight rows per CTA = MMA M
+constexpr int BLOCK_K = 64;       // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;      // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+constexpr uint32_t SPIN_LIMIT = 1u << 20;
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 64) __nanosleep(40);
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in
+// groups of 8 rows (1024 bytes): start address, leading offset 1 (unused for swizzled
+// K-major), stride between 8-row groups 1024 bytes, descriptor version 1, layout SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BLOCK_TOK, int MODE>
+struct Tile {
+    static constexpr int W_TILES = MODE == LP_GEMM_SWIGLU ? 2 : 1;
+    static constexpr int W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
+    static constexpr int X_BYTES = BLOCK_TOK * BLOCK_K * 2;
+    static constexpr int STAGE_BYTES = W_TILES * W_BYTES + X_BYTES;
+    static constexpr int STAGES = (196 * 1024 / STAGE_BYTES) > 8 ? 8 : (196 * 1024 / STAGE_BYTES);
+    static constexpr int ACC_COLS = BLOCK_TOK * W_TILES;
+    static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;       // power of two by construction
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+};
+
+// out: [tokens, ldc]; OUT_BF16 selects the element type of a STORE / SWIGLU output.
+template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                    void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
+                    int up_row_offset, int* __restrict__ status) {
+    using T = Tile<BLOCK_TOK, MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + T::STAGES * T::STAGE_BYTES);
+    uint64_t* empty = full + T::STAGES;
+    uint64_t* acc_ready = empty + T::STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int feat0 = blockIdx.x * BLOCK_FEAT;
+    const int tok0 = blockIdx.y * BLOCK_TOK;
+    const int kb_begin = blockIdx.z * k_blocks_per_split;
+    const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
+    const int nkb = kb_end - kb_begin;            // > 0 by the launcher's choice of grid.z
+
+    // a launch whose status word already reports a failed wait does no work
+    __shared__ int already_failed;
+    if (threadIdx.x == 0) already_failed = *((volatile int*)status);
+    __syncthreads();
+    if (already_failed) return;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)T::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            int issued = 0;
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % T::STAGES;
+                const uint32_t phase = (i / T::STAGES) & 1;
+                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 1); ok = false; break; }
+                uint8_t* stage = smem + s * T::STAGE_BYTES;
+                mbar_expect_tx(&full[s], T::STAGE_BYTES);
+                const int k = (kb_begin + i) * BLOCK_K;
+                tma_load_2d(stage, &map_w, k, feat0, &full[s]);
+                if (MODE == LP_GEMM_SWIGLU) tma_load_2d(stage + T::W_BYTES, &map_w, k, feat0 + up_row_offset, &full[s]);
+                tma_load_2d(stage + T::W_TILES * T::W_BYTES, &map_x, k, tok0, &full[s]);
+                issued = i + 1;
+            }
+            if (!ok) {
+                // consumers may be gone: await the copies still in flight before the CTA's memory is released
+                for (int i = max(0, issued - T::STAGES); i < issued; ++i)
+                    mbar_wait(&full[i % T::STAGES], (i / T::STAGES) & 1);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_TOK >> 3) << 17) |
+                                       ((uint32_t)(BLOCK_FEAT >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % T::STAGES;
+                const uint32_t phase = (i / T::STAGES) & 1;
+                if (!mbar_wait(&full[s], phase)) { atomicExch(status, 2); ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t w_addr = smem_u32(smem + s * T::STAGE_BYTES);
+                const uint32_t x_addr = w_addr + T::W_TILES * T::W_BYTES;
+                const uint64_t dw = smem_desc(w_addr), dx = smem_desc(x_addr);
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const uint64_t step = (uint64_t)((k * UMMA_K * 2) >> 4);
+                    tcgen05_mma(tmem_base, dw + step, dx + step, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    if (MODE == LP_GEMM_SWIGLU) {
+                        const uint64_t du = smem_desc(w_addr + T::W_BYTES);
+                        tcgen05_mma(tmem_base + BLOCK_TOK, du + step, dx + step, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    }
+                }
+                tcgen05_commit(&empty[s]);        // the stage is free once these MMAs have read it
+            }
+            (void)ok;
+            tcgen05_commit(acc_ready);            // arrives when every MMA issued so far is complete
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;             // TMEM lanes 32*quarter .. +31 belong to this warp
+        const bool ready = mbar_wait(acc_ready, 0);
+        if (!ready && lane == 0) atomicExch(status, 3);
+        tcgen05_fence_after();
+        const bool go = __all_sync(0xffffffffu, ready && *((volatile int*)status) == 0);
+        if (go) {
+            const int f = feat0 + quarter * 32 + lane;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            constexpr int CHUNK = BLOCK_TOK >= 32 ? 32 : 16;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
+                uint32_t g[CHUNK], u[MODE == LP_GEMM_SWIGLU ? CHUNK : 1];
+                if (CHUNK == 32) tmem_ld32(lane_addr + c0, g); else tmem_ld16(lane_addr + c0, g);
+                if (MODE == LP_GEMM_SWIGLU) {
+                    if (CHUNK == 32) tmem_ld32(lane_addr + BLOCK_TOK + c0, u); else tmem_ld16(lane_addr + BLOCK_TOK + c0, u);
+                }
+                tmem_ld_wait();
+                if (f < features) {
+#pragma unroll
+                    for (int j = 0; j < CHUNK; ++j) {
+                        const int t = tok0 + c0 + j;
+                        if (t >= tokens) break;
+                        float v = __uint_as_float(g[j]);
+                        if (MODE == LP_GEMM_SWIGLU) v = v / (1.0f + __expf(-v)) * __uint_as_float(u[j]);
+                        const size_t at = (size_t)t * ldc + f;
+                        if (ATOMIC) atomicAdd((float*)out + at, v);
+                        else if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                        else ((float*)out)[at] = v;
+                    }
+                }
+            }
+        }
+        tcgen05_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS));
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with row stride `ld` elements, cut into boxes of box_rows x 64.
+int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
+    EncodeTiled enc = encode_fn();
+    if (!enc) LP_REFUSE("gemm: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) LP_REFUSE("gemm: cuTensorMapEncodeTiled failed with code %d for a [%lld, %lld] matrix",
+                                     (int)r, rows, K);
+    return 0;
+}
+
+template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
+           int splits, int up_offset, int* status, cudaStream_t stream) {
+    using T = Tile<BLOCK_TOK, MODE>;
+    auto kernel = gemm_tcgen05_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+        if (e != cudaSuccess) LP_REFUSE("gemm: cannot reserve %d bytes of shared memory: %s", T::SMEM_BYTES,
+                                        cudaGetErrorString(e));
+        configured = true;
+    }
+    const int per_split = (k_blocks + splits - 1) / splits;
+    const int grid_z = (k_blocks + per_split - 1) / per_split;
+    dim3 grid((features + BLOCK_FEAT - 1) / BLOCK_FEAT, (tokens + BLOCK_TOK - 1) / BLOCK_TOK, grid_z);
+    kernel<<<grid, THREADS, T::SMEM_BYTES, stream>>>(mw, mx, out, tokens, features, ldc, k_blocks, per_split, up_offset,
+                                                     status);
+    return lp_check_launch("gemm_tcgen05");
+}
+
+template <int BLOCK_TOK>
+int dispatch(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens,
+             int features, int ldc, int k_blocks, int splits, int up_offset, int* status, cudaStream_t stream) {
+#define LP_GO(MODE, BF, AT) \
+    return launch<BLOCK_TOK, MODE, BF, AT>(mw, mx, out, tokens, features, ldc, k_blocks, splits, up_offset, status, stream)
+    if (mode == LP_GEMM_SWIGLU) {
+        if constexpr (BLOCK_TOK <= 128) { if (out_bf16) LP_GO(LP_GEMM_SWIGLU, true, false); LP_GO(LP_GEMM_SWIGLU, false, false); }
+        else LP_REFUSE("gemm: the gated epilogue takes token tiles up to 128");
+    }
+    if (atomic) LP_GO(LP_GEMM_STORE, false, true);
+    if (out_bf16) LP_GO(LP_GEMM_STORE, true, false);
+    LP_GO(LP_GEMM_STORE, false, false);
+#undef LP_GO
+}
+
+}  // namespace
+
+// X: [tokens, K] bf16 (row stride ldx); W: [features, K] bf16, or [2*features, K] for SWIGLU (row stride ldw);
+// out: [tokens, ldc] float32 or bfloat16. mode: STORE / ACCUMULATE / SWIGLU. block_tok: 16..256 (a power of two).
+// splits > 1 or ACCUMULATE adds into a float32 `out` with atomics (a STORE with splits needs `out` zeroed before).
+// status: one int in device memory, set non-zero if a wait inside the kernel ran out.
+extern "C" int lp_gemm_tcgen05(const void* X, const void* W, void* out, int out_dtype, int tokens, int features, int K,
+                               int ldx, int ldw, int ldc, int mode, int block_tok, int splits, int* status,
+                               cudaStream_t stream) {
+    if (tokens <= 0 || features <= 0) return 0;
+    if (K <= 0 || K % 8) LP_REFUSE("gemm: inner size %d must be a positive multiple of 8 for the tensor-core path", K);
+    if (ldx % 8 || ldw % 8) LP_REFUSE("gemm: row strides %d / %d must be multiples of 8 elements", ldx, ldw);
+    if (((uintptr_t)X | (uintptr_t)W) & 15) LP_REFUSE("gemm: operands must be 16-byte aligned");
+    if (mode < 0 || mode > 2) LP_REFUSE("gemm: mode %d", mode);
+    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+    if (splits < 1) splits = 1;
+    if (splits > k_blocks) splits = k_blocks;
+    const bool atomic = mode == LP_GEMM_ACCUMULATE || (mode == LP_GEMM_STORE && splits > 1);
+    if (mode == LP_GEMM_SWIGLU && splits > 1) LP_REFUSE("gemm: the gated epilogue cannot be split along K");
+    if (atomic && out_dtype != LP_F32) LP_REFUSE("gemm: sums across CTAs need a float32 output");
+    if (out_dtype != LP_F32 && out_dtype != LP_BF16) LP_REFUSE("gemm: output dtype code %d", out_dtype);
+    const long long w_rows = mode == LP_GEMM_SWIGLU ? 2LL * features : features;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, w_rows, K, ldw, BLOCK_FEAT);
+    if (rc) return rc;
+    rc = make_map(&mx, X, tokens, K, ldx, block_tok);
+    if (rc) return rc;
+    const bool bf = out_dtype == LP_BF16;
+    const int mmode = mode == LP_GEMM_SWIGLU ? LP_GEMM_SWIGLU : LP_GEMM_STORE;
+    switch (block_tok) {
+        case 16: return dispatch<16>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
+        case 32: return dispatch<32>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
+        case 64: return dispatch<64>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
+        case 128: return dispatch<128>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
+        case 256: return dispatch<256>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
+        default: LP_REFUSE("gemm: token tile %d (supported: 16, 32, 64, 128, 256)", block_tok);
+    }
+}

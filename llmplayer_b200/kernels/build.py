@@ -30,6 +30,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_plain": "gemm_plain.cu",
     "attention_plain": "attention_plain.cu",
     "sampling": "sampling.cu",
+    "gemm_tcgen05": "gemm_tcgen05.cu",
 }
 HEADERS = ("common.cuh",)
 

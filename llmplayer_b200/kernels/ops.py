@@ -26,12 +26,16 @@ _SIGNATURES = {
         "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P],
         "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "lp_advance": [_P, _P, _P, _P, _I, _P],
+        "lp_swiglu_combine": [_P, _P, _I, _I, _I, _P],
     },
     "gemm_plain": {
         "lp_gemm_plain": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     },
     "attention_plain": {
         "lp_attention_plain": [_P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+    },
+    "gemm_tcgen05": {
+        "lp_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     },
     "sampling": {
         "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
@@ -210,7 +214,97 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = 
 
 
 def fast_gemm_available() -> bool:
-    return False
+    return True
+
+
+NUM_SMS = 148
+_status = None
+
+
+def kernel_status() -> torch.Tensor:
+    """One int32 in device memory that kernels with bounded waits set when a wait runs out."""
+    global _status
+    if _status is None:
+        _status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return _status
+
+
+def check_kernel_status() -> None:
+    """Raise if a kernel reported a wait that ran out. Reads the word back, which synchronises."""
+    if _status is not None and int(_status.item()) != 0:
+        code = int(_status.item())
+        _status.zero_()
+        raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}: "
+                          "1 = loader, 2 = MMA issuer, 3 = epilogue)")
+
+
+def _token_tile(tokens: int, gated: bool) -> int:
+    for tile in (16, 32, 64, 128):
+        if tokens <= tile:
+            return tile
+    return 128 if gated else 256
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, block_tok: int = 0,
+         splits: int = 0, scratch=None) -> torch.Tensor:
+    """out (=|+=) a @ w.T on the tensor cores (bfloat16 in, float32 accumulation).
+
+    ``a`` [tokens, K] and ``w`` [features, K] (``[2*features, K]`` for ``SWIGLU``) are bfloat16.
+    When few CTAs would cover the output, the K range is split over more of them and the
+    partial sums meet in float32 atomics; a gated product is then summed un-activated into
+    ``scratch(name, shape, dtype)`` and activated by a second small kernel.
+    """
+    _want(a, "gemm a", torch.bfloat16, 2)
+    _want(w, "gemm w", torch.bfloat16, 2)
+    _want(out, "gemm out", ndim=2)
+    M, K = a.shape
+    N = out.shape[1]
+    rows = 2 * N if mode == SWIGLU else N
+    if w.shape != (rows, K) or out.shape[0] != M:
+        raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, mode {mode}")
+    if M == 0:
+        return out
+    lib = library("gemm_tcgen05")
+    status = kernel_status()
+    k_blocks = -(-K // 64)
+
+    def pick_splits(features: int, tile: int) -> int:
+        ctas = -(-features // 128) * -(-M // tile)
+        if ctas >= NUM_SMS // 2 or k_blocks < 8:
+            return 1
+        return max(1, min(NUM_SMS // ctas, k_blocks // 4))
+
+    if mode == SWIGLU:
+        tile = block_tok or _token_tile(M, True)
+        want_splits = splits or pick_splits(2 * N, tile)
+        if want_splits > 1 or tile > 128:
+            # summed across CTAs: plain product into float32 scratch, then the activation
+            gu = scratch("gate_up_sums", (M, 2 * N), torch.float32) if scratch else \
+                torch.empty((M, 2 * N), dtype=torch.float32, device=a.device)
+            gemm(a, w, gu, STORE, block_tok=block_tok, splits=want_splits)
+            _check(lib_elementwise(), lib_elementwise().lp_swiglu_combine(
+                gu.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, _stream()))
+            return out
+        _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
+                                        K, K, N, SWIGLU, tile, 1, status.data_ptr(), _stream()))
+        return out
+    tile = block_tok or _token_tile(M, False)
+    n_splits = splits or pick_splits(N, tile)
+    if mode == ACCUMULATE:
+        if out.dtype != torch.float32:
+            raise KernelError("gemm: accumulation needs a float32 output")
+    elif n_splits > 1:
+        if out.dtype != torch.float32:
+            n_splits = 1
+        else:
+            out.zero_()
+    _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
+                                    K, K, N, mode, tile, n_splits, status.data_ptr(), _stream()))
+    return out
+
+
+def lib_elementwise():
+    return library("elementwise")
 
 
 # --------------------------------------------------------------------------- attention

@@ -26,7 +26,9 @@ class Linear:
         self.out_features, self.in_features = self.weight.shape
 
     def _fast(self) -> bool:
-        return self.runtime.fast and self.weight.dtype == torch.bfloat16 and ops.fast_gemm_available()
+        # the tensor-core kernel wants bfloat16 operands and rows of a multiple of 8 elements (TMA strides)
+        return (self.runtime.fast and self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
+                and ops.fast_gemm_available())
 
     def store(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return self._run(x, out, ops.STORE)
@@ -38,6 +40,6 @@ class Linear:
         return self._run(x, out, ops.SWIGLU)
 
     def _run(self, x, out, mode):
-        if self._fast():
+        if self._fast() and x.dtype == torch.bfloat16:
             return ops.gemm(x, self.weight, out, mode)
         return ops.gemm_plain(x, self.weight, out, mode)

@@ -1,0 +1,100 @@
+"""The matrix-product kernels alone, against a float32 product of the same inputs."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def reference(a, w, mode, out0=None):
+    from llmplayer_b200.kernels import ops
+    a32, w32 = a.double(), w.double()
+    if mode == ops.SWIGLU:
+        F = w.shape[0] // 2
+        g, u = a32 @ w32[:F].T, a32 @ w32[F:].T
+        return (g / (1 + torch.exp(-g))) * u
+    r = a32 @ w32.T
+    return r + out0.double() if mode == ops.ACCUMULATE else r
+
+
+def rel_err(got, ref):
+    return float((got.double() - ref).abs().max() / ref.abs().max())
+
+
+SHAPES = [(1, 64, 64), (5, 100, 72), (8, 3072, 2048), (17, 130, 200), (64, 256, 4096), (70, 264, 136),
+          (300, 520, 328), (1, 128256, 64), (513, 640, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("mode", ["store", "accumulate", "swiglu"])
+def test_tensor_core_gemm(M, N, K, mode):
+    from llmplayer_b200.kernels import ops
+    torch.manual_seed(M * 7 + N + K)
+    dev = "cuda:0"
+    code = {"store": ops.STORE, "accumulate": ops.ACCUMULATE, "swiglu": ops.SWIGLU}[mode]
+    if mode == "swiglu" and N > 4096:
+        pytest.skip("no gated product that wide")
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    w = (torch.randn(N * (2 if mode == "swiglu" else 1), K, device=dev) / K ** 0.5).to(torch.bfloat16)
+    for out_dtype in ([torch.float32] if mode == "accumulate" else [torch.float32, torch.bfloat16]):
+        out0 = torch.randn(M, N, device=dev)
+        out = out0.clone().to(out_dtype)
+        ops.gemm(a, w, out, code)
+        torch.cuda.synchronize()
+        ops.check_kernel_status()
+        ref = reference(a, w, code, out0)
+        tol = 1e-5 if out_dtype == torch.float32 else 5e-3          # bf16 output: one rounding
+        assert rel_err(out, ref) < tol, (M, N, K, mode, out_dtype, rel_err(out, ref))
+
+
+@pytest.mark.parametrize("tile,splits", [(16, 1), (16, 4), (32, 3), (64, 2), (128, 1), (256, 1), (256, 2)])
+def test_every_tile_and_split(tile, splits):
+    from llmplayer_b200.kernels import ops
+    torch.manual_seed(tile + splits)
+    M, N, K = 333, 392, 1096
+    a = torch.randn(M, K, device="cuda:0").to(torch.bfloat16)
+    w = (torch.randn(N, K, device="cuda:0") / K ** 0.5).to(torch.bfloat16)
+    out = torch.full((M, N), 7.0, device="cuda:0")
+    ops.gemm(a, w, out, ops.STORE, block_tok=tile, splits=splits)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    assert rel_err(out, reference(a, w, ops.STORE)) < 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (5, 100, 70), (64, 256, 513), (130, 70, 33)])
+@pytest.mark.parametrize("mode", ["store", "accumulate", "swiglu"])
+@pytest.mark.parametrize("dtypes", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                    (torch.bfloat16, torch.float32)])
+def test_plain_gemm(M, N, K, mode, dtypes):
+    from llmplayer_b200.kernels import ops
+    torch.manual_seed(M + N + K)
+    code = {"store": ops.STORE, "accumulate": ops.ACCUMULATE, "swiglu": ops.SWIGLU}[mode]
+    a = torch.randn(M, K, device="cuda:0").to(dtypes[0])
+    w = (torch.randn(N * (2 if mode == "swiglu" else 1), K, device="cuda:0") / K ** 0.5).to(dtypes[1])
+    out0 = torch.randn(M, N, device="cuda:0")
+    out = out0.clone()
+    ops.gemm_plain(a, w, out, code)
+    assert rel_err(out, reference(a, w, code, out0)) < 2e-6
+
+
+def test_plain_gemm_rows_do_not_depend_on_the_batch():
+    from llmplayer_b200.kernels import ops
+    a = torch.randn(70, 300, device="cuda:0")
+    w = torch.randn(90, 300, device="cuda:0")
+    whole = torch.empty(70, 90, device="cuda:0")
+    ops.gemm_plain(a, w, whole)
+    one = torch.empty(1, 90, device="cuda:0")
+    ops.gemm_plain(a[37:38].contiguous(), w, one)
+    assert torch.equal(whole[37:38], one)
+
+
+def test_refusals():
+    from llmplayer_b200.errors import KernelError
+    from llmplayer_b200.kernels import ops
+    a = torch.randn(4, 20, device="cuda:0").to(torch.bfloat16)
+    w = torch.randn(8, 20, device="cuda:0").to(torch.bfloat16)
+    with pytest.raises(KernelError, match="multiple of 8"):
+        ops.gemm(a, w, torch.empty(4, 8, device="cuda:0"))
+    with pytest.raises(KernelError, match="gemm"):
+        ops.gemm(a, w, torch.empty(4, 9, device="cuda:0"))
+    with pytest.raises(KernelError):
+        ops.gemm_plain(a.cpu(), w, torch.empty(4, 8, device="cuda:0"))
