@@ -1,0 +1,499 @@
+// Tensor-core attention over the paged bfloat16 cache: one kernel for steps that bring
+// many tokens per sequence (prefill), one for steps of one token per sequence (decode),
+// and the merge of a decode step's partial results.
+//
+// Both kernels stream pages of 64 keys (and their values) into shared memory with
+// cp.async (16-byte chunks, rotated per row so that ldmatrix reads are conflict-free),
+// form scores with mma.sync m16n8k16 (bf16 in, fp32 out), keep a running maximum and sum
+// per query row in float32 (online softmax, exp2 with the scale folded in) and accumulate
+// probabilities times values with a second mma. Masks: a key is seen by a query at
+// position p if key <= p and key > p - window (window <= 0: no window).
+//
+//  * prefill: a CTA takes 64 consecutive new tokens of one sequence and one query head;
+//    each of its 4 warps owns 16 query rows and visits the pages its rows can see.
+//  * decode:  a CTA takes one sequence, one key/value head and one share of the pages; the
+//    query heads that share the key/value head are the 16 rows of the MMA, so each key and
+//    value is read once for all of them; each warp owns 16 of a page's 64 keys; the CTA
+//    writes an unnormalised partial result (max, sum, output), merged by a second kernel.
+//
+// Reference: src/main/resources/kernels/cuda/attention.cu:10-108 (one block per head,
+// scores of one query in shared memory) and the online-softmax form of
+// inference/Attention.java:161-207; head mapping kvHead = h / (H/G) (inference/Attention.java:212).
+#include "common.cuh"
+
+namespace {
+
+constexpr int PAGE = 64;
+constexpr float NEG_BIG = -1.0e30f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Position of 16-byte chunk c of row r inside a tile whose rows hold cpr chunks.
+__device__ __forceinline__ int swz(int r, int c, int cpr) {
+    return (cpr & 7) == 0 ? (c ^ (r & 7)) : (c + r) % cpr;
+}
+
+// Copy one page (64 keys and 64 values of one kv head) into a stage: K tile, then V tile.
+__device__ __forceinline__ void load_page(uint8_t* stage, const __nv_bfloat16* pages, int page, int G, int g, int hd,
+                                          int tid, int nthreads) {
+    const int cpr = hd >> 3;
+    const int per_tile = PAGE * cpr;
+    const uint32_t base = smem_u32(stage);
+    const size_t tile_elems = (size_t)PAGE * hd;
+    for (int i = tid; i < 2 * per_tile; i += nthreads) {
+        const int which = i >= per_tile;
+        const int j = which ? i - per_tile : i;
+        const int r = j / cpr, c = j - r * cpr;
+        const __nv_bfloat16* src = pages + (((size_t)page * 2 + which) * G + g) * tile_elems + (size_t)r * hd + c * 8;
+        cp_async16(base + which * (uint32_t)(tile_elems * 2) + r * (hd * 2) + swz(r, c, cpr) * 16, src);
+    }
+}
+
+// S[16 x 16 keys] += Q[16 x hd] K^T for the keys key0..key0+15 of the K tile (two n-tiles of 8 keys).
+template <int KSTEPS>
+__device__ __forceinline__ void scores_16keys(float (*s)[4], const uint32_t (*q)[4], uint32_t k_tile, int key0,
+                                              int hd, int lane) {
+    const int cpr = hd >> 3;
+    const int mat = lane >> 3, row = lane & 7;
+    const int key = key0 + (mat >> 1) * 8 + row;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+        if (kk * 16 < hd) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(k_tile + key * (hd * 2) + swz(key, kk * 2 + (mat & 1), cpr) * 16, b0, b1, b2, b3);
+            mma_bf16(s[0], q[kk], b0, b1);
+            mma_bf16(s[1], q[kk], b2, b3);
+        }
+    }
+}
+
+// O[16 x hd] += P[16 x 16 keys] V for the keys key0..key0+15 of the V tile.
+template <int KSTEPS>
+__device__ __forceinline__ void values_16keys(float (*o)[4], const uint32_t* p, uint32_t v_tile, int key0, int hd,
+                                              int lane) {
+    const int cpr = hd >> 3;
+    const int mat = lane >> 3, row = lane & 7;
+    const int key = key0 + (mat & 1) * 8 + row;
+#pragma unroll
+    for (int dd = 0; dd < KSTEPS; ++dd) {       // 16 output features per step
+        if (dd * 16 < hd) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(v_tile + key * (hd * 2) + swz(key, dd * 2 + (mat >> 1), cpr) * 16, b0, b1, b2, b3);
+            mma_bf16(o[dd * 2], p, b0, b1);
+            mma_bf16(o[dd * 2 + 1], p, b2, b3);
+        }
+    }
+}
+
+// ============================================================================ prefill
+// grid: (tiles of 64 new tokens, H, B); 128 threads.
+template <int HD_MAX>
+__global__ void __launch_bounds__(128)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                         const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table, int pt_stride,
+                         const int* __restrict__ q_start, const int* __restrict__ kv_len, int H, int G, int hd,
+                         float scale_log2, int window) {
+    constexpr int KSTEPS = HD_MAX / 16;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int b = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t_begin = q_start[b], n_new = q_start[b + 1] - t_begin;
+    if (tile * 64 >= n_new) return;
+    const int g = h / (H / G);
+    const int len = kv_len[b];
+    const int pos0 = len - n_new;                       // position of the sequence's first new token
+    const int row0 = tile * 64;                         // first query row of this CTA among the new tokens
+    const int rows = min(64, n_new - row0);
+    const int first_pos = pos0 + row0, last_pos = pos0 + row0 + rows - 1;
+    const int lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+    const int page_lo = lo / PAGE, page_hi = last_pos / PAGE;
+    const int* table = page_table + (size_t)b * pt_stride;
+    const int stage_bytes = 2 * PAGE * hd * 2;
+
+    // query fragments of this warp's 16 rows
+    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+    uint32_t qf[KSTEPS][4];
+    {
+        const __nv_bfloat16* q_lo = q + ((size_t)(t_begin + row0 + min(r_lo, rows - 1)) * H + h) * hd;
+        const __nv_bfloat16* q_hi = q + ((size_t)(t_begin + row0 + min(r_hi, rows - 1)) * H + h) * hd;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            if (kk * 16 < hd) {
+                const int c = kk * 16 + (lane & 3) * 2;
+                qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_lo + c);
+                qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_hi + c);
+                qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_lo + c + 8);
+                qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_hi + c + 8);
+            }
+        }
+    }
+    const int pos_lo = first_pos + min(r_lo, rows - 1), pos_hi = first_pos + min(r_hi, rows - 1);
+    const int warp_last_pos = first_pos + min(warp * 16 + 15, rows - 1);
+    const int warp_first_pos = first_pos + min(warp * 16, rows - 1);
+
+    float o[KSTEPS * 2][4];
+#pragma unroll
+    for (int i = 0; i < KSTEPS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
+
+    load_page(smem, pages, table[page_lo], G, g, hd, tid, 128);
+    cp_async_commit();
+    for (int p = page_lo; p <= page_hi; ++p) {
+        const int cur = (p - page_lo) & 1;
+        if (p + 1 <= page_hi) load_page(smem + (cur ^ 1) * stage_bytes, pages, table[p + 1], G, g, hd, tid, 128);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const int key_base = p * PAGE;
+        // pages wholly after this warp's rows, or wholly before their windows, contribute nothing
+        const bool active = key_base <= warp_last_pos &&
+                            (window <= 0 || key_base + PAGE - 1 > warp_first_pos - window);
+        if (active) {
+            const uint32_t k_tile = smem_u32(smem + cur * stage_bytes);
+            const uint32_t v_tile = k_tile + PAGE * hd * 2;
+            float s[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) scores_16keys<KSTEPS>(&s[ks * 2], qf, k_tile, ks * 16, hd, lane);
+            const bool edge = key_base + PAGE - 1 > warp_first_pos ||
+                              (window > 0 && key_base <= warp_last_pos - window);
+            float mx_lo = NEG_BIG, mx_hi = NEG_BIG;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key_base + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const int pos = (e < 2) ? pos_lo : pos_hi;
+                    float v = s[nt][e] * scale_log2;
+                    if (edge && (key > pos || (window > 0 && key <= pos - window))) v = NEG_BIG;
+                    s[nt][e] = v;
+                    if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+                }
+            }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+            const float a_lo = exp2f(m_lo - mn_lo), a_hi = exp2f(m_hi - mn_hi);
+            m_lo = mn_lo; m_hi = mn_hi;
+            float sum_lo = 0.f, sum_hi = 0.f;
+            uint32_t pf[4][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                float e0 = s[nt][0] <= NEG_BIG ? 0.f : exp2f(s[nt][0] - mn_lo);
+                float e1 = s[nt][1] <= NEG_BIG ? 0.f : exp2f(s[nt][1] - mn_lo);
+                float e2 = s[nt][2] <= NEG_BIG ? 0.f : exp2f(s[nt][2] - mn_hi);
+                float e3 = s[nt][3] <= NEG_BIG ? 0.f : exp2f(s[nt][3] - mn_hi);
+                sum_lo += e0 + e1; sum_hi += e2 + e3;
+                pf[nt >> 1][(nt & 1) * 2] = pack_bf16(e0, e1);
+                pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(e2, e3);
+            }
+            l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
+#pragma unroll
+            for (int i = 0; i < KSTEPS * 2; ++i) { o[i][0] *= a_lo; o[i][1] *= a_lo; o[i][2] *= a_hi; o[i][3] *= a_hi; }
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) values_16keys<KSTEPS>(o, pf[ks], v_tile, ks * 16, hd, lane);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
+#pragma unroll
+    for (int dt = 0; dt < KSTEPS * 2; ++dt) {
+        const int d = dt * 8 + (lane & 3) * 2;
+        if (d < hd) {
+            if (r_lo < rows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(t_begin + row0 + r_lo) * H + h) * hd + d) =
+                    pack_bf16(o[dt][0] * inv_lo, o[dt][1] * inv_lo);
+            if (r_hi < rows)
+                *reinterpret_cast<uint32_t*>(out + ((size_t)(t_begin + row0 + r_hi) * H + h) * hd + d) =
+                    pack_bf16(o[dt][2] * inv_hi, o[dt][3] * inv_hi);
+        }
+    }
+}
+
+// ============================================================================ decode
+// grid: (splits, G * head_groups, B); 128 threads; one new token per sequence.
+// Partial results: part_o[b][head][split][hd] (unnormalised), part_ml[b][head][split][2] = (max, sum),
+// both in log2 units of the scaled scores.
+template <int HD_MAX>
+__global__ void __launch_bounds__(128)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
+                        const int* __restrict__ page_table, int pt_stride, const int* __restrict__ kv_len,
+                        float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G, int hd,
+                        float scale_log2, int window, int pages_per_split, int num_splits, int head_groups) {
+    constexpr int KSTEPS = HD_MAX / 16;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const int split = blockIdx.x, b = blockIdx.z;
+    const int g = blockIdx.y / head_groups, hg = blockIdx.y - g * head_groups;
+    const int R = H / G;
+    const int head0 = g * R + hg * 16;
+    const int nrows = min(16, R - hg * 16);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int len = kv_len[b];
+    const int pos = len - 1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int page_lo = max(lo / PAGE, split * pages_per_split);
+    const int page_hi = min(pos / PAGE, (split + 1) * pages_per_split - 1);
+    const int* table = page_table + (size_t)b * pt_stride;
+    const int stage_bytes = 2 * PAGE * hd * 2;
+    constexpr int STAGES = 3;
+
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    uint32_t qf[KSTEPS][4];
+    {
+        const __nv_bfloat16* q_lo = q + ((size_t)b * H + head0 + min(r_lo, nrows - 1)) * hd;
+        const __nv_bfloat16* q_hi = q + ((size_t)b * H + head0 + min(r_hi, nrows - 1)) * hd;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            if (kk * 16 < hd) {
+                const int c = kk * 16 + (lane & 3) * 2;
+                qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_lo + c);
+                qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_hi + c);
+                qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_lo + c + 8);
+                qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_hi + c + 8);
+            }
+        }
+    }
+    float o[KSTEPS * 2][4];
+#pragma unroll
+    for (int i = 0; i < KSTEPS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
+
+    const int npages = page_hi - page_lo + 1;      // may be <= 0: this share holds nothing of the sequence
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < npages) load_page(smem + s * stage_bytes, pages, table[page_lo + s], G, g, hd, tid, 128);
+        cp_async_commit();
+    }
+    for (int i = 0; i < npages; ++i) {
+        const int nxt = i + STAGES - 1;
+        if (nxt < npages)
+            load_page(smem + (nxt % STAGES) * stage_bytes, pages, table[page_lo + nxt], G, g, hd, tid, 128);
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        __syncthreads();
+        const int key_base = (page_lo + i) * PAGE;
+        const int key0 = warp * 16;                  // this warp's 16 keys of the page
+        if (key_base + key0 <= pos && key_base + key0 + 15 >= lo) {
+            const uint32_t k_tile = smem_u32(smem + (i % STAGES) * stage_bytes);
+            const uint32_t v_tile = k_tile + PAGE * hd * 2;
+            float s[2][4];
+            s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+            scores_16keys<KSTEPS>(s, qf, k_tile, key0, hd, lane);
+            float mx_lo = NEG_BIG, mx_hi = NEG_BIG;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key_base + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    float v = s[nt][e] * scale_log2;
+                    if (key > pos || key < lo) v = NEG_BIG;
+                    s[nt][e] = v;
+                    if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+                }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+            const float a_lo = exp2f(m_lo - mn_lo), a_hi = exp2f(m_hi - mn_hi);
+            m_lo = mn_lo; m_hi = mn_hi;
+            uint32_t pf[4];
+            float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                float e0 = s[nt][0] <= NEG_BIG ? 0.f : exp2f(s[nt][0] - mn_lo);
+                float e1 = s[nt][1] <= NEG_BIG ? 0.f : exp2f(s[nt][1] - mn_lo);
+                float e2 = s[nt][2] <= NEG_BIG ? 0.f : exp2f(s[nt][2] - mn_hi);
+                float e3 = s[nt][3] <= NEG_BIG ? 0.f : exp2f(s[nt][3] - mn_hi);
+                sum_lo += e0 + e1; sum_hi += e2 + e3;
+                pf[nt * 2] = pack_bf16(e0, e1);
+                pf[nt * 2 + 1] = pack_bf16(e2, e3);
+            }
+            l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
+#pragma unroll
+            for (int j = 0; j < KSTEPS * 2; ++j) { o[j][0] *= a_lo; o[j][1] *= a_lo; o[j][2] *= a_hi; o[j][3] *= a_hi; }
+            values_16keys<KSTEPS>(o, pf, v_tile, key0, hd, lane);
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // merge the four warps (each saw a quarter of every page) through shared memory
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    float* sm_m = reinterpret_cast<float*>(smem);            // [4][16]
+    float* sm_l = sm_m + 64;                                 // [4][16]
+    float* sm_o = sm_l + 64;                                 // [4][16][hd]
+    if ((lane & 3) == 0) {
+        sm_m[warp * 16 + r_lo] = m_lo; sm_m[warp * 16 + r_hi] = m_hi;
+        sm_l[warp * 16 + r_lo] = l_lo; sm_l[warp * 16 + r_hi] = l_hi;
+    }
+#pragma unroll
+    for (int dt = 0; dt < KSTEPS * 2; ++dt) {
+        const int d = dt * 8 + (lane & 3) * 2;
+        if (d < hd) {
+            float* lo_row = sm_o + ((size_t)warp * 16 + r_lo) * hd + d;
+            float* hi_row = sm_o + ((size_t)warp * 16 + r_hi) * hd + d;
+            lo_row[0] = o[dt][0]; lo_row[1] = o[dt][1];
+            hi_row[0] = o[dt][2]; hi_row[1] = o[dt][3];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < nrows * hd; idx += 128) {
+        const int r = idx / hd, d = idx - r * hd;
+        float m = fmaxf(fmaxf(sm_m[r], sm_m[16 + r]), fmaxf(sm_m[32 + r], sm_m[48 + r]));
+        float acc = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = exp2f(sm_m[w * 16 + r] - m);
+            acc += sm_o[((size_t)w * 16 + r) * hd + d] * f;
+            l += sm_l[w * 16 + r] * f;
+        }
+        const size_t slot = ((size_t)b * H + head0 + r) * num_splits + split;
+        part_o[slot * hd + d] = acc;
+        if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+    }
+}
+
+// out[b][head][:] = sum_s part_o * 2^(m_s - m*) / sum_s l_s * 2^(m_s - m*); grid: (H, B), hd threads (<= 256).
+__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                       __nv_bfloat16* __restrict__ out, int H, int hd, int num_splits) {
+    const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+    const size_t base = ((size_t)b * H + h) * num_splits;
+    float m = NEG_BIG;
+    for (int s = 0; s < num_splits; ++s) m = fmaxf(m, part_ml[(base + s) * 2]);
+    float acc = 0.f, l = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+        const float ls = part_ml[(base + s) * 2 + 1];
+        if (ls > 0.f) {
+            const float f = exp2f(part_ml[(base + s) * 2] - m);
+            l += ls * f;
+            if (d < hd) acc += part_o[(base + s) * hd + d] * f;
+        }
+    }
+    if (d < hd) out[((size_t)b * H + h) * hd + d] = __float2bfloat16_rn(acc / l);
+}
+
+// Opt in to `bytes` of dynamic shared memory; remembered per kernel so that later calls
+// (also those recorded into a CUDA graph) make no runtime call.
+template <int TAG, typename K> int set_smem(K kernel, int bytes, const char* what) {
+    static int granted = 0;          // one copy per TAG: every kernel instantiation gets its own
+    if (bytes <= granted) return 0;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) {
+        snprintf(lp_error_text, sizeof(lp_error_text), "%s: cannot reserve %d bytes of shared memory: %s", what, bytes,
+                 cudaGetErrorString(e));
+        return (int)e;
+    }
+    granted = bytes;
+    return 0;
+}
+
+int check_geometry(const char* what, int H, int G, int hd) {
+    if (H <= 0 || G <= 0 || H % G) LP_REFUSE("%s: %d query heads over %d key heads", what, H, G);
+    if (hd < 16 || hd > 256 || hd % 16) LP_REFUSE("%s: head size %d (supported: multiples of 16 up to 256)", what, hd);
+    return 0;
+}
+
+}  // namespace
+
+// q, out: [T, H, hd] bf16; pages: [num_pages, 2, G, 64, hd] bf16; q_start: [B+1]; kv_len: [B] (after the step).
+// max_new: the largest number of new tokens of any sequence of the step.
+extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
+                                    const int* q_start, const int* kv_len, int B, int max_new, int H, int G, int hd,
+                                    int page_size, float scale, int window, cudaStream_t stream) {
+    if (B <= 0 || max_new <= 0) return 0;
+    int rc = check_geometry("attention_prefill", H, G, hd);
+    if (rc) return rc;
+    if (page_size != PAGE) LP_REFUSE("attention_prefill: pages of %d positions (built for %d)", page_size, PAGE);
+    if (H > 65535 || B > 65535) LP_REFUSE("attention_prefill: %d heads x %d sequences exceed the grid", H, B);
+    const int smem = 2 * (2 * PAGE * hd * 2);
+    dim3 grid((max_new + 63) / 64, H, B);
+    const float scale_log2 = scale * 1.4426950408889634f;
+#define LP_PREFILL(HDM)                                                                                          \
+    do {                                                                                                         \
+        rc = set_smem<HDM>(attention_prefill_kernel<HDM>, smem, "attention_prefill");                                 \
+        if (rc) return rc;                                                                                       \
+        attention_prefill_kernel<HDM><<<grid, 128, smem, stream>>>(                                              \
+            (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_table, pt_stride,     \
+            q_start, kv_len, H, G, hd, scale_log2, window);                                                      \
+    } while (0)
+    if (hd <= 64) LP_PREFILL(64); else if (hd <= 128) LP_PREFILL(128); else LP_PREFILL(256);
+#undef LP_PREFILL
+    return lp_check_launch("attention_prefill");
+}
+
+// Scratch a decode step needs, in floats: part_o [B, H, splits, hd] then part_ml [B, H, splits, 2].
+extern "C" long long lp_attention_decode_scratch(int B, int H, int hd, int num_splits) {
+    return (long long)B * H * num_splits * (hd + 2);
+}
+
+// q, out: [B, H, hd] bf16 (one token per sequence); kv_len: [B] (after the step). The pages of a sequence
+// are shared out over `num_splits` CTAs, `pages_per_split` each; scratch as sized above.
+extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
+                                   const int* kv_len, float* scratch, int B, int H, int G, int hd, int page_size,
+                                   float scale, int window, int pages_per_split, int num_splits,
+                                   cudaStream_t stream) {
+    if (B <= 0) return 0;
+    int rc = check_geometry("attention_decode", H, G, hd);
+    if (rc) return rc;
+    if (page_size != PAGE) LP_REFUSE("attention_decode: pages of %d positions (built for %d)", page_size, PAGE);
+    if (pages_per_split <= 0 || num_splits <= 0) LP_REFUSE("attention_decode: %d shares of %d pages", num_splits, pages_per_split);
+    const int head_groups = (H / G + 15) / 16;
+    if (G * head_groups > 65535 || B > 65535) LP_REFUSE("attention_decode: grid too large");
+    const int stage = 2 * PAGE * hd * 2;
+    const int merge = (128 + 64 * hd) * 4;
+    const int smem = 3 * stage > merge ? 3 * stage : merge;
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)B * H * num_splits * hd;
+    dim3 grid(num_splits, G * head_groups, B);
+    const float scale_log2 = scale * 1.4426950408889634f;
+#define LP_DECODE(HDM)                                                                                           \
+    do {                                                                                                         \
+        rc = set_smem<1000 + HDM>(attention_decode_kernel<HDM>, smem, "attention_decode");                                   \
+        if (rc) return rc;                                                                                       \
+        attention_decode_kernel<HDM><<<grid, 128, smem, stream>>>(                                               \
+            (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml, \
+            H, G, hd, scale_log2, window, pages_per_split, num_splits, head_groups);                             \
+    } while (0)
+    if (hd <= 64) LP_DECODE(64); else if (hd <= 128) LP_DECODE(128); else LP_DECODE(256);
+#undef LP_DECODE
+    rc = lp_check_launch("attention_decode");
+    if (rc) return rc;
+    attention_merge_kernel<<<dim3(H, B), hd <= 32 ? 32 : (hd + 31) / 32 * 32, 0, stream>>>(
+        part_o, part_ml, (__nv_bfloat16*)out, H, hd, num_splits);
+    return lp_check_launch("attention_merge");
+}

@@ -31,6 +31,7 @@ LIBRARIES: Dict[str, str] = {
     "attention_plain": "attention_plain.cu",
     "sampling": "sampling.cu",
     "gemm_tcgen05": "gemm_tcgen05.cu",
+    "attention_mma": "attention_mma.cu",
 }
 HEADERS = ("common.cuh",)
 

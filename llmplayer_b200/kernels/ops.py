@@ -37,6 +37,10 @@ _SIGNATURES = {
     "gemm_tcgen05": {
         "lp_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     },
+    "attention_mma": {
+        "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+        "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+    },
     "sampling": {
         "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
         "lp_sample_params_size": [],
@@ -333,10 +337,78 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pag
     return out
 
 
+def _check_attention(q, out, pages, page_table, H, G, hd, what):
+    _want(q, f"{what} q", torch.bfloat16, 2)
+    _want(out, f"{what} out", torch.bfloat16, 2)
+    _want(pages, f"{what} pages", torch.bfloat16, 5)
+    _want(page_table, f"{what} page_table", torch.int32, 2)
+    if q.shape[1] != H * hd or out.shape != q.shape:
+        raise KernelError(f"{what}: q {tuple(q.shape)}, out {tuple(out.shape)} for {H} heads of {hd}")
+    if pages.shape[1] != 2 or pages.shape[2] != G or pages.shape[4] != hd:
+        raise KernelError(f"{what}: pages {tuple(pages.shape)} do not fit {G} key heads of {hd}")
+
+
+def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
+                      q_start: torch.Tensor, kv_len: torch.Tensor, max_new: int, *, num_heads: int,
+                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> torch.Tensor:
+    """Tensor-core attention for a step that brings several tokens per sequence.
+    ``q_start`` [B+1]: offsets of each sequence's new tokens; ``kv_len`` [B]: lengths after the step."""
+    _check_attention(q, out, pages, page_table, num_heads, num_kv_heads, head_dim, "attention_prefill")
+    _want(q_start, "attention_prefill q_start", torch.int32, 1)
+    _want(kv_len, "attention_prefill kv_len", torch.int32, 1)
+    B = kv_len.numel()
+    if q_start.numel() != B + 1 or page_table.shape[0] != B:
+        raise KernelError(f"attention_prefill: {B} sequences, {q_start.numel()} offsets, table {tuple(page_table.shape)}")
+    lib = library("attention_mma")
+    _check(lib, lib.lp_attention_prefill(
+        q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+        q_start.data_ptr(), kv_len.data_ptr(), B, int(max_new), num_heads, num_kv_heads, head_dim, pages.shape[3],
+        float(scale), int(window) if window else 0, _stream()))
+    return out
+
+
+def decode_split(batch: int, num_kv_heads: int, num_heads: int, table_width: int):
+    """How a decode step's pages are shared out over CTAs: (pages per share, shares)."""
+    groups = batch * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
+    shares = max(1, min(table_width, -(-4 * NUM_SMS // groups)))
+    per = -(-table_width // shares)
+    return per, -(-table_width // per)
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
+                     kv_len: torch.Tensor, scratch, *, num_heads: int, num_kv_heads: int, head_dim: int,
+                     scale: float, window: Optional[int], pages_per_split: int = 0, num_splits: int = 0) -> torch.Tensor:
+    """Tensor-core attention for a step of one token per sequence. ``scratch(name, shape, dtype)``
+    supplies the float32 buffer for the partial results of the shares."""
+    _check_attention(q, out, pages, page_table, num_heads, num_kv_heads, head_dim, "attention_decode")
+    _want(kv_len, "attention_decode kv_len", torch.int32, 1)
+    B = kv_len.numel()
+    if q.shape[0] != B or page_table.shape[0] != B:
+        raise KernelError(f"attention_decode: {B} sequences, q {tuple(q.shape)}, table {tuple(page_table.shape)}")
+    if not pages_per_split or not num_splits:
+        pages_per_split, num_splits = decode_split(B, num_kv_heads, num_heads, page_table.shape[1])
+    buf = scratch("attention_partials", (B * num_heads * num_splits * (head_dim + 2),), torch.float32)
+    lib = library("attention_mma")
+    _check(lib, lib.lp_attention_decode(
+        q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1], kv_len.data_ptr(),
+        buf.data_ptr(), B, num_heads, num_kv_heads, head_dim, pages.shape[3], float(scale),
+        int(window) if window else 0, pages_per_split, num_splits, _stream()))
+    return out
+
+
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor, *,
               num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
               fast: bool) -> torch.Tensor:
     """Attention of the step's tokens over the cache; picks the kernel for the step's shape."""
+    tensor_cores = (fast and q.dtype == torch.bfloat16 and pages.dtype == torch.bfloat16
+                    and head_dim % 16 == 0 and head_dim <= 256)
+    if tensor_cores and ctx.all_single:
+        return attention_decode(q, out, pages, page_table, ctx.kv_len, ctx.buffer, num_heads=num_heads,
+                                num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window)
+    if tensor_cores:
+        return attention_prefill(q, out, pages, page_table, ctx.q_start, ctx.kv_len, ctx.max_new,
+                                 num_heads=num_heads, num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale,
+                                 window=window)
     return attention_plain(q, out, pages, page_table, ctx.seq_ids, ctx.positions, num_heads=num_heads,
                            num_kv_heads=num_kv_heads, head_dim=head_dim, scale=scale, window=window)
 

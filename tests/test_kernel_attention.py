@@ -1,0 +1,148 @@
+"""The attention kernels alone (plain, tensor-core prefill, tensor-core decode) against a
+float64 softmax attention, on caches whose pages are scattered and partly stale."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+PAGE = 64
+
+
+def build_cache(lengths, G, hd, dtype, seed, extra_pages=5):
+    """Dense K/V per sequence plus their scattered paged form. Unused rows hold large junk."""
+    g = torch.Generator().manual_seed(seed)
+    need = [-(-n // PAGE) for n in lengths]
+    num_pages = sum(need) + extra_pages
+    order = torch.randperm(num_pages, generator=g).tolist()
+    pages = (torch.randn(num_pages, 2, G, PAGE, hd, generator=g) * 30.0).to(dtype)      # junk everywhere
+    width = max(need)
+    table = torch.full((len(lengths), width), -1, dtype=torch.int32)
+    dense = []
+    for b, n in enumerate(lengths):
+        k = torch.randn(n, G, hd, generator=g).to(dtype)
+        v = torch.randn(n, G, hd, generator=g).to(dtype)
+        dense.append((k, v))
+        for blk in range(need[b]):
+            page = order.pop()
+            table[b, blk] = page
+            rows = slice(blk * PAGE, min(n, (blk + 1) * PAGE))
+            cnt = rows.stop - rows.start
+            pages[page, 0, :, :cnt] = k[rows].transpose(0, 1)
+            pages[page, 1, :, :cnt] = v[rows].transpose(0, 1)
+    return dense, pages, table
+
+
+def reference(q, k, v, positions, scale, window):
+    """q [Tq, H, hd]; k, v [Tk, G, hd] (positions 0..Tk-1); float64 softmax attention."""
+    q, k, v = q.double(), k.double(), v.double()
+    H, G = q.shape[1], k.shape[1]
+    out = torch.zeros_like(q)
+    t = torch.arange(k.shape[0])
+    for h in range(H):
+        g = h // (H // G)
+        s = (q[:, h] @ k[:, g].T) * scale
+        ok = t[None, :] <= positions[:, None]
+        if window:
+            ok &= t[None, :] > positions[:, None] - window
+        s = s.masked_fill(~ok, float("-inf"))
+        out[:, h] = torch.softmax(s, dim=-1) @ v[:, g]
+    return out
+
+
+def run_case(kind, lengths, new, H, G, hd, window, dtype, seed=0, crafted=False):
+    """``new[b]`` tokens of sequence b are the step's queries (the last ``new[b]`` positions)."""
+    from llmplayer_b200.kernels import ops
+    dev = "cuda:0"
+    dense, pages, table = build_cache(lengths, G, hd, dtype, seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    T = sum(new)
+    q = torch.randn(T, H, hd, generator=g).to(dtype)
+    positions, seq_ids, q_start = [], [], [0]
+    for b, (n, m) in enumerate(zip(lengths, new)):
+        positions += list(range(n - m, n))
+        seq_ids += [b] * m
+        q_start.append(q_start[-1] + m)
+    positions = torch.tensor(positions)
+    if crafted:
+        # one far key must win: scale a query and a key at the far end of each sequence's context
+        for b, (n, m) in enumerate(zip(lengths, new)):
+            far = 1 if not window else max(0, n - window)      # just inside the window's edge
+            k, v = dense[b]
+            row = q_start[b] + m - 1
+            q[row] = 0
+            q[row, :, 0] = 16.0
+            k[far] = 0
+            k[far, :, 0] = 16.0
+            blk, off = divmod(far, PAGE)
+            pages[table[b, blk], 0, :, off] = k[far]
+    ref = torch.cat([reference(q[q_start[b]:q_start[b + 1]], dense[b][0], dense[b][1],
+                               positions[q_start[b]:q_start[b + 1]], 1.0 / math.sqrt(hd), window)
+                     for b in range(len(lengths))])
+    qd = q.reshape(T, H * hd).to(dev)
+    out = torch.full_like(qd, 7.0)
+    pages_d, table_d = pages.to(dev), table.to(dev)
+    kw = dict(num_heads=H, num_kv_heads=G, head_dim=hd, scale=1.0 / math.sqrt(hd), window=window)
+    kv_len = torch.tensor(lengths, dtype=torch.int32, device=dev)
+    if kind == "plain":
+        ops.attention_plain(qd, out, pages_d, table_d, torch.tensor(seq_ids, dtype=torch.int32, device=dev),
+                            positions.to(torch.int32).to(dev), **kw)
+    elif kind == "prefill":
+        ops.attention_prefill(qd, out, pages_d, table_d, torch.tensor(q_start, dtype=torch.int32, device=dev), kv_len,
+                              max(new), **kw)
+    else:
+        assert all(m == 1 for m in new)
+        scratch = {}
+
+        def buf(name, shape, dt):
+            scratch[name] = torch.full(shape, float("nan"), dtype=dt, device=dev)
+            return scratch[name]
+        ops.attention_decode(qd, out, pages_d, table_d, kv_len, buf, **kw)
+    torch.cuda.synchronize()
+    got = out.reshape(T, H, hd).double().cpu()
+    assert torch.isfinite(got).all()
+    err = float((got - ref).abs().max())
+    if crafted:
+        for b in range(len(lengths)):
+            row = q_start[b + 1] - 1
+            far = 1 if not window else max(0, lengths[b] - window)
+            want = dense[b][1][far].double()            # the far key dominates: output = its value
+            H_G = H // G
+            for h in range(H):
+                assert (got[row, h] - want[h // H_G]).abs().max() < 0.05, (b, h)
+    return err
+
+
+GEOMETRIES = [(4, 2, 16), (3, 1, 32), (6, 3, 48), (32, 8, 64), (8, 2, 128), (2, 2, 256), (20, 1, 64)]
+
+
+@pytest.mark.parametrize("H,G,hd", GEOMETRIES)
+@pytest.mark.parametrize("window", [None, 70])
+def test_plain_attention(H, G, hd, window):
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 2e-2)):
+        err = run_case("plain", [1, 64, 65, 300], [1, 64, 3, 150], H, G, hd, window, dtype)
+        assert err < tol, err
+
+
+@pytest.mark.parametrize("H,G,hd", GEOMETRIES)
+@pytest.mark.parametrize("window", [None, 70])
+def test_tensor_core_prefill(H, G, hd, window):
+    err = run_case("prefill", [1, 64, 65, 300, 129], [1, 64, 3, 150, 129], H, G, hd, window, torch.bfloat16)
+    assert err < 2e-2, err
+
+
+@pytest.mark.parametrize("H,G,hd", GEOMETRIES)
+@pytest.mark.parametrize("window", [None, 70])
+def test_tensor_core_decode(H, G, hd, window):
+    lengths = [1, 64, 65, 700, 129, 17]
+    err = run_case("decode", lengths, [1] * len(lengths), H, G, hd, window, torch.bfloat16)
+    assert err < 2e-2, err
+
+
+@pytest.mark.parametrize("kind", ["plain", "prefill", "decode"])
+@pytest.mark.parametrize("window", [None, 200])
+def test_a_far_key_among_hundreds_is_found(kind, window):
+    lengths = [900, 333]
+    new = [1, 1] if kind == "decode" else [5, 1]
+    run_case(kind, lengths, new, 8, 2, 64, window, torch.bfloat16, seed=3, crafted=True)
