@@ -35,29 +35,69 @@ extern "C" int lp_embed(const void* table, int table_dtype, const int* tokens, f
 // ---------------------------------------------------------------- RMS norm
 // out[r, i] = x[row(r), i] * (1 / sqrt(sum_i x^2 / d + eps)) * w[i]; one block per row.
 // When `add` is given, x[row] += add[row] first (in float32) and the sum is stored back:
-// the residual sum and the norm that follows it in one pass.
+// the residual sum and the norm that follows it in one pass. The row is read once and kept
+// in registers (up to PER * 256 values; wider rows take the two-pass kernel below).
+// `zero` (optional): a float32 buffer that the blocks clear on the side, for the product that
+// follows the norm and sums its partial results with atomics.
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_PER = 16;
+
+__device__ __forceinline__ void clear_on_the_side(float* zero, long long zero_count) {
+    if (zero) {
+        const long long stride = (long long)gridDim.x * blockDim.x;
+        for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < zero_count; i += stride) zero[i] = 0.f;
+    }
+}
+
 template <typename TOut, typename TAdd>
-__global__ void rmsnorm_kernel(float* __restrict__ x, const TAdd* __restrict__ add,
-                               const int* __restrict__ rows, const float* __restrict__ w,
-                               TOut* __restrict__ out, int d, float eps) {
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_kernel(float* __restrict__ x, const TAdd* __restrict__ add, const int* __restrict__ rows,
+               const float* __restrict__ w, TOut* __restrict__ out, int d, float eps, float* __restrict__ zero,
+               long long zero_count) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long long src = rows ? rows[r] : r;
+    float* xr = x + src * d;
+    float v[NORM_PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_PER; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        v[k] = 0.f;
+        if (i < d) {
+            float t = xr[i];
+            if (add) { t += lp_to_float(add[src * d + i]); xr[i] = t; }
+            v[k] = t;
+            ss += t * t;
+        }
+    }
+    clear_on_the_side(zero, zero_count);
+    ss = lp_block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    TOut* o = out + (long long)r * d;
+#pragma unroll
+    for (int k = 0; k < NORM_PER; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < d) o[i] = lp_from_float<TOut>(v[k] * scale * w[i]);
+    }
+}
+
+template <typename TOut, typename TAdd>
+__global__ void rmsnorm_wide_kernel(float* __restrict__ x, const TAdd* __restrict__ add,
+                                    const int* __restrict__ rows, const float* __restrict__ w,
+                                    TOut* __restrict__ out, int d, float eps, float* __restrict__ zero,
+                                    long long zero_count) {
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const long long src = rows ? rows[r] : r;
     float* xr = x + src * d;
     float ss = 0.f;
-    if (add) {
-        const TAdd* ar = add + src * d;
-        for (int i = threadIdx.x; i < d; i += blockDim.x) {
-            const float v = xr[i] + lp_to_float(ar[i]);
-            xr[i] = v;
-            ss += v * v;
-        }
-    } else {
-        for (int i = threadIdx.x; i < d; i += blockDim.x) {
-            const float v = xr[i];
-            ss += v * v;
-        }
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float t = xr[i];
+        if (add) { t += lp_to_float(add[src * d + i]); xr[i] = t; }
+        ss += t * t;
     }
+    clear_on_the_side(zero, zero_count);
     ss = lp_block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)d + eps);
     TOut* o = out + (long long)r * d;
@@ -65,13 +105,21 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const TAdd* __restrict__ a
 }
 
 extern "C" int lp_rmsnorm(float* x, const void* add, int add_dtype, const int* rows, const float* w, void* out,
-                          int out_dtype, int R, int d, float eps, cudaStream_t stream) {
+                          int out_dtype, int R, int d, float eps, float* zero, long long zero_count,
+                          cudaStream_t stream) {
     if (R <= 0) return 0;
     if (d <= 0) LP_REFUSE("rmsnorm: width %d", d);
     if (add && rows) LP_REFUSE("rmsnorm: a fused residual add cannot be combined with a row selection");
-    const int threads = d >= 2048 ? 512 : (d >= 512 ? 256 : 128);
-#define LP_LAUNCH_NORM(TOUT, TADD) \
-    rmsnorm_kernel<TOUT, TADD><<<R, threads, 0, stream>>>(x, (const TADD*)add, rows, w, (TOUT*)out, d, eps)
+    const bool wide = d > NORM_THREADS * NORM_PER;
+#define LP_LAUNCH_NORM(TOUT, TADD)                                                                              \
+    do {                                                                                                        \
+        if (wide)                                                                                               \
+            rmsnorm_wide_kernel<TOUT, TADD><<<R, 512, 0, stream>>>(x, (const TADD*)add, rows, w, (TOUT*)out, d, \
+                                                                   eps, zero, zero_count);                      \
+        else                                                                                                    \
+            rmsnorm_kernel<TOUT, TADD><<<R, NORM_THREADS, 0, stream>>>(x, (const TADD*)add, rows, w, (TOUT*)out, \
+                                                                       d, eps, zero, zero_count);               \
+    } while (0)
     if (out_dtype == LP_F32 && add_dtype == LP_F32) LP_LAUNCH_NORM(float, float);
     else if (out_dtype == LP_F32 && add_dtype == LP_BF16) LP_LAUNCH_NORM(float, __nv_bfloat16);
     else if (out_dtype == LP_BF16 && add_dtype == LP_F32) LP_LAUNCH_NORM(__nv_bfloat16, float);
@@ -82,46 +130,54 @@ extern "C" int lp_rmsnorm(float* x, const void* add, int add_dtype, const int* r
 }
 
 // ---------------------------------------------------------------- rotation + cache write
-// One block per (token, head) of the fused projection output
+// One block per token of the fused projection output
 //   qkv[t] = [ H query heads | G key heads | G value heads ] x head_dim   (float32).
 // Queries and keys: the first `rd` features of a head are rotated by
-// angle = float(position) * inv_freq[pair]; the rest pass through. Queries go to
-// q_out[t, h, :]; keys and values go to the page of the token's sequence that holds
-// its position:  pages[page][0|1][g][position % page_size][:].
+// angle = float(position) * inv_freq[pair] (cosine and sine are formed once per token and
+// shared by all its heads); the rest pass through. Queries go to q_out[t, h, :]; keys and
+// values go to the page of the token's sequence that holds its position:
+//   pages[page][0|1][g][position % page_size][:].
 template <typename TQ, typename TKV>
-__global__ void rope_cache_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ inv_freq,
-                                  const int* __restrict__ positions, const int* __restrict__ seq_ids,
-                                  const int* __restrict__ page_table, int pt_stride, TQ* __restrict__ q_out,
-                                  TKV* __restrict__ pages, int H, int G, int hd, int rd, int interleaved,
-                                  int page_size) {
+__global__ void __launch_bounds__(256)
+rope_cache_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ inv_freq,
+                  const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                  const int* __restrict__ page_table, int pt_stride, TQ* __restrict__ q_out,
+                  TKV* __restrict__ pages, int H, int G, int hd, int rd, int interleaved, int page_size) {
+    __shared__ float cs[128], sn[128];          // rd / 2 <= 128
     const int t = blockIdx.x;
-    const int head = blockIdx.y;             // 0..H-1 queries, then G keys, then G values
     const int pos = positions[t];
-    const float* src = qkv + (long long)t * ld + (long long)head * hd;
-    const bool is_q = head < H;
-    const bool is_v = head >= H + G;
-    long long dst_off = 0;
-    if (!is_q) {
-        const int g = is_v ? head - H - G : head - H;
-        const int page = page_table[(long long)seq_ids[t] * pt_stride + pos / page_size];
-        dst_off = ((((long long)page * 2 + (is_v ? 1 : 0)) * G + g) * page_size + (pos % page_size)) * hd;
-    }
     const int half = rd >> 1;
-    for (int e = threadIdx.x; e < hd; e += blockDim.x) {
-        float val = src[e];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float angle = (float)pos * inv_freq[i];
+        sincosf(angle, &sn[i], &cs[i]);
+    }
+    __syncthreads();
+    const float* src = qkv + (long long)t * ld;
+    const int heads = pages ? H + 2 * G : H;
+    long long page_base = 0;
+    if (pages) {
+        const int page = page_table[(long long)seq_ids[t] * pt_stride + pos / page_size];
+        page_base = (long long)page * 2 * G * page_size * hd + (long long)(pos % page_size) * hd;
+    }
+    const int total = heads * hd;
+    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+        const int head = idx / hd, e = idx - head * hd;
+        const bool is_q = head < H, is_v = head >= H + G;
+        float val = src[idx];
         if (!is_v && e < rd) {
             int pair, partner;
             bool first;
             if (interleaved) { pair = e >> 1; first = (e & 1) == 0; partner = e ^ 1; }
             else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
-            const float angle = (float)pos * inv_freq[pair];
-            float sn, cs;
-            sincosf(angle, &sn, &cs);
-            const float other = src[partner];
-            val = first ? val * cs - other * sn : other * sn + val * cs;
+            const float other = src[head * hd + partner];
+            val = first ? val * cs[pair] - other * sn[pair] : other * sn[pair] + val * cs[pair];
         }
-        if (is_q) q_out[((long long)t * H + head) * hd + e] = lp_from_float<TQ>(val);
-        else pages[dst_off + e] = lp_from_float<TKV>(val);
+        if (is_q) {
+            q_out[((long long)t * H + head) * hd + e] = lp_from_float<TQ>(val);
+        } else {
+            const int g = is_v ? head - H - G : head - H;
+            pages[page_base + ((long long)(is_v ? G : 0) + g) * page_size * hd + e] = lp_from_float<TKV>(val);
+        }
     }
 }
 
@@ -132,18 +188,17 @@ extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_fr
     if (T <= 0) return 0;
     if (hd <= 0 || H <= 0 || G < 0) LP_REFUSE("rope_cache_write: heads %d/%d of %d", H, G, hd);
     if (rd < 0 || rd > hd || (rd & 1)) LP_REFUSE("rope_cache_write: rotary width %d of a head of %d", rd, hd);
+    if (rd > 256) LP_REFUSE("rope_cache_write: rotary width %d (supported: up to 256)", rd);
     if (rd > 0 && !inv_freq) LP_REFUSE("rope_cache_write: rotation without frequencies");
     const int heads = pages ? H + 2 * G : H;
     if (ld < heads * hd) LP_REFUSE("rope_cache_write: row of %d values for %d heads of %d", ld, heads, hd);
     if (pages && page_size <= 0) LP_REFUSE("rope_cache_write: page size %d", page_size);
-    if (heads > 65535) LP_REFUSE("rope_cache_write: %d heads exceed the grid", heads);
-    dim3 grid(T, heads);
-    const int threads = hd <= 64 ? 64 : (hd <= 128 ? 128 : 256);
+    const int threads = heads * hd >= 1024 ? 256 : 128;
 #define LP_LAUNCH_ROPE(TQ, TKV)                                                                          \
-    rope_cache_kernel<TQ, TKV><<<grid, threads, 0, stream>>>(qkv, ld, inv_freq, positions, seq_ids,       \
-                                                             page_table, pt_stride, (TQ*)q_out,           \
-                                                             (TKV*)pages, H, G, hd, rd, interleaved,     \
-                                                             page_size)
+    rope_cache_kernel<TQ, TKV><<<T, threads, 0, stream>>>(qkv, ld, inv_freq, positions, seq_ids,           \
+                                                         page_table, pt_stride, (TQ*)q_out,               \
+                                                         (TKV*)pages, H, G, hd, rd, interleaved,         \
+                                                         page_size)
     if (q_dtype == LP_F32 && kv_dtype == LP_F32) LP_LAUNCH_ROPE(float, float);
     else if (q_dtype == LP_BF16 && kv_dtype == LP_BF16) LP_LAUNCH_ROPE(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == LP_F32 && kv_dtype == LP_BF16) LP_LAUNCH_ROPE(float, __nv_bfloat16);

@@ -109,3 +109,14 @@ class StepContext:
 
     def buffer(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)
+
+    # A norm can zero, on the side, the buffer that the product after it sums into. The
+    # block says so here, and the product picks the note up (once).
+    _cleared = False
+
+    def note_cleared(self) -> None:
+        self._cleared = True
+
+    def take_cleared(self) -> bool:
+        was, self._cleared = self._cleared, False
+        return was

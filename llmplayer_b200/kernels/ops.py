@@ -23,7 +23,7 @@ _P, _I, _F = c_void_p, c_int, c_float
 _SIGNATURES = {
     "elementwise": {
         "lp_embed": [_P, _I, _P, _P, _I, _I, _P],
-        "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P],
+        "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P, ctypes.c_longlong, _P],
         "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "lp_advance": [_P, _P, _P, _P, _I, _P],
         "lp_swiglu_combine": [_P, _P, _I, _I, _I, _P],
@@ -133,11 +133,13 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch
 
 # --------------------------------------------------------------------------- norm
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+            rows: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None,
+            clear: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[r] = x[rows[r]] / sqrt(mean(x^2) + eps) * weight, float32 inside.
 
     ``add`` (same shape as x) is first added into x in place: the residual sum
-    fused with the norm that follows it.
+    fused with the norm that follows it. ``clear``: a float32 buffer that is set to
+    zero on the side (for a product after the norm that sums partial results into it).
     """
     _want(x, "rmsnorm x", torch.float32, 2)
     _want(weight, "rmsnorm weight", torch.float32, 1)
@@ -158,9 +160,12 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         if add.shape != x.shape:
             raise KernelError(f"rmsnorm: add {tuple(add.shape)} does not match x {tuple(x.shape)}")
         add_code = _code(add, "rmsnorm add")
+    if clear is not None:
+        _want(clear, "rmsnorm clear", torch.float32)
     lib = library("elementwise")
     _check(lib, lib.lp_rmsnorm(x.data_ptr(), _ptr(add), add_code, _ptr(rows), weight.data_ptr(), out.data_ptr(),
-                               _code(out, "rmsnorm out"), R, d, float(eps), _stream()))
+                               _code(out, "rmsnorm out"), R, d, float(eps), _ptr(clear),
+                               clear.numel() if clear is not None else 0, _stream()))
     return out
 
 
@@ -249,14 +254,38 @@ def _token_tile(tokens: int, gated: bool) -> int:
     return 128 if gated else 256
 
 
+def gemm_plan(tokens: int, features: int, k: int, mode: int):
+    """(token tile, splits, scratch) that :func:`gemm` uses for these sizes. ``scratch`` names
+    the float32 buffer a gated product is summed into un-activated when too few CTAs would
+    cover it fused (None: the activation is applied in the product's own epilogue)."""
+    k_blocks = -(-k // 64)
+
+    def pick(feats: int, tile: int) -> int:
+        ctas = -(-feats // 128) * -(-tokens // tile)
+        if ctas >= NUM_SMS // 2 or k_blocks < 8:
+            return 1
+        return max(1, min(NUM_SMS // ctas, k_blocks // 4))
+
+    if mode == SWIGLU:
+        tile = _token_tile(tokens, True)
+        fused_ctas = -(-features // 128) * -(-tokens // tile)
+        if fused_ctas >= (NUM_SMS * 3) // 4:
+            return tile, 1, None
+        return tile, pick(2 * features, tile), "gate_up_sums"
+    tile = _token_tile(tokens, False)
+    return tile, pick(features, tile), None
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, block_tok: int = 0,
-         splits: int = 0, scratch=None) -> torch.Tensor:
+         splits: int = 0, scratch=None, cleared: bool = False) -> torch.Tensor:
     """out (=|+=) a @ w.T on the tensor cores (bfloat16 in, float32 accumulation).
 
     ``a`` [tokens, K] and ``w`` [features, K] (``[2*features, K]`` for ``SWIGLU``) are bfloat16.
     When few CTAs would cover the output, the K range is split over more of them and the
     partial sums meet in float32 atomics; a gated product is then summed un-activated into
-    ``scratch(name, shape, dtype)`` and activated by a second small kernel.
+    ``scratch(name, shape, dtype)`` and activated by a second small kernel. ``cleared``:
+    the buffer that partial sums go to (``out``, or the scratch of a gated product) is
+    already zero. ``block_tok`` / ``splits`` override the plan (tests).
     """
     _want(a, "gemm a", torch.bfloat16, 2)
     _want(w, "gemm w", torch.bfloat16, 2)
@@ -270,45 +299,34 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
         return out
     lib = library("gemm_tcgen05")
     status = kernel_status()
-    k_blocks = -(-K // 64)
-
-    def pick_splits(features: int, tile: int) -> int:
-        ctas = -(-features // 128) * -(-M // tile)
-        if ctas >= NUM_SMS // 2 or k_blocks < 8:
-            return 1
-        return max(1, min(NUM_SMS // ctas, k_blocks // 4))
-
+    tile, n_splits, via = gemm_plan(M, N, K, mode)
+    tile = block_tok or tile
+    n_splits = splits or n_splits
     if mode == SWIGLU:
-        tile = block_tok or _token_tile(M, True)
-        want_splits = splits or pick_splits(2 * N, tile)
-        if want_splits > 1 or tile > 128:
-            # summed across CTAs: plain product into float32 scratch, then the activation
+        if via is not None or n_splits > 1 or tile > 128:
+            # too few CTAs fused: plain product into float32 scratch (summed across CTAs), then the activation
             gu = scratch("gate_up_sums", (M, 2 * N), torch.float32) if scratch else \
                 torch.empty((M, 2 * N), dtype=torch.float32, device=a.device)
-            gemm(a, w, gu, STORE, block_tok=block_tok, splits=want_splits)
-            _check(lib_elementwise(), lib_elementwise().lp_swiglu_combine(
-                gu.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, _stream()))
+            gemm(a, w, gu, STORE, block_tok=tile, splits=n_splits, cleared=cleared)
+            ew = library("elementwise")
+            _check(ew, ew.lp_swiglu_combine(gu.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, _stream()))
             return out
         _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
                                         K, K, N, SWIGLU, tile, 1, status.data_ptr(), _stream()))
         return out
-    tile = block_tok or _token_tile(M, False)
-    n_splits = splits or pick_splits(N, tile)
     if mode == ACCUMULATE:
         if out.dtype != torch.float32:
             raise KernelError("gemm: accumulation needs a float32 output")
     elif n_splits > 1:
         if out.dtype != torch.float32:
             n_splits = 1
-        else:
+        elif not cleared:
             out.zero_()
     _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
                                     K, K, N, mode, tile, n_splits, status.data_ptr(), _stream()))
     return out
 
 
-def lib_elementwise():
-    return library("elementwise")
 
 
 # --------------------------------------------------------------------------- attention

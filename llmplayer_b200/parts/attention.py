@@ -65,6 +65,9 @@ class Attention(Part):
         return KVRequest(s.num_kv_heads, s.head_dim, s.window)
 
     # ------------------------------------------------------------------ step
+    def buffer_to_clear(self, ctx, tokens: int):
+        return self.qkv.sums_into(ctx, tokens, "qkv", ops.STORE)
+
     def forward(self, ctx, cache, x: torch.Tensor, residual: torch.Tensor) -> None:
         s, rt = self.spec, self.runtime
         if cache is None:
@@ -73,7 +76,7 @@ class Attention(Part):
         H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim
         table = ctx.page_tables[cache.group_index]
         qkv = ctx.buffer("qkv", (T, self.qkv.out_features), torch.float32)
-        self.qkv.store(x, qkv)
+        self.qkv.store(x, qkv, ctx)
         q = ctx.buffer("q", (T, H * hd), rt.act_dtype)
         ops.rope_cache_write(
             qkv, self.position.inv_freq, ctx.positions, ctx.seq_ids, table, q,
@@ -83,7 +86,7 @@ class Attention(Part):
         o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
         ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd,
                       scale=s.scale, window=s.window, fast=rt.fast)
-        self.out.accumulate(o, residual)
+        self.out.accumulate(o, residual, ctx)
 
 
 MIXERS.register("attention", Attention)

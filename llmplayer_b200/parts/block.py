@@ -41,10 +41,22 @@ class PreNormBlock(Part):
     def forward(self, ctx, cache, residual: torch.Tensor) -> None:
         act = self.runtime.act_dtype
         h = ctx.buffer("normed", tuple(residual.shape), act)
-        self.mixer_norm.apply(residual, h)
+        self._norm(ctx, self.mixer_norm, self.mixer, residual, h)
         self.mixer.forward(ctx, cache, h, residual)
-        self.ffn_norm.apply(residual, h)
+        self._norm(ctx, self.ffn_norm, self.ffn, residual, h)
         self.ffn.forward(ctx, h, residual)
+
+    @staticmethod
+    def _norm(ctx, norm, consumer, residual, h) -> None:
+        """Norm the residual stream for ``consumer``; if the consumer's first product wants a
+        zeroed buffer (``buffer_to_clear(ctx, tokens)``), the norm clears it on the side."""
+        ask = getattr(consumer, "buffer_to_clear", None)
+        clear = ask(ctx, residual.shape[0]) if ask is not None else None
+        if clear is not None:
+            norm.apply(residual, h, clear=clear)
+            ctx.note_cleared()
+        else:
+            norm.apply(residual, h)
 
 
 BLOCKS.register("prenorm", PreNormBlock)

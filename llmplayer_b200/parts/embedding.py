@@ -54,4 +54,4 @@ class LinearHead(Part):
         """logits[i] = head(norm(residual[rows[i]])), float32."""
         h = ctx.buffer("head_in", (rows.numel(), self.spec.hidden_size), self.runtime.act_dtype)
         self.norm.apply(residual, h, rows=rows)
-        return self.proj.store(h, logits)
+        return self.proj.store(h, logits, ctx)

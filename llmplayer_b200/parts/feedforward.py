@@ -12,6 +12,7 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
+from ..kernels import ops
 from .base import FEED_FORWARDS, Part, Runtime
 from .linear import Linear
 from .specs import MATRIX, SwiGLUSpec, TensorSpec
@@ -37,10 +38,13 @@ class SwiGLU(Part):
         self.gate_up = Linear([tensors[s.gate], tensors[s.up]], runtime)
         self.down = Linear([tensors[s.down]], runtime)
 
+    def buffer_to_clear(self, ctx, tokens: int):
+        return self.gate_up.sums_into(ctx, tokens, "ffn_hidden", ops.SWIGLU)
+
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor) -> None:
         h = ctx.buffer("ffn_hidden", (x.shape[0], self.spec.intermediate_size), self.runtime.act_dtype)
-        self.gate_up.swiglu(x, h)
-        self.down.accumulate(h, residual)
+        self.gate_up.swiglu(x, h, ctx)
+        self.down.accumulate(h, residual, ctx)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

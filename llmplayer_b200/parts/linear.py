@@ -30,16 +30,32 @@ class Linear:
         return (self.runtime.fast and self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
                 and ops.fast_gemm_available())
 
-    def store(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        return self._run(x, out, ops.STORE)
+    def store(self, x: torch.Tensor, out: torch.Tensor, ctx=None) -> torch.Tensor:
+        return self._run(x, out, ops.STORE, ctx)
 
-    def accumulate(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        return self._run(x, out, ops.ACCUMULATE)
+    def accumulate(self, x: torch.Tensor, out: torch.Tensor, ctx=None) -> torch.Tensor:
+        return self._run(x, out, ops.ACCUMULATE, ctx)
 
-    def swiglu(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        return self._run(x, out, ops.SWIGLU)
+    def swiglu(self, x: torch.Tensor, out: torch.Tensor, ctx=None) -> torch.Tensor:
+        return self._run(x, out, ops.SWIGLU, ctx)
 
-    def _run(self, x, out, mode):
+    def sums_into(self, ctx, tokens: int, out_name: str, mode: int):
+        """The float32 buffer that this product, run for ``tokens`` rows, will add partial
+        sums into and that must therefore be zero beforehand; None if it stores its result.
+        ``out_name``: the workspace name of its output."""
+        if not self._fast() or mode == ops.ACCUMULATE:
+            return None
+        features = self.out_features // 2 if mode == ops.SWIGLU else self.out_features
+        _, splits, scratch = ops.gemm_plan(tokens, features, self.in_features, mode)
+        if splits <= 1:
+            return None
+        if scratch is not None:
+            return ctx.buffer(scratch, (tokens, self.out_features), torch.float32)
+        return ctx.buffer(out_name, (tokens, self.out_features), torch.float32)
+
+    def _run(self, x, out, mode, ctx):
         if self._fast() and x.dtype == torch.bfloat16:
-            return ops.gemm(x, self.weight, out, mode)
+            scratch = ctx.buffer if ctx is not None else None
+            cleared = ctx.take_cleared() if ctx is not None else False
+            return ops.gemm(x, self.weight, out, mode, scratch=scratch, cleared=cleared)
         return ops.gemm_plain(x, self.weight, out, mode)

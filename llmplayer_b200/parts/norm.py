@@ -27,9 +27,10 @@ class RMSNorm(Part):
         self.weight = runtime.gain(tensors[self.spec.weight])
 
     def apply(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
-              add: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``out[r] = norm(x[rows[r]])``; ``add`` is summed into ``x`` first (in place)."""
-        return ops.rmsnorm(x, self.weight, self.spec.eps, out, rows=rows, add=add)
+              add: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``out[r] = norm(x[rows[r]])``; ``add`` is summed into ``x`` first (in place);
+        ``clear`` is a float32 buffer zeroed on the side."""
+        return ops.rmsnorm(x, self.weight, self.spec.eps, out, rows=rows, add=add, clear=clear)
 
 
 NORMS.register("rmsnorm", RMSNorm)
