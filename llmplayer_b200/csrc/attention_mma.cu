@@ -497,3 +497,44 @@ extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, 
         part_o, part_ml, (__nv_bfloat16*)out, H, hd, num_splits);
     return lp_check_launch("attention_merge");
 }
+
+// ---------------------------------------------------------------- decode without allocation
+// See attention_noalloc.h. The scratch of lp_attention_decode lives in this file-scope device
+// array; host code must not pass the array's name to a kernel (in host code it is only a
+// stand-in), so its device address is looked up once per device and kept.
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float lp_decode_static_scratch[LP_NOALLOC_SCRATCH_FLOATS];
+static float* lp_decode_static_address[64] = {};
+
+extern "C" int lp_attention_decode_noalloc(const void* q, void* out, const void* pages, const int* page_table,
+                                           int pt_stride, const int* kv_len, int B, int H, int G, int hd,
+                                           int page_size, float scale, int window, int pages_per_split,
+                                           int num_splits, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (H <= 0 || hd <= 0 || num_splits <= 0) LP_REFUSE("attention_decode_noalloc: %d heads of %d in %d shares", H, hd, num_splits);
+    const long long need = lp_attention_decode_scratch(B, H, hd, num_splits);
+    if (need > LP_NOALLOC_SCRATCH_FLOATS)
+        LP_REFUSE("attention_decode_noalloc: %d sequences x %d heads x %d shares need %lld floats of scratch, "
+                  "the built-in array holds %lld; use fewer shares or lp_attention_decode with your own scratch",
+                  B, H, num_splits, need, (long long)LP_NOALLOC_SCRATCH_FLOATS);
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) {
+        snprintf(lp_error_text, sizeof(lp_error_text), "attention_decode_noalloc: %s", cudaGetErrorString(err));
+        return (int)err;
+    }
+    if (device < 0 || device >= 64) LP_REFUSE("attention_decode_noalloc: device index %d", device);
+    if (!lp_decode_static_address[device]) {
+        float* address = nullptr;
+        err = cudaGetSymbolAddress((void**)&address, lp_decode_static_scratch);
+        if (err != cudaSuccess || !address) {
+            snprintf(lp_error_text, sizeof(lp_error_text), "attention_decode_noalloc: cannot find the scratch array: %s",
+                     cudaGetErrorString(err));
+            return err != cudaSuccess ? (int)err : -1;
+        }
+        lp_decode_static_address[device] = address;
+    }
+    return lp_attention_decode(q, out, pages, page_table, pt_stride, kv_len, lp_decode_static_address[device], B, H, G,
+                               hd, page_size, scale, window, pages_per_split, num_splits, stream);
+}

@@ -33,7 +33,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_mma": "attention_mma.cu",
 }
-HEADERS = ("common.cuh",)
+HEADERS = ("common.cuh", "attention_noalloc.h")
 
 NVCC_FLAGS: List[str] = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
