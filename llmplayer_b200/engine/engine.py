@@ -42,6 +42,8 @@ class Engine:
         self._sampler = None
         self.last_generation_stats = None
         self.last_step_h2d_bytes = 0
+        self.use_graphs = True
+        self._graphs = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -117,15 +119,53 @@ class Engine:
         slots = [s.slot for s in sequences]
         counts = [s.num_new for s in sequences]
         self.cache.reserve(slots, counts)
-        return StepContext(self.workspace, sequences, tokens, self.cache.page_tables(slots), rows)
+        tables = self.cache.page_tables(slots)
+        width = 1
+        if all(n == 1 for n in counts):
+            # steps of one token each are replayed from captured graphs: keep the shape of the
+            # page tables stable while sequences grow (padding entries are never read)
+            longest = max((len(t) for group in tables for t in group), default=1)
+            width = -(-longest // 8) * 8
+        return StepContext(self.workspace, sequences, tokens, tables, rows, min_table_width=width)
 
     def run(self, ctx: StepContext) -> torch.Tensor:
         """Run a planned step; returns float32 logits [wanted, vocab] (valid until the next step)."""
         logits = self.workspace.get("logits", (ctx.num_wanted, self.vocab_size), torch.float32)
         self.last_step_h2d_bytes = ctx.h2d_bytes
-        self.model.forward(ctx, self.cache, ctx.rows, logits)
+        if self.use_graphs and self.runtime.fast and ctx.all_single:
+            self._run_captured(ctx, logits)
+        else:
+            self.model.forward(ctx, self.cache, ctx.rows, logits)
         self.cache.commit([s.slot for s in ctx.sequences], [s.num_new for s in ctx.sequences])
         return logits
+
+    def _run_captured(self, ctx: StepContext, logits: torch.Tensor) -> None:
+        """A step of one token per sequence, through a CUDA graph of the model walk for its shape
+        (batch, page-table widths, wanted rows). The first step of a shape runs directly, the
+        second is captured, later ones are replayed; the step's integers were copied to the
+        device beforehand, and the graph reads them there (the reference replays its captured
+        forward pass the same way: java21 inference/CudaForwardPass.java:1760-1812)."""
+        key = (ctx.num_sequences, tuple(t.shape[1] for t in ctx.page_tables), ctx.num_wanted, ctx.meta.data_ptr())
+        entry = self._graphs.get(key)
+        if entry is not None and entry[1] != self.workspace.version:
+            entry = None                                  # a buffer moved since the capture
+        if entry is None:
+            self.model.forward(ctx, self.cache, ctx.rows, logits)
+            self._graphs[key] = (None, self.workspace.version)
+            return
+        graph = entry[0]
+        if graph is None:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, self.cache, ctx.rows, logits)
+            if entry[1] != self.workspace.version:        # should not happen: the first run sized everything
+                self._graphs.pop(key, None)
+                self.model.forward(ctx, self.cache, ctx.rows, logits)
+                return
+            if len(self._graphs) > 64:
+                self._graphs.clear()
+            self._graphs[key] = (graph, entry[1])
+        graph.replay()
 
     def step(self, entries: Sequence[Tuple[int, Sequence[int]]], want: Sequence[Sequence[int]]) -> torch.Tensor:
         """Run the given new tokens of each slot, as one batch, from the cache.
