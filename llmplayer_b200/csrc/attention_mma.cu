@@ -121,6 +121,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
                          float scale_log2, int window) {
     constexpr int KSTEPS = HD_MAX / 16;
     extern __shared__ __align__(128) uint8_t smem[];
+    lp_grid_release();
+    lp_grid_wait();
     const int b = blockIdx.z, h = blockIdx.y, tile = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int t_begin = q_start[b], n_new = q_start[b + 1] - t_begin;
@@ -250,10 +252,13 @@ template <int HD_MAX>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
                         const int* __restrict__ page_table, int pt_stride, const int* __restrict__ kv_len,
-                        float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G, int hd,
-                        float scale_log2, int window, int pages_per_split, int num_splits, int head_groups) {
+                        float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
+                        int H, int G, int hd, float scale_log2, int window, int pages_per_split, int num_splits,
+                        int head_groups) {
     constexpr int KSTEPS = HD_MAX / 16;
     extern __shared__ __align__(128) uint8_t smem[];
+    lp_grid_release();
+    lp_grid_wait();
     const int split = blockIdx.x, b = blockIdx.z;
     const int g = blockIdx.y / head_groups, hg = blockIdx.y - g * head_groups;
     const int R = H / G;
@@ -382,15 +387,21 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             acc += sm_o[((size_t)w * 16 + r) * hd + d] * f;
             l += sm_l[w * 16 + r] * f;
         }
-        const size_t slot = ((size_t)b * H + head0 + r) * num_splits + split;
-        part_o[slot * hd + d] = acc;
-        if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+        if (num_splits == 1) {                      // the only share: this is the result
+            out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(acc / l);
+        } else {
+            const size_t slot = ((size_t)b * H + head0 + r) * num_splits + split;
+            part_o[slot * hd + d] = acc;
+            if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+        }
     }
 }
 
 // out[b][head][:] = sum_s part_o * 2^(m_s - m*) / sum_s l_s * 2^(m_s - m*); grid: (H, B), hd threads (<= 256).
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int H, int hd, int num_splits) {
+    lp_grid_release();
+    lp_grid_wait();
     const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const size_t base = ((size_t)b * H + h) * num_splits;
     float m = NEG_BIG;
@@ -447,7 +458,7 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
     do {                                                                                                         \
         rc = set_smem<HDM>(attention_prefill_kernel<HDM>, smem, "attention_prefill");                                 \
         if (rc) return rc;                                                                                       \
-        attention_prefill_kernel<HDM><<<grid, 128, smem, stream>>>(                                              \
+        lp_launch(attention_prefill_kernel<HDM>, grid, 128, smem, stream,                                        \
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_table, pt_stride,     \
             q_start, kv_len, H, G, hd, scale_log2, window);                                                      \
     } while (0)
@@ -485,16 +496,16 @@ extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, 
     do {                                                                                                         \
         rc = set_smem<1000 + HDM>(attention_decode_kernel<HDM>, smem, "attention_decode");                                   \
         if (rc) return rc;                                                                                       \
-        attention_decode_kernel<HDM><<<grid, 128, smem, stream>>>(                                               \
+        lp_launch(attention_decode_kernel<HDM>, grid, 128, smem, stream,                                         \
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml, \
-            H, G, hd, scale_log2, window, pages_per_split, num_splits, head_groups);                             \
+            (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, head_groups);        \
     } while (0)
     if (hd <= 64) LP_DECODE(64); else if (hd <= 128) LP_DECODE(128); else LP_DECODE(256);
 #undef LP_DECODE
     rc = lp_check_launch("attention_decode");
-    if (rc) return rc;
-    attention_merge_kernel<<<dim3(H, B), hd <= 32 ? 32 : (hd + 31) / 32 * 32, 0, stream>>>(
-        part_o, part_ml, (__nv_bfloat16*)out, H, hd, num_splits);
+    if (rc || num_splits == 1) return rc;
+    lp_launch(attention_merge_kernel, dim3(H, B), hd <= 32 ? 32 : (hd + 31) / 32 * 32, 0, stream,
+              (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, H, hd, num_splits);
     return lp_check_launch("attention_merge");
 }
 

@@ -35,6 +35,43 @@ static inline int lp_check_launch(const char* what) {
     return 0;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// Kernels of a step follow one another on one stream. Launched with lp_launch, a kernel may
+// begin (be scheduled, set up, even prefetch what no earlier kernel writes) while its
+// predecessor still runs; it must call lp_grid_wait() before it touches anything an earlier
+// kernel wrote or read-modifies, and calls lp_grid_release() so that its own successor may
+// start early. Every kernel waits, so completion stays transitive along the stream.
+// LLMPLAYER_B200_PDL=0 in the environment turns the early start off.
+__device__ __forceinline__ void lp_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void lp_grid_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+#include <utility>
+static inline bool lp_pdl_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char* v = getenv("LLMPLAYER_B200_PDL");
+        state = (v && v[0] == '0') ? 0 : 1;
+    }
+    return state == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t lp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = lp_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+
 __device__ __forceinline__ float lp_to_float(float v) { return v; }
 __device__ __forceinline__ float lp_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -11,6 +11,8 @@
 template <typename TW>
 __global__ void embed_kernel(const TW* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int d) {
+    lp_grid_release();
+    lp_grid_wait();
     const int t = blockIdx.x;
     const long long row = tokens[t];
     const TW* src = table + row * d;
@@ -24,9 +26,9 @@ extern "C" int lp_embed(const void* table, int table_dtype, const int* tokens, f
     if (d <= 0) LP_REFUSE("embed: width %d", d);
     const int threads = d >= 1024 ? 256 : 128;
     if (table_dtype == LP_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>((const float*)table, tokens, out, d);
+        lp_launch(embed_kernel<float>, T, threads, 0, stream, (const float*)table, tokens, out, d);
     else if (table_dtype == LP_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, tokens, out, d);
+        lp_launch(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, d);
     else
         LP_REFUSE("embed: table dtype code %d", table_dtype);
     return lp_check_launch("embed");
@@ -55,6 +57,8 @@ rmsnorm_kernel(float* __restrict__ x, const TAdd* __restrict__ add, const int* _
                const float* __restrict__ w, TOut* __restrict__ out, int d, float eps, float* __restrict__ zero,
                long long zero_count) {
     __shared__ float scratch[32];
+    lp_grid_release();
+    lp_grid_wait();
     const int r = blockIdx.x;
     const long long src = rows ? rows[r] : r;
     float* xr = x + src * d;
@@ -88,6 +92,8 @@ __global__ void rmsnorm_wide_kernel(float* __restrict__ x, const TAdd* __restric
                                     TOut* __restrict__ out, int d, float eps, float* __restrict__ zero,
                                     long long zero_count) {
     __shared__ float scratch[32];
+    lp_grid_release();
+    lp_grid_wait();
     const int r = blockIdx.x;
     const long long src = rows ? rows[r] : r;
     float* xr = x + src * d;
@@ -114,11 +120,11 @@ extern "C" int lp_rmsnorm(float* x, const void* add, int add_dtype, const int* r
 #define LP_LAUNCH_NORM(TOUT, TADD)                                                                              \
     do {                                                                                                        \
         if (wide)                                                                                               \
-            rmsnorm_wide_kernel<TOUT, TADD><<<R, 512, 0, stream>>>(x, (const TADD*)add, rows, w, (TOUT*)out, d, \
-                                                                   eps, zero, zero_count);                      \
+            lp_launch(rmsnorm_wide_kernel<TOUT, TADD>, R, 512, 0, stream, x, (const TADD*)add, rows, w,          \
+                      (TOUT*)out, d, eps, zero, zero_count);                                                    \
         else                                                                                                    \
-            rmsnorm_kernel<TOUT, TADD><<<R, NORM_THREADS, 0, stream>>>(x, (const TADD*)add, rows, w, (TOUT*)out, \
-                                                                       d, eps, zero, zero_count);               \
+            lp_launch(rmsnorm_kernel<TOUT, TADD>, R, NORM_THREADS, 0, stream, x, (const TADD*)add, rows, w,      \
+                      (TOUT*)out, d, eps, zero, zero_count);                                                    \
     } while (0)
     if (out_dtype == LP_F32 && add_dtype == LP_F32) LP_LAUNCH_NORM(float, float);
     else if (out_dtype == LP_F32 && add_dtype == LP_BF16) LP_LAUNCH_NORM(float, __nv_bfloat16);
@@ -142,8 +148,11 @@ __global__ void __launch_bounds__(256)
 rope_cache_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ inv_freq,
                   const int* __restrict__ positions, const int* __restrict__ seq_ids,
                   const int* __restrict__ page_table, int pt_stride, TQ* __restrict__ q_out,
-                  TKV* __restrict__ pages, int H, int G, int hd, int rd, int interleaved, int page_size) {
+                  TKV* __restrict__ pages, int H, int G, int hd, int rd, int interleaved, int page_size,
+                  int heads_per_block) {
     __shared__ float cs[128], sn[128];          // rd / 2 <= 128
+    lp_grid_release();
+    lp_grid_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = rd >> 1;
@@ -159,8 +168,9 @@ rope_cache_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
         const int page = page_table[(long long)seq_ids[t] * pt_stride + pos / page_size];
         page_base = (long long)page * 2 * G * page_size * hd + (long long)(pos % page_size) * hd;
     }
-    const int total = heads * hd;
-    for (int idx = threadIdx.x; idx < total; idx += blockDim.x) {
+    const int head_begin = blockIdx.y * heads_per_block;
+    const int head_end = min(heads, head_begin + heads_per_block);
+    for (int idx = head_begin * hd + threadIdx.x; idx < head_end * hd; idx += blockDim.x) {
         const int head = idx / hd, e = idx - head * hd;
         const bool is_q = head < H, is_v = head >= H + G;
         float val = src[idx];
@@ -193,12 +203,20 @@ extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_fr
     const int heads = pages ? H + 2 * G : H;
     if (ld < heads * hd) LP_REFUSE("rope_cache_write: row of %d values for %d heads of %d", ld, heads, hd);
     if (pages && page_size <= 0) LP_REFUSE("rope_cache_write: page size %d", page_size);
-    const int threads = heads * hd >= 1024 ? 256 : 128;
+    // many tokens: one block per token takes all its heads; few tokens: the heads are shared out
+    int heads_per_block = heads;
+    if (T < 256) {
+        heads_per_block = (512 + hd - 1) / hd;
+        if (heads_per_block < 1) heads_per_block = 1;
+        if (heads_per_block > heads) heads_per_block = heads;
+    }
+    const int parts = (heads + heads_per_block - 1) / heads_per_block;
+    const int threads = heads_per_block * hd >= 1024 ? 256 : 128;
+    dim3 grid(T, parts);
 #define LP_LAUNCH_ROPE(TQ, TKV)                                                                          \
-    rope_cache_kernel<TQ, TKV><<<T, threads, 0, stream>>>(qkv, ld, inv_freq, positions, seq_ids,           \
-                                                         page_table, pt_stride, (TQ*)q_out,               \
-                                                         (TKV*)pages, H, G, hd, rd, interleaved,         \
-                                                         page_size)
+    lp_launch(rope_cache_kernel<TQ, TKV>, grid, threads, 0, stream, qkv, ld, inv_freq, positions, seq_ids, \
+              page_table, pt_stride, (TQ*)q_out, (TKV*)pages, H, G, hd, rd, interleaved, page_size,       \
+              heads_per_block)
     if (q_dtype == LP_F32 && kv_dtype == LP_F32) LP_LAUNCH_ROPE(float, float);
     else if (q_dtype == LP_BF16 && kv_dtype == LP_BF16) LP_LAUNCH_ROPE(__nv_bfloat16, __nv_bfloat16);
     else if (q_dtype == LP_F32 && kv_dtype == LP_BF16) LP_LAUNCH_ROPE(float, __nv_bfloat16);
@@ -215,6 +233,8 @@ extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_fr
 // same reason: java21 inference/CudaForwardPass.java:138-141).
 __global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ positions, int* __restrict__ kv_len,
                                const int* __restrict__ sampled, int B) {
+    lp_grid_release();
+    lp_grid_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < B) {
         tokens[i] = sampled[i];
@@ -225,7 +245,7 @@ __global__ void advance_kernel(int* __restrict__ tokens, int* __restrict__ posit
 
 extern "C" int lp_advance(int* tokens, int* positions, int* kv_len, const int* sampled, int B, cudaStream_t stream) {
     if (B <= 0) return 0;
-    advance_kernel<<<(B + 127) / 128, 128, 0, stream>>>(tokens, positions, kv_len, sampled, B);
+    lp_launch(advance_kernel, (B + 127) / 128, 128, 0, stream, tokens, positions, kv_len, sampled, B);
     return lp_check_launch("advance");
 }
 
@@ -234,6 +254,8 @@ extern "C" int lp_advance(int* tokens, int* positions, int* kv_len, const int* s
 // Used where the gate/up product was summed across CTAs and could not apply the activation itself.
 template <typename TOut>
 __global__ void swiglu_combine_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int F, long long total) {
+    lp_grid_release();
+    lp_grid_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long t = i / F;
@@ -247,9 +269,9 @@ extern "C" int lp_swiglu_combine(const float* gu, void* out, int out_dtype, int 
     const long long total = (long long)T * F;
     const int blocks = (int)((total + 255) / 256);
     if (out_dtype == LP_BF16)
-        swiglu_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)out, F, total);
+        lp_launch(swiglu_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gu, (__nv_bfloat16*)out, F, total);
     else if (out_dtype == LP_F32)
-        swiglu_combine_kernel<float><<<blocks, 256, 0, stream>>>(gu, (float*)out, F, total);
+        lp_launch(swiglu_combine_kernel<float>, blocks, 256, 0, stream, gu, (float*)out, F, total);
     else
         LP_REFUSE("swiglu_combine: output dtype code %d", out_dtype);
     return lp_check_launch("swiglu_combine");

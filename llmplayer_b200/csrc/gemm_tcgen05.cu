@@ -119,7 +119,11 @@ struct Tile {
     static constexpr int W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
     static constexpr int X_BYTES = BLOCK_TOK * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = W_TILES * W_BYTES + X_BYTES;
-    static constexpr int STAGES = (196 * 1024 / STAGE_BYTES) > 8 ? 8 : (196 * 1024 / STAGE_BYTES);
+    // token tiles up to 64 stream weights for a few sequences: two such CTAs fit an SM, so the next
+    // product's CTAs can set up and prefetch weights while the current one drains; larger tiles
+    // (prompts) take the whole shared memory for a deeper ring
+    static constexpr int BUDGET = BLOCK_TOK <= 64 ? 110 * 1024 : 196 * 1024;
+    static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
     static constexpr int ACC_COLS = BLOCK_TOK * W_TILES;
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;       // power of two by construction
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
@@ -146,11 +150,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
     const int nkb = kb_end - kb_begin;            // > 0 by the launcher's choice of grid.z
 
-    // a launch whose status word already reports a failed wait does no work
-    __shared__ int already_failed;
-    if (threadIdx.x == 0) already_failed = *((volatile int*)status);
-    __syncthreads();
-    if (already_failed) return;
+    lp_grid_release();          // the next kernel on the stream may set itself up behind this one
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < T::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -172,7 +172,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
+            // Weights are written by no kernel of a step: the first ring of weight tiles is requested
+            // before waiting for the previous kernel, the activation tiles only after it.
+            const int early = min(nkb, T::STAGES);
+            for (int i = 0; i < early; ++i) {
+                uint8_t* stage = smem + i * T::STAGE_BYTES;
+                mbar_expect_tx(&full[i], T::STAGE_BYTES);
+                const int k = (kb_begin + i) * BLOCK_K;
+                tma_load_2d(stage, &map_w, k, feat0, &full[i]);
+                if (MODE == LP_GEMM_SWIGLU) tma_load_2d(stage + T::W_BYTES, &map_w, k, feat0 + up_row_offset, &full[i]);
+            }
+            lp_grid_wait();
+            for (int i = 0; i < early; ++i)
+                tma_load_2d(smem + i * T::STAGE_BYTES + T::W_TILES * T::W_BYTES, &map_x, (kb_begin + i) * BLOCK_K, tok0,
+                            &full[i]);
+            issued = early;
+            for (int i = early; i < nkb && ok; ++i) {
                 const int s = i % T::STAGES;
                 const uint32_t phase = (i / T::STAGES) & 1;
                 if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 1); ok = false; break; }
@@ -311,8 +326,12 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
     const int per_split = (k_blocks + splits - 1) / splits;
     const int grid_z = (k_blocks + per_split - 1) / per_split;
     dim3 grid((features + BLOCK_FEAT - 1) / BLOCK_FEAT, (tokens + BLOCK_TOK - 1) / BLOCK_TOK, grid_z);
-    kernel<<<grid, THREADS, T::SMEM_BYTES, stream>>>(mw, mx, out, tokens, features, ldc, k_blocks, per_split, up_offset,
-                                                     status);
+    cudaError_t err = lp_launch(kernel, grid, THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
+                                k_blocks, per_split, up_offset, status);
+    if (err != cudaSuccess) {
+        snprintf(lp_error_text, sizeof(lp_error_text), "gemm_tcgen05: %s", cudaGetErrorString(err));
+        return (int)err;
+    }
     return lp_check_launch("gemm_tcgen05");
 }
 
@@ -322,8 +341,8 @@ int dispatch(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const 
 #define LP_GO(MODE, BF, AT) \
     return launch<BLOCK_TOK, MODE, BF, AT>(mw, mx, out, tokens, features, ldc, k_blocks, splits, up_offset, status, stream)
     if (mode == LP_GEMM_SWIGLU) {
-        if constexpr (BLOCK_TOK <= 128) { if (out_bf16) LP_GO(LP_GEMM_SWIGLU, true, false); LP_GO(LP_GEMM_SWIGLU, false, false); }
-        else LP_REFUSE("gemm: the gated epilogue takes token tiles up to 128");
+        if (out_bf16) LP_GO(LP_GEMM_SWIGLU, true, false);
+        LP_GO(LP_GEMM_SWIGLU, false, false);
     }
     if (atomic) LP_GO(LP_GEMM_STORE, false, true);
     if (out_bf16) LP_GO(LP_GEMM_STORE, true, false);

@@ -200,6 +200,8 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
               const float* __restrict__ edit_subtract, const float* __restrict__ edit_factor,
               int* __restrict__ out_token, float* __restrict__ out_prob) {
     __shared__ Shared sh;
+    lp_grid_release();
+    lp_grid_wait();
     const int b = blockIdx.x, tid = threadIdx.x;
     const LpSampleParams p = params[b];
     const float* src = logits + (long long)p.logits_row * logits_stride;
@@ -396,9 +398,84 @@ extern "C" int lp_sample(const float* logits, long long logits_stride, float* wo
                          int* out_token, float* out_prob, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (vocab <= 0) LP_REFUSE("sample: vocabulary of %d", vocab);
-    sample_kernel<<<B, THREADS, 0, stream>>>(logits, logits_stride, work, vocab, (const LpSampleParams*)params,
-                                             edit_token, edit_subtract, edit_factor, out_token, out_prob);
+    lp_launch(sample_kernel, B, THREADS, 0, stream, logits, logits_stride, work, vocab, (const LpSampleParams*)params,
+              edit_token, edit_subtract, edit_factor, out_token, out_prob);
     return lp_check_launch("sample");
 }
 
 extern "C" int lp_sample_params_size() { return (int)sizeof(LpSampleParams); }
+
+// ---------------------------------------------------------------- greedy choice for whole batches
+// First-maximum argmax of each row in two stages, so that a few rows still use many SMs:
+// grid (ARGMAX_CHUNKS, B) finds the best of each slice, then one block per row picks among them.
+namespace {
+constexpr int ARGMAX_CHUNKS = 32;
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+    return bi < 0 || v > bv || (v == bv && i < bi);
+}
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits, long long stride, int V, float* __restrict__ part_val,
+                      int* __restrict__ part_idx) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    lp_grid_release();
+    lp_grid_wait();
+    const int b = blockIdx.y, c = blockIdx.x;
+    const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int begin = c * per, end = min(V, begin + per);
+    const float* row = logits + (long long)b * stride;
+    float bv = -INFINITY;
+    int bi = -1;
+    for (int i = begin + threadIdx.x; i < end; i += 256) {
+        const float v = row[i];
+        if (bi < 0 || v > bv) { bv = v; bi = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (si[w] >= 0 && better(sv[w], si[w], bv, bi)) { bv = sv[w]; bi = si[w]; }
+        part_val[b * ARGMAX_CHUNKS + c] = bv;
+        part_idx[b * ARGMAX_CHUNKS + c] = bi;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_val, const int* __restrict__ part_idx,
+                                    int* __restrict__ out_token) {
+    lp_grid_release();
+    lp_grid_wait();
+    const int b = blockIdx.x, lane = threadIdx.x;       // 32 threads, one per slice
+    float bv = part_val[b * ARGMAX_CHUNKS + lane];
+    int bi = part_idx[b * ARGMAX_CHUNKS + lane];
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out_token[b] = bi < 0 ? 0 : bi;
+}
+}  // namespace
+
+// scratch: B * 32 floats followed by B * 32 ints (lp_argmax_scratch_bytes).
+extern "C" long long lp_argmax_scratch_bytes(int B) { return (long long)B * ARGMAX_CHUNKS * 8; }
+
+extern "C" int lp_argmax(const float* logits, long long stride, int V, int B, void* scratch, int* out_token,
+                         cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (V <= 0) LP_REFUSE("argmax: vocabulary of %d", V);
+    if (B > 65535) LP_REFUSE("argmax: %d rows exceed the grid", B);
+    float* part_val = (float*)scratch;
+    int* part_idx = (int*)(part_val + (size_t)B * ARGMAX_CHUNKS);
+    lp_launch(argmax_partial_kernel, dim3(ARGMAX_CHUNKS, B), 256, 0, stream, logits, stride, V, part_val, part_idx);
+    int rc = lp_check_launch("argmax");
+    if (rc) return rc;
+    lp_launch(argmax_final_kernel, B, 32, 0, stream, (const float*)part_val, (const int*)part_idx, out_token);
+    return lp_check_launch("argmax");
+}

@@ -62,7 +62,7 @@ class DecodeSession:
             raise
 
     def _sample(self, logits: torch.Tensor) -> None:
-        ops.sample(logits, self._work, self._params, self._edit_i, self._edit_f, self._edit_f, self.sampled, self._prob)
+        ops.argmax(logits, self._work.view(-1), self.sampled)
 
     def _one_step(self) -> None:
         eng, ctx = self.engine, self.ctx

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "sampling": {
         "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
         "lp_sample_params_size": [],
+        "lp_argmax": [_P, ctypes.c_longlong, _I, _I, _P, _P, _P],
     },
 }
 
@@ -251,7 +252,7 @@ def _token_tile(tokens: int, gated: bool) -> int:
     for tile in (16, 32, 64, 128):
         if tokens <= tile:
             return tile
-    return 128 if gated else 256
+    return 256
 
 
 def gemm_plan(tokens: int, features: int, k: int, mode: int):
@@ -303,7 +304,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
     tile = block_tok or tile
     n_splits = splits or n_splits
     if mode == SWIGLU:
-        if via is not None or n_splits > 1 or tile > 128:
+        if via is not None or n_splits > 1:
             # too few CTAs fused: plain product into float32 scratch (summed across CTAs), then the activation
             gu = scratch("gate_up_sums", (M, 2 * N), torch.float32) if scratch else \
                 torch.empty((M, 2 * N), dtype=torch.float32, device=a.device)
@@ -388,7 +389,9 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
 def decode_split(batch: int, num_kv_heads: int, num_heads: int, table_width: int):
     """How a decode step's pages are shared out over CTAs: (pages per share, shares)."""
     groups = batch * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
-    shares = max(1, min(table_width, -(-4 * NUM_SMS // groups)))
+    if table_width <= 2 or groups >= 4 * NUM_SMS:
+        return table_width, 1                   # nothing to share out, or sequences enough to fill the GPU
+    shares = max(1, min(-(-table_width // 2), -(-3 * NUM_SMS // groups)))
     per = -(-table_width // shares)
     return per, -(-table_width // per)
 
@@ -465,3 +468,16 @@ def advance(tokens: torch.Tensor, positions: torch.Tensor, kv_len: torch.Tensor,
     lib = library("elementwise")
     _check(lib, lib.lp_advance(tokens.data_ptr(), positions.data_ptr(), kv_len.data_ptr(), sampled.data_ptr(), B,
                                _stream()))
+
+
+def argmax(logits: torch.Tensor, scratch: torch.Tensor, out_token: torch.Tensor) -> None:
+    """out_token[b] = index of the first maximum of row b of the float32 ``logits``.
+    ``scratch``: at least 64 float32 per row."""
+    _want(logits, "argmax logits", torch.float32, 2)
+    _want(scratch, "argmax scratch", torch.float32, 1)
+    _want(out_token, "argmax out", torch.int32, 1)
+    B, V = logits.shape
+    if out_token.numel() != B or scratch.numel() < 64 * B:
+        raise KernelError(f"argmax: {B} rows, {out_token.numel()} outputs, scratch of {scratch.numel()}")
+    lib = library("sampling")
+    _check(lib, lib.lp_argmax(logits.data_ptr(), V, V, B, scratch.data_ptr(), out_token.data_ptr(), _stream()))

@@ -46,6 +46,20 @@ def test_tensor_core_gemm(M, N, K, mode):
         assert rel_err(out, ref) < tol, (M, N, K, mode, out_dtype, rel_err(out, ref))
 
 
+@pytest.mark.parametrize("tile", [16, 32, 64, 128, 256])
+def test_gated_epilogue_at_every_tile(tile):
+    from llmplayer_b200.kernels import ops
+    torch.manual_seed(tile)
+    M, F, K = 300, 264, 520
+    a = torch.randn(M, K, device="cuda:0").to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, device="cuda:0") / K ** 0.5).to(torch.bfloat16)
+    out = torch.full((M, F), 7.0, device="cuda:0", dtype=torch.bfloat16)
+    ops.gemm(a, w, out, ops.SWIGLU, block_tok=tile, splits=1, scratch=None)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    assert rel_err(out, reference(a, w, ops.SWIGLU)) < 5e-3
+
+
 @pytest.mark.parametrize("tile,splits", [(16, 1), (16, 4), (32, 3), (64, 2), (128, 1), (256, 1), (256, 2)])
 def test_every_tile_and_split(tile, splits):
     from llmplayer_b200.kernels import ops

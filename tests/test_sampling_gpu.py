@@ -71,3 +71,13 @@ def test_draws_do_not_depend_on_the_batch():
         rows = torch.stack([y[t], x[t]]).to(dev)
         b.append(batch.sample(rows, [0, 1], [other, together])[1])
     assert a == b
+
+
+@pytest.mark.parametrize("B,V", [(1, 1000), (8, 128256), (64, 5003)])
+def test_batched_argmax_takes_the_first_maximum(B, V):
+    from llmplayer_b200.kernels import ops
+    x = make_logits(V, B, seed=B, spread=2.0).to("cuda:0")
+    x[:, V - 1] = x.max(dim=1).values          # a tie with the maximum at the far end must lose
+    out = torch.empty(B, dtype=torch.int32, device="cuda:0")
+    ops.argmax(x, torch.empty(64 * B, device="cuda:0"), out)
+    assert out.tolist() == [P.argmax_first(row) for row in x.cpu()]
