@@ -248,31 +248,3 @@ extern "C" int lp_advance(int* tokens, int* positions, int* kv_len, const int* s
     lp_launch(advance_kernel, (B + 127) / 128, 128, 0, stream, tokens, positions, kv_len, sampled, B);
     return lp_check_launch("advance");
 }
-
-// ---------------------------------------------------------------- gated activation on summed projections
-// gu: [T, 2F] float32 (gate columns, then up columns); out[t, i] = silu(gate) * up.
-// Used where the gate/up product was summed across CTAs and could not apply the activation itself.
-template <typename TOut>
-__global__ void swiglu_combine_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int F, long long total) {
-    lp_grid_release();
-    lp_grid_wait();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= total) return;
-    const long long t = i / F;
-    const int c = (int)(i - t * F);
-    const float g = gu[t * 2 * F + c], u = gu[t * 2 * F + F + c];
-    out[i] = lp_from_float<TOut>(g / (1.0f + __expf(-g)) * u);
-}
-
-extern "C" int lp_swiglu_combine(const float* gu, void* out, int out_dtype, int T, int F, cudaStream_t stream) {
-    if (T <= 0 || F <= 0) return 0;
-    const long long total = (long long)T * F;
-    const int blocks = (int)((total + 255) / 256);
-    if (out_dtype == LP_BF16)
-        lp_launch(swiglu_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gu, (__nv_bfloat16*)out, F, total);
-    else if (out_dtype == LP_F32)
-        lp_launch(swiglu_combine_kernel<float>, blocks, 256, 0, stream, gu, (float*)out, F, total);
-    else
-        LP_REFUSE("swiglu_combine: output dtype code %d", out_dtype);
-    return lp_check_launch("swiglu_combine");
-}

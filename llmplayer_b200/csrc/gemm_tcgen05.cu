@@ -10,8 +10,13 @@
 // split over CTAs (grid.z); partial sums then meet in float32 atomics.
 //
 // Epilogues: store (float32 or bfloat16), add into a float32 output (the residual
-// stream, or split-K partial sums), or the gated activation silu(gate) * up for W that
-// stacks the gate rows over the up rows.
+// stream, or split-K partial sums), or the gated activation silu(gate) * up. For the
+// latter W interleaves gate and up rows in blocks of 64 (rows 128t..128t+63 = gate features
+// 64t..64t+63, rows 128t+64..128t+127 = the same features of up), so one accumulator tile
+// holds both halves of 64 output features; the gate half crosses to the warps that hold
+// the up half through shared memory. For large token tiles (prompts) a second form keeps a
+// gate and an up accumulator of 128 features each, filled from 64-row boxes of the same
+// layout, so that the activation needs no exchange.
 //
 // Counterparts in the reference are its one-warp-per-row SIMT kernels
 // (src/main/resources/kernels/cuda/matmul_bf16.cu:6-37, silu_mul.cu:6-15).
@@ -26,6 +31,7 @@
 #define LP_GEMM_STORE 0
 #define LP_GEMM_ACCUMULATE 1
 #define LP_GEMM_SWIGLU 2
+#define LP_GEMM_SWIGLU_WIDE 3   // same result and weight layout; two accumulators, 128 output features per CTA
 
 namespace {
 
@@ -113,9 +119,24 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// The weight tile(s) of one k-block. WIDE: gate rows of two neighbouring 64-feature blocks form the
+// first 128-row tile, their up rows the second (the tensor map's box is 64 rows then).
+template <int MODE>
+__device__ __forceinline__ void load_weights(uint8_t* stage, const CUtensorMap* map_w, int k, int cta, uint64_t* bar) {
+    if (MODE == LP_GEMM_SWIGLU_WIDE) {
+        const int row = cta * 256;
+        tma_load_2d(stage, map_w, k, row, bar);                  // gate, features 128 cta ..
+        tma_load_2d(stage + 8192, map_w, k, row + 128, bar);     // gate, features 128 cta + 64 ..
+        tma_load_2d(stage + 16384, map_w, k, row + 64, bar);     // up
+        tma_load_2d(stage + 24576, map_w, k, row + 192, bar);    // up
+    } else {
+        tma_load_2d(stage, map_w, k, cta * BLOCK_FEAT, bar);
+    }
+}
+
 template <int BLOCK_TOK, int MODE>
 struct Tile {
-    static constexpr int W_TILES = MODE == LP_GEMM_SWIGLU ? 2 : 1;
+    static constexpr int W_TILES = MODE == LP_GEMM_SWIGLU_WIDE ? 2 : 1;
     static constexpr int W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
     static constexpr int X_BYTES = BLOCK_TOK * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = W_TILES * W_BYTES + X_BYTES;
@@ -144,7 +165,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int feat0 = blockIdx.x * BLOCK_FEAT;
+    const int feat0 = blockIdx.x * BLOCK_FEAT;          // first weight row of this CTA
     const int tok0 = blockIdx.y * BLOCK_TOK;
     const int kb_begin = blockIdx.z * k_blocks_per_split;
     const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
@@ -179,8 +200,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint8_t* stage = smem + i * T::STAGE_BYTES;
                 mbar_expect_tx(&full[i], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BLOCK_K;
-                tma_load_2d(stage, &map_w, k, feat0, &full[i]);
-                if (MODE == LP_GEMM_SWIGLU) tma_load_2d(stage + T::W_BYTES, &map_w, k, feat0 + up_row_offset, &full[i]);
+                load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[i]);
             }
             lp_grid_wait();
             for (int i = 0; i < early; ++i)
@@ -194,8 +214,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint8_t* stage = smem + s * T::STAGE_BYTES;
                 mbar_expect_tx(&full[s], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BLOCK_K;
-                tma_load_2d(stage, &map_w, k, feat0, &full[s]);
-                if (MODE == LP_GEMM_SWIGLU) tma_load_2d(stage + T::W_BYTES, &map_w, k, feat0 + up_row_offset, &full[s]);
+                load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[s]);
                 tma_load_2d(stage + T::W_TILES * T::W_BYTES, &map_x, k, tok0, &full[s]);
                 issued = i + 1;
             }
@@ -224,7 +243,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                     const uint64_t step = (uint64_t)((k * UMMA_K * 2) >> 4);
                     tcgen05_mma(tmem_base, dw + step, dx + step, idesc, (i > 0 || k > 0) ? 1u : 0u);
-                    if (MODE == LP_GEMM_SWIGLU) {
+                    if (MODE == LP_GEMM_SWIGLU_WIDE) {
                         const uint64_t du = smem_desc(w_addr + T::W_BYTES);
                         tcgen05_mma(tmem_base + BLOCK_TOK, du + step, dx + step, idesc, (i > 0 || k > 0) ? 1u : 0u);
                     }
@@ -242,29 +261,70 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!ready && lane == 0) atomicExch(status, 3);
         tcgen05_fence_after();
         const bool go = __all_sync(0xffffffffu, ready && *((volatile int*)status) == 0);
-        if (go) {
-            const int f = feat0 + quarter * 32 + lane;
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            constexpr int CHUNK = BLOCK_TOK >= 32 ? 32 : 16;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        constexpr int CHUNK = BLOCK_TOK >= 32 ? 32 : 16;
+        if (MODE != LP_GEMM_SWIGLU) {
+            if (go) {
+                const int f = feat0 + quarter * 32 + lane;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
-                uint32_t g[CHUNK], u[MODE == LP_GEMM_SWIGLU ? CHUNK : 1];
-                if (CHUNK == 32) tmem_ld32(lane_addr + c0, g); else tmem_ld16(lane_addr + c0, g);
-                if (MODE == LP_GEMM_SWIGLU) {
-                    if (CHUNK == 32) tmem_ld32(lane_addr + BLOCK_TOK + c0, u); else tmem_ld16(lane_addr + BLOCK_TOK + c0, u);
-                }
-                tmem_ld_wait();
-                if (f < features) {
+                for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
+                    uint32_t g[CHUNK], u[MODE == LP_GEMM_SWIGLU_WIDE ? CHUNK : 1];
+                    if (CHUNK == 32) tmem_ld32(lane_addr + c0, g); else tmem_ld16(lane_addr + c0, g);
+                    if (MODE == LP_GEMM_SWIGLU_WIDE) {
+                        if (CHUNK == 32) tmem_ld32(lane_addr + BLOCK_TOK + c0, u);
+                        else tmem_ld16(lane_addr + BLOCK_TOK + c0, u);
+                    }
+                    tmem_ld_wait();
+                    if (f < features) {
 #pragma unroll
-                    for (int j = 0; j < CHUNK; ++j) {
-                        const int t = tok0 + c0 + j;
-                        if (t >= tokens) break;
-                        float v = __uint_as_float(g[j]);
-                        if (MODE == LP_GEMM_SWIGLU) v = v / (1.0f + __expf(-v)) * __uint_as_float(u[j]);
-                        const size_t at = (size_t)t * ldc + f;
-                        if (ATOMIC) atomicAdd((float*)out + at, v);
-                        else if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
-                        else ((float*)out)[at] = v;
+                        for (int j = 0; j < CHUNK; ++j) {
+                            const int t = tok0 + c0 + j;
+                            if (t >= tokens) break;
+                            float v = __uint_as_float(g[j]);
+                            if (MODE == LP_GEMM_SWIGLU_WIDE) v = __fdividef(v, 1.0f + __expf(-v)) * __uint_as_float(u[j]);
+                            const size_t at = (size_t)t * ldc + f;
+                            if (ATOMIC) atomicAdd((float*)out + at, v);
+                            else if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                            else ((float*)out)[at] = v;
+                        }
+                    }
+                }
+            }
+        } else {
+            // rows 0..63 of the tile are gate, rows 64..127 up, of the same 64 output features. Every load
+            // has been consumed by now, so the ring's memory carries the gate half across.
+            float* cross = reinterpret_cast<float*>(smem);            // [64][BLOCK_TOK + 1]
+            constexpr int LD = BLOCK_TOK + 1;
+            const int local = (quarter & 1) * 32 + lane;              // feature within the 64
+            if (go && quarter < 2) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
+                    uint32_t g[CHUNK];
+                    if (CHUNK == 32) tmem_ld32(lane_addr + c0, g); else tmem_ld16(lane_addr + c0, g);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < CHUNK; ++j) cross[local * LD + c0 + j] = __uint_as_float(g[j]);
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps
+            if (go && quarter >= 2) {
+                const int f = blockIdx.x * (BLOCK_FEAT / 2) + local;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
+                    uint32_t u[CHUNK];
+                    if (CHUNK == 32) tmem_ld32(lane_addr + c0, u); else tmem_ld16(lane_addr + c0, u);
+                    tmem_ld_wait();
+                    if (f < features) {
+#pragma unroll
+                        for (int j = 0; j < CHUNK; ++j) {
+                            const int t = tok0 + c0 + j;
+                            if (t >= tokens) break;
+                            const float gate = cross[local * LD + c0 + j];
+                            const float v = __fdividef(gate, 1.0f + __expf(-gate)) * __uint_as_float(u[j]);
+                            const size_t at = (size_t)t * ldc + f;
+                            if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                            else ((float*)out)[at] = v;
+                        }
                     }
                 }
             }
@@ -325,7 +385,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
     }
     const int per_split = (k_blocks + splits - 1) / splits;
     const int grid_z = (k_blocks + per_split - 1) / per_split;
-    dim3 grid((features + BLOCK_FEAT - 1) / BLOCK_FEAT, (tokens + BLOCK_TOK - 1) / BLOCK_TOK, grid_z);
+    const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;     // output features per CTA
+    dim3 grid((features + per_cta - 1) / per_cta, (tokens + BLOCK_TOK - 1) / BLOCK_TOK, grid_z);
     cudaError_t err = lp_launch(kernel, grid, THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
                                 k_blocks, per_split, up_offset, status);
     if (err != cudaSuccess) {
@@ -341,8 +402,13 @@ int dispatch(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const 
 #define LP_GO(MODE, BF, AT) \
     return launch<BLOCK_TOK, MODE, BF, AT>(mw, mx, out, tokens, features, ldc, k_blocks, splits, up_offset, status, stream)
     if (mode == LP_GEMM_SWIGLU) {
-        if (out_bf16) LP_GO(LP_GEMM_SWIGLU, true, false);
-        LP_GO(LP_GEMM_SWIGLU, false, false);
+        if constexpr (BLOCK_TOK >= 128) {
+            if (out_bf16) LP_GO(LP_GEMM_SWIGLU_WIDE, true, false);
+            LP_GO(LP_GEMM_SWIGLU_WIDE, false, false);
+        } else {
+            if (out_bf16) LP_GO(LP_GEMM_SWIGLU, true, false);
+            LP_GO(LP_GEMM_SWIGLU, false, false);
+        }
     }
     if (atomic) LP_GO(LP_GEMM_STORE, false, true);
     if (out_bf16) LP_GO(LP_GEMM_STORE, true, false);
@@ -352,7 +418,8 @@ int dispatch(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const 
 
 }  // namespace
 
-// X: [tokens, K] bf16 (row stride ldx); W: [features, K] bf16, or [2*features, K] for SWIGLU (row stride ldw);
+// X: [tokens, K] bf16 (row stride ldx); W: [features, K] bf16 (row stride ldw); for SWIGLU, W holds
+// 128 rows per 64 output features (64 gate rows, then the 64 up rows), features rounded up to 64;
 // out: [tokens, ldc] float32 or bfloat16. mode: STORE / ACCUMULATE / SWIGLU. block_tok: 16..256 (a power of two).
 // splits > 1 or ACCUMULATE adds into a float32 `out` with atomics (a STORE with splits needs `out` zeroed before).
 // status: one int in device memory, set non-zero if a wait inside the kernel ran out.
@@ -371,9 +438,10 @@ extern "C" int lp_gemm_tcgen05(const void* X, const void* W, void* out, int out_
     if (mode == LP_GEMM_SWIGLU && splits > 1) LP_REFUSE("gemm: the gated epilogue cannot be split along K");
     if (atomic && out_dtype != LP_F32) LP_REFUSE("gemm: sums across CTAs need a float32 output");
     if (out_dtype != LP_F32 && out_dtype != LP_BF16) LP_REFUSE("gemm: output dtype code %d", out_dtype);
-    const long long w_rows = mode == LP_GEMM_SWIGLU ? 2LL * features : features;
+    const long long w_rows = mode == LP_GEMM_SWIGLU ? 128LL * ((features + 63) / 64) : features;
     CUtensorMap mw, mx;
-    int rc = make_map(&mw, W, w_rows, K, ldw, BLOCK_FEAT);
+    const bool wide = mode == LP_GEMM_SWIGLU && block_tok >= 128;
+    int rc = make_map(&mw, W, w_rows, K, ldw, wide ? 64 : BLOCK_FEAT);
     if (rc) return rc;
     rc = make_map(&mx, X, tokens, K, ldx, block_tok);
     if (rc) return rc;

@@ -26,7 +26,6 @@ _SIGNATURES = {
         "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P, ctypes.c_longlong, _P],
         "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "lp_advance": [_P, _P, _P, _P, _I, _P],
-        "lp_swiglu_combine": [_P, _P, _I, _I, _I, _P],
     },
     "gemm_plain": {
         "lp_gemm_plain": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -255,70 +254,61 @@ def _token_tile(tokens: int, gated: bool) -> int:
     return 256
 
 
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """The weight layout of the tensor-core gated product: for every 64 output features, their 64
+    gate rows followed by their 64 up rows (features padded with zero rows to a multiple of 64)."""
+    F, K = gate.shape
+    if up.shape != gate.shape:
+        raise KernelError(f"gate {tuple(gate.shape)} and up {tuple(up.shape)} differ")
+    pad = -F % 64
+    if pad:
+        zeros = torch.zeros((pad, K), dtype=gate.dtype, device=gate.device)
+        gate, up = torch.cat([gate, zeros]), torch.cat([up, zeros])
+    blocks = (F + pad) // 64
+    return torch.stack([gate.view(blocks, 64, K), up.view(blocks, 64, K)], dim=1).reshape(2 * (F + pad), K).contiguous()
+
+
 def gemm_plan(tokens: int, features: int, k: int, mode: int):
-    """(token tile, splits, scratch) that :func:`gemm` uses for these sizes. ``scratch`` names
-    the float32 buffer a gated product is summed into un-activated when too few CTAs would
-    cover it fused (None: the activation is applied in the product's own epilogue)."""
+    """(token tile, splits) that :func:`gemm` uses for these sizes."""
     k_blocks = -(-k // 64)
-
-    def pick(feats: int, tile: int) -> int:
-        ctas = -(-feats // 128) * -(-tokens // tile)
-        if ctas >= NUM_SMS // 2 or k_blocks < 8:
-            return 1
-        return max(1, min(NUM_SMS // ctas, k_blocks // 4))
-
+    tile = _token_tile(tokens, mode == SWIGLU)
     if mode == SWIGLU:
-        tile = _token_tile(tokens, True)
-        fused_ctas = -(-features // 128) * -(-tokens // tile)
-        if fused_ctas >= (NUM_SMS * 3) // 4:
-            return tile, 1, None
-        return tile, pick(2 * features, tile), "gate_up_sums"
-    tile = _token_tile(tokens, False)
-    return tile, pick(features, tile), None
+        return tile, 1
+    ctas = -(-features // 128) * -(-tokens // tile)
+    if ctas >= NUM_SMS // 2 or k_blocks < 8:
+        return tile, 1
+    return tile, max(1, min(NUM_SMS // ctas, k_blocks // 4))
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, block_tok: int = 0,
-         splits: int = 0, scratch=None, cleared: bool = False) -> torch.Tensor:
+         splits: int = 0, cleared: bool = False) -> torch.Tensor:
     """out (=|+=) a @ w.T on the tensor cores (bfloat16 in, float32 accumulation).
 
-    ``a`` [tokens, K] and ``w`` [features, K] (``[2*features, K]`` for ``SWIGLU``) are bfloat16.
-    When few CTAs would cover the output, the K range is split over more of them and the
-    partial sums meet in float32 atomics; a gated product is then summed un-activated into
-    ``scratch(name, shape, dtype)`` and activated by a second small kernel. ``cleared``:
-    the buffer that partial sums go to (``out``, or the scratch of a gated product) is
-    already zero. ``block_tok`` / ``splits`` override the plan (tests).
+    ``a`` [tokens, K] and ``w`` [features, K] are bfloat16; for ``SWIGLU``, ``w`` is the
+    interleaved gate/up matrix of :func:`interleave_gate_up` and ``out`` [tokens, features] gets
+    silu(gate) * up. When few CTAs would cover the output, the K range is split over more of
+    them and the partial sums meet in float32 atomics; ``cleared`` says that ``out`` is already
+    zero for that. ``block_tok`` / ``splits`` override the plan (tests).
     """
     _want(a, "gemm a", torch.bfloat16, 2)
     _want(w, "gemm w", torch.bfloat16, 2)
     _want(out, "gemm out", ndim=2)
     M, K = a.shape
     N = out.shape[1]
-    rows = 2 * N if mode == SWIGLU else N
+    rows = 128 * (-(-N // 64)) if mode == SWIGLU else N
     if w.shape != (rows, K) or out.shape[0] != M:
         raise KernelError(f"gemm: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, mode {mode}")
     if M == 0:
         return out
     lib = library("gemm_tcgen05")
     status = kernel_status()
-    tile, n_splits, via = gemm_plan(M, N, K, mode)
+    tile, n_splits = gemm_plan(M, N, K, mode)
     tile = block_tok or tile
-    n_splits = splits or n_splits
-    if mode == SWIGLU:
-        if via is not None or n_splits > 1:
-            # too few CTAs fused: plain product into float32 scratch (summed across CTAs), then the activation
-            gu = scratch("gate_up_sums", (M, 2 * N), torch.float32) if scratch else \
-                torch.empty((M, 2 * N), dtype=torch.float32, device=a.device)
-            gemm(a, w, gu, STORE, block_tok=tile, splits=n_splits, cleared=cleared)
-            ew = library("elementwise")
-            _check(ew, ew.lp_swiglu_combine(gu.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, _stream()))
-            return out
-        _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
-                                        K, K, N, SWIGLU, tile, 1, status.data_ptr(), _stream()))
-        return out
+    n_splits = 1 if mode == SWIGLU else (splits or n_splits)
     if mode == ACCUMULATE:
         if out.dtype != torch.float32:
             raise KernelError("gemm: accumulation needs a float32 output")
-    elif n_splits > 1:
+    elif mode == STORE and n_splits > 1:
         if out.dtype != torch.float32:
             n_splits = 1
         elif not cleared:
@@ -326,8 +316,6 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
     _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
                                     K, K, N, mode, tile, n_splits, status.data_ptr(), _stream()))
     return out
-
-
 
 
 # --------------------------------------------------------------------------- attention

@@ -12,7 +12,6 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
-from ..kernels import ops
 from .base import FEED_FORWARDS, Part, Runtime
 from .linear import Linear
 from .specs import MATRIX, SwiGLUSpec, TensorSpec
@@ -35,11 +34,8 @@ class SwiGLU(Part):
     def load(self, tensors: Mapping[str, torch.Tensor], runtime: Runtime) -> None:
         super().load(tensors, runtime)
         s = self.spec
-        self.gate_up = Linear([tensors[s.gate], tensors[s.up]], runtime)
+        self.gate_up = Linear([tensors[s.gate], tensors[s.up]], runtime, gated=True)
         self.down = Linear([tensors[s.down]], runtime)
-
-    def buffer_to_clear(self, ctx, tokens: int):
-        return self.gate_up.sums_into(ctx, tokens, "ffn_hidden", ops.SWIGLU)
 
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor) -> None:
         h = ctx.buffer("ffn_hidden", (x.shape[0], self.spec.intermediate_size), self.runtime.act_dtype)

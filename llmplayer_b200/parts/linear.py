@@ -15,15 +15,29 @@ from .base import Runtime
 
 
 class Linear:
-    """out (=|+=) x @ W^T, or the gated product when W stacks gate rows over up rows."""
+    """out (=|+=) x @ W^T for W = the given matrices stacked by rows; ``gated=True`` takes a
+    (gate, up) pair and offers the gated product silu(x gate^T) * (x up^T)."""
 
-    def __init__(self, parts: Sequence[torch.Tensor], runtime: Runtime):
+    def __init__(self, parts: Sequence[torch.Tensor], runtime: Runtime, gated: bool = False):
         mats = [runtime.matrix(p) for p in parts]
         if len({m.dtype for m in mats}) > 1:        # mixed storage: widen to the widest
             mats = [m.to(torch.float32) for m in mats]
-        self.weight = mats[0] if len(mats) == 1 else torch.cat(mats, dim=0).contiguous()
         self.runtime = runtime
-        self.out_features, self.in_features = self.weight.shape
+        self.gated = gated
+        self.in_features = mats[0].shape[1]
+        self.out_features = sum(m.shape[0] for m in mats)
+        self.interleaved = False
+        if gated:
+            if len(mats) != 2 or mats[0].shape != mats[1].shape:
+                raise ValueError("a gated product takes a gate and an up matrix of equal shape")
+            self.out_features = mats[0].shape[0]
+            self.interleaved = (runtime.fast and mats[0].dtype == torch.bfloat16 and self.in_features % 8 == 0
+                                and ops.fast_gemm_available())
+        if self.interleaved:
+            # the tensor-core kernel wants gate and up rows of the same features side by side
+            self.weight = ops.interleave_gate_up(mats[0], mats[1])
+        else:
+            self.weight = mats[0] if len(mats) == 1 else torch.cat(mats, dim=0).contiguous()
 
     def _fast(self) -> bool:
         # the tensor-core kernel wants bfloat16 operands and rows of a multiple of 8 elements (TMA strides)
@@ -43,19 +57,15 @@ class Linear:
         """The float32 buffer that this product, run for ``tokens`` rows, will add partial
         sums into and that must therefore be zero beforehand; None if it stores its result.
         ``out_name``: the workspace name of its output."""
-        if not self._fast() or mode == ops.ACCUMULATE:
+        if not self._fast() or mode != ops.STORE:
             return None
-        features = self.out_features // 2 if mode == ops.SWIGLU else self.out_features
-        _, splits, scratch = ops.gemm_plan(tokens, features, self.in_features, mode)
+        _, splits = ops.gemm_plan(tokens, self.out_features, self.in_features, mode)
         if splits <= 1:
             return None
-        if scratch is not None:
-            return ctx.buffer(scratch, (tokens, self.out_features), torch.float32)
         return ctx.buffer(out_name, (tokens, self.out_features), torch.float32)
 
     def _run(self, x, out, mode, ctx):
-        if self._fast() and x.dtype == torch.bfloat16:
-            scratch = ctx.buffer if ctx is not None else None
+        if self._fast() and x.dtype == torch.bfloat16 and (mode != ops.SWIGLU or self.interleaved):
             cleared = ctx.take_cleared() if ctx is not None else False
-            return ops.gemm(x, self.weight, out, mode, scratch=scratch, cleared=cleared)
+            return ops.gemm(x, self.weight, out, mode, cleared=cleared)
         return ops.gemm_plain(x, self.weight, out, mode)

@@ -35,10 +35,11 @@ def test_tensor_core_gemm(M, N, K, mode):
         pytest.skip("no gated product that wide")
     a = torch.randn(M, K, device=dev).to(torch.bfloat16)
     w = (torch.randn(N * (2 if mode == "swiglu" else 1), K, device=dev) / K ** 0.5).to(torch.bfloat16)
+    w_kernel = ops.interleave_gate_up(w[:N], w[N:]) if mode == "swiglu" else w
     for out_dtype in ([torch.float32] if mode == "accumulate" else [torch.float32, torch.bfloat16]):
         out0 = torch.randn(M, N, device=dev)
         out = out0.clone().to(out_dtype)
-        ops.gemm(a, w, out, code)
+        ops.gemm(a, w_kernel, out, code)
         torch.cuda.synchronize()
         ops.check_kernel_status()
         ref = reference(a, w, code, out0)
@@ -54,7 +55,7 @@ def test_gated_epilogue_at_every_tile(tile):
     a = torch.randn(M, K, device="cuda:0").to(torch.bfloat16)
     w = (torch.randn(2 * F, K, device="cuda:0") / K ** 0.5).to(torch.bfloat16)
     out = torch.full((M, F), 7.0, device="cuda:0", dtype=torch.bfloat16)
-    ops.gemm(a, w, out, ops.SWIGLU, block_tok=tile, splits=1, scratch=None)
+    ops.gemm(a, ops.interleave_gate_up(w[:F], w[F:]), out, ops.SWIGLU, block_tok=tile)
     torch.cuda.synchronize()
     ops.check_kernel_status()
     assert rel_err(out, reference(a, w, ops.SWIGLU)) < 5e-3
