@@ -244,6 +244,176 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
     }
 }
 
+// ============================================================================ prefill, head sizes 64 and 128
+// The same algorithm with the head size known at compile time: the ldmatrix addresses of a lane
+// are computed once, the scale is folded into the exponent's FMA, exp2 is the hardware
+// approximation (relative error 2^-22, far below bfloat16's), and the tiles with the most keys
+// (the last ones of a prompt) are started first.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD, int ROWS>
+__global__ void __launch_bounds__(ROWS * 2)
+attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                               const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table,
+                               int pt_stride, const int* __restrict__ q_start, const int* __restrict__ kv_len, int H,
+                               int G, float scale_log2, int window) {
+    constexpr int KSTEPS = HD / 16;
+    constexpr int CPR = HD / 8;                       // 16-byte chunks per row: a multiple of 8
+    constexpr int ROW = HD * 2;
+    constexpr int TILE = PAGE * ROW;                  // bytes of a K (or V) tile
+    constexpr int STAGE = 2 * TILE;
+    extern __shared__ __align__(128) uint8_t smem[];
+    lp_grid_release();
+    lp_grid_wait();
+    const int b = blockIdx.z, h = blockIdx.y, tile = gridDim.x - 1 - blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t_begin = q_start[b], n_new = q_start[b + 1] - t_begin;
+    if (tile * ROWS >= n_new) return;
+    const int g = h / (H / G);
+    const int len = kv_len[b];
+    const int pos0 = len - n_new;
+    const int row0 = tile * ROWS;
+    const int rows = min(ROWS, n_new - row0);
+    const int first_pos = pos0 + row0, last_pos = pos0 + row0 + rows - 1;
+    const int lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+    const int page_lo = lo / PAGE, page_hi = last_pos / PAGE;
+    const int* table = page_table + (size_t)b * pt_stride;
+
+    const int r_lo = warp * 16 + (lane >> 2), r_hi = r_lo + 8;
+    uint32_t qf[KSTEPS][4];
+    {
+        const __nv_bfloat16* q_lo = q + ((size_t)(t_begin + row0 + min(r_lo, rows - 1)) * H + h) * HD;
+        const __nv_bfloat16* q_hi = q + ((size_t)(t_begin + row0 + min(r_hi, rows - 1)) * H + h) * HD;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            const int c = kk * 16 + (lane & 3) * 2;
+            qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_lo + c);
+            qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_hi + c);
+            qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_lo + c + 8);
+            qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_hi + c + 8);
+        }
+    }
+    const int pos_lo = first_pos + min(r_lo, rows - 1), pos_hi = first_pos + min(r_hi, rows - 1);
+    const int warp_last_pos = first_pos + min(warp * 16 + 15, rows - 1);
+    const int warp_first_pos = first_pos + min(warp * 16, rows - 1);
+
+    // byte offsets of this lane's ldmatrix rows inside a slice of 16 keys
+    uint32_t k_off[KSTEPS], v_off[KSTEPS];
+    {
+        const int mat = lane >> 3, row = lane & 7;
+        const int kr = (mat >> 1) * 8 + row, vr = (mat & 1) * 8 + row;
+#pragma unroll
+        for (int i = 0; i < KSTEPS; ++i) {
+            k_off[i] = kr * ROW + (((i * 2 + (mat & 1)) ^ (kr & 7)) << 4);
+            v_off[i] = vr * ROW + (((i * 2 + (mat >> 1)) ^ (vr & 7)) << 4);
+        }
+    }
+
+    float o[KSTEPS * 2][4];
+#pragma unroll
+    for (int i = 0; i < KSTEPS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;      // maxima in scaled log2 units
+
+    load_page(smem, pages, table[page_lo], G, g, HD, tid, ROWS * 2);
+    cp_async_commit();
+    for (int p = page_lo; p <= page_hi; ++p) {
+        const int cur = (p - page_lo) & 1;
+        if (p + 1 <= page_hi) load_page(smem + (cur ^ 1) * STAGE, pages, table[p + 1], G, g, HD, tid, ROWS * 2);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const int key_base = p * PAGE;
+        const bool active = key_base <= warp_last_pos &&
+                            (window <= 0 || key_base + PAGE - 1 > warp_first_pos - window);
+        if (active) {
+            const uint32_t k_tile = smem_u32(smem + cur * STAGE);
+            const uint32_t v_tile = k_tile + TILE;
+            float s[8][4];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4(k_tile + ks * 16 * ROW + k_off[kk], b0, b1, b2, b3);
+                    mma_bf16(s[ks * 2], qf[kk], b0, b1);
+                    mma_bf16(s[ks * 2 + 1], qf[kk], b2, b3);
+                }
+            }
+            const bool edge = key_base + PAGE - 1 > warp_first_pos ||
+                              (window > 0 && key_base <= warp_last_pos - window);
+            if (edge) {
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key_base + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        const int pos = (e < 2) ? pos_lo : pos_hi;
+                        if (key > pos || (window > 0 && key <= pos - window)) s[nt][e] = -INFINITY;
+                    }
+            }
+            float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                mx_lo = fmaxf(mx_lo, fmaxf(s[nt][0], s[nt][1]));
+                mx_hi = fmaxf(mx_hi, fmaxf(s[nt][2], s[nt][3]));
+            }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo * scale_log2), mn_hi = fmaxf(m_hi, mx_hi * scale_log2);
+            const float a_lo = fast_exp2(m_lo - mn_lo), a_hi = fast_exp2(m_hi - mn_hi);
+            m_lo = mn_lo; m_hi = mn_hi;
+            float sum_lo = 0.f, sum_hi = 0.f;
+            uint32_t pf[4][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) {
+                const float e0 = fast_exp2(fmaf(s[nt][0], scale_log2, -mn_lo));      // exp2(-inf) = 0 for masked keys
+                const float e1 = fast_exp2(fmaf(s[nt][1], scale_log2, -mn_lo));
+                const float e2 = fast_exp2(fmaf(s[nt][2], scale_log2, -mn_hi));
+                const float e3 = fast_exp2(fmaf(s[nt][3], scale_log2, -mn_hi));
+                sum_lo += e0 + e1; sum_hi += e2 + e3;
+                pf[nt >> 1][(nt & 1) * 2] = pack_bf16(e0, e1);
+                pf[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(e2, e3);
+            }
+            l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
+#pragma unroll
+            for (int i = 0; i < KSTEPS * 2; ++i) { o[i][0] *= a_lo; o[i][1] *= a_lo; o[i][2] *= a_hi; o[i][3] *= a_hi; }
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+                for (int dd = 0; dd < KSTEPS; ++dd) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(v_tile + ks * 16 * ROW + v_off[dd], b0, b1, b2, b3);
+                    mma_bf16(o[dd * 2], pf[ks], b0, b1);
+                    mma_bf16(o[dd * 2 + 1], pf[ks], b2, b3);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    const float inv_lo = 1.0f / l_lo, inv_hi = 1.0f / l_hi;
+#pragma unroll
+    for (int dt = 0; dt < KSTEPS * 2; ++dt) {
+        const int d = dt * 8 + (lane & 3) * 2;
+        if (r_lo < rows)
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(t_begin + row0 + r_lo) * H + h) * HD + d) =
+                pack_bf16(o[dt][0] * inv_lo, o[dt][1] * inv_lo);
+        if (r_hi < rows)
+            *reinterpret_cast<uint32_t*>(out + ((size_t)(t_begin + row0 + r_hi) * H + h) * HD + d) =
+                pack_bf16(o[dt][2] * inv_hi, o[dt][3] * inv_hi);
+    }
+}
+
 // ============================================================================ decode
 // grid: (splits, G * head_groups, B); 128 threads; one new token per sequence.
 // Partial results: part_o[b][head][split][hd] (unnormalised), part_ml[b][head][split][2] = (max, sum),
@@ -462,7 +632,23 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_table, pt_stride,     \
             q_start, kv_len, H, G, hd, scale_log2, window);                                                      \
     } while (0)
-    if (hd <= 64) LP_PREFILL(64); else if (hd <= 128) LP_PREFILL(128); else LP_PREFILL(256);
+#define LP_PREFILL_EXACT(HD, ROWS)                                                                               \
+    do {                                                                                                         \
+        rc = set_smem<2000 + HD + ROWS>(attention_prefill_exact_kernel<HD, ROWS>, smem, "attention_prefill");    \
+        if (rc) return rc;                                                                                       \
+        dim3 grid_exact((max_new + ROWS - 1) / ROWS, H, B);                                                      \
+        lp_launch(attention_prefill_exact_kernel<HD, ROWS>, grid_exact, ROWS * 2, smem, stream,                  \
+                  (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_table,         \
+                  pt_stride, q_start, kv_len, H, G, scale_log2, window);                                         \
+    } while (0)
+    // long prompts: 128 query rows share each page of keys; short ones keep 64 rows for more CTAs
+    const bool tall = (long long)((max_new + 127) / 128) * H * B >= 1184;
+    if (hd == 64 && tall) LP_PREFILL_EXACT(64, 128);
+    else if (hd == 64) LP_PREFILL_EXACT(64, 64);
+    else if (hd == 128 && tall) LP_PREFILL_EXACT(128, 128);
+    else if (hd == 128) LP_PREFILL_EXACT(128, 64);
+    else if (hd <= 64) LP_PREFILL(64); else if (hd <= 128) LP_PREFILL(128); else LP_PREFILL(256);
+#undef LP_PREFILL_EXACT
 #undef LP_PREFILL
     return lp_check_launch("attention_prefill");
 }
