@@ -126,6 +126,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (both are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points and the prefill")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="measure only the 2,048-token prefill (small runs for profiling)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -155,7 +157,7 @@ def main() -> int:
     tmp = tempfile.mkdtemp(prefix="llmplayer_b200_bench_")
     try:
         write_random_model(config_from_dict(cfg), 2, tmp, dtype="bfloat16")
-        max_batch = max(args.batch, 1 if args.no_points else 64)
+        max_batch = 1 if args.prefill_only else max(args.batch, 1 if args.no_points else 64)
         engine = Engine.load(tmp, dtype="bfloat16", context_length=args.context, max_batch=max_batch)
     finally:
         shutil.rmtree(tmp, ignore_errors=True)
@@ -190,6 +192,30 @@ def main() -> int:
         finally:
             session.close()
 
+    def timed_prefill(T=2048):
+        slot = engine.acquire()
+        ptoks = prompts(1, T)[0]
+        for _ in range(2):                       # warm-up passes over the same slot
+            engine.step([(slot, ptoks)], [[T - 1]])
+            engine.release(slot)
+            slot = engine.acquire()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step([(slot, ptoks)], [[T - 1]])
+        stop.record()
+        torch.cuda.synchronize()
+        engine.release(slot)
+        ms = start.elapsed_time(stop)
+        flops = prefill_flops(cfg, layers, T)
+        return {"value": T / (ms / 1e3), "tokens": T, "ms": ms,
+                "frac": flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), "of": peaks["source"]}
+
+    if args.prefill_only:
+        print(json.dumps({"metric": "prefill tok/s (Llama-3.2-1B shape, bf16)", "impl": "ours", "layers": layers,
+                          "model_layers": model_layers, "prefill": timed_prefill()}))
+        return 0
+
     main_run = timed_decode(args.batch, args.steps, args.warmup, sample_clocks=True)
     bytes_step = decode_bytes(cfg, layers, args.batch, main_run["context"], engine)
     achieved = bytes_step / (main_run["ms_per_step"] / 1e3) / 1e9
@@ -223,24 +249,7 @@ def main() -> int:
                      "frac": achieved / peaks["hbm_gbs"], "of": peaks["source"]},
     }
     if not args.no_points:
-        T = 2048
-        slot = engine.acquire()
-        ptoks = prompts(1, T)[0]
-        for _ in range(2):                       # warm-up passes over the same slot
-            engine.step([(slot, ptoks)], [[T - 1]])
-            engine.release(slot)
-            slot = engine.acquire()
-        torch.cuda.synchronize()
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        start.record()
-        engine.step([(slot, ptoks)], [[T - 1]])
-        stop.record()
-        torch.cuda.synchronize()
-        engine.release(slot)
-        ms = start.elapsed_time(stop)
-        flops = prefill_flops(cfg, layers, T)
-        result["prefill"] = {"value": T / (ms / 1e3), "tokens": T, "ms": ms,
-                             "frac": flops / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), "of": peaks["source"]}
+        result["prefill"] = timed_prefill()
         points = {}
         for b in (1, 64):
             steps = max(16, args.steps // 2)
