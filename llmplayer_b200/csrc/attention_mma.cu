@@ -54,6 +54,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// exp2 by the hardware approximation (relative error about 2^-22, far below bfloat16's rounding)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Position of 16-byte chunk c of row r inside a tile whose rows hold cpr chunks.
 __device__ __forceinline__ int swz(int r, int c, int cpr) {
     return (cpr & 7) == 0 ? (c ^ (r & 7)) : (c + r) % cpr;
@@ -249,12 +256,6 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __r
 // are computed once, the scale is folded into the exponent's FMA, exp2 is the hardware
 // approximation (relative error 2^-22, far below bfloat16's), and the tiles with the most keys
 // (the last ones of a prompt) are started first.
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 template <int HD, int ROWS>
 __global__ void __launch_bounds__(ROWS * 2)
 attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
@@ -418,14 +419,47 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
 // grid: (splits, G * head_groups, B); 128 threads; one new token per sequence.
 // Partial results: part_o[b][head][split][hd] (unnormalised), part_ml[b][head][split][2] = (max, sum),
 // both in log2 units of the scaled scores.
-template <int HD_MAX>
+//
+// FUSED: the kernel starts from the float32 fused projection output qkv[b] = [H q heads | G k heads |
+// G v heads] instead of rotated bf16 queries: it rotates the queries of its heads itself, and the CTA
+// whose share holds the new token's position rotates the new key, writes key and value into the cache
+// and into its own shared-memory copy of that page. The last CTA of a (sequence, kv head) to finish
+// merges the shares (a counter per group, zero before the launch and zero again after it).
+struct FusedDecodeArgs {
+    const float* qkv;          // [B, ld]
+    int ld;
+    const float* inv_freq;     // [rd / 2] or null
+    int rd, interleaved;
+    __nv_bfloat16* pages_rw;   // same pages, writable; null: this layer keeps no keys of its own
+    int* counters;             // [B * G * head_groups]
+};
+
+__device__ __forceinline__ float rotated(const float* head, int e, int rd, int interleaved, const float* cs,
+                                         const float* sn) {
+    float val = head[e];
+    if (e < rd) {
+        const int half = rd >> 1;
+        int pair, partner;
+        bool first;
+        if (interleaved) { pair = e >> 1; first = (e & 1) == 0; partner = e ^ 1; }
+        else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
+        const float other = head[partner];
+        val = first ? val * cs[pair] - other * sn[pair] : other * sn[pair] + val * cs[pair];
+    }
+    return val;
+}
+
+// HD_EXACT > 0: the head size is that constant (index arithmetic of the copies and of ldmatrix folds
+// into shifts and masks); 0: any multiple of 16 up to HD_MAX, taken from `hd_arg`.
+template <int HD_MAX, bool FUSED, int HD_EXACT>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
                         const int* __restrict__ page_table, int pt_stride, const int* __restrict__ kv_len,
                         float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
-                        int H, int G, int hd, float scale_log2, int window, int pages_per_split, int num_splits,
-                        int head_groups) {
+                        int H, int G, int hd_arg, float scale_log2, int window, int pages_per_split, int num_splits,
+                        int head_groups, FusedDecodeArgs fused) {
     constexpr int KSTEPS = HD_MAX / 16;
+    const int hd = HD_EXACT > 0 ? HD_EXACT : hd_arg;
     extern __shared__ __align__(128) uint8_t smem[];
     lp_grid_release();
     lp_grid_wait();
@@ -443,10 +477,59 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const int* table = page_table + (size_t)b * pt_stride;
     const int stage_bytes = 2 * PAGE * hd * 2;
     constexpr int STAGES = 3;
+    const int npages = page_hi - page_lo + 1;      // may be <= 0: this share holds nothing of the sequence
+
+    // the ring is requested first; what follows overlaps with the copies
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < npages) load_page(smem + s * stage_bytes, pages, table[page_lo + s], G, g, hd, tid, 128);
+        cp_async_commit();
+    }
 
     const int r_lo = lane >> 2, r_hi = r_lo + 8;
     uint32_t qf[KSTEPS][4];
-    {
+    // FUSED: extra shared memory behind the ring: rotated queries [16][hd] bf16, the new key and value, cos, sin
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * stage_bytes);
+    __nv_bfloat16* new_k = q_s + 16 * hd;
+    __nv_bfloat16* new_v = new_k + hd;
+    float* cs = reinterpret_cast<float*>(new_v + hd);
+    float* sn = cs + 128;
+    const bool holds_new = FUSED && fused.pages_rw != nullptr && pos / PAGE >= page_lo && pos / PAGE <= page_hi;
+    if (FUSED) {
+        const int half = fused.rd >> 1;
+        for (int i = tid; i < half; i += 128) sincosf((float)pos * fused.inv_freq[i], &sn[i], &cs[i]);
+        __syncthreads();
+        const float* row = fused.qkv + (size_t)b * fused.ld;
+        for (int idx = tid; idx < 16 * hd; idx += 128) {
+            const int r = idx / hd, e = idx - r * hd;
+            const float v = r < nrows ? rotated(row + (size_t)(head0 + r) * hd, e, fused.rd, fused.interleaved, cs, sn) : 0.f;
+            q_s[idx] = __float2bfloat16_rn(v);
+        }
+        if (holds_new) {
+            for (int e = tid; e < hd; e += 128) {
+                new_k[e] = __float2bfloat16_rn(rotated(row + (size_t)(H + g) * hd, e, fused.rd, fused.interleaved, cs, sn));
+                new_v[e] = __float2bfloat16_rn(row[(size_t)(H + G + g) * hd + e]);
+            }
+        }
+        __syncthreads();
+        if (holds_new && hg == 0) {           // one CTA per (sequence, kv head) stores the new row
+            const size_t base = ((size_t)table[pos / PAGE] * 2 * G + g) * PAGE * hd + (size_t)(pos % PAGE) * hd;
+            for (int e = tid; e < hd; e += 128) {
+                fused.pages_rw[base + e] = new_k[e];
+                fused.pages_rw[base + (size_t)G * PAGE * hd + e] = new_v[e];
+            }
+        }
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            if (kk * 16 < hd) {
+                const int c = kk * 16 + (lane & 3) * 2;
+                qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_s + r_lo * hd + c);
+                qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_s + r_hi * hd + c);
+                qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_s + r_lo * hd + c + 8);
+                qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_s + r_hi * hd + c + 8);
+            }
+        }
+    } else {
         const __nv_bfloat16* q_lo = q + ((size_t)b * H + head0 + min(r_lo, nrows - 1)) * hd;
         const __nv_bfloat16* q_hi = q + ((size_t)b * H + head0 + min(r_hi, nrows - 1)) * hd;
 #pragma unroll
@@ -465,12 +548,6 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     for (int i = 0; i < KSTEPS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
 
-    const int npages = page_hi - page_lo + 1;      // may be <= 0: this share holds nothing of the sequence
-#pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < npages) load_page(smem + s * stage_bytes, pages, table[page_lo + s], G, g, hd, tid, 128);
-        cp_async_commit();
-    }
     for (int i = 0; i < npages; ++i) {
         const int nxt = i + STAGES - 1;
         if (nxt < npages)
@@ -479,10 +556,21 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         cp_async_wait<STAGES - 1>();
         __syncthreads();
         const int key_base = (page_lo + i) * PAGE;
+        const uint32_t k_tile = smem_u32(smem + (i % STAGES) * stage_bytes);
+        const uint32_t v_tile = k_tile + PAGE * hd * 2;
+        if (FUSED && holds_new && page_lo + i == pos / PAGE) {
+            // the copy of this page predates the new token: put its key and value in place
+            const int cpr = hd >> 3, row = pos % PAGE;
+            uint8_t* tile = smem + (i % STAGES) * stage_bytes;
+            for (int c = tid; c < 2 * cpr; c += 128) {
+                const int which = c >= cpr, cc = which ? c - cpr : c;
+                const uint4 v = *reinterpret_cast<const uint4*>((which ? new_v : new_k) + cc * 8);
+                *reinterpret_cast<uint4*>(tile + which * (PAGE * hd * 2) + row * (hd * 2) + swz(row, cc, cpr) * 16) = v;
+            }
+            __syncthreads();
+        }
         const int key0 = warp * 16;                  // this warp's 16 keys of the page
         if (key_base + key0 <= pos && key_base + key0 + 15 >= lo) {
-            const uint32_t k_tile = smem_u32(smem + (i % STAGES) * stage_bytes);
-            const uint32_t v_tile = k_tile + PAGE * hd * 2;
             float s[2][4];
             s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
             scores_16keys<KSTEPS>(s, qf, k_tile, key0, hd, lane);
@@ -502,16 +590,16 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
             mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
             const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-            const float a_lo = exp2f(m_lo - mn_lo), a_hi = exp2f(m_hi - mn_hi);
+            const float a_lo = fast_exp2(m_lo - mn_lo), a_hi = fast_exp2(m_hi - mn_hi);
             m_lo = mn_lo; m_hi = mn_hi;
             uint32_t pf[4];
             float sum_lo = 0.f, sum_hi = 0.f;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                float e0 = s[nt][0] <= NEG_BIG ? 0.f : exp2f(s[nt][0] - mn_lo);
-                float e1 = s[nt][1] <= NEG_BIG ? 0.f : exp2f(s[nt][1] - mn_lo);
-                float e2 = s[nt][2] <= NEG_BIG ? 0.f : exp2f(s[nt][2] - mn_hi);
-                float e3 = s[nt][3] <= NEG_BIG ? 0.f : exp2f(s[nt][3] - mn_hi);
+                float e0 = s[nt][0] <= NEG_BIG ? 0.f : fast_exp2(s[nt][0] - mn_lo);
+                float e1 = s[nt][1] <= NEG_BIG ? 0.f : fast_exp2(s[nt][1] - mn_lo);
+                float e2 = s[nt][2] <= NEG_BIG ? 0.f : fast_exp2(s[nt][2] - mn_hi);
+                float e3 = s[nt][3] <= NEG_BIG ? 0.f : fast_exp2(s[nt][3] - mn_hi);
                 sum_lo += e0 + e1; sum_hi += e2 + e3;
                 pf[nt * 2] = pack_bf16(e0, e1);
                 pf[nt * 2 + 1] = pack_bf16(e2, e3);
@@ -553,7 +641,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         float acc = 0.f, l = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float f = exp2f(sm_m[w * 16 + r] - m);
+            const float f = fast_exp2(sm_m[w * 16 + r] - m);
             acc += sm_o[((size_t)w * 16 + r) * hd + d] * f;
             l += sm_l[w * 16 + r] * f;
         }
@@ -563,6 +651,38 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
             const size_t slot = ((size_t)b * H + head0 + r) * num_splits + split;
             part_o[slot * hd + d] = acc;
             if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+        }
+    }
+    if (FUSED && num_splits > 1) {
+        // the last share of this (sequence, kv head, head group) to arrive merges them all
+        __shared__ int last;
+        __threadfence();
+        __syncthreads();
+        int* counter = fused.counters + ((size_t)b * G + g) * head_groups + hg;
+        if (tid == 0) {
+            const int ticket = atomicAdd(counter, 1);
+            last = ticket == num_splits - 1;
+            if (last) *counter = 0;                 // ready for the next launch
+        }
+        __syncthreads();
+        if (last) {
+            __threadfence();
+            for (int idx = tid; idx < nrows * hd; idx += 128) {
+                const int r = idx / hd, d = idx - r * hd;
+                const size_t base = ((size_t)b * H + head0 + r) * num_splits;
+                float m = NEG_BIG;
+                for (int s2 = 0; s2 < num_splits; ++s2) m = fmaxf(m, __ldcg(part_ml + (base + s2) * 2));
+                float acc = 0.f, l = 0.f;
+                for (int s2 = 0; s2 < num_splits; ++s2) {
+                    const float ls = __ldcg(part_ml + (base + s2) * 2 + 1);
+                    if (ls > 0.f) {
+                        const float f = fast_exp2(__ldcg(part_ml + (base + s2) * 2) - m);
+                        l += ls * f;
+                        acc += __ldcg(part_o + (base + s2) * hd + d) * f;
+                    }
+                }
+                out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(acc / l);
+            }
         }
     }
 }
@@ -678,21 +798,67 @@ extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, 
     float* part_ml = scratch + (size_t)B * H * num_splits * hd;
     dim3 grid(num_splits, G * head_groups, B);
     const float scale_log2 = scale * 1.4426950408889634f;
-#define LP_DECODE(HDM)                                                                                           \
+#define LP_DECODE(HDM, EXACT)                                                                                    \
     do {                                                                                                         \
-        rc = set_smem<1000 + HDM>(attention_decode_kernel<HDM>, smem, "attention_decode");                                   \
+        rc = set_smem<1000 + HDM + EXACT>(attention_decode_kernel<HDM, false, EXACT>, smem, "attention_decode"); \
         if (rc) return rc;                                                                                       \
-        lp_launch(attention_decode_kernel<HDM>, grid, 128, smem, stream,                                         \
+        lp_launch(attention_decode_kernel<HDM, false, EXACT>, grid, 128, smem, stream,                           \
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml, \
-            (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, head_groups);        \
+            (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, head_groups,         \
+            FusedDecodeArgs{});                                                                                  \
     } while (0)
-    if (hd <= 64) LP_DECODE(64); else if (hd <= 128) LP_DECODE(128); else LP_DECODE(256);
+    if (hd == 64) LP_DECODE(64, 64); else if (hd == 128) LP_DECODE(128, 128);
+    else if (hd <= 64) LP_DECODE(64, 0); else if (hd <= 128) LP_DECODE(128, 0); else LP_DECODE(256, 0);
 #undef LP_DECODE
     rc = lp_check_launch("attention_decode");
     if (rc || num_splits == 1) return rc;
     lp_launch(attention_merge_kernel, dim3(H, B), hd <= 32 ? 32 : (hd + 31) / 32 * 32, 0, stream,
               (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, H, hd, num_splits);
     return lp_check_launch("attention_merge");
+}
+
+// Decode attention that starts from the fused projection output: rotation of queries and of the new key,
+// the cache write of the new key and value, attention over the pages and the merge of the shares in one
+// kernel. qkv: [B, ld] float32 = [H query heads | G key heads | G value heads] x hd (keys and values only
+// if `pages_rw` is given: a layer that attends over another run's cache has none). counters: int32
+// [B * G * head_groups], zero before the first call; the kernel leaves them zero.
+extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* inv_freq, int rd, int interleaved,
+                                         void* out, void* pages, int write_kv, const int* page_table, int pt_stride,
+                                         const int* kv_len, float* scratch, int* counters, int B, int H, int G,
+                                         int hd, int page_size, float scale, int window, int pages_per_split,
+                                         int num_splits, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    int rc = check_geometry("attention_decode_fused", H, G, hd);
+    if (rc) return rc;
+    if (page_size != PAGE) LP_REFUSE("attention_decode_fused: pages of %d positions (built for %d)", page_size, PAGE);
+    if (pages_per_split <= 0 || num_splits <= 0) LP_REFUSE("attention_decode_fused: %d shares of %d pages", num_splits, pages_per_split);
+    if (rd < 0 || rd > hd || (rd & 1) || rd > 256) LP_REFUSE("attention_decode_fused: rotary width %d of a head of %d", rd, hd);
+    if (rd > 0 && !inv_freq) LP_REFUSE("attention_decode_fused: rotation without frequencies");
+    if (ld < (write_kv ? H + 2 * G : H) * hd) LP_REFUSE("attention_decode_fused: row of %d values", ld);
+    const int head_groups = (H / G + 15) / 16;
+    if (G * head_groups > 65535 || B > 65535) LP_REFUSE("attention_decode_fused: grid too large");
+    const int stage = 2 * PAGE * hd * 2;
+    const int extra = (16 * hd + 2 * hd) * 2 + 256 * 4;
+    const int merge = (128 + 64 * hd) * 4;
+    const int smem = (3 * stage > merge ? 3 * stage : merge) + extra;
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)B * H * num_splits * hd;
+    dim3 grid(num_splits, G * head_groups, B);
+    const float scale_log2 = scale * 1.4426950408889634f;
+    FusedDecodeArgs fused{qkv, ld, inv_freq, rd, interleaved, write_kv ? (__nv_bfloat16*)pages : nullptr, counters};
+#define LP_DECODE_FUSED(HDM, EXACT)                                                                              \
+    do {                                                                                                         \
+        rc = set_smem<3000 + HDM + EXACT>(attention_decode_kernel<HDM, true, EXACT>, smem, "attention_decode_fused"); \
+        if (rc) return rc;                                                                                       \
+        lp_launch(attention_decode_kernel<HDM, true, EXACT>, grid, 128, smem, stream, (const __nv_bfloat16*)nullptr, \
+                  (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml,                   \
+                  (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, head_groups,   \
+                  fused);                                                                                        \
+    } while (0)
+    if (hd == 64) LP_DECODE_FUSED(64, 64); else if (hd == 128) LP_DECODE_FUSED(128, 128);
+    else if (hd <= 64) LP_DECODE_FUSED(64, 0); else if (hd <= 128) LP_DECODE_FUSED(128, 0); else LP_DECODE_FUSED(256, 0);
+#undef LP_DECODE_FUSED
+    return lp_check_launch("attention_decode_fused");
 }
 
 // ---------------------------------------------------------------- decode without allocation

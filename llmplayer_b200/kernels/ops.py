@@ -39,6 +39,8 @@ _SIGNATURES = {
     "attention_mma": {
         "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+        "lp_attention_decode_fused": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
+                                      _I, _I, _P],
     },
     "sampling": {
         "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
@@ -401,6 +403,49 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pa
     _check(lib, lib.lp_attention_decode(
         q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1], kv_len.data_ptr(),
         buf.data_ptr(), B, num_heads, num_kv_heads, head_dim, pages.shape[3], float(scale),
+        int(window) if window else 0, pages_per_split, num_splits, _stream()))
+    return out
+
+
+_decode_counters = None
+
+
+def attention_decode_fused(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], out: torch.Tensor,
+                           pages: torch.Tensor, page_table: torch.Tensor, kv_len: torch.Tensor, scratch, *,
+                           num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, interleaved: bool,
+                           write_kv: bool, scale: float, window: Optional[int], pages_per_split: int = 0,
+                           num_splits: int = 0) -> torch.Tensor:
+    """A decode step's attention from the float32 fused projection ``qkv`` [B, (H + 2G) * hd]
+    (``[B, H * hd]`` when ``write_kv`` is false): rotates the queries, rotates and stores the new
+    key, stores the new value, attends over the pages and merges the shares, in one kernel."""
+    global _decode_counters
+    _want(qkv, "attention_decode_fused qkv", torch.float32, 2)
+    _want(out, "attention_decode_fused out", torch.bfloat16, 2)
+    _want(pages, "attention_decode_fused pages", torch.bfloat16, 5)
+    _want(page_table, "attention_decode_fused page_table", torch.int32, 2)
+    _want(kv_len, "attention_decode_fused kv_len", torch.int32, 1)
+    H, G, hd = num_heads, num_kv_heads, head_dim
+    B = kv_len.numel()
+    heads = H + 2 * G if write_kv else H
+    if qkv.shape != (B, heads * hd) or out.shape != (B, H * hd) or page_table.shape[0] != B:
+        raise KernelError(f"attention_decode_fused: qkv {tuple(qkv.shape)}, out {tuple(out.shape)}, {B} sequences")
+    if pages.shape[1] != 2 or pages.shape[2] != G or pages.shape[4] != hd:
+        raise KernelError(f"attention_decode_fused: pages {tuple(pages.shape)} do not fit {G} key heads of {hd}")
+    if rotary_dim > 0:
+        _want(inv_freq, "attention_decode_fused inv_freq", torch.float32, 1)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError(f"attention_decode_fused: {inv_freq.numel()} frequencies for a rotary width of {rotary_dim}")
+    if not pages_per_split or not num_splits:
+        pages_per_split, num_splits = decode_split(B, G, H, page_table.shape[1])
+    groups = B * G * (-(-(H // G) // 16))
+    if _decode_counters is None or _decode_counters.numel() < groups or _decode_counters.device != qkv.device:
+        _decode_counters = torch.zeros(max(groups, 1 << 14), dtype=torch.int32, device=qkv.device)
+    buf = scratch("attention_partials", (B * H * num_splits * (hd + 2),), torch.float32)
+    lib = library("attention_mma")
+    _check(lib, lib.lp_attention_decode_fused(
+        qkv.data_ptr(), qkv.shape[1], _ptr(inv_freq) if rotary_dim > 0 else None, rotary_dim, 1 if interleaved else 0,
+        out.data_ptr(), pages.data_ptr(), 1 if write_kv else 0, page_table.data_ptr(), page_table.shape[1],
+        kv_len.data_ptr(), buf.data_ptr(), _decode_counters.data_ptr(), B, H, G, hd, pages.shape[3], float(scale),
         int(window) if window else 0, pages_per_split, num_splits, _stream()))
     return out
 

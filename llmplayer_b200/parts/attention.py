@@ -77,13 +77,21 @@ class Attention(Part):
         table = ctx.page_tables[cache.group_index]
         qkv = ctx.buffer("qkv", (T, self.qkv.out_features), torch.float32)
         self.qkv.store(x, qkv, ctx)
+        o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
+        if rt.fast and ctx.all_single and cache.pages.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256:
+            # one token per sequence: rotation, cache write, attention and the merge of its shares in one kernel
+            ops.attention_decode_fused(
+                qkv, self.position.inv_freq, o, cache.pages, table, ctx.kv_len, ctx.buffer, num_heads=H,
+                num_kv_heads=G, head_dim=hd, rotary_dim=self.position.rotary_dim,
+                interleaved=self.position.interleaved, write_kv=not s.shares_kv, scale=s.scale, window=s.window)
+            self.out.accumulate(o, residual, ctx)
+            return
         q = ctx.buffer("q", (T, H * hd), rt.act_dtype)
         ops.rope_cache_write(
             qkv, self.position.inv_freq, ctx.positions, ctx.seq_ids, table, q,
             None if s.shares_kv else cache.pages,
             num_heads=H, num_kv_heads=G, head_dim=hd, rotary_dim=self.position.rotary_dim,
             interleaved=self.position.interleaved)
-        o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
         ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd,
                       scale=s.scale, window=s.window, fast=rt.fast)
         self.out.accumulate(o, residual, ctx)

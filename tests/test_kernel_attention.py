@@ -146,3 +146,47 @@ def test_a_far_key_among_hundreds_is_found(kind, window):
     lengths = [900, 333]
     new = [1, 1] if kind == "decode" else [5, 1]
     run_case(kind, lengths, new, 8, 2, 64, window, torch.bfloat16, seed=3, crafted=True)
+
+
+@pytest.mark.parametrize("H,G,hd,rd,pairing", [(32, 8, 64, 64, "split_half"), (6, 3, 48, 32, "interleaved"),
+                                               (20, 1, 64, 64, "split_half"), (4, 2, 128, 0, "split_half")])
+@pytest.mark.parametrize("window", [None, 70])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_fused_decode_equals_rotation_then_attention(H, G, hd, rd, pairing, window, splits):
+    """The fused decode kernel (rotation, cache write, attention, merge) against the separate kernels."""
+    from llmplayer_b200.kernels import ops
+    dev = "cuda:0"
+    lengths = [1, 64, 65, 700, 129, 17]
+    B = len(lengths)
+    _, pages, table = build_cache(lengths, G, hd, torch.bfloat16, seed=hd + H)
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, (H + 2 * G) * hd, generator=g).to(dev)
+    inv = (torch.rand(max(rd // 2, 1), generator=g) * 0.5).to(dev) if rd else None
+    table_d = table.to(dev)
+    kv_len = torch.tensor(lengths, dtype=torch.int32, device=dev)
+    positions = kv_len - 1
+    seq_ids = torch.arange(B, dtype=torch.int32, device=dev)
+    kw = dict(num_heads=H, num_kv_heads=G, head_dim=hd)
+    per = -(-table.shape[1] // splits)
+    n_splits = -(-table.shape[1] // per)
+
+    def scratch(name, shape, dt):
+        return torch.full(shape, float("nan"), dtype=dt, device=dev)
+
+    pages_a = pages.to(dev).clone()
+    q = torch.empty(B, H * hd, dtype=torch.bfloat16, device=dev)
+    ops.rope_cache_write(qkv, inv, positions, seq_ids, table_d, q, pages_a, rotary_dim=rd,
+                         interleaved=(pairing == "interleaved"), **kw)
+    want = torch.zeros_like(q)
+    ops.attention_decode(q, want, pages_a, table_d, kv_len, scratch, scale=hd ** -0.5, window=window,
+                         pages_per_split=per, num_splits=n_splits, **kw)
+
+    pages_b = pages.to(dev).clone()
+    got = torch.full_like(q, 3.0)
+    for _ in range(2):                       # twice: the share counters must be back at zero
+        ops.attention_decode_fused(qkv, inv, got, pages_b, table_d, kv_len, scratch, rotary_dim=rd,
+                                   interleaved=(pairing == "interleaved"), write_kv=True, scale=hd ** -0.5,
+                                   window=window, pages_per_split=per, num_splits=n_splits, **kw)
+    torch.cuda.synchronize()
+    assert torch.equal(pages_a, pages_b)                      # the same keys and values were stored
+    assert float((got.float() - want.float()).abs().max()) <= 2e-2
