@@ -134,6 +134,20 @@ __device__ __forceinline__ void load_weights(uint8_t* stage, const CUtensorMap* 
     }
 }
 
+// An RMS norm of the (float32) output rows, done by the last CTA to finish once every CTA has added
+// its part: out_norm[t, i] = out[t, i] / sqrt(mean_i out[t]^2 + eps) * weight[i] in bfloat16. For
+// products that add into the residual stream of a few decoding sequences, where the norm would
+// otherwise be a kernel of its own between two products. `counter` is zero before the launch and zero
+// again after it; `clear` (optional) is a float32 buffer the same CTA sets to zero.
+struct NormAfter {
+    const float* weight;       // null: no norm
+    __nv_bfloat16* out_norm;
+    float eps;
+    int* counter;
+    float* clear;
+    long long clear_count;
+};
+
 template <int BLOCK_TOK, int MODE>
 struct Tile {
     static constexpr int W_TILES = MODE == LP_GEMM_SWIGLU_WIDE ? 2 : 1;
@@ -143,7 +157,7 @@ struct Tile {
     // token tiles up to 64 stream weights for a few sequences: two such CTAs fit an SM, so the next
     // product's CTAs can set up and prefetch weights while the current one drains; larger tiles
     // (prompts) take the whole shared memory for a deeper ring
-    static constexpr int BUDGET = BLOCK_TOK <= 64 ? 110 * 1024 : 196 * 1024;
+    static constexpr int BUDGET = BLOCK_TOK <= 128 ? 110 * 1024 : 196 * 1024;
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
     static constexpr int ACC_COLS = BLOCK_TOK * W_TILES;
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;       // power of two by construction
@@ -155,7 +169,7 @@ template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
-                    int up_row_offset, int* __restrict__ status) {
+                    int up_row_offset, int* __restrict__ status, NormAfter norm) {
     using T = Tile<BLOCK_TOK, MODE>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -330,11 +344,62 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
         }
         tcgen05_fence_before();
+        if (ATOMIC) __threadfence();          // this thread's additions are out before the CTA is counted below
     }
     __syncthreads();
     if (warp == 1) {
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS));
+    }
+    if (ATOMIC && norm.weight != nullptr) {
+        __shared__ int is_last;
+        if (threadIdx.x == 0) {
+            const int total = gridDim.x * gridDim.y * gridDim.z;
+            const int ticket = atomicAdd(norm.counter, 1);
+            is_last = ticket == total - 1;
+            if (is_last) *norm.counter = 0;
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            // one warp per row; a lane takes the float4 chunks lane, lane + 32, ... (features % 128 == 0),
+            // eight independent loads at a time
+            const float* sums = (const float*)out;
+            const int chunks = features >> 7;                            // float4 chunks per lane
+            for (int t = warp; t < tokens; t += THREADS / 32) {
+                const float4* row = reinterpret_cast<const float4*>(sums + (size_t)t * ldc);
+                float ss = 0.f;
+                for (int c0 = 0; c0 < chunks; c0 += 8) {
+                    float4 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        v[u] = c0 + u < chunks ? __ldcg(row + (c0 + u) * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+                }
+                ss = lp_warp_sum(ss);
+                const float scale = 1.0f / sqrtf(ss / (float)features + norm.eps);
+                const float4* gain = reinterpret_cast<const float4*>(norm.weight);
+                uint2* dst = reinterpret_cast<uint2*>(norm.out_norm + (size_t)t * features);
+                for (int c0 = 0; c0 < chunks; c0 += 8) {
+                    float4 v[8], g[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (c0 + u < chunks) { v[u] = __ldcg(row + (c0 + u) * 32 + lane); g[u] = gain[(c0 + u) * 32 + lane]; }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (c0 + u < chunks) {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * scale * g[u].x, v[u].y * scale * g[u].y);
+                            __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * scale * g[u].z, v[u].w * scale * g[u].w);
+                            uint2 packed;
+                            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                            dst[(c0 + u) * 32 + lane] = packed;
+                        }
+                }
+            }
+            for (long long i = threadIdx.x; i < norm.clear_count; i += THREADS) norm.clear[i] = 0.f;
+        }
     }
 }
 
@@ -373,7 +438,7 @@ int make_map(CUtensorMap* map, const void* base, long long rows, long long K, lo
 
 template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
-           int splits, int up_offset, int* status, cudaStream_t stream) {
+           int splits, int up_offset, int* status, const NormAfter& norm, cudaStream_t stream) {
     using T = Tile<BLOCK_TOK, MODE>;
     auto kernel = gemm_tcgen05_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC>;
     static bool configured = false;
@@ -388,7 +453,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
     const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;     // output features per CTA
     dim3 grid((features + per_cta - 1) / per_cta, (tokens + BLOCK_TOK - 1) / BLOCK_TOK, grid_z);
     cudaError_t err = lp_launch(kernel, grid, THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
-                                k_blocks, per_split, up_offset, status);
+                                k_blocks, per_split, up_offset, status, norm);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_tcgen05: %s", cudaGetErrorString(err));
         return (int)err;
@@ -398,9 +463,10 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
 
 template <int BLOCK_TOK>
 int dispatch(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens,
-             int features, int ldc, int k_blocks, int splits, int up_offset, int* status, cudaStream_t stream) {
+             int features, int ldc, int k_blocks, int splits, int up_offset, int* status, const NormAfter& norm,
+             cudaStream_t stream) {
 #define LP_GO(MODE, BF, AT) \
-    return launch<BLOCK_TOK, MODE, BF, AT>(mw, mx, out, tokens, features, ldc, k_blocks, splits, up_offset, status, stream)
+    return launch<BLOCK_TOK, MODE, BF, AT>(mw, mx, out, tokens, features, ldc, k_blocks, splits, up_offset, status, norm, stream)
     if (mode == LP_GEMM_SWIGLU) {
         if constexpr (BLOCK_TOK >= 128) {
             if (out_bf16) LP_GO(LP_GEMM_SWIGLU_WIDE, true, false);
@@ -423,9 +489,13 @@ int dispatch(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const 
 // out: [tokens, ldc] float32 or bfloat16. mode: STORE / ACCUMULATE / SWIGLU. block_tok: 16..256 (a power of two).
 // splits > 1 or ACCUMULATE adds into a float32 `out` with atomics (a STORE with splits needs `out` zeroed before).
 // status: one int in device memory, set non-zero if a wait inside the kernel ran out.
+// norm_weight (optional, ACCUMULATE only, ldc == features): after the sums are complete, the last CTA writes
+// the RMS norm of every output row to norm_out (bf16 [tokens, features]) and zeroes norm_clear; norm_counter
+// is one int32, zero before the call.
 extern "C" int lp_gemm_tcgen05(const void* X, const void* W, void* out, int out_dtype, int tokens, int features, int K,
                                int ldx, int ldw, int ldc, int mode, int block_tok, int splits, int* status,
-                               cudaStream_t stream) {
+                               const float* norm_weight, float norm_eps, void* norm_out, float* norm_clear,
+                               long long norm_clear_count, int* norm_counter, cudaStream_t stream) {
     if (tokens <= 0 || features <= 0) return 0;
     if (K <= 0 || K % 8) LP_REFUSE("gemm: inner size %d must be a positive multiple of 8 for the tensor-core path", K);
     if (ldx % 8 || ldw % 8) LP_REFUSE("gemm: row strides %d / %d must be multiples of 8 elements", ldx, ldw);
@@ -445,14 +515,21 @@ extern "C" int lp_gemm_tcgen05(const void* X, const void* W, void* out, int out_
     if (rc) return rc;
     rc = make_map(&mx, X, tokens, K, ldx, block_tok);
     if (rc) return rc;
+    NormAfter norm{};
+    if (norm_weight) {
+        if (mode != LP_GEMM_ACCUMULATE || ldc != features || features % 128 || !norm_out || !norm_counter)
+            LP_REFUSE("gemm: a following norm needs an accumulating product over whole rows of a multiple of 128");
+        norm = NormAfter{norm_weight, (__nv_bfloat16*)norm_out, norm_eps, norm_counter, norm_clear,
+                         norm_clear ? norm_clear_count : 0};
+    }
     const bool bf = out_dtype == LP_BF16;
     const int mmode = mode == LP_GEMM_SWIGLU ? LP_GEMM_SWIGLU : LP_GEMM_STORE;
     switch (block_tok) {
-        case 16: return dispatch<16>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
-        case 32: return dispatch<32>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
-        case 64: return dispatch<64>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
-        case 128: return dispatch<128>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
-        case 256: return dispatch<256>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, stream);
+        case 16: return dispatch<16>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, norm, stream);
+        case 32: return dispatch<32>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, norm, stream);
+        case 64: return dispatch<64>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, norm, stream);
+        case 128: return dispatch<128>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, norm, stream);
+        case 256: return dispatch<256>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, norm, stream);
         default: LP_REFUSE("gemm: token tile %d (supported: 16, 32, 64, 128, 256)", block_tok);
     }
 }

@@ -7,6 +7,7 @@ layout's list of runs (a layer may run twice, or attend over an earlier run's ca
 """
 from __future__ import annotations
 
+import inspect
 from typing import Dict, List, Mapping, Optional
 
 import torch
@@ -31,6 +32,8 @@ class Model:
             if run.reads_cache_of is not None and not 0 <= run.reads_cache_of < i:
                 raise ConfigError(f"run {i} reads the cache of run {run.reads_cache_of}, which does not precede it")
         self.runtime: Optional[Runtime] = None
+        # blocks whose forward takes (normed_ready, next_block) can hand a fused norm to the next block
+        self._chains = ["next_block" in inspect.signature(b.forward).parameters for b in self.blocks]
 
     # ------------------------------------------------------------------ tensors
     def tensor_specs(self) -> Dict[str, TensorSpec]:
@@ -68,8 +71,16 @@ class Model:
         d = self.layout.embedding.hidden_size
         x = ctx.buffer("residual", (ctx.num_tokens, d), torch.float32)
         self.embedding.forward(ctx.tokens, x)
+        ready = False        # whether the previous block already normed the stream for this one
         for i, run in enumerate(self.runs):
-            self.blocks[run.layer].forward(ctx, cache.view(self.cache_owner(i)), x)
+            block = self.blocks[run.layer]
+            following = self.blocks[self.runs[i + 1].layer] if i + 1 < len(self.runs) else None
+            if self._chains[run.layer]:
+                ready = bool(block.forward(ctx, cache.view(self.cache_owner(i)), x, normed_ready=ready,
+                                           next_block=following))
+            else:
+                block.forward(ctx, cache.view(self.cache_owner(i)), x)
+                ready = False
         if rows.numel():
             self.head.forward(ctx, x, rows, logits)
         return logits

@@ -34,7 +34,8 @@ _SIGNATURES = {
         "lp_attention_plain": [_P, _P, _I, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
     },
     "gemm_tcgen05": {
-        "lp_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "lp_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P,
+                            ctypes.c_longlong, _P, _P],
     },
     "attention_mma": {
         "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -250,10 +251,12 @@ def check_kernel_status() -> None:
 
 
 def _token_tile(tokens: int, gated: bool) -> int:
-    for tile in (16, 32, 64, 128):
+    # up to 64 tokens: the smallest tile that holds them; beyond: 128, of which two CTAs share an SM
+    # (so one's epilogue runs under the other's MMAs); 256 remains available to callers
+    for tile in (16, 32, 64):
         if tokens <= tile:
             return tile
-    return 256
+    return 128
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -282,8 +285,12 @@ def gemm_plan(tokens: int, features: int, k: int, mode: int):
     return tile, max(1, min(NUM_SMS // ctas, k_blocks // 4))
 
 
+FUSED_NORM_MAX_TOKENS = 4
+_gemm_counter = None
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, block_tok: int = 0,
-         splits: int = 0, cleared: bool = False) -> torch.Tensor:
+         splits: int = 0, cleared: bool = False, norm_after=None) -> torch.Tensor:
     """out (=|+=) a @ w.T on the tensor cores (bfloat16 in, float32 accumulation).
 
     ``a`` [tokens, K] and ``w`` [features, K] are bfloat16; for ``SWIGLU``, ``w`` is the
@@ -291,7 +298,13 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
     silu(gate) * up. When few CTAs would cover the output, the K range is split over more of
     them and the partial sums meet in float32 atomics; ``cleared`` says that ``out`` is already
     zero for that. ``block_tok`` / ``splits`` override the plan (tests).
+
+    ``norm_after = (gain, eps, normed_out, clear)`` (``ACCUMULATE`` only, at most
+    ``FUSED_NORM_MAX_TOKENS`` rows): once all CTAs have added their parts, the last one writes
+    the RMS norm of every row of ``out`` to ``normed_out`` (bfloat16) and zeroes ``clear``
+    (a float32 tensor or None).
     """
+    global _gemm_counter
     _want(a, "gemm a", torch.bfloat16, 2)
     _want(w, "gemm w", torch.bfloat16, 2)
     _want(out, "gemm out", ndim=2)
@@ -315,8 +328,23 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
             n_splits = 1
         elif not cleared:
             out.zero_()
+    norm_args = (None, 0.0, None, None, 0, None)
+    if norm_after is not None:
+        gain, eps, normed, clear = norm_after
+        if mode != ACCUMULATE or M > FUSED_NORM_MAX_TOKENS:
+            raise KernelError("gemm: a following norm needs an accumulating product of few rows")
+        _want(gain, "gemm norm gain", torch.float32, 1)
+        _want(normed, "gemm normed out", torch.bfloat16, 2)
+        if gain.numel() != N or normed.shape != (M, N):
+            raise KernelError(f"gemm: norm gain {tuple(gain.shape)}, normed out {tuple(normed.shape)} for [{M}, {N}]")
+        if clear is not None:
+            _want(clear, "gemm norm clear", torch.float32)
+        if _gemm_counter is None or _gemm_counter.device != a.device:
+            _gemm_counter = torch.zeros(1, dtype=torch.int32, device=a.device)
+        norm_args = (gain.data_ptr(), float(eps), normed.data_ptr(), _ptr(clear),
+                     clear.numel() if clear is not None else 0, _gemm_counter.data_ptr())
     _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
-                                    K, K, N, mode, tile, n_splits, status.data_ptr(), _stream()))
+                                    K, K, N, mode, tile, n_splits, status.data_ptr(), *norm_args, _stream()))
     return out
 
 

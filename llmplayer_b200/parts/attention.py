@@ -68,7 +68,8 @@ class Attention(Part):
     def buffer_to_clear(self, ctx, tokens: int):
         return self.qkv.sums_into(ctx, tokens, "qkv", ops.STORE)
 
-    def forward(self, ctx, cache, x: torch.Tensor, residual: torch.Tensor) -> None:
+    def forward(self, ctx, cache, x: torch.Tensor, residual: torch.Tensor, then_norm=None) -> bool:
+        """Adds the layer's output into ``residual``; returns whether ``then_norm`` was fused."""
         s, rt = self.spec, self.runtime
         if cache is None:
             raise ConfigError("attention needs a key/value cache (its own or another run's)")
@@ -84,8 +85,7 @@ class Attention(Part):
                 qkv, self.position.inv_freq, o, cache.pages, table, ctx.kv_len, ctx.buffer, num_heads=H,
                 num_kv_heads=G, head_dim=hd, rotary_dim=self.position.rotary_dim,
                 interleaved=self.position.interleaved, write_kv=not s.shares_kv, scale=s.scale, window=s.window)
-            self.out.accumulate(o, residual, ctx)
-            return
+            return self.out.accumulate(o, residual, ctx, then_norm)
         q = ctx.buffer("q", (T, H * hd), rt.act_dtype)
         ops.rope_cache_write(
             qkv, self.position.inv_freq, ctx.positions, ctx.seq_ids, table, q,
@@ -94,7 +94,7 @@ class Attention(Part):
             interleaved=self.position.interleaved)
         ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd,
                       scale=s.scale, window=s.window, fast=rt.fast)
-        self.out.accumulate(o, residual, ctx)
+        return self.out.accumulate(o, residual, ctx, then_norm)
 
 
 MIXERS.register("attention", Attention)

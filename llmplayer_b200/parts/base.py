@@ -16,7 +16,7 @@ step. No part knows which model it is in.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, Dict, Mapping
+from typing import Callable, Dict, Mapping, Optional
 
 import torch
 
@@ -79,6 +79,16 @@ class Runtime:
     def gain(self, t: torch.Tensor) -> torch.Tensor:
         """A norm's gain: float32 always (widening is exact)."""
         return t.to(device=self.device, dtype=torch.float32).contiguous()
+
+
+@dataclass
+class FollowingNorm:
+    """A norm that comes right after a part's last product, offered to that part for fusion:
+    if the part can make its product write ``norm(residual)`` to ``out`` (and zero ``clear``, a
+    float32 buffer or None) on the way, it does so and says so by returning True."""
+    norm: object
+    out: torch.Tensor
+    clear: Optional[torch.Tensor] = None
 
 
 class Part:

@@ -5,11 +5,12 @@ x in float32 (inference/TransformerBlock.java:73-78, :109, :116-122, :149).
 """
 from __future__ import annotations
 
+import inspect
 from typing import Dict, Mapping
 
 import torch
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Part, Runtime
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, FollowingNorm, Part, Runtime
 from .specs import BlockSpec, TensorSpec
 
 
@@ -20,6 +21,9 @@ class PreNormBlock(Part):
         self.mixer = MIXERS.build(spec.mixer)
         self.ffn_norm = NORMS.build(spec.ffn_norm)
         self.ffn = FEED_FORWARDS.build(spec.ffn)
+        # parts may offer to write the norm that follows them (a `then_norm` argument of forward)
+        self._mixer_fuses = "then_norm" in inspect.signature(self.mixer.forward).parameters
+        self._ffn_fuses = "then_norm" in inspect.signature(self.ffn.forward).parameters
 
     def children(self):
         return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
@@ -38,20 +42,50 @@ class PreNormBlock(Part):
     def cache_request(self):
         return self.mixer.cache_request()
 
-    def forward(self, ctx, cache, residual: torch.Tensor) -> None:
+    def forward(self, ctx, cache, residual: torch.Tensor, normed_ready: bool = False, next_block=None) -> bool:
+        """Run the layer on the residual stream in place.
+
+        ``normed_ready``: the previous block already left ``norm(residual)`` of this block's first
+        norm in the shared "normed" buffer. ``next_block``: the block that runs next, so that this
+        block's last product can write that block's first norm on the way. Returns whether it did.
+        """
         act = self.runtime.act_dtype
+        tokens = residual.shape[0]
         h = ctx.buffer("normed", tuple(residual.shape), act)
-        self._norm(ctx, self.mixer_norm, self.mixer, residual, h)
-        self.mixer.forward(ctx, cache, h, residual)
-        self._norm(ctx, self.ffn_norm, self.ffn, residual, h)
+        if not normed_ready:
+            self._norm(ctx, self.mixer_norm, self.mixer, residual, h)
+        fused = False
+        if self._mixer_fuses:
+            follow = FollowingNorm(self.ffn_norm, h, self._clear_for(ctx, self.ffn, tokens))
+            fused = bool(self.mixer.forward(ctx, cache, h, residual, then_norm=follow))
+            if fused and follow.clear is not None:
+                ctx.note_cleared()
+        else:
+            self.mixer.forward(ctx, cache, h, residual)
+        if not fused:
+            self._norm(ctx, self.ffn_norm, self.ffn, residual, h)
+        nxt = getattr(next_block, "mixer_norm", None)
+        if self._ffn_fuses and nxt is not None and getattr(next_block, "kind_prenorm", False):
+            follow = FollowingNorm(nxt, h, self._clear_for(ctx, next_block.mixer, tokens))
+            done = bool(self.ffn.forward(ctx, h, residual, then_norm=follow))
+            if done and follow.clear is not None:
+                ctx.note_cleared()
+            return done
         self.ffn.forward(ctx, h, residual)
+        return False
+
+    kind_prenorm = True
+
+    @staticmethod
+    def _clear_for(ctx, consumer, tokens):
+        ask = getattr(consumer, "buffer_to_clear", None)
+        return ask(ctx, tokens) if ask is not None else None
 
     @staticmethod
     def _norm(ctx, norm, consumer, residual, h) -> None:
         """Norm the residual stream for ``consumer``; if the consumer's first product wants a
         zeroed buffer (``buffer_to_clear(ctx, tokens)``), the norm clears it on the side."""
-        ask = getattr(consumer, "buffer_to_clear", None)
-        clear = ask(ctx, residual.shape[0]) if ask is not None else None
+        clear = PreNormBlock._clear_for(ctx, consumer, residual.shape[0])
         if clear is not None:
             norm.apply(residual, h, clear=clear)
             ctx.note_cleared()

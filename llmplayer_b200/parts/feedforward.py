@@ -37,10 +37,11 @@ class SwiGLU(Part):
         self.gate_up = Linear([tensors[s.gate], tensors[s.up]], runtime, gated=True)
         self.down = Linear([tensors[s.down]], runtime)
 
-    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor) -> None:
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, then_norm=None) -> bool:
+        """Adds the feed-forward's output into ``residual``; returns whether ``then_norm`` was fused."""
         h = ctx.buffer("ffn_hidden", (x.shape[0], self.spec.intermediate_size), self.runtime.act_dtype)
         self.gate_up.swiglu(x, h, ctx)
-        self.down.accumulate(h, residual, ctx)
+        return self.down.accumulate(h, residual, ctx, then_norm)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

@@ -47,8 +47,22 @@ class Linear:
     def store(self, x: torch.Tensor, out: torch.Tensor, ctx=None) -> torch.Tensor:
         return self._run(x, out, ops.STORE, ctx)
 
-    def accumulate(self, x: torch.Tensor, out: torch.Tensor, ctx=None) -> torch.Tensor:
-        return self._run(x, out, ops.ACCUMULATE, ctx)
+    def accumulate(self, x: torch.Tensor, out: torch.Tensor, ctx=None, then_norm=None) -> bool:
+        """out += x @ W^T. ``then_norm`` (a :class:`FollowingNorm`): if this product runs on the
+        tensor cores for a few rows and the norm is an RMS norm over whole rows, the product's
+        last CTA also writes the norm; returns whether it did."""
+        if (then_norm is not None and self._fast() and x.dtype == torch.bfloat16
+                and x.shape[0] <= ops.FUSED_NORM_MAX_TOKENS and getattr(then_norm.norm, "fusable_rms", False)
+                and then_norm.out.dtype == torch.bfloat16 and out.shape[1] == self.out_features
+                and self.out_features % 128 == 0):
+            if ctx is not None:
+                ctx.take_cleared()
+            norm = then_norm.norm
+            ops.gemm(x, self.weight, out, ops.ACCUMULATE,
+                     norm_after=(norm.weight, norm.spec.eps, then_norm.out, then_norm.clear))
+            return True
+        self._run(x, out, ops.ACCUMULATE, ctx)
+        return False
 
     def swiglu(self, x: torch.Tensor, out: torch.Tensor, ctx=None) -> torch.Tensor:
         return self._run(x, out, ops.SWIGLU, ctx)

@@ -15,6 +15,8 @@ from .specs import GAIN, NormSpec, TensorSpec
 
 
 class RMSNorm(Part):
+    fusable_rms = True      # a product that adds into the residual stream may write this norm on the way
+
     def __init__(self, spec: NormSpec):
         self.spec = spec
         self.weight: Optional[torch.Tensor] = None

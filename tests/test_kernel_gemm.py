@@ -113,3 +113,28 @@ def test_refusals():
         ops.gemm(a, w, torch.empty(4, 9, device="cuda:0"))
     with pytest.raises(KernelError):
         ops.gemm_plain(a.cpu(), w, torch.empty(4, 8, device="cuda:0"))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 2048), (4, 2048, 8192), (2, 640, 328), (4, 128, 200), (3, 3072, 512)])
+def test_accumulate_with_the_following_norm(M, N, K):
+    """The product adds into the residual rows; its last CTA then writes their RMS norm and
+    clears a buffer. Twice in a row: the CTA counter must be back at zero."""
+    from llmplayer_b200.kernels import ops
+    torch.manual_seed(N + K)
+    dev = "cuda:0"
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev) / K ** 0.5).to(torch.bfloat16)
+    gain = (1 + 0.1 * torch.randn(N, device=dev))
+    for _ in range(2):
+        out0 = torch.randn(M, N, device=dev)
+        out = out0.clone()
+        normed = torch.full((M, N), 9.0, device=dev, dtype=torch.bfloat16)
+        junk = torch.full((3000,), 4.0, device=dev)
+        ops.gemm(a, w, out, ops.ACCUMULATE, norm_after=(gain, 1e-5, normed, junk))
+        torch.cuda.synchronize()
+        ops.check_kernel_status()
+        ref = reference(a, w, ops.ACCUMULATE, out0)
+        assert rel_err(out, ref) < 1e-5
+        want = ref * torch.rsqrt((ref * ref).mean(dim=1, keepdim=True) + 1e-5) * gain.double()
+        assert rel_err(normed, want) < 8e-3                  # one bfloat16 rounding
+        assert float(junk.abs().sum()) == 0.0
