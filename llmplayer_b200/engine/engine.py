@@ -44,6 +44,7 @@ class Engine:
         self.last_step_h2d_bytes = 0
         self.use_graphs = True
         self._graphs = {}
+        self._last_ctx: Optional[StepContext] = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -173,7 +174,38 @@ class Engine:
         ``entries``: ``(slot, new token ids)`` per sequence; ``want[i]``: the places
         among sequence i's new tokens whose logits are returned, in order.
         """
-        return self.run(self.plan(entries, want))
+        ctx = self._continue(entries, want)
+        if ctx is None:
+            ctx = self.plan(entries, want)
+        self._last_ctx = ctx if ctx.all_single else None
+        return self.run(ctx)
+
+    def _continue(self, entries, want) -> Optional[StepContext]:
+        """The previous step's description moved on by one token, when this step brings one token
+        for each of the same sequences and wants the same rows (the usual decode step); else None."""
+        last = self._last_ctx
+        if last is None or len(entries) != last.num_sequences:
+            return None
+        tokens: List[int] = []
+        for (slot, toks), places, seq in zip(entries, want, last.sequences):
+            if slot != seq.slot or len(toks) != 1 or list(places) != [0]:
+                return None
+            tok = int(toks[0])
+            if not 0 <= tok < self.vocab_size:
+                return None                     # the full check in plan() raises the error
+            tokens.append(tok)
+        if last.wanted_rows != list(range(last.num_sequences)):
+            return None
+        slots = [s.slot for s in last.sequences]
+        for s in slots:
+            if not self.cache.slots.is_held(s) or self.cache.length(s) + 1 > self.context_length:
+                return None
+        if any(self.cache.length(s.slot) != s.first_position + 1 for s in last.sequences):
+            return None                         # something else ran on these slots meanwhile
+        self.cache.reserve(slots, [1] * len(slots))
+        if not last.advance(tokens, self.cache.page_tables(slots)):
+            return None
+        return last
 
     # ------------------------------------------------------------------ generation
     def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers) -> List[int]:

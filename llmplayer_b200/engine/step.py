@@ -25,13 +25,40 @@ class SequenceStep:
     first_position: int   # position of its first new token = its length before the step
 
 
+class _NoEvent:
+    """Stands in for a CUDA event where copies are synchronous (no GPU)."""
+
+    def record(self) -> None:
+        pass
+
+    def synchronize(self) -> None:
+        pass
+
+
 class Workspace:
     """Named scratch buffers that persist across steps and only ever grow."""
 
     def __init__(self, device):
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
+        self._pinned: Dict[str, tuple] = {}
         self.version = 0      # bumped whenever a buffer moved (captured graphs are stale then)
+
+    def pinned(self, name: str, count: int):
+        """A page-locked int32 host buffer of at least ``count`` entries and the event that marks
+        the end of the last copy out of it; both persist, and the buffer is waited for before reuse."""
+        entry = self._pinned.get(name)
+        if entry is None or entry[0].numel() < count:
+            host = torch.zeros(max(count, 256), dtype=torch.int32)
+            event = None
+            if torch.cuda.is_available() and torch.device(self.device).type == "cuda":
+                host = host.pin_memory()
+                event = torch.cuda.Event()
+            entry = (host, event if event is not None else _NoEvent())
+            self._pinned[name] = entry
+        else:
+            entry[1].synchronize()
+        return entry
 
     def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         count = 1
@@ -53,10 +80,13 @@ def _round_up(n: int, m: int) -> int:
 class StepContext:
     """Device-side description of a step plus the host-side list of its sequences.
 
-    Device tensors (all int32): ``tokens[T]``, ``positions[T]``, ``seq_ids[T]``
-    (index of the token's sequence in this step), ``slots[B]``, ``q_start[B+1]``,
-    ``kv_len[B]`` (length after the step), ``page_tables[g][B, P_g]`` per cache group,
-    ``rows[W]`` (tokens whose logits are wanted).
+    Device tensors (all int32, views of one buffer that is filled by one copy): ``tokens[T]``,
+    ``positions[T]``, ``kv_len[B]`` (length after the step), ``seq_ids[T]`` (index of the token's
+    sequence in this step), ``slots[B]``, ``q_start[B+1]``, ``page_tables[g][B, P_g]`` per cache
+    group, ``rows[W]`` (tokens whose logits are wanted).
+
+    A context of one token per sequence can be moved on to the next step of the same sequences
+    (:meth:`advance`): only the tokens, positions and lengths are copied again.
     """
 
     def __init__(self, workspace: Workspace, sequences: List[SequenceStep], tokens: Sequence[int],
@@ -70,24 +100,31 @@ class StepContext:
         self.all_single = all(s.num_new == 1 for s in sequences)
         self.max_kv_len = max((s.first_position + s.num_new for s in sequences), default=0)
         self.num_wanted = W = len(wanted_rows)
+        self.wanted_rows = list(wanted_rows)
 
         widths = [max([min_table_width] + [len(t) for t in group]) for group in page_tables]
-        sizes = [T, T, T, B, B + 1, B] + [B * w for w in widths] + [W]
+        self._widths = widths
+        self._table_lengths = [[len(t) for t in group] for group in page_tables]
+        # the arrays that change from one decode step to the next come first and lie together
+        sizes = [T, T, B, T, B, B + 1] + [B * w for w in widths] + [W]
         offsets, total = [], 0
         for n in sizes:
             offsets.append(total)
             total += _round_up(max(n, 1), 4)          # keep every array 16-byte aligned
-        host = torch.zeros(total, dtype=torch.int32)
-        view = host.numpy()
-        o = offsets
+        self._offsets = o = offsets
+        self._moving = offsets[3]                      # tokens, positions, kv_len: the first `_moving` ints
+        host, self._copied = workspace.pinned(meta_name, total)
+        self._host = host
+        view = self._view = host.numpy()
+        view[:total] = 0
         view[o[0]:o[0] + T] = tokens
         for i, s in enumerate(sequences):
             view[o[1] + s.start:o[1] + s.start + s.num_new] = range(s.first_position, s.first_position + s.num_new)
-            view[o[2] + s.start:o[2] + s.start + s.num_new] = i
-            view[o[3] + i] = s.slot
-            view[o[4] + i] = s.start
-            view[o[5] + i] = s.first_position + s.num_new
-        view[o[4] + B] = T
+            view[o[2] + i] = s.first_position + s.num_new
+            view[o[3] + s.start:o[3] + s.start + s.num_new] = i
+            view[o[4] + i] = s.slot
+            view[o[5] + i] = s.start
+        view[o[5] + B] = T
         for g, group in enumerate(page_tables):
             base, w = o[6 + g], widths[g]
             for i, table in enumerate(group):
@@ -95,17 +132,56 @@ class StepContext:
         view[o[-1]:o[-1] + W] = wanted_rows
 
         meta = workspace.get(meta_name, (total,), torch.int32)
-        self.h2d_bytes = total * 4
-        meta.copy_(host.pin_memory() if torch.cuda.is_available() else host, non_blocking=False)
+        self._total = total
         self.meta = meta
+        self._upload(total)
         self.tokens = meta[o[0]:o[0] + T]
         self.positions = meta[o[1]:o[1] + T]
-        self.seq_ids = meta[o[2]:o[2] + T]
-        self.slots = meta[o[3]:o[3] + B]
-        self.q_start = meta[o[4]:o[4] + B + 1]
-        self.kv_len = meta[o[5]:o[5] + B]
+        self.kv_len = meta[o[2]:o[2] + B]
+        self.seq_ids = meta[o[3]:o[3] + T]
+        self.slots = meta[o[4]:o[4] + B]
+        self.q_start = meta[o[5]:o[5] + B + 1]
         self.page_tables = [meta[o[6 + g]:o[6 + g] + B * w].view(B, w) for g, w in enumerate(widths)]
         self.rows = meta[o[-1]:o[-1] + W]
+
+    def _upload(self, count: int) -> None:
+        """Copy the first ``count`` integers of the pinned host image to the device, asynchronously;
+        the event lets the next writer of the host image wait until the copy has read it."""
+        self.h2d_bytes = count * 4
+        if self._host.is_pinned():
+            self.meta[:count].copy_(self._host[:count], non_blocking=True)
+            self._copied.record()
+        else:
+            self.meta[:count].copy_(self._host[:count])
+
+    def advance(self, tokens: Sequence[int], page_tables: List[List[List[int]]]) -> bool:
+        """Move a context of one token per sequence on by one step: new tokens, positions and
+        lengths one further, page tables as they are now. False if the tables outgrew the
+        context's shape (the caller then builds a new context)."""
+        o, B = self._offsets, self.num_sequences
+        grown = False
+        for g, group in enumerate(page_tables):
+            for i, table in enumerate(group):
+                if len(table) > self._widths[g]:
+                    return False
+                if len(table) != self._table_lengths[g][i]:
+                    grown = True
+        self._copied.synchronize()                     # the previous copy has read the host image
+        view = self._view
+        view[o[0]:o[0] + B] = tokens
+        view[o[1]:o[1] + B] += 1
+        view[o[2]:o[2] + B] += 1
+        if grown:
+            for g, group in enumerate(page_tables):
+                base, w = o[6 + g], self._widths[g]
+                for i, table in enumerate(group):
+                    view[base + i * w:base + i * w + len(table)] = table
+                    self._table_lengths[g][i] = len(table)
+        self.sequences = [SequenceStep(s.slot, s.start, 1, s.first_position + 1) for s in self.sequences]
+        self.max_kv_len += 1
+        self._cleared = False
+        self._upload(self._total if grown else self._moving)
+        return True
 
     def buffer(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)
