@@ -226,7 +226,8 @@ def main() -> int:
     engine.generate(e2e_prompts, SamplerConfig.greedy(), max_tokens=args.steps, stop_token_ids=())
     st = engine.last_generation_stats
     e2e = {"value": st.decode_tokens_per_second, "unit": "tokens/s",
-           "h2d_bytes_per_step": engine.last_step_h2d_bytes, "d2h_bytes_per_step": 8 * args.batch}
+           "h2d_bytes_per_step": engine.last_step_h2d_bytes + engine._sampler.last_h2d_bytes,
+           "d2h_bytes_per_step": engine._sampler.last_d2h_bytes}
 
     result = {
         "metric": "decode tok/s (Llama-3.2-1B shape, bf16, batch %d)" % args.batch,

@@ -95,6 +95,7 @@ class BatchSampler:
         self._constant = {}          # greedy batches without logit edits: parameters stay on the device
         self._dummy = None
         self.last_h2d_bytes = 0
+        self.last_d2h_bytes = 0
 
     def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers: Sequence[SequenceSampler]) -> List[int]:
         B = len(samplers)
@@ -112,6 +113,7 @@ class BatchSampler:
             # first-maximum argmax of every row, spread over many blocks
             ops.argmax(logits, self._work.view(-1), out_tok)
             self.last_h2d_bytes = 0
+            self.last_d2h_bytes = 4 * B
             chosen = out_tok.cpu().tolist()
             for s, tok in zip(samplers, chosen):
                 s.accept(tok, 1.0)
@@ -152,6 +154,7 @@ class BatchSampler:
                 self._constant[key] = params_dev
         ops.sample(logits, self._work[:B], params_dev, edit_tok, edit_sub, edit_fac, out_tok, out_prob)
         host = self._out[:2 * B].cpu()                       # one copy back: tokens, then probabilities
+        self.last_d2h_bytes = 8 * B
         chosen = host[:B].tolist()
         probs = host[B:].view(torch.float32).tolist()
         for s, tok, pr in zip(samplers, chosen, probs):
