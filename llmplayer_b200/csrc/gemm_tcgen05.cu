@@ -177,6 +177,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     uint64_t* empty = full + T::STAGES;
     uint64_t* acc_ready = empty + T::STAGES;
     uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    volatile uint32_t* failed = tmem_slot + 1;     // set by a role whose wait ran out; read by the epilogue
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int feat0 = blockIdx.x * BLOCK_FEAT;          // first weight row of this CTA
@@ -188,6 +189,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     lp_grid_release();          // the next kernel on the stream may set itself up behind this one
 
     if (threadIdx.x == 0) {
+        *failed = 0;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
         for (int s = 0; s < T::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -224,7 +228,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int i = early; i < nkb && ok; ++i) {
                 const int s = i % T::STAGES;
                 const uint32_t phase = (i / T::STAGES) & 1;
-                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 1); ok = false; break; }
+                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
                 uint8_t* stage = smem + s * T::STAGE_BYTES;
                 mbar_expect_tx(&full[s], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BLOCK_K;
@@ -248,7 +252,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % T::STAGES;
                 const uint32_t phase = (i / T::STAGES) & 1;
-                if (!mbar_wait(&full[s], phase)) { atomicExch(status, 2); ok = false; break; }
+                if (!mbar_wait(&full[s], phase)) { atomicExch(status, 2); *failed = 1; ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t w_addr = smem_u32(smem + s * T::STAGE_BYTES);
                 const uint32_t x_addr = w_addr + T::W_TILES * T::W_BYTES;
@@ -274,7 +278,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const bool ready = mbar_wait(acc_ready, 0);
         if (!ready && lane == 0) atomicExch(status, 3);
         tcgen05_fence_after();
-        const bool go = __all_sync(0xffffffffu, ready && *((volatile int*)status) == 0);
+        const bool go = __all_sync(0xffffffffu, ready && *failed == 0);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         constexpr int CHUNK = BLOCK_TOK >= 32 ? 32 : 16;
         if (MODE != LP_GEMM_SWIGLU) {
