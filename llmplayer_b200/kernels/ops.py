@@ -43,6 +43,10 @@ _SIGNATURES = {
         "lp_attention_decode_fused": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
                                       _I, _I, _P],
     },
+    "attention_tcgen05": {
+        "lp_attention_prefill_tc": [_P, _P, _P, ctypes.c_longlong, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I,
+                                    _P, _P],
+    },
     "sampling": {
         "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
         "lp_sample_params_size": [],
@@ -385,6 +389,9 @@ def _check_attention(q, out, pages, page_table, H, G, hd, what):
         raise KernelError(f"{what}: pages {tuple(pages.shape)} do not fit {G} key heads of {hd}")
 
 
+tcgen05_attention = True      # tests switch it off to reach the mma.sync kernel at every size
+
+
 def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
                       q_start: torch.Tensor, kv_len: torch.Tensor, max_new: int, *, num_heads: int,
                       num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> torch.Tensor:
@@ -396,6 +403,15 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
     B = kv_len.numel()
     if q_start.numel() != B + 1 or page_table.shape[0] != B:
         raise KernelError(f"attention_prefill: {B} sequences, {q_start.numel()} offsets, table {tuple(page_table.shape)}")
+    if head_dim == 64 and max_new > 64 and tcgen05_attention:
+        # long runs of new tokens with heads of 64: scores and P V on the tcgen05 tensor cores
+        lib = library("attention_tcgen05")
+        _check(lib, lib.lp_attention_prefill_tc(
+            q.data_ptr(), out.data_ptr(), pages.data_ptr(), pages.shape[0], page_table.data_ptr(),
+            page_table.shape[1], q_start.data_ptr(), kv_len.data_ptr(), B, q.shape[0], int(max_new), num_heads,
+            num_kv_heads, head_dim, pages.shape[3], float(scale), int(window) if window else 0,
+            kernel_status().data_ptr(), _stream()))
+        return out
     lib = library("attention_mma")
     _check(lib, lib.lp_attention_prefill(
         q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1],

@@ -128,8 +128,21 @@ def test_plain_attention(H, G, hd, window):
 @pytest.mark.parametrize("H,G,hd", GEOMETRIES)
 @pytest.mark.parametrize("window", [None, 70])
 def test_tensor_core_prefill(H, G, hd, window):
+    """Heads of 64 with long runs of new tokens take the tcgen05 kernel, everything else mma.sync."""
     err = run_case("prefill", [1, 64, 65, 300, 129], [1, 64, 3, 150, 129], H, G, hd, window, torch.bfloat16)
     assert err < 2e-2, err
+
+
+@pytest.mark.parametrize("H,G", [(32, 8), (20, 1), (3, 3)])
+@pytest.mark.parametrize("window", [None, 70, 200])
+@pytest.mark.parametrize("tcgen05", [True, False])
+def test_both_prefill_kernels_at_head_size_64(H, G, window, tcgen05, monkeypatch):
+    from llmplayer_b200.kernels import ops
+    monkeypatch.setattr(ops, "tcgen05_attention", tcgen05)
+    lengths, new = [700, 128, 129, 391, 65], [700, 128, 100, 130, 65]        # whole prompts and continued ones
+    err = run_case("prefill", lengths, new, H, G, 64, window, torch.bfloat16, seed=7)
+    assert err < 2e-2, err
+    run_case("prefill", [900, 333], [200, 70], H, G, 64, window, torch.bfloat16, seed=3, crafted=True)
 
 
 @pytest.mark.parametrize("H,G,hd", GEOMETRIES)
