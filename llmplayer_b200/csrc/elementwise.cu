@@ -170,23 +170,27 @@ rope_cache_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
     }
     const int head_begin = blockIdx.y * heads_per_block;
     const int head_end = min(heads, head_begin + heads_per_block);
-    for (int idx = head_begin * hd + threadIdx.x; idx < head_end * hd; idx += blockDim.x) {
-        const int head = idx / hd, e = idx - head * hd;
+    // a warp takes whole heads, its lanes the features: no division in the loop
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    for (int head = head_begin + warp; head < head_end; head += nwarps) {
         const bool is_q = head < H, is_v = head >= H + G;
-        float val = src[idx];
-        if (!is_v && e < rd) {
-            int pair, partner;
-            bool first;
-            if (interleaved) { pair = e >> 1; first = (e & 1) == 0; partner = e ^ 1; }
-            else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
-            const float other = src[head * hd + partner];
-            val = first ? val * cs[pair] - other * sn[pair] : other * sn[pair] + val * cs[pair];
-        }
-        if (is_q) {
-            q_out[((long long)t * H + head) * hd + e] = lp_from_float<TQ>(val);
-        } else {
-            const int g = is_v ? head - H - G : head - H;
-            pages[page_base + ((long long)(is_v ? G : 0) + g) * page_size * hd + e] = lp_from_float<TKV>(val);
+        const float* hsrc = src + (long long)head * hd;
+        for (int e = lane; e < hd; e += 32) {
+            float val = hsrc[e];
+            if (!is_v && e < rd) {
+                int pair, partner;
+                bool first;
+                if (interleaved) { pair = e >> 1; first = (e & 1) == 0; partner = e ^ 1; }
+                else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
+                const float other = hsrc[partner];
+                val = first ? val * cs[pair] - other * sn[pair] : other * sn[pair] + val * cs[pair];
+            }
+            if (is_q) {
+                q_out[((long long)t * H + head) * hd + e] = lp_from_float<TQ>(val);
+            } else {
+                const int g = is_v ? head - H - G : head - H;
+                pages[page_base + ((long long)(is_v ? G : 0) + g) * page_size * hd + e] = lp_from_float<TKV>(val);
+            }
         }
     }
 }
