@@ -59,3 +59,58 @@ def test_steps_are_checked(tmp_path):
         eng.step([(other, [1])], [[0]])
     eng.release(slot)
     assert eng.step([(other, [1])], [[0]]).shape == (1, 256)
+
+
+def test_full_width_layers_bfloat16_against_float32(tmp_path):
+    """Two layers at the Llama-3.2-1B widths (2048 wide, 32/8 heads of 64, 8192, vocabulary 128256, llama3
+    rope scaling): the bfloat16 engine (tensor-core products and attention at their real sizes, prompt and
+    decode kernels) against the float32 engine, whole and then token by token."""
+    from llmplayer_b200 import Engine
+    from llmplayer_b200.config import config_from_dict
+    from llmplayer_b200.weights import write_random_model
+    raw = {
+        "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 2048, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256,
+        "rope_theta": 500000.0, "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                                                  "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+        "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072,
+    }
+    model_dir = str(tmp_path / "wide")
+    write_random_model(config_from_dict(raw), 2, model_dir, dtype="bfloat16")
+    tokens = random_tokens(333, 128256, seed=4)
+    want = [0, 100, 199, 200, 332]
+    logits = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.load(model_dir, dtype=dtype, max_tokens=512)
+        slot = eng.acquire()
+        whole = eng.step([(slot, tokens)], [want]).cpu().clone()
+        eng.release(slot)
+        slot = eng.acquire()
+        eng.step([(slot, tokens[:200])], [[]])
+        tail = [eng.step([(slot, [t])], [[0]]).cpu().clone() for t in tokens[200:]]
+        eng.release(slot)
+        logits[dtype] = (whole, torch.cat([tail[0], tail[-1]]))
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+    ref_whole, ref_tail = logits["float32"]
+    assert torch.equal(ref_whole[3:], ref_tail)                       # float32: cutting into steps changes nothing
+    assert_close(logits["bfloat16"][0], ref_whole, "bfloat16", "1B widths, whole")
+    assert_close(logits["bfloat16"][1], ref_tail, "bfloat16", "1B widths, decoded")
+
+
+@pytest.mark.parametrize("stored,dtype", [("float32", "bfloat16"), ("bfloat16", "float32")])
+def test_stored_and_compute_dtypes_may_differ(tmp_path, stored, dtype):
+    """A folder stored in 32 bits run in bfloat16 keeps its float32 matrices (plain products with
+    bfloat16 activations); a bfloat16 folder run in float32 is widened exactly."""
+    from llmplayer_b200 import Engine
+    model_dir = make_model(tmp_path, "B", dtype=stored)
+    tokens = random_tokens(70, TINY["B"][0]["vocab_size"], seed=2)
+    eng = Engine.load(model_dir, dtype=dtype, max_tokens=128)
+    if dtype == "bfloat16":
+        assert eng.model.blocks[0].mixer.qkv.weight.dtype == torch.float32        # stored in 32 bits: stays so
+    slot = eng.acquire()
+    got = [eng.step([(slot, tokens[:40])], [list(range(40))]).cpu().clone()]
+    got += [eng.step([(slot, [t])], [[0]]).cpu().clone() for t in tokens[40:]]
+    eng.release(slot)
+    assert_close(torch.cat(got), plain_logits(model_dir, tokens), dtype, f"{stored} folder in {dtype}")
