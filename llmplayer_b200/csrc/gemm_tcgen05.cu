@@ -324,6 +324,197 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     }
 }
 
+// ------------------------------------------------------------------ persistent form for prompts
+// One CTA per SM walks over output tiles (tile = blockIdx.x, + gridDim.x, ...). Tensor memory holds two
+// accumulators: while the epilogue warps read tile i out of one, the MMA thread fills the other with
+// tile i + 1, and the loader keeps the ring of stages full across tile boundaries. No split of K, no
+// norm fusion: this form serves steps with hundreds of tokens.
+template <int BLOCK_TOK, int MODE>
+struct PersistentTile {
+    static constexpr int W_TILES = MODE == LP_GEMM_SWIGLU_WIDE ? 2 : 1;
+    static constexpr int W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
+    static constexpr int X_BYTES = BLOCK_TOK * BLOCK_K * 2;
+    static constexpr int STAGE_BYTES = W_TILES * W_BYTES + X_BYTES;
+    static constexpr int STAGES = (196 * 1024) / STAGE_BYTES;
+    static constexpr int ACC_COLS = BLOCK_TOK * W_TILES;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;                // 512 for both uses below
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(TMEM_COLS == 512 || TMEM_COLS == 256, "two accumulators must fit tensor memory");
+};
+
+template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                       void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int feat_tiles,
+                       int num_tiles, int* __restrict__ status) {
+    using T = PersistentTile<BLOCK_TOK, MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + T::STAGES * T::STAGE_BYTES);
+    uint64_t* empty = full + T::STAGES;
+    uint64_t* acc_full = empty + T::STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;           // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile uint32_t* failed = tmem_slot + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    lp_grid_release();
+    if (threadIdx.x == 0) {
+        *failed = 0;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        for (int s = 0; s < T::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int k = 0; k < 2; ++k) { mbar_init(&acc_full[k], 1); mbar_init(&acc_empty[k], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)T::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ loader: one ring across all tiles
+        if (lane == 0) {
+            lp_grid_wait();
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int ft = tile % feat_tiles, tt = tile / feat_tiles;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % T::STAGES;
+                    if (!mbar_wait(&empty[s], ((it / T::STAGES) & 1) ^ 1)) { atomicExch(status, 21); *failed = 1; ok = false; break; }
+                    uint8_t* stage = smem + s * T::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], T::STAGE_BYTES);
+                    load_weights<MODE>(stage, &map_w, kb * BLOCK_K, ft, &full[s]);
+                    tma_load_2d(stage + T::W_TILES * T::W_BYTES, &map_x, kb * BLOCK_K, tt * BLOCK_TOK, &full[s]);
+                }
+            }
+            if (!ok) {
+                for (int i = max(0, it - T::STAGES); i < it; ++i) mbar_wait(&full[i % T::STAGES], (i / T::STAGES) & 1);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer: alternating accumulators
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_TOK >> 3) << 17) |
+                                       ((uint32_t)(BLOCK_FEAT >> 4) << 24);
+            int it = 0, j = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++j) {
+                const int ab = j & 1;
+                if (!mbar_wait(&acc_empty[ab], ((j >> 1) & 1) ^ 1)) { atomicExch(status, 22); *failed = 1; ok = false; break; }
+                tcgen05_fence_after();
+                const uint32_t acc = tmem_base + ab * T::ACC_COLS;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % T::STAGES;
+                    if (!mbar_wait(&full[s], (it / T::STAGES) & 1)) { atomicExch(status, 23); *failed = 1; ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t w_addr = smem_u32(smem + s * T::STAGE_BYTES);
+                    const uint32_t x_addr = w_addr + T::W_TILES * T::W_BYTES;
+                    const uint64_t dw = smem_desc(w_addr), dx = smem_desc(x_addr);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t step = (uint64_t)((k * UMMA_K * 2) >> 4);
+                        tcgen05_mma(acc, dw + step, dx + step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        if (MODE == LP_GEMM_SWIGLU_WIDE) {
+                            const uint64_t du = smem_desc(w_addr + T::W_BYTES);
+                            tcgen05_mma(acc + BLOCK_TOK, du + step, dx + step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        }
+                    }
+                    tcgen05_commit(&empty[s]);
+                }
+                tcgen05_commit(&acc_full[ab]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ epilogue: drains one accumulator at a time
+        const int quarter = warp & 3;
+        constexpr int CHUNK = 32;
+        int j = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
+            const int ab = j & 1;
+            const int ft = tile % feat_tiles, tt = tile / feat_tiles;
+            if (ok && !mbar_wait(&acc_full[ab], (j >> 1) & 1)) { if (lane == 0) atomicExch(status, 24); *failed = 1; ok = false; }
+            tcgen05_fence_after();
+            const bool go = __all_sync(0xffffffffu, ok && *failed == 0);
+            if (go) {
+                const uint32_t lane_addr = tmem_base + ab * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+                const int f = ft * BLOCK_FEAT + quarter * 32 + lane;
+                const int tok0 = tt * BLOCK_TOK;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
+                    uint32_t g[CHUNK], u[MODE == LP_GEMM_SWIGLU_WIDE ? CHUNK : 1];
+                    tmem_ld32(lane_addr + c0, g);
+                    if (MODE == LP_GEMM_SWIGLU_WIDE) tmem_ld32(lane_addr + BLOCK_TOK + c0, u);
+                    tmem_ld_wait();
+                    if (f < features) {
+#pragma unroll
+                        for (int jj = 0; jj < CHUNK; ++jj) {
+                            const int t = tok0 + c0 + jj;
+                            if (t >= tokens) break;
+                            float v = __uint_as_float(g[jj]);
+                            if (MODE == LP_GEMM_SWIGLU_WIDE) v = __fdividef(v, 1.0f + __expf(-v)) * __uint_as_float(u[jj]);
+                            const size_t at = (size_t)t * ldc + f;
+                            if (ATOMIC) atomicAdd((float*)out + at, v);
+                            else if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                            else ((float*)out)[at] = v;
+                        }
+                    }
+                }
+            }
+            // hand the accumulator back to the MMA thread
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[ab])) : "memory");
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS));
+    }
+}
+
+template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc,
+                      int k_blocks, int* status, cudaStream_t stream) {
+    using T = PersistentTile<BLOCK_TOK, MODE>;
+    auto kernel = gemm_persistent_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
+        if (e != cudaSuccess) LP_REFUSE("gemm: cannot reserve %d bytes of shared memory: %s", T::SMEM_BYTES,
+                                        cudaGetErrorString(e));
+        configured = true;
+    }
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const int feat_tiles = (features + BLOCK_FEAT - 1) / BLOCK_FEAT;
+    const int num_tiles = feat_tiles * ((tokens + BLOCK_TOK - 1) / BLOCK_TOK);
+    const int grid = num_tiles < sms ? num_tiles : sms;
+    cudaError_t err = lp_launch(kernel, dim3(grid), THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
+                                k_blocks, feat_tiles, num_tiles, status);
+    if (err != cudaSuccess) {
+        snprintf(lp_error_text, sizeof(lp_error_text), "gemm_persistent: %s", cudaGetErrorString(err));
+        return (int)err;
+    }
+    return lp_check_launch("gemm_persistent");
+}
+
 template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
            int splits, int up_offset, int* status, const NormAfter& norm, cudaStream_t stream) {
@@ -377,6 +568,36 @@ int dispatch(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const 
 // out: [tokens, ldc] float32 or bfloat16. mode: STORE / ACCUMULATE / SWIGLU. block_tok: 16..256 (a power of two).
 // splits > 1 or ACCUMULATE adds into a float32 `out` with atomics (a STORE with splits needs `out` zeroed before).
 // status: one int in device memory, set non-zero if a wait inside the kernel ran out.
+// The persistent form (see above) for steps with many tokens: STORE (float32 / bfloat16), ACCUMULATE
+// (float32, atomics) with 256-token tiles, SWIGLU (interleaved gate/up rows) with 128-token tiles.
+extern "C" int lp_gemm_persistent(const void* X, const void* W, void* out, int out_dtype, int tokens, int features,
+                                  int K, int ldx, int ldw, int ldc, int mode, int* status, cudaStream_t stream) {
+    if (tokens <= 0 || features <= 0) return 0;
+    if (K <= 0 || K % 8) LP_REFUSE("gemm: inner size %d must be a positive multiple of 8 for the tensor-core path", K);
+    if (ldx % 8 || ldw % 8) LP_REFUSE("gemm: row strides %d / %d must be multiples of 8 elements", ldx, ldw);
+    if (((uintptr_t)X | (uintptr_t)W) & 15) LP_REFUSE("gemm: operands must be 16-byte aligned");
+    if (mode < 0 || mode > 2) LP_REFUSE("gemm: mode %d", mode);
+    if (out_dtype != LP_F32 && out_dtype != LP_BF16) LP_REFUSE("gemm: output dtype code %d", out_dtype);
+    if (mode == LP_GEMM_ACCUMULATE && out_dtype != LP_F32) LP_REFUSE("gemm: sums across CTAs need a float32 output");
+    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+    const bool gated = mode == LP_GEMM_SWIGLU;
+    const long long w_rows = gated ? 128LL * ((features + 63) / 64) : features;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, w_rows, K, ldw, gated ? 64 : BLOCK_FEAT);
+    if (rc) return rc;
+    rc = make_map(&mx, X, tokens, K, ldx, gated ? 128 : 256);
+    if (rc) return rc;
+    const bool bf = out_dtype == LP_BF16;
+    if (gated) {
+        if (bf) return launch_persistent<128, LP_GEMM_SWIGLU_WIDE, true, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+        return launch_persistent<128, LP_GEMM_SWIGLU_WIDE, false, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+    }
+    if (mode == LP_GEMM_ACCUMULATE)
+        return launch_persistent<256, LP_GEMM_STORE, false, true>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+    if (bf) return launch_persistent<256, LP_GEMM_STORE, true, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+    return launch_persistent<256, LP_GEMM_STORE, false, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+}
+
 // norm_weight (optional, ACCUMULATE only, ldc == features): after the sums are complete, the last CTA writes
 // the RMS norm of every output row to norm_out (bf16 [tokens, features]) and zeroes norm_clear; norm_counter
 // is one int32, zero before the call.

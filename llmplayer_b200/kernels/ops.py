@@ -36,6 +36,7 @@ _SIGNATURES = {
     "gemm_tcgen05": {
         "lp_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P,
                             ctypes.c_longlong, _P, _P],
+        "lp_gemm_persistent": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     },
     "attention_mma": {
         "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -290,7 +291,19 @@ def gemm_plan(tokens: int, features: int, k: int, mode: int):
 
 
 FUSED_NORM_MAX_TOKENS = 4
+PERSISTENT_MIN_TOKENS = 512
 _gemm_counter = None
+
+
+def _persistent_pays(tokens: int, features: int, k: int, mode: int) -> bool:
+    """Whether the persistent form (one CTA per SM walking 128 x 256 tiles, 128 x 128 x 2 when gated)
+    fills the SMs at least as well as separate CTAs of 128 x 128 tiles, two to an SM."""
+    feat_tiles = -(-features // 128)
+    persistent_tiles = feat_tiles * -(-tokens // (128 if mode == SWIGLU else 256))
+    separate_ctas = feat_tiles * -(-tokens // 128)
+    fill_p = persistent_tiles / (-(-persistent_tiles // NUM_SMS) * NUM_SMS)
+    fill_s = separate_ctas / (-(-separate_ctas // (2 * NUM_SMS)) * 2 * NUM_SMS)
+    return fill_p > fill_s + 0.02 or (k >= 4096 and fill_p >= fill_s)
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, block_tok: int = 0,
@@ -321,6 +334,14 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
         return out
     lib = library("gemm_tcgen05")
     status = kernel_status()
+    if (M >= PERSISTENT_MIN_TOKENS and not block_tok and not splits and norm_after is None
+            and _persistent_pays(M, N, K, mode)):
+        # many tokens: one CTA per SM walks over the tiles, epilogue and MMAs of neighbouring tiles overlap
+        if mode == ACCUMULATE and out.dtype != torch.float32:
+            raise KernelError("gemm: accumulation needs a float32 output")
+        _check(lib, lib.lp_gemm_persistent(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
+                                           K, K, N, mode, status.data_ptr(), _stream()))
+        return out
     tile, n_splits = gemm_plan(M, N, K, mode)
     tile = block_tok or tile
     n_splits = 1 if mode == SWIGLU else (splits or n_splits)

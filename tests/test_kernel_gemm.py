@@ -21,7 +21,7 @@ def rel_err(got, ref):
 
 
 SHAPES = [(1, 64, 64), (5, 100, 72), (8, 3072, 2048), (17, 130, 200), (64, 256, 4096), (70, 264, 136),
-          (300, 520, 328), (1, 128256, 64), (513, 640, 1024)]
+          (300, 520, 328), (1, 128256, 64), (513, 640, 1024), (2048, 392, 264), (777, 3000, 136)]
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
