@@ -1,0 +1,392 @@
+// The decode-step attention unit and the mma.sync / cp.async helpers it shares with the prompt
+// kernels: one (sequence, key/value head, share of the pages) handled by 128 threads. Used by the
+// stand-alone decode kernels and by the persistent step program.
+#pragma once
+
+#include "common.cuh"
+
+namespace {
+
+#ifndef LP_SMEM_U32_DEFINED
+#define LP_SMEM_U32_DEFINED
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+#endif
+constexpr int PAGE = 64;
+constexpr float NEG_BIG = -1.0e30f;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// exp2 by the hardware approximation (relative error about 2^-22, far below bfloat16's rounding)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Position of 16-byte chunk c of row r inside a tile whose rows hold cpr chunks.
+__device__ __forceinline__ int swz(int r, int c, int cpr) {
+    return (cpr & 7) == 0 ? (c ^ (r & 7)) : (c + r) % cpr;
+}
+
+// Copy one page (64 keys and 64 values of one kv head) into a stage: K tile, then V tile.
+__device__ __forceinline__ void load_page(uint8_t* stage, const __nv_bfloat16* pages, int page, int G, int g, int hd,
+                                          int tid, int nthreads) {
+    const int cpr = hd >> 3;
+    const int per_tile = PAGE * cpr;
+    const uint32_t base = smem_u32(stage);
+    const size_t tile_elems = (size_t)PAGE * hd;
+    for (int i = tid; i < 2 * per_tile; i += nthreads) {
+        const int which = i >= per_tile;
+        const int j = which ? i - per_tile : i;
+        const int r = j / cpr, c = j - r * cpr;
+        const __nv_bfloat16* src = pages + (((size_t)page * 2 + which) * G + g) * tile_elems + (size_t)r * hd + c * 8;
+        cp_async16(base + which * (uint32_t)(tile_elems * 2) + r * (hd * 2) + swz(r, c, cpr) * 16, src);
+    }
+}
+
+// S[16 x 16 keys] += Q[16 x hd] K^T for the keys key0..key0+15 of the K tile (two n-tiles of 8 keys).
+template <int KSTEPS>
+__device__ __forceinline__ void scores_16keys(float (*s)[4], const uint32_t (*q)[4], uint32_t k_tile, int key0,
+                                              int hd, int lane) {
+    const int cpr = hd >> 3;
+    const int mat = lane >> 3, row = lane & 7;
+    const int key = key0 + (mat >> 1) * 8 + row;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+        if (kk * 16 < hd) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(k_tile + key * (hd * 2) + swz(key, kk * 2 + (mat & 1), cpr) * 16, b0, b1, b2, b3);
+            mma_bf16(s[0], q[kk], b0, b1);
+            mma_bf16(s[1], q[kk], b2, b3);
+        }
+    }
+}
+
+// O[16 x hd] += P[16 x 16 keys] V for the keys key0..key0+15 of the V tile.
+template <int KSTEPS>
+__device__ __forceinline__ void values_16keys(float (*o)[4], const uint32_t* p, uint32_t v_tile, int key0, int hd,
+                                              int lane) {
+    const int cpr = hd >> 3;
+    const int mat = lane >> 3, row = lane & 7;
+    const int key = key0 + (mat & 1) * 8 + row;
+#pragma unroll
+    for (int dd = 0; dd < KSTEPS; ++dd) {       // 16 output features per step
+        if (dd * 16 < hd) {
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(v_tile + key * (hd * 2) + swz(key, dd * 2 + (mat >> 1), cpr) * 16, b0, b1, b2, b3);
+            mma_bf16(o[dd * 2], p, b0, b1);
+            mma_bf16(o[dd * 2 + 1], p, b2, b3);
+        }
+    }
+}
+
+// ============================================================================ decode
+// grid: (splits, G * head_groups, B); 128 threads; one new token per sequence.
+// Partial results: part_o[b][head][split][hd] (unnormalised), part_ml[b][head][split][2] = (max, sum),
+// both in log2 units of the scaled scores.
+//
+// FUSED: the kernel starts from the float32 fused projection output qkv[b] = [H q heads | G k heads |
+// G v heads] instead of rotated bf16 queries: it rotates the queries of its heads itself, and the CTA
+// whose share holds the new token's position rotates the new key, writes key and value into the cache
+// and into its own shared-memory copy of that page. The last CTA of a (sequence, kv head) to finish
+// merges the shares (a counter per group, zero before the launch and zero again after it).
+struct FusedDecodeArgs {
+    const float* qkv;          // [B, ld]
+    int ld;
+    const float* inv_freq;     // [rd / 2] or null
+    int rd, interleaved;
+    __nv_bfloat16* pages_rw;   // same pages, writable; null: this layer keeps no keys of its own
+    int* counters;             // [B * G * head_groups]
+};
+
+__device__ __forceinline__ float rotated(const float* head, int e, int rd, int interleaved, const float* cs,
+                                         const float* sn) {
+    float val = __ldcg(head + e);
+    if (e < rd) {
+        const int half = rd >> 1;
+        int pair, partner;
+        bool first;
+        if (interleaved) { pair = e >> 1; first = (e & 1) == 0; partner = e ^ 1; }
+        else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
+        const float other = __ldcg(head + partner);
+        val = first ? val * cs[pair] - other * sn[pair] : other * sn[pair] + val * cs[pair];
+    }
+    return val;
+}
+
+// HD_EXACT > 0: the head size is that constant (index arithmetic of the copies and of ldmatrix folds
+// into shifts and masks); 0: any multiple of 16 up to HD_MAX, taken from `hd_arg`.
+// One unit of the decode kernel: share `split` of the pages of sequence `b` for key/value head and head
+// group `by` (= g * head_groups + hg), run by 128 threads numbered `tid`, with `smem` as their scratch.
+// NAMED: the 128 threads are part of a larger CTA and meet at named barrier 1 instead of __syncthreads.
+template <bool NAMED> __device__ __forceinline__ void unit_sync() {
+    if (NAMED) asm volatile("bar.sync 1, 128;" ::: "memory");
+    else __syncthreads();
+}
+
+// STAGES: pages in flight (the scratch holds STAGES key and value tiles).
+// `before_inputs()` is called once the unit has requested its first pages and computed its angles, right
+// before it reads what the step itself produced (the projection output): a caller whose inputs come
+// from an earlier operation of the same kernel waits for that operation there, so that the page
+// copies (the cache holds nothing the step writes, except the new row this unit patches in itself)
+// are already in flight.
+template <int HD_MAX, bool FUSED, int HD_EXACT, bool NAMED, int STAGES, typename Before>
+__device__ __forceinline__ void attention_decode_unit(
+    uint8_t* smem, const int tid, const int split, const int by, const int b, const __nv_bfloat16* __restrict__ q,
+    const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table, int pt_stride,
+    const int* __restrict__ kv_len, float* __restrict__ part_o, float* __restrict__ part_ml,
+    __nv_bfloat16* __restrict__ out, int H, int G, int hd_arg, float scale_log2, int window, int pages_per_split,
+    int num_splits, int head_groups, const FusedDecodeArgs& fused, Before&& before_inputs) {
+    constexpr int KSTEPS = HD_MAX / 16;
+    const int hd = HD_EXACT > 0 ? HD_EXACT : hd_arg;
+    const int g = by / head_groups, hg = by - g * head_groups;
+    const int R = H / G;
+    const int head0 = g * R + hg * 16;
+    const int nrows = min(16, R - hg * 16);
+    const int warp = tid >> 5, lane = tid & 31;
+    const int len = kv_len[b];
+    const int pos = len - 1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int page_lo = max(lo / PAGE, split * pages_per_split);
+    const int page_hi = min(pos / PAGE, (split + 1) * pages_per_split - 1);
+    const int* table = page_table + (size_t)b * pt_stride;
+    const int stage_bytes = 2 * PAGE * hd * 2;
+    const int npages = page_hi - page_lo + 1;      // may be <= 0: this share holds nothing of the sequence
+
+    // the ring is requested first; what follows overlaps with the copies
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < npages) load_page(smem + s * stage_bytes, pages, table[page_lo + s], G, g, hd, tid, 128);
+        cp_async_commit();
+    }
+
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    uint32_t qf[KSTEPS][4];
+    // FUSED: extra shared memory behind the ring: rotated queries [16][hd] bf16, the new key and value, cos, sin
+    __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * stage_bytes);
+    __nv_bfloat16* new_k = q_s + 16 * hd;
+    __nv_bfloat16* new_v = new_k + hd;
+    float* cs = reinterpret_cast<float*>(new_v + hd);
+    float* sn = cs + 128;
+    const bool holds_new = FUSED && fused.pages_rw != nullptr && pos / PAGE >= page_lo && pos / PAGE <= page_hi;
+    if (FUSED) {
+        const int half = fused.rd >> 1;
+        for (int i = tid; i < half; i += 128) sincosf((float)pos * fused.inv_freq[i], &sn[i], &cs[i]);
+        unit_sync<NAMED>();
+        before_inputs();
+        const float* row = fused.qkv + (size_t)b * fused.ld;
+        for (int idx = tid; idx < 16 * hd; idx += 128) {
+            const int r = idx / hd, e = idx - r * hd;
+            const float v = r < nrows ? rotated(row + (size_t)(head0 + r) * hd, e, fused.rd, fused.interleaved, cs, sn) : 0.f;
+            q_s[idx] = __float2bfloat16_rn(v);
+        }
+        if (holds_new) {
+            for (int e = tid; e < hd; e += 128) {
+                new_k[e] = __float2bfloat16_rn(rotated(row + (size_t)(H + g) * hd, e, fused.rd, fused.interleaved, cs, sn));
+                new_v[e] = __float2bfloat16_rn(__ldcg(row + (size_t)(H + G + g) * hd + e));
+            }
+        }
+        unit_sync<NAMED>();
+        if (holds_new && hg == 0) {           // one CTA per (sequence, kv head) stores the new row
+            const size_t base = ((size_t)table[pos / PAGE] * 2 * G + g) * PAGE * hd + (size_t)(pos % PAGE) * hd;
+            for (int e = tid; e < hd; e += 128) {
+                fused.pages_rw[base + e] = new_k[e];
+                fused.pages_rw[base + (size_t)G * PAGE * hd + e] = new_v[e];
+            }
+        }
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            if (kk * 16 < hd) {
+                const int c = kk * 16 + (lane & 3) * 2;
+                qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_s + r_lo * hd + c);
+                qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_s + r_hi * hd + c);
+                qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_s + r_lo * hd + c + 8);
+                qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_s + r_hi * hd + c + 8);
+            }
+        }
+    } else {
+        before_inputs();
+        const __nv_bfloat16* q_lo = q + ((size_t)b * H + head0 + min(r_lo, nrows - 1)) * hd;
+        const __nv_bfloat16* q_hi = q + ((size_t)b * H + head0 + min(r_hi, nrows - 1)) * hd;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+            if (kk * 16 < hd) {
+                const int c = kk * 16 + (lane & 3) * 2;
+                qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_lo + c);
+                qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_hi + c);
+                qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_lo + c + 8);
+                qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_hi + c + 8);
+            }
+        }
+    }
+    float o[KSTEPS * 2][4];
+#pragma unroll
+    for (int i = 0; i < KSTEPS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
+
+    for (int i = 0; i < npages; ++i) {
+        const int nxt = i + STAGES - 1;
+        if (nxt < npages)
+            load_page(smem + (nxt % STAGES) * stage_bytes, pages, table[page_lo + nxt], G, g, hd, tid, 128);
+        cp_async_commit();
+        cp_async_wait<STAGES - 1>();
+        unit_sync<NAMED>();
+        const int key_base = (page_lo + i) * PAGE;
+        const uint32_t k_tile = smem_u32(smem + (i % STAGES) * stage_bytes);
+        const uint32_t v_tile = k_tile + PAGE * hd * 2;
+        if (FUSED && holds_new && page_lo + i == pos / PAGE) {
+            // the copy of this page predates the new token: put its key and value in place
+            const int cpr = hd >> 3, row = pos % PAGE;
+            uint8_t* tile = smem + (i % STAGES) * stage_bytes;
+            for (int c = tid; c < 2 * cpr; c += 128) {
+                const int which = c >= cpr, cc = which ? c - cpr : c;
+                const uint4 v = *reinterpret_cast<const uint4*>((which ? new_v : new_k) + cc * 8);
+                *reinterpret_cast<uint4*>(tile + which * (PAGE * hd * 2) + row * (hd * 2) + swz(row, cc, cpr) * 16) = v;
+            }
+            unit_sync<NAMED>();
+        }
+        const int key0 = warp * 16;                  // this warp's 16 keys of the page
+        if (key_base + key0 <= pos && key_base + key0 + 15 >= lo) {
+            float s[2][4];
+            s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+            scores_16keys<KSTEPS>(s, qf, k_tile, key0, hd, lane);
+            float mx_lo = NEG_BIG, mx_hi = NEG_BIG;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key_base + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    float v = s[nt][e] * scale_log2;
+                    if (key > pos || key < lo) v = NEG_BIG;
+                    s[nt][e] = v;
+                    if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+                }
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+            const float a_lo = fast_exp2(m_lo - mn_lo), a_hi = fast_exp2(m_hi - mn_hi);
+            m_lo = mn_lo; m_hi = mn_hi;
+            uint32_t pf[4];
+            float sum_lo = 0.f, sum_hi = 0.f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                float e0 = s[nt][0] <= NEG_BIG ? 0.f : fast_exp2(s[nt][0] - mn_lo);
+                float e1 = s[nt][1] <= NEG_BIG ? 0.f : fast_exp2(s[nt][1] - mn_lo);
+                float e2 = s[nt][2] <= NEG_BIG ? 0.f : fast_exp2(s[nt][2] - mn_hi);
+                float e3 = s[nt][3] <= NEG_BIG ? 0.f : fast_exp2(s[nt][3] - mn_hi);
+                sum_lo += e0 + e1; sum_hi += e2 + e3;
+                pf[nt * 2] = pack_bf16(e0, e1);
+                pf[nt * 2 + 1] = pack_bf16(e2, e3);
+            }
+            l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
+#pragma unroll
+            for (int j = 0; j < KSTEPS * 2; ++j) { o[j][0] *= a_lo; o[j][1] *= a_lo; o[j][2] *= a_hi; o[j][3] *= a_hi; }
+            values_16keys<KSTEPS>(o, pf, v_tile, key0, hd, lane);
+        }
+        unit_sync<NAMED>();
+    }
+    cp_async_wait<0>();
+    unit_sync<NAMED>();
+
+    // merge the four warps (each saw a quarter of every page) through shared memory
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    float* sm_m = reinterpret_cast<float*>(smem);            // [4][16]
+    float* sm_l = sm_m + 64;                                 // [4][16]
+    float* sm_o = sm_l + 64;                                 // [4][16][hd]
+    if ((lane & 3) == 0) {
+        sm_m[warp * 16 + r_lo] = m_lo; sm_m[warp * 16 + r_hi] = m_hi;
+        sm_l[warp * 16 + r_lo] = l_lo; sm_l[warp * 16 + r_hi] = l_hi;
+    }
+#pragma unroll
+    for (int dt = 0; dt < KSTEPS * 2; ++dt) {
+        const int d = dt * 8 + (lane & 3) * 2;
+        if (d < hd) {
+            float* lo_row = sm_o + ((size_t)warp * 16 + r_lo) * hd + d;
+            float* hi_row = sm_o + ((size_t)warp * 16 + r_hi) * hd + d;
+            lo_row[0] = o[dt][0]; lo_row[1] = o[dt][1];
+            hi_row[0] = o[dt][2]; hi_row[1] = o[dt][3];
+        }
+    }
+    unit_sync<NAMED>();
+    for (int idx = tid; idx < nrows * hd; idx += 128) {
+        const int r = idx / hd, d = idx - r * hd;
+        float m = fmaxf(fmaxf(sm_m[r], sm_m[16 + r]), fmaxf(sm_m[32 + r], sm_m[48 + r]));
+        float acc = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = fast_exp2(sm_m[w * 16 + r] - m);
+            acc += sm_o[((size_t)w * 16 + r) * hd + d] * f;
+            l += sm_l[w * 16 + r] * f;
+        }
+        if (num_splits == 1) {                      // the only share: this is the result
+            out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(acc / l);
+        } else {
+            const size_t slot = ((size_t)b * H + head0 + r) * num_splits + split;
+            part_o[slot * hd + d] = acc;
+            if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
+        }
+    }
+    if (FUSED && num_splits > 1) {
+        // the last share of this (sequence, kv head, head group) to arrive merges them all
+        __shared__ int last;
+        __threadfence();
+        unit_sync<NAMED>();
+        int* counter = fused.counters + ((size_t)b * G + g) * head_groups + hg;
+        if (tid == 0) {
+            const int ticket = atomicAdd(counter, 1);
+            last = ticket == num_splits - 1;
+            if (last) *counter = 0;                 // ready for the next launch
+        }
+        unit_sync<NAMED>();
+        if (last) {
+            __threadfence();
+            for (int idx = tid; idx < nrows * hd; idx += 128) {
+                const int r = idx / hd, d = idx - r * hd;
+                const size_t base = ((size_t)b * H + head0 + r) * num_splits;
+                float m = NEG_BIG;
+                for (int s2 = 0; s2 < num_splits; ++s2) m = fmaxf(m, __ldcg(part_ml + (base + s2) * 2));
+                float acc = 0.f, l = 0.f;
+                for (int s2 = 0; s2 < num_splits; ++s2) {
+                    const float ls = __ldcg(part_ml + (base + s2) * 2 + 1);
+                    if (ls > 0.f) {
+                        const float f = fast_exp2(__ldcg(part_ml + (base + s2) * 2) - m);
+                        l += ls * f;
+                        acc += __ldcg(part_o + (base + s2) * hd + d) * f;
+                    }
+                }
+                out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(acc / l);
+            }
+        }
+    }
+    unit_sync<NAMED>();          // the scratch may be reused by the caller's next unit
+}
+
+}  // namespace

@@ -11,7 +11,10 @@ namespace {
 constexpr int BLOCK_K = 64;       // 64 bf16 = 128 bytes = one swizzle row
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 
+#ifndef LP_SMEM_U32_DEFINED
+#define LP_SMEM_U32_DEFINED
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+#endif
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));

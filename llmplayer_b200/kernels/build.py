@@ -33,8 +33,9 @@ LIBRARIES: Dict[str, str] = {
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_mma": "attention_mma.cu",
     "attention_tcgen05": "attention_tcgen05.cu",
+    "decode_program": "decode_program.cu",
 }
-HEADERS = ("common.cuh", "attention_noalloc.h", "tcgen05_utils.cuh")
+HEADERS = ("common.cuh", "attention_noalloc.h", "tcgen05_utils.cuh", "attention_decode.cuh")
 
 NVCC_FLAGS: List[str] = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

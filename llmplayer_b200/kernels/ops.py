@@ -48,6 +48,18 @@ _SIGNATURES = {
         "lp_attention_prefill_tc": [_P, _P, _P, ctypes.c_longlong, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I,
                                     _P, _P],
     },
+    "decode_program": {
+        "lp_program_op_bytes": [],
+        "lp_program_max_tokens": [],
+        "lp_program_operand_bytes": [_I],
+        "lp_program_attention_bytes": [_I],
+        "lp_program_product": [_P, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _I, _I, _I, _P, _I, _P, _P, _F, _I, _I,
+                               _P, _I, _P, _I],
+        "lp_program_attention": [_P, _P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
+                                 _I, _I],
+        "lp_program_prologue": [_P, _I, _P, _P, _I, _I, _I, _P, _I, _P, _P],
+        "lp_program_launch": [_P, _I, _I, _I, _P, _P, _P, _P],
+    },
     "sampling": {
         "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
         "lp_sample_params_size": [],
@@ -252,7 +264,8 @@ def check_kernel_status() -> None:
         code = int(_status.item())
         _status.zero_()
         raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}: "
-                          "1 = loader, 2 = MMA issuer, 3 = epilogue)")
+                          "1 = loader, 2 = MMA issuer, 3 = epilogue; 2x the same in the persistent product; "
+                          "31-34 = roles of the step program, 40 = its barrier between operations)")
 
 
 def _token_tile(tokens: int, gated: bool) -> int:

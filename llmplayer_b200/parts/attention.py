@@ -68,6 +68,25 @@ class Attention(Part):
     def buffer_to_clear(self, ctx, tokens: int):
         return self.qkv.sums_into(ctx, tokens, "qkv", ops.STORE)
 
+    def emit(self, program, ctx, cache, residual: torch.Tensor, norm) -> None:
+        """The layer as operations of a step program: projection of the normed stream, rotation +
+        cache write + attention, output projection added into the stream."""
+        from ..engine.program import ProgramRefused
+        s = self.spec
+        if cache is None or cache.pages.dtype != torch.bfloat16:
+            raise ProgramRefused("attention without a bfloat16 cache")
+        T = residual.shape[0]
+        H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim
+        qkv = ctx.buffer("qkv", (T, self.qkv.out_features), torch.float32)
+        self.qkv.emit(program, residual, qkv, ops.STORE, norm=norm)
+        o = ctx.buffer("attn_out", (T, H * hd), torch.bfloat16)
+        program.attention(
+            qkv=qkv, inv_freq=self.position.inv_freq, rotary_dim=self.position.rotary_dim,
+            interleaved=self.position.interleaved, out=o, pages=cache.pages, write_kv=not s.shares_kv,
+            page_table=ctx.page_tables[cache.group_index], kv_len=ctx.kv_len, scratch=ctx.buffer, num_heads=H,
+            num_kv_heads=G, head_dim=hd, scale=s.scale, window=s.window)
+        self.out.emit(program, o, residual, ops.ACCUMULATE)
+
     def forward(self, ctx, cache, x: torch.Tensor, residual: torch.Tensor, then_norm=None) -> bool:
         """Adds the layer's output into ``residual``; returns whether ``then_norm`` was fused."""
         s, rt = self.spec, self.runtime

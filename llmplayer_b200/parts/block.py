@@ -76,6 +76,15 @@ class PreNormBlock(Part):
 
     kind_prenorm = True
 
+    def emit(self, program, ctx, cache, residual: torch.Tensor) -> None:
+        """The layer as operations of a step program: each half's norm is applied by the half's
+        first product on the way in, so the parts must be able to emit and the norms to be fused."""
+        from ..engine.program import ProgramRefused
+        if not hasattr(self.mixer, "emit") or not hasattr(self.ffn, "emit"):
+            raise ProgramRefused("a part that only runs as kernels of its own")
+        self.mixer.emit(program, ctx, cache, residual, self.mixer_norm)
+        self.ffn.emit(program, ctx, residual, self.ffn_norm)
+
     @staticmethod
     def _clear_for(ctx, consumer, tokens):
         ask = getattr(consumer, "buffer_to_clear", None)

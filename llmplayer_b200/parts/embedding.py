@@ -33,6 +33,9 @@ class Embedding(Part):
     def forward(self, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         return ops.embed(self.table, tokens, out)
 
+    def emit(self, program, tokens: torch.Tensor, out: torch.Tensor) -> None:
+        program.embed(self.table, tokens, out)
+
 
 class LinearHead(Part):
     def __init__(self, spec: HeadSpec):
@@ -55,3 +58,6 @@ class LinearHead(Part):
         h = ctx.buffer("head_in", (rows.numel(), self.spec.hidden_size), self.runtime.act_dtype)
         self.norm.apply(residual, h, rows=rows)
         return self.proj.store(h, logits, ctx)
+
+    def emit(self, program, residual: torch.Tensor, rows: torch.Tensor, logits: torch.Tensor) -> None:
+        self.proj.emit(program, residual, logits, ops.STORE, norm=self.norm, x_rows=rows, tokens=rows.numel())

@@ -37,6 +37,13 @@ class SwiGLU(Part):
         self.gate_up = Linear([tensors[s.gate], tensors[s.up]], runtime, gated=True)
         self.down = Linear([tensors[s.down]], runtime)
 
+    def emit(self, program, ctx, residual: torch.Tensor, norm) -> None:
+        """The layer as operations of a step program (engine/program.py)."""
+        from ..kernels import ops
+        h = ctx.buffer("ffn_hidden", (residual.shape[0], self.spec.intermediate_size), torch.bfloat16)
+        self.gate_up.emit(program, residual, h, ops.SWIGLU, norm=norm)
+        self.down.emit(program, h, residual, ops.ACCUMULATE)
+
     def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, then_norm=None) -> bool:
         """Adds the feed-forward's output into ``residual``; returns whether ``then_norm`` was fused."""
         h = ctx.buffer("ffn_hidden", (x.shape[0], self.spec.intermediate_size), self.runtime.act_dtype)

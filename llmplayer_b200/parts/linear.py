@@ -78,6 +78,19 @@ class Linear:
             return None
         return ctx.buffer(out_name, (tokens, self.out_features), torch.float32)
 
+    def emit(self, program, x: torch.Tensor, out: torch.Tensor, mode: int, *, norm=None, x_rows=None,
+             tokens=None) -> None:
+        """Append this product to a step program (engine/program.py); ``norm``: the RMS norm part
+        whose output the product takes, applied to the float32 ``x`` on the way in."""
+        from ..engine.program import ADD, STORE as P_STORE, SWIGLU as P_SWIGLU, ProgramRefused
+        if not self._fast() or (mode == ops.SWIGLU and not self.interleaved):
+            raise ProgramRefused("a product outside the tensor-core path")
+        if norm is not None and not getattr(norm, "fusable_rms", False):
+            raise ProgramRefused("a norm that the product cannot apply to its input")
+        epilogue = {ops.STORE: P_STORE, ops.ACCUMULATE: ADD, ops.SWIGLU: P_SWIGLU}[mode]
+        program.product(self.weight, x=x, out=out, epilogue=epilogue, features=self.out_features,
+                        norm=None if norm is None else (norm.weight, norm.spec.eps), x_rows=x_rows, tokens=tokens)
+
     def _run(self, x, out, mode, ctx):
         if self._fast() and x.dtype == torch.bfloat16 and (mode != ops.SWIGLU or self.interleaved):
             cleared = ctx.take_cleared() if ctx is not None else False
