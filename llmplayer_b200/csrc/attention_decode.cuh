@@ -122,6 +122,11 @@ struct FusedDecodeArgs {
     int rd, interleaved;
     __nv_bfloat16* pages_rw;   // same pages, writable; null: this layer keeps no keys of its own
     int* counters;             // [B * G * head_groups]
+    // optional: qkv[b] still lacks the factor of an RMS norm of its input, 1 / sqrt(row_sumsq[b] / norm_width +
+    // norm_eps) (the projection took bfloat16(x * gain) and left the row's factor to its reader)
+    const float* row_sumsq;
+    float norm_eps;
+    int norm_width;
 };
 
 __device__ __forceinline__ float rotated(const float* head, int e, int rd, int interleaved, const float* cs,
@@ -199,16 +204,18 @@ __device__ __forceinline__ void attention_decode_unit(
         for (int i = tid; i < half; i += 128) sincosf((float)pos * fused.inv_freq[i], &sn[i], &cs[i]);
         unit_sync<NAMED>();
         before_inputs();
+        const float in_scale = fused.row_sumsq
+            ? 1.0f / sqrtf(__ldcg(fused.row_sumsq + b) / (float)fused.norm_width + fused.norm_eps) : 1.0f;
         const float* row = fused.qkv + (size_t)b * fused.ld;
         for (int idx = tid; idx < 16 * hd; idx += 128) {
             const int r = idx / hd, e = idx - r * hd;
             const float v = r < nrows ? rotated(row + (size_t)(head0 + r) * hd, e, fused.rd, fused.interleaved, cs, sn) : 0.f;
-            q_s[idx] = __float2bfloat16_rn(v);
+            q_s[idx] = __float2bfloat16_rn(v * in_scale);
         }
         if (holds_new) {
             for (int e = tid; e < hd; e += 128) {
-                new_k[e] = __float2bfloat16_rn(rotated(row + (size_t)(H + g) * hd, e, fused.rd, fused.interleaved, cs, sn));
-                new_v[e] = __float2bfloat16_rn(__ldcg(row + (size_t)(H + G + g) * hd + e));
+                new_k[e] = __float2bfloat16_rn(rotated(row + (size_t)(H + g) * hd, e, fused.rd, fused.interleaved, cs, sn) * in_scale);
+                new_v[e] = __float2bfloat16_rn(__ldcg(row + (size_t)(H + G + g) * hd + e) * in_scale);
             }
         }
         unit_sync<NAMED>();

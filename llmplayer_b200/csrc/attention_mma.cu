@@ -472,14 +472,18 @@ extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, 
 // the cache write of the new key and value, attention over the pages and the merge of the shares in one
 // kernel. qkv: [B, ld] float32 = [H query heads | G key heads | G value heads] x hd (keys and values only
 // if `pages_rw` is given: a layer that attends over another run's cache has none). counters: int32
-// [B * G * head_groups], zero before the first call; the kernel leaves them zero.
+// [B * G * head_groups], zero before the first call; the kernel leaves them zero. row_sumsq (optional, [B]):
+// the projection left out the factor of its input's RMS norm; the kernel applies 1 / sqrt(row_sumsq[b] /
+// norm_width + norm_eps) to the queries, the key and the value it reads.
 extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* inv_freq, int rd, int interleaved,
                                          void* out, void* pages, int write_kv, const int* page_table, int pt_stride,
                                          const int* kv_len, float* scratch, int* counters, int B, int H, int G,
                                          int hd, int page_size, float scale, int window, int pages_per_split,
-                                         int num_splits, cudaStream_t stream) {
+                                         int num_splits, const float* row_sumsq, float norm_eps, int norm_width,
+                                         cudaStream_t stream) {
     if (B <= 0) return 0;
     int rc = check_geometry("attention_decode_fused", H, G, hd);
+    if (row_sumsq && norm_width <= 0) LP_REFUSE("attention_decode_fused: a row factor over %d values", norm_width);
     if (rc) return rc;
     if (page_size != PAGE) LP_REFUSE("attention_decode_fused: pages of %d positions (built for %d)", page_size, PAGE);
     if (pages_per_split <= 0 || num_splits <= 0) LP_REFUSE("attention_decode_fused: %d shares of %d pages", num_splits, pages_per_split);
@@ -496,7 +500,8 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
     float* part_ml = scratch + (size_t)B * H * num_splits * hd;
     dim3 grid(num_splits, G * head_groups, B);
     const float scale_log2 = scale * 1.4426950408889634f;
-    FusedDecodeArgs fused{qkv, ld, inv_freq, rd, interleaved, write_kv ? (__nv_bfloat16*)pages : nullptr, counters};
+    FusedDecodeArgs fused{qkv, ld, inv_freq, rd, interleaved, write_kv ? (__nv_bfloat16*)pages : nullptr, counters,
+                          row_sumsq, norm_eps, norm_width};
 #define LP_DECODE_FUSED(HDM, EXACT)                                                                              \
     do {                                                                                                         \
         rc = set_smem<3000 + HDM + EXACT>(attention_decode_kernel<HDM, true, EXACT>, smem, "attention_decode_fused"); \

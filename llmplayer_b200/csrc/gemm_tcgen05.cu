@@ -65,6 +65,64 @@ struct NormAfter {
     long long clear_count;
 };
 
+// The tail of a product that adds into `out` with atomics: the last CTA to get here writes the norm (see NormAfter).
+// Called by all threads of the CTA after their additions and a __threadfence().
+template <int NTHREADS>
+__device__ __forceinline__ void norm_after_tail(const NormAfter& norm, const void* out, int tokens, int features, int ldc) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int THREADS = NTHREADS;
+    if (norm.weight != nullptr) {
+        __shared__ int is_last;
+        if (threadIdx.x == 0) {
+            const int total = gridDim.x * gridDim.y * gridDim.z;
+            const int ticket = atomicAdd(norm.counter, 1);
+            is_last = ticket == total - 1;
+            if (is_last) *norm.counter = 0;
+        }
+        __syncthreads();
+        if (is_last) {
+            __threadfence();
+            // one warp per row; a lane takes the float4 chunks lane, lane + 32, ... (features % 128 == 0),
+            // eight independent loads at a time
+            const float* sums = (const float*)out;
+            const int chunks = features >> 7;                            // float4 chunks per lane
+            for (int t = warp; t < tokens; t += THREADS / 32) {
+                const float4* row = reinterpret_cast<const float4*>(sums + (size_t)t * ldc);
+                float ss = 0.f;
+                for (int c0 = 0; c0 < chunks; c0 += 8) {
+                    float4 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        v[u] = c0 + u < chunks ? __ldcg(row + (c0 + u) * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+                }
+                ss = lp_warp_sum(ss);
+                const float scale = 1.0f / sqrtf(ss / (float)features + norm.eps);
+                const float4* gain = reinterpret_cast<const float4*>(norm.weight);
+                uint2* dst = reinterpret_cast<uint2*>(norm.out_norm + (size_t)t * features);
+                for (int c0 = 0; c0 < chunks; c0 += 8) {
+                    float4 v[8], g[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (c0 + u < chunks) { v[u] = __ldcg(row + (c0 + u) * 32 + lane); g[u] = gain[(c0 + u) * 32 + lane]; }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (c0 + u < chunks) {
+                            __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * scale * g[u].x, v[u].y * scale * g[u].y);
+                            __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * scale * g[u].z, v[u].w * scale * g[u].w);
+                            uint2 packed;
+                            packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                            packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                            dst[(c0 + u) * 32 + lane] = packed;
+                        }
+                }
+            }
+            for (long long i = threadIdx.x; i < norm.clear_count; i += THREADS) norm.clear[i] = 0.f;
+        }
+    }
+}
+
 template <int BLOCK_TOK, int MODE>
 struct Tile {
     static constexpr int W_TILES = MODE == LP_GEMM_SWIGLU_WIDE ? 2 : 1;
@@ -272,56 +330,317 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS));
     }
-    if (ATOMIC && norm.weight != nullptr) {
-        __shared__ int is_last;
-        if (threadIdx.x == 0) {
-            const int total = gridDim.x * gridDim.y * gridDim.z;
-            const int ticket = atomicAdd(norm.counter, 1);
-            is_last = ticket == total - 1;
-            if (is_last) *norm.counter = 0;
+    if (ATOMIC) norm_after_tail<THREADS>(norm, out, tokens, features, ldc);
+}
+
+// ------------------------------------------------------------------ a handful of tokens: mma.sync consumers
+// For up to 16 tokens the tcgen05 path is bound by its issue rate, not by memory: one tcgen05.mma takes
+// about 142 cycles whatever its shape (measured: M 64/128, N 16..256), and with the weights as the
+// 128-row operand it consumes only 4 KB of them, some 40-50 GB/s per SM, below an SM's share of HBM.
+// Here the same ring of TMA stages feeds four warps that read the swizzled tiles with ldmatrix and
+// multiply with mma.sync m16n8k16: the 8 tokens of an n-tile are exactly the instruction's N, nothing
+// is issued by a single thread, and the sums stay in registers (no tensor memory, no accumulator
+// hand-over). Warp w owns weight rows 16 w .. 16 w + 15 and 64 + 16 w .. 64 + 16 w + 15 of the
+// 128-row tile: in the interleaved gate/up layout those are the gate and the up rows of the same 16
+// features, so the gated activation needs no exchange.
+//
+// XNORM: the activations are the float32 residual stream and the product applies an RMS norm on the way in.
+// The tile of x comes as float32 (two boxes of 16 rows x 32 values per k-block); a consumer forms its B
+// fragment as bfloat16(x * gain) and the first consumer warp sums x^2 per token. The row's factor
+// 1 / sqrt(mean x^2 + eps) is a scalar per token, so it is applied to the sums at the end: by this kernel when
+// a CTA sees the whole K range, else (K shared out over CTAs, partial sums meeting in atomics) the CTAs
+// with blockIdx.x == 0 add their share of the sum of squares to `sumsq_out` and the reader of the output
+// applies the factor. `zero` (optional) is cleared on the side by one CTA.
+constexpr int FEW_THREADS = 160;          // warp 0: TMA; warps 1-4: consumers
+constexpr int FEW_W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
+template <bool XNORM> struct FewTile {
+    static constexpr int X_BYTES = XNORM ? 2 * 16 * 128 : 16 * BLOCK_K * 2;
+    static constexpr int GAIN_BYTES = XNORM ? 1024 : 0;           // 64 floats of gain per k-block, padded to the tiles' alignment
+    static constexpr int STAGE_BYTES = FEW_W_BYTES + X_BYTES + GAIN_BYTES;
+    static constexpr int STAGES = XNORM ? 5 : 6;                  // two CTAs fit an SM either way
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+struct NormBefore {
+    const float* gain;        // [K]
+    float eps;
+    int K;
+    float* sumsq_out;         // [tokens]: used when K is shared out over CTAs
+    float* zero;              // optional buffer cleared on the side
+    int zero_count;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_m16n8k16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// NT: n-tiles of 8 tokens (1 or 2). MODE: STORE or SWIGLU (interleaved rows). out as in the tcgen05 kernel.
+template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
+__global__ void __launch_bounds__(FEW_THREADS, 2)
+gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
+                   int* __restrict__ status, NormAfter norm, NormBefore before) {
+    constexpr int FEW_STAGES = FewTile<XNORM>::STAGES;
+    constexpr int FEW_STAGE_BYTES = FewTile<XNORM>::STAGE_BYTES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + FEW_STAGES * FEW_STAGE_BYTES);
+    uint64_t* empty = full + FEW_STAGES;
+    volatile uint32_t* failed = (volatile uint32_t*)(empty + FEW_STAGES);
+    float* row_scale = (float*)(failed + 1);          // [16], XNORM
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kb_begin = blockIdx.z * k_blocks_per_split;
+    const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
+    const int nkb = kb_end - kb_begin;
+
+    lp_grid_release();
+    if (threadIdx.x == 0) {
+        *failed = 0;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        for (int s = 0; s < FEW_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // weights are written by no kernel of a step: the first ring is requested before waiting for
+            // the previous kernel, the activation tiles only after it
+            constexpr int TILE_BYTES = FEW_W_BYTES + FewTile<XNORM>::X_BYTES;
+            // what nothing in the step writes (weights, the norm's gain) ...
+            auto load_constants = [&](int i, int s) {
+                uint8_t* stage = smem + s * FEW_STAGE_BYTES;
+                const int k = (kb_begin + i) * BLOCK_K;
+                uint32_t gain_bytes = 0;
+                if (XNORM) gain_bytes = (uint32_t)min(BLOCK_K, before.K - k) * 4u;
+                mbar_expect_tx(&full[s], TILE_BYTES + gain_bytes);
+                tma_load_2d(stage, &map_w, k, blockIdx.x * BLOCK_FEAT, &full[s]);
+                if (XNORM) bulk_load(stage + TILE_BYTES, before.gain + k, gain_bytes, &full[s]);
+            };
+            // ... and the activations, which the previous kernel produced
+            auto load_activations = [&](int i, int s) {
+                uint8_t* xs = smem + s * FEW_STAGE_BYTES + FEW_W_BYTES;
+                const int k = (kb_begin + i) * BLOCK_K;
+                tma_load_2d(xs, &map_x, k, 0, &full[s]);
+                if (XNORM) tma_load_2d(xs + 2048, &map_x, k + 32, 0, &full[s]);
+            };
+            const int early = min(nkb, FEW_STAGES);
+            for (int i = 0; i < early; ++i) load_constants(i, i);
+            lp_grid_wait();
+            for (int i = 0; i < early; ++i) load_activations(i, i);
+            int issued = early;
+            bool ok = true;
+            for (int i = early; i < nkb; ++i) {
+                const int s = i % FEW_STAGES;
+                const uint32_t phase = (i / FEW_STAGES) & 1;
+                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
+                load_constants(i, s);
+                load_activations(i, s);
+                issued = i + 1;
+            }
+            if (!ok) {
+                for (int i = max(0, issued - FEW_STAGES); i < issued; ++i)
+                    mbar_wait(&full[i % FEW_STAGES], (i / FEW_STAGES) & 1);
+            }
         }
-        __syncthreads();
-        if (is_last) {
-            __threadfence();
-            // one warp per row; a lane takes the float4 chunks lane, lane + 32, ... (features % 128 == 0),
-            // eight independent loads at a time
-            const float* sums = (const float*)out;
-            const int chunks = features >> 7;                            // float4 chunks per lane
-            for (int t = warp; t < tokens; t += THREADS / 32) {
-                const float4* row = reinterpret_cast<const float4*>(sums + (size_t)t * ldc);
-                float ss = 0.f;
-                for (int c0 = 0; c0 < chunks; c0 += 8) {
-                    float4 v[8];
+        __syncwarp();
+    } else {
+        lp_grid_wait();                        // the epilogue adds into / overwrites what earlier kernels use
+        const int w = warp - 1;
+        const int g = lane >> 2, t = lane & 3;
+        if (before.zero != nullptr && blockIdx.x == 0 && blockIdx.z == 0)
+            for (int i = threadIdx.x - 32; i < before.zero_count; i += 128) before.zero[i] = 0.f;
+        float ss[NT];                          // XNORM, warp w == 0: this lane's share of sum x^2 of token g + 8 nt
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        v[u] = c0 + u < chunks ? __ldcg(row + (c0 + u) * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int nt = 0; nt < NT; ++nt) ss[nt] = 0.f;
+        float acc[2][NT][4];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) acc[mt][nt][0] = acc[mt][nt][1] = acc[mt][nt][2] = acc[mt][nt][3] = 0.f;
+        // ldmatrix.x4: lane l gives the address of row (l & 7) + 8 * ((l >> 3) & 1), 16-byte chunk (l >> 4) of the 16 x 16 tile
+        const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int a_chunk = lane >> 4;
+        bool ok = true;
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % FEW_STAGES;
+            const uint32_t phase = (i / FEW_STAGES) & 1;
+            if (!mbar_wait(&full[s], phase)) { if (lane == 0) atomicExch(status, 2); *failed = 1; ok = false; break; }
+            const uint32_t w_tile = smem_u32(smem + s * FEW_STAGE_BYTES);
+            const uint8_t* x_tile = smem + s * FEW_STAGE_BYTES + FEW_W_BYTES;
+#pragma unroll
+            for (int ks = 0; ks < BLOCK_K / 16; ++ks) {
+                uint32_t b[NT][2];
+                if (XNORM) {
+                    // float32 tile: value k of the k-block lies in box k / 32, 16-byte chunk (k % 32) / 4 of its row
+                    const int k_lo = ks * 16 + 2 * t, k_hi = k_lo + 8;
+                    const int k_abs = (kb_begin + i) * BLOCK_K;
+                    // the gain of this k-block came with the stage; beyond K it is unset (and x is zero there)
+                    const float* gain_tile = reinterpret_cast<const float*>(x_tile + FewTile<XNORM>::X_BYTES);
+                    float2 g_lo = make_float2(0.f, 0.f), g_hi = g_lo;
+                    if (k_abs + k_lo < before.K) g_lo = *reinterpret_cast<const float2*>(gain_tile + k_lo);
+                    if (k_abs + k_hi < before.K) g_hi = *reinterpret_cast<const float2*>(gain_tile + k_hi);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const int row = g + 8 * nt;
+                        const uint8_t* xr = x_tile + row * 128;
+                        const float2 lo = *reinterpret_cast<const float2*>(
+                            xr + (k_lo >> 5) * 2048 + ((((k_lo & 31) >> 2) ^ g) << 4) + (k_lo & 3) * 4);
+                        const float2 hi = *reinterpret_cast<const float2*>(
+                            xr + (k_hi >> 5) * 2048 + ((((k_hi & 31) >> 2) ^ g) << 4) + (k_hi & 3) * 4);
+                        ss[nt] += lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
+                        __nv_bfloat162 p = __floats2bfloat162_rn(lo.x * g_lo.x, lo.y * g_lo.y);
+                        b[nt][0] = *reinterpret_cast<uint32_t*>(&p);
+                        p = __floats2bfloat162_rn(hi.x * g_hi.x, hi.y * g_hi.y);
+                        b[nt][1] = *reinterpret_cast<uint32_t*>(&p);
+                    }
+                } else {
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const int row = g + 8 * nt;                    // token; row & 7 == g
+                        const uint8_t* xr = x_tile + row * 128 + t * 4;
+                        b[nt][0] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks) ^ g) << 4));
+                        b[nt][1] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks + 1) ^ g) << 4));
+                    }
                 }
-                ss = lp_warp_sum(ss);
-                const float scale = 1.0f / sqrtf(ss / (float)features + norm.eps);
-                const float4* gain = reinterpret_cast<const float4*>(norm.weight);
-                uint2* dst = reinterpret_cast<uint2*>(norm.out_norm + (size_t)t * features);
-                for (int c0 = 0; c0 < chunks; c0 += 8) {
-                    float4 v[8], g[8];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        if (c0 + u < chunks) { v[u] = __ldcg(row + (c0 + u) * 32 + lane); g[u] = gain[(c0 + u) * 32 + lane]; }
+                for (int mt = 0; mt < 2; ++mt) {
+                    const int row = (w + 4 * mt) * 16 + a_row;
+                    uint32_t a[4];
+                    ldmatrix_x4(w_tile + row * 128 + (((2 * ks + a_chunk) ^ (row & 7)) << 4), a[0], a[1], a[2], a[3]);
 #pragma unroll
-                    for (int u = 0; u < 8; ++u)
-                        if (c0 + u < chunks) {
-                            __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * scale * g[u].x, v[u].y * scale * g[u].y);
-                            __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * scale * g[u].z, v[u].w * scale * g[u].w);
-                            uint2 packed;
-                            packed.x = *reinterpret_cast<uint32_t*>(&lo);
-                            packed.y = *reinterpret_cast<uint32_t*>(&hi);
-                            dst[(c0 + u) * 32 + lane] = packed;
-                        }
+                    for (int nt = 0; nt < NT; ++nt) mma_m16n8k16(acc[mt][nt], a, b[nt][0], b[nt][1]);
                 }
             }
-            for (long long i = threadIdx.x; i < norm.clear_count; i += THREADS) norm.clear[i] = 0.f;
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[s])) : "memory");
         }
+        ok = ok && *failed == 0;
+        if (XNORM) {
+            // sum x^2 of token g + 8 nt: over the four lanes that share g
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 1);
+                ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 2);
+            }
+            if (gridDim.z == 1) {
+                if (w == 0 && t == 0) {
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) row_scale[g + 8 * nt] = 1.0f / sqrtf(ss[nt] / (float)before.K + before.eps);
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");         // the four consumer warps
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) acc[mt][nt][e] *= row_scale[nt * 8 + 2 * t + (e & 1)];
+            } else if (blockIdx.x == 0 && w == 0 && t == 0 && ok) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                    if (g + 8 * nt < tokens) atomicAdd(before.sumsq_out + g + 8 * nt, ss[nt]);
+            }
+        }
+        // c fragment: c0, c1 = (row g, tokens 2t, 2t + 1); c2, c3 = (row g + 8, same tokens)
+        if (ok) {
+            if (MODE == LP_GEMM_SWIGLU) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int f = blockIdx.x * (BLOCK_FEAT / 2) + w * 16 + g + (e >> 1) * 8;
+                        const int tok = nt * 8 + 2 * t + (e & 1);
+                        if (f < features && tok < tokens) {
+                            const float gate = acc[0][nt][e], up = acc[1][nt][e];
+                            const float v = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+                            const size_t at = (size_t)tok * ldc + f;
+                            if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                            else ((float*)out)[at] = v;
+                        }
+                    }
+            } else {
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int f = blockIdx.x * BLOCK_FEAT + (w + 4 * mt) * 16 + g + (e >> 1) * 8;
+                            const int tok = nt * 8 + 2 * t + (e & 1);
+                            if (f < features && tok < tokens) {
+                                const float v = acc[mt][nt][e];
+                                const size_t at = (size_t)tok * ldc + f;
+                                if (ATOMIC) atomicAdd((float*)out + at, v);
+                                else if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                                else ((float*)out)[at] = v;
+                            }
+                        }
+            }
+        }
+        if (ATOMIC) __threadfence();
     }
+    __syncthreads();
+    if (ATOMIC) norm_after_tail<FEW_THREADS>(norm, out, tokens, features, ldc);
+}
+
+template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
+int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
+                  int splits, int* status, const NormAfter& norm, const NormBefore& before, cudaStream_t stream) {
+    auto kernel = gemm_fewtok_kernel<NT, MODE, OUT_BF16, ATOMIC, XNORM>;
+    constexpr int FEW_SMEM_BYTES = FewTile<XNORM>::SMEM_BYTES;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FEW_SMEM_BYTES);
+        if (e != cudaSuccess) LP_REFUSE("gemm: cannot reserve %d bytes of shared memory: %s", FEW_SMEM_BYTES,
+                                        cudaGetErrorString(e));
+        configured = true;
+    }
+    const int per_split = (k_blocks + splits - 1) / splits;
+    const int grid_z = (k_blocks + per_split - 1) / per_split;
+    const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;
+    dim3 grid((features + per_cta - 1) / per_cta, 1, grid_z);
+    cudaError_t err = lp_launch(kernel, grid, FEW_THREADS, FEW_SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
+                                k_blocks, per_split, status, norm, before);
+    if (err != cudaSuccess) {
+        snprintf(lp_error_text, sizeof(lp_error_text), "gemm_fewtok: %s", cudaGetErrorString(err));
+        return (int)err;
+    }
+    return lp_check_launch("gemm_fewtok");
+}
+
+template <int NT, bool XNORM>
+int dispatch_fewtok(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const CUtensorMap& mx, void* out,
+                    int tokens, int features, int ldc, int k_blocks, int splits, int* status, const NormAfter& norm,
+                    const NormBefore& before, cudaStream_t stream) {
+#define LP_GO(MODE, BF, AT) \
+    return launch_fewtok<NT, MODE, BF, AT, XNORM>(mw, mx, out, tokens, features, ldc, k_blocks, splits, status, norm, before, stream)
+    if (mode == LP_GEMM_SWIGLU) {
+        if (out_bf16) LP_GO(LP_GEMM_SWIGLU, true, false);
+        LP_GO(LP_GEMM_SWIGLU, false, false);
+    }
+    if (atomic) LP_GO(LP_GEMM_STORE, false, true);
+    if (out_bf16) LP_GO(LP_GEMM_STORE, true, false);
+    LP_GO(LP_GEMM_STORE, false, false);
+#undef LP_GO
+}
+
+static bool fewtok_enabled() {
+    static int state = -1;
+    if (state < 0) {
+        const char* v = getenv("LLMPLAYER_B200_FEWTOK");
+        state = (v && v[0] == '0') ? 0 : 1;
+    }
+    return state == 1;
 }
 
 // ------------------------------------------------------------------ persistent form for prompts
@@ -633,6 +952,12 @@ extern "C" int lp_gemm_tcgen05(const void* X, const void* W, void* out, int out_
     }
     const bool bf = out_dtype == LP_BF16;
     const int mmode = mode == LP_GEMM_SWIGLU ? LP_GEMM_SWIGLU : LP_GEMM_STORE;
+    if (block_tok == 16 && tokens <= 16 && fewtok_enabled()) {
+        // a handful of tokens: the mma.sync consumers (LLMPLAYER_B200_FEWTOK=0 keeps the tcgen05 kernel)
+        const NormBefore none{};
+        if (tokens <= 8) return dispatch_fewtok<1, false>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, status, norm, none, stream);
+        return dispatch_fewtok<2, false>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, status, norm, none, stream);
+    }
     switch (block_tok) {
         case 16: return dispatch<16>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, norm, stream);
         case 32: return dispatch<32>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, norm, stream);
@@ -641,4 +966,48 @@ extern "C" int lp_gemm_tcgen05(const void* X, const void* W, void* out, int out_
         case 256: return dispatch<256>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, norm, stream);
         default: LP_REFUSE("gemm: token tile %d (supported: 16, 32, 64, 128, 256)", block_tok);
     }
+}
+
+// A product for at most 16 tokens (the mma.sync kernel above) with what a decode step fuses around it.
+// x_dtype LP_F32: X is the float32 residual stream and the product applies the RMS norm (gain, eps) on the
+// way in; with splits > 1 the output then still lacks the rows' factors and `sumsq_out` [tokens] (zero before
+// the call) receives sum x^2 per token for the reader to apply them. x_dtype LP_BF16: X as in lp_gemm_tcgen05.
+// `zero` (optional): zero_count floats cleared on the side (nothing else in flight may use them).
+extern "C" int lp_gemm_fewtok(const void* X, int x_dtype, const void* W, void* out, int out_dtype, int tokens,
+                              int features, int K, int ldx, int ldw, int ldc, int mode, int splits, int* status,
+                              const float* gain, float eps, float* sumsq_out, float* zero, int zero_count,
+                              cudaStream_t stream) {
+    if (tokens <= 0 || features <= 0) return 0;
+    if (tokens > 16) LP_REFUSE("gemm_fewtok: %d tokens (at most 16)", tokens);
+    if (K <= 0 || K % 8) LP_REFUSE("gemm: inner size %d must be a positive multiple of 8 for the tensor-core path", K);
+    const bool xnorm = x_dtype == LP_F32;
+    if (x_dtype != LP_F32 && x_dtype != LP_BF16) LP_REFUSE("gemm_fewtok: activation dtype code %d", x_dtype);
+    if (ldw % 8 || ldx % (xnorm ? 4 : 8)) LP_REFUSE("gemm: row strides %d / %d must be multiples of 16 bytes", ldx, ldw);
+    if (((uintptr_t)X | (uintptr_t)W) & 15) LP_REFUSE("gemm: operands must be 16-byte aligned");
+    if (mode < 0 || mode > 2) LP_REFUSE("gemm: mode %d", mode);
+    if (xnorm && (!gain || ((uintptr_t)gain & 15))) LP_REFUSE("gemm_fewtok: a float32 input needs the norm's gain, 16-byte aligned");
+    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+    if (splits < 1) splits = 1;
+    if (splits > k_blocks) splits = k_blocks;
+    const bool atomic = mode == LP_GEMM_ACCUMULATE || (mode == LP_GEMM_STORE && splits > 1);
+    if (mode == LP_GEMM_SWIGLU && splits > 1) LP_REFUSE("gemm: the gated epilogue cannot be split along K");
+    if (atomic && out_dtype != LP_F32) LP_REFUSE("gemm: sums across CTAs need a float32 output");
+    if (out_dtype != LP_F32 && out_dtype != LP_BF16) LP_REFUSE("gemm: output dtype code %d", out_dtype);
+    const int per_split = (k_blocks + splits - 1) / splits;
+    if (xnorm && (k_blocks + per_split - 1) / per_split > 1 && !sumsq_out)
+        LP_REFUSE("gemm_fewtok: a normed input shared out over %d CTAs needs a place for the sums of squares", splits);
+    const long long w_rows = mode == LP_GEMM_SWIGLU ? 128LL * ((features + 63) / 64) : features;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, w_rows, K, ldw, BLOCK_FEAT);
+    if (rc) return rc;
+    rc = xnorm ? make_map_f32(&mx, X, tokens, K, ldx, 16) : make_map(&mx, X, tokens, K, ldx, 16);
+    if (rc) return rc;
+    const NormAfter after{};
+    const NormBefore before{gain, eps, K, sumsq_out, zero, zero ? zero_count : 0};
+    const bool bf = out_dtype == LP_BF16;
+    const int mmode = mode == LP_GEMM_SWIGLU ? LP_GEMM_SWIGLU : LP_GEMM_STORE;
+#define LP_FEW(NT, XN) dispatch_fewtok<NT, XN>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, status, after, before, stream)
+    if (xnorm) return tokens <= 8 ? LP_FEW(1, true) : LP_FEW(2, true);
+    return tokens <= 8 ? LP_FEW(1, false) : LP_FEW(2, false);
+#undef LP_FEW
 }

@@ -72,6 +72,17 @@ class Workspace:
             self.version += 1
         return buf[:count].view(*shape)
 
+    def get_zeroed(self, name: str, count: int) -> torch.Tensor:
+        """A float32 buffer of ``count`` values that is zero when first handed out and that its users
+        promise to leave zero again after each use (partial sums that meet in atomics)."""
+        key = (name, torch.float32)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < count:
+            buf = torch.zeros(max(count, 1), dtype=torch.float32, device=self.device)
+            self._buffers[key] = buf
+            self.version += 1
+        return buf[:count]
+
 
 def _round_up(n: int, m: int) -> int:
     return -(-n // m) * m

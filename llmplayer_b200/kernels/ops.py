@@ -37,12 +37,13 @@ _SIGNATURES = {
         "lp_gemm_tcgen05": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P,
                             ctypes.c_longlong, _P, _P],
         "lp_gemm_persistent": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
+        "lp_gemm_fewtok": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _I, _P],
     },
     "attention_mma": {
         "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
         "lp_attention_decode_fused": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
-                                      _I, _I, _P],
+                                      _I, _I, _P, _F, _I, _P],
     },
     "attention_tcgen05": {
         "lp_attention_prefill_tc": [_P, _P, _P, ctypes.c_longlong, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I,
@@ -386,6 +387,53 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
     return out
 
 
+FEW_TOKENS = 16
+
+
+def gemm_few(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, norm=None,
+             sumsq: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None) -> bool:
+    """out (=|+=) f(x) @ w.T for at most ``FEW_TOKENS`` rows, with what a decode step fuses around it.
+
+    ``norm = (gain, eps)``: ``x`` is the float32 residual stream and the product applies the RMS norm on
+    the way in. If the K range is then shared out over CTAs (few output features), ``out`` still lacks each
+    row's factor: ``sumsq`` [rows] (zero beforehand) receives the rows' sums of squares, the reader applies
+    ``1 / sqrt(sumsq / K + eps)``, and the function returns True. ``out`` must be zero beforehand in that
+    case, as for any ``STORE`` whose partial sums meet in atomics. ``zero``: a float32 buffer cleared on the
+    side. Without ``norm``, ``x`` is bfloat16."""
+    _want(w, "gemm_few w", torch.bfloat16, 2)
+    _want(out, "gemm_few out", ndim=2)
+    _want(x, "gemm_few x", torch.float32 if norm is not None else torch.bfloat16, 2)
+    M, K = x.shape
+    N = out.shape[1]
+    rows = 128 * (-(-N // 64)) if mode == SWIGLU else N
+    if w.shape != (rows, K) or out.shape[0] != M or M > FEW_TOKENS:
+        raise KernelError(f"gemm_few: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, mode {mode}")
+    _, splits = gemm_plan(M, N, K, mode)
+    if mode == STORE and splits > 1 and out.dtype != torch.float32:
+        splits = 1
+    gain = eps = None
+    if norm is not None:
+        gain, eps = norm
+        _want(gain, "gemm_few gain", torch.float32, 1)
+        if gain.numel() != K:
+            raise KernelError(f"gemm_few: a gain of {gain.numel()} values for rows of {K}")
+        if splits > 1 and sumsq is None:
+            splits = 1
+    deferred = norm is not None and splits > 1
+    if deferred:
+        _want(sumsq, "gemm_few sumsq", torch.float32, 1)
+        if sumsq.numel() < M:
+            raise KernelError(f"gemm_few: {sumsq.numel()} sums of squares for {M} rows")
+    if zero is not None:
+        _want(zero, "gemm_few zero", torch.float32)
+    lib = library("gemm_tcgen05")
+    _check(lib, lib.lp_gemm_fewtok(
+        x.data_ptr(), _code(x, "gemm_few x"), w.data_ptr(), out.data_ptr(), _code(out, "gemm_few out"), M, N, K, K, K, N,
+        mode, splits, kernel_status().data_ptr(), _ptr(gain), float(eps) if eps is not None else 0.0,
+        sumsq.data_ptr() if deferred else None, _ptr(zero), zero.numel() if zero is not None else 0, _stream()))
+    return deferred
+
+
 # --------------------------------------------------------------------------- attention
 def attention_plain(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page_table: torch.Tensor,
                     seq_ids: torch.Tensor, positions: torch.Tensor, *, num_heads: int, num_kv_heads: int,
@@ -492,10 +540,13 @@ def attention_decode_fused(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], 
                            pages: torch.Tensor, page_table: torch.Tensor, kv_len: torch.Tensor, scratch, *,
                            num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, interleaved: bool,
                            write_kv: bool, scale: float, window: Optional[int], pages_per_split: int = 0,
-                           num_splits: int = 0) -> torch.Tensor:
+                           num_splits: int = 0, row_sumsq: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
+                           norm_width: int = 0) -> torch.Tensor:
     """A decode step's attention from the float32 fused projection ``qkv`` [B, (H + 2G) * hd]
     (``[B, H * hd]`` when ``write_kv`` is false): rotates the queries, rotates and stores the new
-    key, stores the new value, attends over the pages and merges the shares, in one kernel."""
+    key, stores the new value, attends over the pages and merges the shares, in one kernel.
+    ``row_sumsq`` [B]: ``qkv`` still lacks the factor of the RMS norm of its input; row b is scaled by
+    ``1 / sqrt(row_sumsq[b] / norm_width + norm_eps)`` as it is read."""
     global _decode_counters
     _want(qkv, "attention_decode_fused qkv", torch.float32, 2)
     _want(out, "attention_decode_fused out", torch.bfloat16, 2)
@@ -524,7 +575,8 @@ def attention_decode_fused(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], 
         qkv.data_ptr(), qkv.shape[1], _ptr(inv_freq) if rotary_dim > 0 else None, rotary_dim, 1 if interleaved else 0,
         out.data_ptr(), pages.data_ptr(), 1 if write_kv else 0, page_table.data_ptr(), page_table.shape[1],
         kv_len.data_ptr(), buf.data_ptr(), _decode_counters.data_ptr(), B, H, G, hd, pages.shape[3], float(scale),
-        int(window) if window else 0, pages_per_split, num_splits, _stream()))
+        int(window) if window else 0, pages_per_split, num_splits, _ptr(row_sumsq), float(norm_eps), int(norm_width),
+        _stream()))
     return out
 
 

@@ -18,7 +18,7 @@ import torch
 from ..cache.sequence_cache import KVRequest
 from ..errors import ConfigError
 from ..kernels import ops
-from .base import MIXERS, POSITIONS, Part, Runtime
+from .base import MIXERS, POSITIONS, Part, PendingNorm, Runtime
 from .linear import Linear
 from .specs import MATRIX, AttentionSpec, TensorSpec
 
@@ -87,13 +87,44 @@ class Attention(Part):
             num_kv_heads=G, head_dim=hd, scale=s.scale, window=s.window)
         self.out.emit(program, o, residual, ops.ACCUMULATE)
 
-    def forward(self, ctx, cache, x: torch.Tensor, residual: torch.Tensor, then_norm=None) -> bool:
-        """Adds the layer's output into ``residual``; returns whether ``then_norm`` was fused."""
+    takes_pending_norm = True     # the projection applies the norm of its input itself when a step is small
+
+    def _forward_few(self, ctx, cache, pending: PendingNorm, residual: torch.Tensor) -> None:
+        """A step of one token for each of a handful of sequences, in three kernels: projection of the
+        normed stream (norm applied on the way in), rotation + cache write + attention, output projection.
+        The projection's partial sums meet in a buffer that is zero between uses; it leaves each row's
+        norm factor to the attention kernel and gives it the row's sum of squares instead."""
+        s = self.spec
+        T = residual.shape[0]
+        H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim
+        F = self.qkv.out_features
+        sums = ctx.workspace.get_zeroed("qkv_partial_sums", ops.FEW_TOKENS + ops.FEW_TOKENS * F)
+        sumsq, qkv = sums[:ops.FEW_TOKENS], sums[ops.FEW_TOKENS:ops.FEW_TOKENS + T * F].view(T, F)
+        deferred = self.qkv.few(pending.source, qkv, ops.STORE, norm=pending.norm, sumsq=sumsq)
+        o = ctx.buffer("attn_out", (T, H * hd), torch.bfloat16)
+        ops.attention_decode_fused(
+            qkv, self.position.inv_freq, o, cache.pages, ctx.page_tables[cache.group_index], ctx.kv_len, ctx.buffer,
+            num_heads=H, num_kv_heads=G, head_dim=hd, rotary_dim=self.position.rotary_dim,
+            interleaved=self.position.interleaved, write_kv=not s.shares_kv, scale=s.scale, window=s.window,
+            row_sumsq=sumsq if deferred else None, norm_eps=pending.norm.spec.eps, norm_width=residual.shape[1])
+        self.out.few(o, residual, ops.ACCUMULATE, zero=sums[:ops.FEW_TOKENS + T * F])
+
+    def forward(self, ctx, cache, x, residual: torch.Tensor, then_norm=None) -> bool:
+        """Adds the layer's output into ``residual``; returns whether ``then_norm`` was fused.
+        ``x``: the normed stream, or a :class:`PendingNorm` of it."""
         s, rt = self.spec, self.runtime
         if cache is None:
             raise ConfigError("attention needs a key/value cache (its own or another run's)")
-        T = x.shape[0]
         H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim
+        if isinstance(x, PendingNorm):
+            T = residual.shape[0]
+            if (rt.fast and ctx.all_single and x.fusable and cache.pages.dtype == torch.bfloat16 and hd % 16 == 0
+                    and hd <= 256 and self.qkv.can_few(T, ops.STORE) and self.out.can_few(T, ops.ACCUMULATE)
+                    and residual.dtype == torch.float32):
+                self._forward_few(ctx, cache, x, residual)
+                return False
+            x = x.tensor()
+        T = x.shape[0]
         table = ctx.page_tables[cache.group_index]
         qkv = ctx.buffer("qkv", (T, self.qkv.out_features), torch.float32)
         self.qkv.store(x, qkv, ctx)

@@ -91,6 +91,28 @@ class FollowingNorm:
     clear: Optional[torch.Tensor] = None
 
 
+class PendingNorm:
+    """``norm(source)`` that has not been computed yet: what a block hands to a part that declares
+    ``takes_pending_norm = True`` instead of the normed tensor. Such a part may apply the norm inside
+    its first product (it finds the float32 ``source`` and the ``norm`` part here); whenever it cannot,
+    ``tensor()`` runs the norm as a kernel of its own (once) and returns the result."""
+
+    def __init__(self, source: torch.Tensor, norm, materialize: Callable[[], torch.Tensor]):
+        self.source = source
+        self.norm = norm
+        self._materialize = materialize
+        self._tensor: Optional[torch.Tensor] = None
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = self._materialize()
+        return self._tensor
+
+    @property
+    def fusable(self) -> bool:
+        return bool(getattr(self.norm, "fusable_rms", False))
+
+
 class Part:
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}

@@ -10,7 +10,7 @@ from typing import Dict, Mapping
 
 import torch
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, FollowingNorm, Part, Runtime
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, FollowingNorm, Part, PendingNorm, Runtime
 from .specs import BlockSpec, TensorSpec
 
 
@@ -52,26 +52,47 @@ class PreNormBlock(Part):
         act = self.runtime.act_dtype
         tokens = residual.shape[0]
         h = ctx.buffer("normed", tuple(residual.shape), act)
-        if not normed_ready:
+
+        def pending(norm, consumer):
+            def run():
+                self._norm(ctx, norm, consumer, residual, h)
+                return h
+            return PendingNorm(residual, norm, run)
+
+        # a part that takes a pending norm gets (stream, norm) and may apply the norm in its first product
+        mixer_pends = bool(getattr(self.mixer, "takes_pending_norm", False))
+        ffn_pends = bool(getattr(self.ffn, "takes_pending_norm", False))
+        if normed_ready:
+            mixer_in = h
+        elif mixer_pends:
+            mixer_in = pending(self.mixer_norm, self.mixer)
+        else:
             self._norm(ctx, self.mixer_norm, self.mixer, residual, h)
+            mixer_in = h
         fused = False
-        if self._mixer_fuses:
+        if self._mixer_fuses and not ffn_pends:
             follow = FollowingNorm(self.ffn_norm, h, self._clear_for(ctx, self.ffn, tokens))
-            fused = bool(self.mixer.forward(ctx, cache, h, residual, then_norm=follow))
+            fused = bool(self.mixer.forward(ctx, cache, mixer_in, residual, then_norm=follow))
             if fused and follow.clear is not None:
                 ctx.note_cleared()
         else:
-            self.mixer.forward(ctx, cache, h, residual)
-        if not fused:
+            self.mixer.forward(ctx, cache, mixer_in, residual)
+        if fused:
+            ffn_in = h
+        elif ffn_pends:
+            ffn_in = pending(self.ffn_norm, self.ffn)
+        else:
             self._norm(ctx, self.ffn_norm, self.ffn, residual, h)
+            ffn_in = h
         nxt = getattr(next_block, "mixer_norm", None)
-        if self._ffn_fuses and nxt is not None and getattr(next_block, "kind_prenorm", False):
+        next_pends = bool(getattr(getattr(next_block, "mixer", None), "takes_pending_norm", False))
+        if self._ffn_fuses and nxt is not None and getattr(next_block, "kind_prenorm", False) and not next_pends:
             follow = FollowingNorm(nxt, h, self._clear_for(ctx, next_block.mixer, tokens))
-            done = bool(self.ffn.forward(ctx, h, residual, then_norm=follow))
+            done = bool(self.ffn.forward(ctx, ffn_in, residual, then_norm=follow))
             if done and follow.clear is not None:
                 ctx.note_cleared()
             return done
-        self.ffn.forward(ctx, h, residual)
+        self.ffn.forward(ctx, ffn_in, residual)
         return False
 
     kind_prenorm = True

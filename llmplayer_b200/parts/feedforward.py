@@ -12,7 +12,7 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
-from .base import FEED_FORWARDS, Part, Runtime
+from .base import FEED_FORWARDS, Part, PendingNorm, Runtime
 from .linear import Linear
 from .specs import MATRIX, SwiGLUSpec, TensorSpec
 
@@ -44,8 +44,21 @@ class SwiGLU(Part):
         self.gate_up.emit(program, residual, h, ops.SWIGLU, norm=norm)
         self.down.emit(program, h, residual, ops.ACCUMULATE)
 
-    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, then_norm=None) -> bool:
-        """Adds the feed-forward's output into ``residual``; returns whether ``then_norm`` was fused."""
+    takes_pending_norm = True     # the gated product applies the norm of its input itself when a step is small
+
+    def forward(self, ctx, x, residual: torch.Tensor, then_norm=None) -> bool:
+        """Adds the feed-forward's output into ``residual``; returns whether ``then_norm`` was fused.
+        ``x``: the normed stream, or a :class:`PendingNorm` of it."""
+        from ..kernels import ops
+        if isinstance(x, PendingNorm):
+            T = residual.shape[0]
+            if (self.runtime.fast and x.fusable and residual.dtype == torch.float32
+                    and self.gate_up.can_few(T, ops.SWIGLU) and self.down.can_few(T, ops.ACCUMULATE)):
+                h = ctx.buffer("ffn_hidden", (T, self.spec.intermediate_size), torch.bfloat16)
+                self.gate_up.few(x.source, h, ops.SWIGLU, norm=x.norm)
+                self.down.few(h, residual, ops.ACCUMULATE)
+                return False
+            x = x.tensor()
         h = ctx.buffer("ffn_hidden", (x.shape[0], self.spec.intermediate_size), self.runtime.act_dtype)
         self.gate_up.swiglu(x, h, ctx)
         return self.down.accumulate(h, residual, ctx, then_norm)

@@ -78,6 +78,17 @@ class Linear:
             return None
         return ctx.buffer(out_name, (tokens, self.out_features), torch.float32)
 
+    def can_few(self, tokens: int, mode: int) -> bool:
+        """Whether :meth:`few` serves this product for ``tokens`` rows."""
+        return self._fast() and tokens <= ops.FEW_TOKENS and (mode != ops.SWIGLU or self.interleaved)
+
+    def few(self, x: torch.Tensor, out: torch.Tensor, mode: int, *, norm=None, sumsq=None, zero=None) -> bool:
+        """The product for a handful of rows with what a decode step fuses around it (see
+        :func:`ops.gemm_few`); ``norm``: an RMS norm part applied to the float32 ``x`` on the way in.
+        Returns whether ``out`` still lacks the rows' factors (then ``sumsq`` holds their sums of squares)."""
+        return ops.gemm_few(x, self.weight, out, mode, norm=None if norm is None else (norm.weight, norm.spec.eps),
+                            sumsq=sumsq, zero=zero)
+
     def emit(self, program, x: torch.Tensor, out: torch.Tensor, mode: int, *, norm=None, x_rows=None,
              tokens=None) -> None:
         """Append this product to a step program (engine/program.py); ``norm``: the RMS norm part
