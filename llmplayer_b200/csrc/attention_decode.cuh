@@ -378,15 +378,32 @@ __device__ __forceinline__ void attention_decode_unit(
             for (int idx = tid; idx < nrows * hd; idx += 128) {
                 const int r = idx / hd, d = idx - r * hd;
                 const size_t base = ((size_t)b * H + head0 + r) * num_splits;
+                // the shares' (max, sum, output) are requested eight shares at a time, then combined
                 float m = NEG_BIG;
-                for (int s2 = 0; s2 < num_splits; ++s2) m = fmaxf(m, __ldcg(part_ml + (base + s2) * 2));
+                for (int s0 = 0; s0 < num_splits; s0 += 8) {
+                    float mm[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) mm[u] = s0 + u < num_splits ? __ldcg(part_ml + (base + s0 + u) * 2) : NEG_BIG;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) m = fmaxf(m, mm[u]);
+                }
                 float acc = 0.f, l = 0.f;
-                for (int s2 = 0; s2 < num_splits; ++s2) {
-                    const float ls = __ldcg(part_ml + (base + s2) * 2 + 1);
-                    if (ls > 0.f) {
-                        const float f = fast_exp2(__ldcg(part_ml + (base + s2) * 2) - m);
-                        l += ls * f;
-                        acc += __ldcg(part_o + (base + s2) * hd + d) * f;
+                for (int s0 = 0; s0 < num_splits; s0 += 8) {
+                    float mm[8], ll[8], oo[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const bool in = s0 + u < num_splits;
+                        mm[u] = in ? __ldcg(part_ml + (base + s0 + u) * 2) : NEG_BIG;
+                        ll[u] = in ? __ldcg(part_ml + (base + s0 + u) * 2 + 1) : 0.f;
+                        oo[u] = in ? __ldcg(part_o + (base + s0 + u) * hd + d) : 0.f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        if (ll[u] > 0.f) {
+                            const float f = fast_exp2(mm[u] - m);
+                            l += ll[u] * f;
+                            acc += oo[u] * f;
+                        }
                     }
                 }
                 out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(acc / l);

@@ -323,7 +323,11 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
 
 // ============================================================================ decode
 // grid: (splits, G * head_groups, B); 128 threads; one new token per sequence (attention_decode.cuh).
-template <int HD_MAX, bool FUSED, int HD_EXACT>
+// The fused form that writes the new key and value itself requests its first pages before it waits
+// for the previous kernel: within a step nothing else writes lengths, page tables or these pages, and
+// the new row is put into the unit's own copy of the page. Every other form waits first (the pages
+// may hold a row that the previous kernel wrote).
+template <int HD_MAX, bool FUSED, int HD_EXACT, int STAGES>
 __global__ void __launch_bounds__(128)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
                         const int* __restrict__ page_table, int pt_stride, const int* __restrict__ kv_len,
@@ -332,10 +336,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         int head_groups, FusedDecodeArgs fused) {
     extern __shared__ __align__(128) uint8_t smem[];
     lp_grid_release();
-    lp_grid_wait();
-    attention_decode_unit<HD_MAX, FUSED, HD_EXACT, false, 3>(
+    const bool early = FUSED && fused.pages_rw != nullptr;
+    if (!early) lp_grid_wait();
+    attention_decode_unit<HD_MAX, FUSED, HD_EXACT, false, STAGES>(
         smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, q, pages, page_table, pt_stride, kv_len, part_o, part_ml,
-        out, H, G, hd_arg, scale_log2, window, pages_per_split, num_splits, head_groups, fused, [] {});
+        out, H, G, hd_arg, scale_log2, window, pages_per_split, num_splits, head_groups, fused,
+        [early] { if (early) lp_grid_wait(); });
 }
 
 // out[b][head][:] = sum_s part_o * 2^(m_s - m*) / sum_s l_s * 2^(m_s - m*); grid: (H, B), hd threads (<= 256).
@@ -451,9 +457,9 @@ extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, 
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LP_DECODE(HDM, EXACT)                                                                                    \
     do {                                                                                                         \
-        rc = set_smem<1000 + HDM + EXACT>(attention_decode_kernel<HDM, false, EXACT>, smem, "attention_decode"); \
+        rc = set_smem<1000 + HDM + EXACT>(attention_decode_kernel<HDM, false, EXACT, 3>, smem, "attention_decode"); \
         if (rc) return rc;                                                                                       \
-        lp_launch(attention_decode_kernel<HDM, false, EXACT>, grid, 128, smem, stream,                           \
+        lp_launch(attention_decode_kernel<HDM, false, EXACT, 3>, grid, 128, smem, stream,                           \
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml, \
             (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, head_groups,         \
             FusedDecodeArgs{});                                                                                  \
@@ -495,24 +501,31 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
     const int stage = 2 * PAGE * hd * 2;
     const int extra = (16 * hd + 2 * hd) * 2 + 256 * 4;
     const int merge = (128 + 64 * hd) * 4;
-    const int smem = (3 * stage > merge ? 3 * stage : merge) + extra;
+    // long shares of small heads keep six pages in flight instead of three, unless there are CTAs enough
+    // to hide the latency by their number (the deeper ring halves how many fit an SM)
+    const int stages = (hd <= 64 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= 2 * 148) ? 6 : 3;
+    const int smem = (stages * stage > merge ? stages * stage : merge) + extra;
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)B * H * num_splits * hd;
     dim3 grid(num_splits, G * head_groups, B);
     const float scale_log2 = scale * 1.4426950408889634f;
     FusedDecodeArgs fused{qkv, ld, inv_freq, rd, interleaved, write_kv ? (__nv_bfloat16*)pages : nullptr, counters,
                           row_sumsq, norm_eps, norm_width};
-#define LP_DECODE_FUSED(HDM, EXACT)                                                                              \
+#define LP_DECODE_FUSED(HDM, EXACT, ST)                                                                          \
     do {                                                                                                         \
-        rc = set_smem<3000 + HDM + EXACT>(attention_decode_kernel<HDM, true, EXACT>, smem, "attention_decode_fused"); \
+        rc = set_smem<3000 + HDM + EXACT + 7 * ST>(attention_decode_kernel<HDM, true, EXACT, ST>, smem,          \
+                                                   "attention_decode_fused");                                    \
         if (rc) return rc;                                                                                       \
-        lp_launch(attention_decode_kernel<HDM, true, EXACT>, grid, 128, smem, stream, (const __nv_bfloat16*)nullptr, \
-                  (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml,                   \
-                  (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, head_groups,   \
-                  fused);                                                                                        \
+        lp_launch(attention_decode_kernel<HDM, true, EXACT, ST>, grid, 128, smem, stream,                        \
+                  (const __nv_bfloat16*)nullptr, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len,     \
+                  part_o, part_ml, (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split,           \
+                  num_splits, head_groups, fused);                                                               \
     } while (0)
-    if (hd == 64) LP_DECODE_FUSED(64, 64); else if (hd == 128) LP_DECODE_FUSED(128, 128);
-    else if (hd <= 64) LP_DECODE_FUSED(64, 0); else if (hd <= 128) LP_DECODE_FUSED(128, 0); else LP_DECODE_FUSED(256, 0);
+    if (hd == 64) { if (stages == 6) LP_DECODE_FUSED(64, 64, 6); else LP_DECODE_FUSED(64, 64, 3); }
+    else if (hd == 128) LP_DECODE_FUSED(128, 128, 3);
+    else if (hd <= 64) { if (stages == 6) LP_DECODE_FUSED(64, 0, 6); else LP_DECODE_FUSED(64, 0, 3); }
+    else if (hd <= 128) LP_DECODE_FUSED(128, 0, 3);
+    else LP_DECODE_FUSED(256, 0, 3);
 #undef LP_DECODE_FUSED
     return lp_check_launch("attention_decode_fused");
 }

@@ -503,11 +503,11 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
 
 
 def decode_split(batch: int, num_kv_heads: int, num_heads: int, table_width: int):
-    """How a decode step's pages are shared out over CTAs: (pages per share, shares)."""
+    """How a decode step's pages are shared out over CTAs: (pages per share, shares). A share and the
+    merge of shares cost several dependent round trips to memory, so a sequence is cut only into shares
+    of at least 8 pages, and no further than fills the GPU twice."""
     groups = batch * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
-    if table_width <= 2 or groups >= 4 * NUM_SMS:
-        return table_width, 1                   # nothing to share out, or sequences enough to fill the GPU
-    shares = max(1, min(-(-table_width // 2), -(-3 * NUM_SMS // groups)))
+    shares = max(1, min(table_width // 8, -(-2 * NUM_SMS // groups)))
     per = -(-table_width // shares)
     return per, -(-table_width // per)
 
