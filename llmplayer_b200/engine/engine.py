@@ -16,7 +16,7 @@ import torch
 from ..cache.pages import PAGE_SIZE
 from ..cache.sequence_cache import SequenceCache
 from ..config.registry import ArchitectureConfig, load_config
-from ..errors import RequestError
+from ..errors import LLMPlayerError, RequestError
 from ..kernels import ops
 from ..parts.base import Runtime
 from ..weights.loader import load_tensors
@@ -45,6 +45,7 @@ class Engine:
         self.use_graphs = True
         self._graphs = {}
         self._last_ctx: Optional[StepContext] = None
+        self._prepared = None          # (context, page tables): the next decode step's pages, reserved ahead
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -202,10 +203,33 @@ class Engine:
                 return None
         if any(self.cache.length(s.slot) != s.first_position + 1 for s in last.sequences):
             return None                         # something else ran on these slots meanwhile
-        self.cache.reserve(slots, [1] * len(slots))
-        if not last.advance(tokens, self.cache.page_tables(slots)):
+        prepared, self._prepared = self._prepared, None
+        if prepared is not None and prepared[0] is last:
+            tables = prepared[1]                # reserved while the device was still busy with the last step
+        else:
+            self.cache.reserve(slots, [1] * len(slots))
+            tables = self.cache.page_tables(slots)
+        if not last.advance(tokens, tables):
             return None
         return last
+
+    def _prepare_continue(self) -> None:
+        """Called while the device works on the step just launched: reserve the pages of the next
+        one-token step of the same sequences, which needs no token. Harmless if that step never comes."""
+        self._prepared = None
+        last = self._last_ctx
+        if last is None:
+            return
+        slots = [s.slot for s in last.sequences]
+        for s in last.sequences:
+            if (not self.cache.slots.is_held(s.slot) or self.cache.length(s.slot) != s.first_position + 1
+                    or s.first_position + 2 > self.context_length):
+                return
+        try:
+            self.cache.reserve(slots, [1] * len(slots))
+        except LLMPlayerError:
+            return                              # the step itself will report it
+        self._prepared = (last, self.cache.page_tables(slots))
 
     # ------------------------------------------------------------------ generation
     def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers) -> List[int]:
@@ -213,7 +237,7 @@ class Engine:
         if self._sampler is None:
             from ..sampling.sampler import BatchSampler
             self._sampler = BatchSampler(self.vocab_size, self.runtime.device)
-        return self._sampler.sample(logits, rows, samplers)
+        return self._sampler.sample(logits, rows, samplers, while_waiting=self._prepare_continue)
 
     def fits(self, token_counts: Sequence[int]) -> bool:
         """Whether sequences of these final lengths can be held at once, beside what is held now."""

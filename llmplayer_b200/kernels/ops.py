@@ -110,8 +110,19 @@ def _check(lib: ctypes.CDLL, code: int) -> None:
         raise KernelError(lib.lp_last_error().decode("utf-8", "replace") or f"kernel call failed with code {code}")
 
 
+_device_index = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The raw handle of torch's current stream (asked of torch's C layer directly: this is on the path of
+    every launch)."""
+    global _device_index
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    try:
+        return torch._C._cuda_getCurrentRawStream(_device_index)
+    except AttributeError:                        # a torch without that entry
+        return torch.cuda.current_stream().cuda_stream
 
 
 def _code(t: torch.Tensor, what: str) -> int:

@@ -92,12 +92,29 @@ class BatchSampler:
         self.device = device
         self._work = None
         self._out = None
+        self._host = None            # page-locked landing place of the results
+        self._done = None
         self._constant = {}          # greedy batches without logit edits: parameters stay on the device
         self._dummy = None
         self.last_h2d_bytes = 0
         self.last_d2h_bytes = 0
 
-    def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers: Sequence[SequenceSampler]) -> List[int]:
+    def _read_back(self, count: int, while_waiting) -> torch.Tensor:
+        """The first ``count`` result words on the host. The copy is asynchronous into page-locked memory;
+        ``while_waiting`` (a callable or None) runs on the host until the device has got there."""
+        if self._host is None or self._host.numel() < count:
+            self._host = torch.empty(max(count, 64), dtype=torch.int32).pin_memory()
+            self._done = torch.cuda.Event()
+        host = self._host[:count]
+        host.copy_(self._out[:count], non_blocking=True)
+        self._done.record()
+        if while_waiting is not None:
+            while_waiting()
+        self._done.synchronize()
+        return host
+
+    def sample(self, logits: torch.Tensor, rows: Sequence[int], samplers: Sequence[SequenceSampler],
+               while_waiting=None) -> List[int]:
         B = len(samplers)
         dev = self.device
         if self._work is None or self._work.shape[0] < B:
@@ -114,7 +131,7 @@ class BatchSampler:
             ops.argmax(logits, self._work.view(-1), out_tok)
             self.last_h2d_bytes = 0
             self.last_d2h_bytes = 4 * B
-            chosen = out_tok.cpu().tolist()
+            chosen = self._read_back(B, while_waiting).tolist()
             for s, tok in zip(samplers, chosen):
                 s.accept(tok, 1.0)
             return chosen
@@ -153,7 +170,7 @@ class BatchSampler:
                     self._constant.clear()
                 self._constant[key] = params_dev
         ops.sample(logits, self._work[:B], params_dev, edit_tok, edit_sub, edit_fac, out_tok, out_prob)
-        host = self._out[:2 * B].cpu()                       # one copy back: tokens, then probabilities
+        host = self._read_back(2 * B, while_waiting)         # one copy back: tokens, then probabilities
         self.last_d2h_bytes = 8 * B
         chosen = host[:B].tolist()
         probs = host[B:].view(torch.float32).tolist()
