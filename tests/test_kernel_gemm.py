@@ -138,3 +138,73 @@ def test_accumulate_with_the_following_norm(M, N, K):
         want = ref * torch.rsqrt((ref * ref).mean(dim=1, keepdim=True) + 1e-5) * gain.double()
         assert rel_err(normed, want) < 8e-3                  # one bfloat16 rounding
         assert float(junk.abs().sum()) == 0.0
+
+
+# --------------------------------------------------------------------------- a handful of tokens
+FEW_SHAPES = [(1, 64, 64), (3, 200, 72), (8, 3072, 2048), (9, 130, 200), (16, 520, 328), (5, 96, 1000)]
+
+
+@pytest.mark.parametrize("M,N,K", FEW_SHAPES)
+@pytest.mark.parametrize("mode", ["store", "accumulate", "swiglu"])
+def test_few_token_product(M, N, K, mode):
+    """The mma.sync kernel for at most 16 rows with bfloat16 activations, against a float64 product."""
+    from llmplayer_b200.kernels import ops
+    torch.manual_seed(M * 11 + N + K)
+    dev = "cuda:0"
+    code = {"store": ops.STORE, "accumulate": ops.ACCUMULATE, "swiglu": ops.SWIGLU}[mode]
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    w = (torch.randn(N * (2 if mode == "swiglu" else 1), K, device=dev) / K ** 0.5).to(torch.bfloat16)
+    w_kernel = ops.interleave_gate_up(w[:N], w[N:]) if mode == "swiglu" else w
+    out0 = torch.randn(M, N, device=dev) if mode == "accumulate" else torch.zeros(M, N, device=dev)
+    out = out0.clone()
+    side = torch.full((37,), 3.0, device=dev)
+    ops.gemm_few(a, w_kernel, out, code, zero=side)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    assert rel_err(out, reference(a, w, code, out0)) < 1e-5
+    assert float(side.abs().max()) == 0.0, "the buffer to clear on the side was not cleared"
+
+
+@pytest.mark.parametrize("M,N,K", FEW_SHAPES)
+@pytest.mark.parametrize("mode", ["store", "swiglu"])
+def test_few_token_product_applies_the_norm(M, N, K, mode):
+    """x float32 -> RMS norm (gain, eps) -> product, in one kernel: either the kernel applies the row
+    factor itself, or (K shared out over CTAs) it reports the rows' sums of squares instead."""
+    from llmplayer_b200.kernels import ops
+    torch.manual_seed(M * 13 + N + K)
+    dev = "cuda:0"
+    code = {"store": ops.STORE, "swiglu": ops.SWIGLU}[mode]
+    eps = 3e-6
+    x = torch.randn(M, K, device=dev) * 3.0
+    x[0, 5 % K] = 40.0                                  # a row whose factor differs clearly from the others'
+    gain = 1.0 + 0.3 * torch.randn(K, device=dev)
+    w = (torch.randn(N * (2 if mode == "swiglu" else 1), K, device=dev) / K ** 0.5).to(torch.bfloat16)
+    w_kernel = ops.interleave_gate_up(w[:N], w[N:]) if mode == "swiglu" else w
+    out = torch.zeros(M, N, device=dev)
+    sumsq = torch.zeros(16, device=dev)
+    deferred = ops.gemm_few(x, w_kernel, out, code, norm=(gain, eps), sumsq=sumsq)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    xd = x.double()
+    factor = 1.0 / torch.sqrt((xd * xd).mean(dim=1, keepdim=True) + eps)
+    # the kernel rounds x * gain to bfloat16 and applies the row factor in float32 afterwards
+    operand = (x * gain).to(torch.bfloat16)
+    ref = reference(operand, w, code) if mode == "store" else None
+    if mode == "store":
+        if deferred:
+            assert rel_err(sumsq[:M], (xd * xd).sum(dim=1)) < 1e-5
+            got = out.double() * factor
+        else:
+            got = out.double()
+        assert rel_err(got, ref * factor) < 1e-5
+    else:
+        assert not deferred
+        F = N
+        g = (operand.double() @ w.double()[:F].T) * factor
+        u = (operand.double() @ w.double()[F:].T) * factor
+        assert rel_err(out, (g / (1 + torch.exp(-g))) * u) < 1e-5
+    # and against the norm as the model defines it (rounding of the normed row to bfloat16 differs slightly)
+    normed = (xd * factor * gain.double())
+    full = reference(normed.float().to(torch.bfloat16), w, code)
+    got = out.double() * factor if deferred else out.double()
+    assert rel_err(got, full) < 2e-2
