@@ -345,20 +345,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // features, so the gated activation needs no exchange.
 //
 // XNORM: the activations are the float32 residual stream and the product applies an RMS norm on the way in.
-// The tile of x comes as float32 (two boxes of 16 rows x 32 values per k-block); a consumer forms its B
-// fragment as bfloat16(x * gain) and the first consumer warp sums x^2 per token. The row's factor
+// The tile of x comes as float32 (two boxes of rows x 32 values per k-block) with the gain's 64 values; the
+// a fifth warp turns it into the bfloat16 operand bfloat16(x * gain) a stage ahead of the consumers (a
+// half-warp per token row, which also sums x^2) and hands it over through a barrier of its own. The row's factor
 // 1 / sqrt(mean x^2 + eps) is a scalar per token, so it is applied to the sums at the end: by this kernel when
 // a CTA sees the whole K range, else (K shared out over CTAs, partial sums meeting in atomics) the CTAs
 // with blockIdx.x == 0 add their share of the sum of squares to `sumsq_out` and the reader of the output
-// applies the factor. `zero` (optional) is cleared on the side by one CTA.
-constexpr int FEW_THREADS = 160;          // warp 0: TMA; warps 1-4: consumers
+// applies the factor. `zero` (optional) is cleared on the side, a slice by every CTA.
+constexpr int FEW_THREADS = 160;          // warp 0: TMA; warps 1-4: consumers; XNORM adds warp 5, which makes the operand
 constexpr int FEW_W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
-template <bool XNORM> struct FewTile {
-    static constexpr int X_BYTES = XNORM ? 2 * 16 * 128 : 16 * BLOCK_K * 2;
+template <bool XNORM, int NT> struct FewTile {
+    static constexpr int X_ROWS = NT <= 2 ? 16 : 8 * NT;          // rows of the activation tile (tokens, padded)
+    static constexpr int X_BOX_BYTES = X_ROWS * 128;              // one box: X_ROWS x 128 bytes
+    static constexpr int X_BYTES = XNORM ? 2 * X_BOX_BYTES : X_BOX_BYTES;
     static constexpr int GAIN_BYTES = XNORM ? 1024 : 0;           // 64 floats of gain per k-block, padded to the tiles' alignment
     static constexpr int STAGE_BYTES = FEW_W_BYTES + X_BYTES + GAIN_BYTES;
-    static constexpr int STAGES = XNORM ? 5 : 6;                  // two CTAs fit an SM either way
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr int FIT = (110 * 1024) / STAGE_BYTES;        // two CTAs fit an SM
+    static constexpr int STAGES = FIT > 6 ? 6 : FIT;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512;
 };
 
 struct NormBefore {
@@ -382,20 +386,23 @@ __device__ __forceinline__ void mma_m16n8k16(float* c, const uint32_t* a, uint32
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// NT: n-tiles of 8 tokens (1 or 2). MODE: STORE or SWIGLU (interleaved rows). out as in the tcgen05 kernel.
+// NT: n-tiles of 8 tokens (1, 2, 4 or 8). MODE: STORE or SWIGLU (interleaved rows). out as in the tcgen05 kernel.
 template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
-__global__ void __launch_bounds__(FEW_THREADS, 2)
+__global__ void __launch_bounds__(FEW_THREADS + (XNORM ? 32 : 0), 2)
 gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
                    int* __restrict__ status, NormAfter norm, NormBefore before) {
-    constexpr int FEW_STAGES = FewTile<XNORM>::STAGES;
-    constexpr int FEW_STAGE_BYTES = FewTile<XNORM>::STAGE_BYTES;
+    using FT = FewTile<XNORM, NT>;
+    constexpr int FEW_STAGES = FT::STAGES;
+    constexpr int FEW_STAGE_BYTES = FT::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + FEW_STAGES * FEW_STAGE_BYTES);
     uint64_t* empty = full + FEW_STAGES;
-    volatile uint32_t* failed = (volatile uint32_t*)(empty + FEW_STAGES);
-    float* row_scale = (float*)(failed + 1);          // [16], XNORM
+    uint64_t* made = empty + FEW_STAGES;              // XNORM: the bfloat16 operand of the stage is ready
+    volatile uint32_t* failed = (volatile uint32_t*)(made + FEW_STAGES);
+    float* row_scale = (float*)(failed + 1);          // [8 NT], XNORM
+    constexpr int NTHREADS = FEW_THREADS + (XNORM ? 32 : 0);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kb_begin = blockIdx.z * k_blocks_per_split;
@@ -407,16 +414,74 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         *failed = 0;
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-        for (int s = 0; s < FEW_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); }
+        for (int s = 0; s < FEW_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); mbar_init(&made[s], 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    if (warp == 0) {
+    if (XNORM && warp == 5) {
+        // ------------------------------------------------------------ operand maker
+        // float32 tile: value k of the k-block lies in box k / 32, 16-byte chunk (k % 32) / 4 of its row; the gain
+        // beyond K is unset (and x is zero there). Per k-block, thread `lane` takes quads lane, lane + 32, ...:
+        // row = index / 16, so a half-warp shares a row and the warp covers two rows per pass.
+        constexpr int PASSES = 4 * NT;
+        float ss[PASSES];
+#pragma unroll
+        for (int it = 0; it < PASSES; ++it) ss[it] = 0.f;
+        bool ok = true;
+        for (int i = 0; i < nkb && ok; ++i) {
+            const int s = i % FEW_STAGES;
+            const uint32_t phase = (i / FEW_STAGES) & 1;
+            if (!mbar_wait(&full[s], phase)) { if (lane == 0) atomicExch(status, 4); *failed = 1; ok = false; break; }
+            uint8_t* x_tile = smem + s * FEW_STAGE_BYTES + FEW_W_BYTES;
+            const float* gain_tile = reinterpret_cast<const float*>(x_tile + FT::X_BYTES);
+            const int k_abs = (kb_begin + i) * BLOCK_K;
+            // the bfloat16 operand takes the place of the first float32 box: everything is read first
+            uint2 packed[PASSES];
+#pragma unroll
+            for (int it = 0; it < PASSES; ++it) {
+                const int idx = lane + it * 32;
+                const int row = idx >> 4, k = (idx & 15) * 4;
+                const float4 v = *reinterpret_cast<const float4*>(
+                    x_tile + (k >> 5) * FT::X_BOX_BYTES + row * 128 + ((((k & 31) >> 2) ^ (row & 7)) << 4));
+                float4 gn = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (k_abs + k < before.K) gn = *reinterpret_cast<const float4*>(gain_tile + k);
+                ss[it] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * gn.x, v.y * gn.y);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * gn.z, v.w * gn.w);
+                packed[it].x = *reinterpret_cast<uint32_t*>(&lo);
+                packed[it].y = *reinterpret_cast<uint32_t*>(&hi);
+            }
+            __syncwarp();                              // every lane has read its share of the float32 tile
+#pragma unroll
+            for (int it = 0; it < PASSES; ++it) {
+                const int idx = lane + it * 32;
+                const int row = idx >> 4, k = (idx & 15) * 4;
+                *reinterpret_cast<uint2*>(x_tile + row * 128 + (((k >> 3) ^ (row & 7)) << 4) + (k & 7) * 2) = packed[it];
+            }
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&made[s])) : "memory");
+        }
+        // sum x^2 of a token row: over the half-warp that converted it
+#pragma unroll
+        for (int it = 0; it < PASSES; ++it) {
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) ss[it] += __shfl_xor_sync(0xffffffffu, ss[it], o);
+        }
+        if ((lane & 15) == 0) {
+#pragma unroll
+            for (int it = 0; it < PASSES; ++it) {
+                const int row = (lane >> 4) + 2 * it;
+                if (gridDim.z == 1) row_scale[row] = 1.0f / sqrtf(ss[it] / (float)before.K + before.eps);
+                else if (blockIdx.x == 0 && ok && row < tokens) atomicAdd(before.sumsq_out + row, ss[it]);
+            }
+        }
+        if (gridDim.z == 1) asm volatile("bar.sync 1, 160;" ::: "memory");   // with the four consumer warps
+    } else if (warp == 0) {
         if (lane == 0) {
             // weights are written by no kernel of a step: the first ring is requested before waiting for
             // the previous kernel, the activation tiles only after it
-            constexpr int TILE_BYTES = FEW_W_BYTES + FewTile<XNORM>::X_BYTES;
+            constexpr int TILE_BYTES = FEW_W_BYTES + FT::X_BYTES;
             // what nothing in the step writes (weights, the norm's gain) ...
             auto load_constants = [&](int i, int s) {
                 uint8_t* stage = smem + s * FEW_STAGE_BYTES;
@@ -432,7 +497,7 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 uint8_t* xs = smem + s * FEW_STAGE_BYTES + FEW_W_BYTES;
                 const int k = (kb_begin + i) * BLOCK_K;
                 tma_load_2d(xs, &map_x, k, 0, &full[s]);
-                if (XNORM) tma_load_2d(xs + 2048, &map_x, k + 32, 0, &full[s]);
+                if (XNORM) tma_load_2d(xs + FT::X_BOX_BYTES, &map_x, k + 32, 0, &full[s]);
             };
             const int early = min(nkb, FEW_STAGES);
             for (int i = 0; i < early; ++i) load_constants(i, i);
@@ -458,11 +523,10 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         lp_grid_wait();                        // the epilogue adds into / overwrites what earlier kernels use
         const int w = warp - 1;
         const int g = lane >> 2, t = lane & 3;
-        if (before.zero != nullptr && blockIdx.x == 0 && blockIdx.z == 0)
-            for (int i = threadIdx.x - 32; i < before.zero_count; i += 128) before.zero[i] = 0.f;
-        float ss[NT];                          // XNORM, warp w == 0: this lane's share of sum x^2 of token g + 8 nt
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) ss[nt] = 0.f;
+        if (before.zero != nullptr) {          // all CTAs share the clearing
+            const int cta = blockIdx.z * gridDim.x + blockIdx.x, ctas = gridDim.x * gridDim.z;
+            for (int i = cta * 128 + threadIdx.x - 32; i < before.zero_count; i += ctas * 128) before.zero[i] = 0.f;
+        }
         float acc[2][NT][4];
 #pragma unroll
         for (int mt = 0; mt < 2; ++mt)
@@ -475,43 +539,23 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int i = 0; i < nkb; ++i) {
             const int s = i % FEW_STAGES;
             const uint32_t phase = (i / FEW_STAGES) & 1;
-            if (!mbar_wait(&full[s], phase)) { if (lane == 0) atomicExch(status, 2); *failed = 1; ok = false; break; }
+            if (!mbar_wait(&full[s], phase)) { if (lane == 0) atomicExch(status, 2); *failed = 1; ok = false; }
             const uint32_t w_tile = smem_u32(smem + s * FEW_STAGE_BYTES);
             const uint8_t* x_tile = smem + s * FEW_STAGE_BYTES + FEW_W_BYTES;
+            if (XNORM) {
+                if (ok && !mbar_wait(&made[s], phase)) { if (lane == 0) atomicExch(status, 5); *failed = 1; ok = false; }
+                // the bfloat16 operand now lies where the first float32 box was
+            }
+            if (!ok) break;
 #pragma unroll
             for (int ks = 0; ks < BLOCK_K / 16; ++ks) {
                 uint32_t b[NT][2];
-                if (XNORM) {
-                    // float32 tile: value k of the k-block lies in box k / 32, 16-byte chunk (k % 32) / 4 of its row
-                    const int k_lo = ks * 16 + 2 * t, k_hi = k_lo + 8;
-                    const int k_abs = (kb_begin + i) * BLOCK_K;
-                    // the gain of this k-block came with the stage; beyond K it is unset (and x is zero there)
-                    const float* gain_tile = reinterpret_cast<const float*>(x_tile + FewTile<XNORM>::X_BYTES);
-                    float2 g_lo = make_float2(0.f, 0.f), g_hi = g_lo;
-                    if (k_abs + k_lo < before.K) g_lo = *reinterpret_cast<const float2*>(gain_tile + k_lo);
-                    if (k_abs + k_hi < before.K) g_hi = *reinterpret_cast<const float2*>(gain_tile + k_hi);
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        const int row = g + 8 * nt;
-                        const uint8_t* xr = x_tile + row * 128;
-                        const float2 lo = *reinterpret_cast<const float2*>(
-                            xr + (k_lo >> 5) * 2048 + ((((k_lo & 31) >> 2) ^ g) << 4) + (k_lo & 3) * 4);
-                        const float2 hi = *reinterpret_cast<const float2*>(
-                            xr + (k_hi >> 5) * 2048 + ((((k_hi & 31) >> 2) ^ g) << 4) + (k_hi & 3) * 4);
-                        ss[nt] += lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
-                        __nv_bfloat162 p = __floats2bfloat162_rn(lo.x * g_lo.x, lo.y * g_lo.y);
-                        b[nt][0] = *reinterpret_cast<uint32_t*>(&p);
-                        p = __floats2bfloat162_rn(hi.x * g_hi.x, hi.y * g_hi.y);
-                        b[nt][1] = *reinterpret_cast<uint32_t*>(&p);
-                    }
-                } else {
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) {
-                        const int row = g + 8 * nt;                    // token; row & 7 == g
-                        const uint8_t* xr = x_tile + row * 128 + t * 4;
-                        b[nt][0] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks) ^ g) << 4));
-                        b[nt][1] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks + 1) ^ g) << 4));
-                    }
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int row = g + 8 * nt;                    // token; row & 7 == g
+                    const uint8_t* xr = x_tile + row * 128 + t * 4;
+                    b[nt][0] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks) ^ g) << 4));
+                    b[nt][1] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks + 1) ^ g) << 4));
                 }
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
@@ -526,30 +570,14 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[s])) : "memory");
         }
         ok = ok && *failed == 0;
-        if (XNORM) {
-            // sum x^2 of token g + 8 nt: over the four lanes that share g
+        if (XNORM && gridDim.z == 1) {
+            asm volatile("bar.sync 1, 160;" ::: "memory");             // the operand maker has written the rows' factors
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 1);
-                ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 2);
-            }
-            if (gridDim.z == 1) {
-                if (w == 0 && t == 0) {
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) row_scale[g + 8 * nt] = 1.0f / sqrtf(ss[nt] / (float)before.K + before.eps);
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");         // the four consumer warps
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) acc[mt][nt][e] *= row_scale[nt * 8 + 2 * t + (e & 1)];
-            } else if (blockIdx.x == 0 && w == 0 && t == 0 && ok) {
+            for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
-                    if (g + 8 * nt < tokens) atomicAdd(before.sumsq_out + g + 8 * nt, ss[nt]);
-            }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[mt][nt][e] *= row_scale[nt * 8 + 2 * t + (e & 1)];
         }
         // c fragment: c0, c1 = (row g, tokens 2t, 2t + 1); c2, c3 = (row g + 8, same tokens)
         if (ok) {
@@ -590,14 +618,14 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (ATOMIC) __threadfence();
     }
     __syncthreads();
-    if (ATOMIC) norm_after_tail<FEW_THREADS>(norm, out, tokens, features, ldc);
+    if (ATOMIC) norm_after_tail<NTHREADS>(norm, out, tokens, features, ldc);
 }
 
 template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
 int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
                   int splits, int* status, const NormAfter& norm, const NormBefore& before, cudaStream_t stream) {
     auto kernel = gemm_fewtok_kernel<NT, MODE, OUT_BF16, ATOMIC, XNORM>;
-    constexpr int FEW_SMEM_BYTES = FewTile<XNORM>::SMEM_BYTES;
+    constexpr int FEW_SMEM_BYTES = FewTile<XNORM, NT>::SMEM_BYTES;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FEW_SMEM_BYTES);
@@ -609,8 +637,8 @@ int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int t
     const int grid_z = (k_blocks + per_split - 1) / per_split;
     const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;
     dim3 grid((features + per_cta - 1) / per_cta, 1, grid_z);
-    cudaError_t err = lp_launch(kernel, grid, FEW_THREADS, FEW_SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
-                                k_blocks, per_split, status, norm, before);
+    cudaError_t err = lp_launch(kernel, grid, FEW_THREADS + (XNORM ? 32 : 0), FEW_SMEM_BYTES, stream, mw, mx, out, tokens,
+                                features, ldc, k_blocks, per_split, status, norm, before);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_fewtok: %s", cudaGetErrorString(err));
         return (int)err;
@@ -968,7 +996,7 @@ extern "C" int lp_gemm_tcgen05(const void* X, const void* W, void* out, int out_
     }
 }
 
-// A product for at most 16 tokens (the mma.sync kernel above) with what a decode step fuses around it.
+// A product for at most 64 tokens (the mma.sync kernel above) with what a decode step fuses around it.
 // x_dtype LP_F32: X is the float32 residual stream and the product applies the RMS norm (gain, eps) on the
 // way in; with splits > 1 the output then still lacks the rows' factors and `sumsq_out` [tokens] (zero before
 // the call) receives sum x^2 per token for the reader to apply them. x_dtype LP_BF16: X as in lp_gemm_tcgen05.
@@ -978,7 +1006,7 @@ extern "C" int lp_gemm_fewtok(const void* X, int x_dtype, const void* W, void* o
                               const float* gain, float eps, float* sumsq_out, float* zero, int zero_count,
                               cudaStream_t stream) {
     if (tokens <= 0 || features <= 0) return 0;
-    if (tokens > 16) LP_REFUSE("gemm_fewtok: %d tokens (at most 16)", tokens);
+    if (tokens > 64) LP_REFUSE("gemm_fewtok: %d tokens (at most 64)", tokens);
     if (K <= 0 || K % 8) LP_REFUSE("gemm: inner size %d must be a positive multiple of 8 for the tensor-core path", K);
     const bool xnorm = x_dtype == LP_F32;
     if (x_dtype != LP_F32 && x_dtype != LP_BF16) LP_REFUSE("gemm_fewtok: activation dtype code %d", x_dtype);
@@ -1000,14 +1028,16 @@ extern "C" int lp_gemm_fewtok(const void* X, int x_dtype, const void* W, void* o
     CUtensorMap mw, mx;
     int rc = make_map(&mw, W, w_rows, K, ldw, BLOCK_FEAT);
     if (rc) return rc;
-    rc = xnorm ? make_map_f32(&mx, X, tokens, K, ldx, 16) : make_map(&mx, X, tokens, K, ldx, 16);
+    const int nt = tokens <= 8 ? 1 : tokens <= 16 ? 2 : tokens <= 32 ? 4 : 8;
+    const int x_rows = nt <= 2 ? 16 : 8 * nt;
+    rc = xnorm ? make_map_f32(&mx, X, tokens, K, ldx, x_rows) : make_map(&mx, X, tokens, K, ldx, x_rows);
     if (rc) return rc;
     const NormAfter after{};
     const NormBefore before{gain, eps, K, sumsq_out, zero, zero ? zero_count : 0};
     const bool bf = out_dtype == LP_BF16;
     const int mmode = mode == LP_GEMM_SWIGLU ? LP_GEMM_SWIGLU : LP_GEMM_STORE;
 #define LP_FEW(NT, XN) dispatch_fewtok<NT, XN>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, status, after, before, stream)
-    if (xnorm) return tokens <= 8 ? LP_FEW(1, true) : LP_FEW(2, true);
-    return tokens <= 8 ? LP_FEW(1, false) : LP_FEW(2, false);
+    if (xnorm) return nt == 1 ? LP_FEW(1, true) : nt == 2 ? LP_FEW(2, true) : nt == 4 ? LP_FEW(4, true) : LP_FEW(8, true);
+    return nt == 1 ? LP_FEW(1, false) : nt == 2 ? LP_FEW(2, false) : nt == 4 ? LP_FEW(4, false) : LP_FEW(8, false);
 #undef LP_FEW
 }

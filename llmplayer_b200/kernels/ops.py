@@ -398,7 +398,13 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
     return out
 
 
-FEW_TOKENS = 16
+import os as _os
+FEW_TOKENS_MAX = 64                  # what the few-token kernel takes
+# Up to where the parts choose it with the norm inside. Measured at the 1B shape: at 8 tokens the step
+# takes 0.79 ms against 0.85 ms with separate norm kernels; from 9 tokens on the float32 rows of x that every
+# CTA then reads (twice the bytes of the normed bfloat16 rows, the same lines for all CTAs) cost more than the
+# norm kernels they save (16 tokens: 0.92 ms against 0.88 ms).
+FEW_TOKENS = int(_os.environ.get("LLMPLAYER_B200_FEW_TOKENS", "8"))
 
 
 def gemm_few(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, norm=None,
@@ -417,7 +423,7 @@ def gemm_few(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = ST
     M, K = x.shape
     N = out.shape[1]
     rows = 128 * (-(-N // 64)) if mode == SWIGLU else N
-    if w.shape != (rows, K) or out.shape[0] != M or M > FEW_TOKENS:
+    if w.shape != (rows, K) or out.shape[0] != M or M > FEW_TOKENS_MAX:
         raise KernelError(f"gemm_few: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}, mode {mode}")
     _, splits = gemm_plan(M, N, K, mode)
     if mode == STORE and splits > 1 and out.dtype != torch.float32:

@@ -141,13 +141,14 @@ def test_accumulate_with_the_following_norm(M, N, K):
 
 
 # --------------------------------------------------------------------------- a handful of tokens
-FEW_SHAPES = [(1, 64, 64), (3, 200, 72), (8, 3072, 2048), (9, 130, 200), (16, 520, 328), (5, 96, 1000)]
+FEW_SHAPES = [(1, 64, 64), (3, 200, 72), (8, 3072, 2048), (9, 130, 200), (16, 520, 328), (5, 96, 1000),
+              (33, 200, 136), (64, 264, 520), (24, 2048, 2048)]
 
 
 @pytest.mark.parametrize("M,N,K", FEW_SHAPES)
 @pytest.mark.parametrize("mode", ["store", "accumulate", "swiglu"])
 def test_few_token_product(M, N, K, mode):
-    """The mma.sync kernel for at most 16 rows with bfloat16 activations, against a float64 product."""
+    """The mma.sync kernel for at most 64 rows with bfloat16 activations, against a float64 product."""
     from llmplayer_b200.kernels import ops
     torch.manual_seed(M * 11 + N + K)
     dev = "cuda:0"
@@ -181,7 +182,7 @@ def test_few_token_product_applies_the_norm(M, N, K, mode):
     w = (torch.randn(N * (2 if mode == "swiglu" else 1), K, device=dev) / K ** 0.5).to(torch.bfloat16)
     w_kernel = ops.interleave_gate_up(w[:N], w[N:]) if mode == "swiglu" else w
     out = torch.zeros(M, N, device=dev)
-    sumsq = torch.zeros(16, device=dev)
+    sumsq = torch.zeros(64, device=dev)
     deferred = ops.gemm_few(x, w_kernel, out, code, norm=(gain, eps), sumsq=sumsq)
     torch.cuda.synchronize()
     ops.check_kernel_status()
