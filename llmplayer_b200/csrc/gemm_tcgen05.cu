@@ -30,6 +30,7 @@
 #define LP_GEMM_ACCUMULATE 1
 #define LP_GEMM_SWIGLU 2
 #define LP_GEMM_SWIGLU_WIDE 3   // same result and weight layout; two accumulators, 128 output features per CTA
+#define LP_GEMM_SWIGLU_TOKM 4   // same again, persistent form only: 128 tokens are the MMA's M, 256 weight rows its N
 
 namespace {
 
@@ -40,7 +41,9 @@ constexpr int THREADS = 192;      // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5:
 // first 128-row tile, their up rows the second (the tensor map's box is 64 rows then).
 template <int MODE>
 __device__ __forceinline__ void load_weights(uint8_t* stage, const CUtensorMap* map_w, int k, int cta, uint64_t* bar) {
-    if (MODE == LP_GEMM_SWIGLU_WIDE) {
+    if (MODE == LP_GEMM_SWIGLU_TOKM) {
+        tma_load_2d(stage, map_w, k, cta * 256, bar);            // one box of 256 rows: gate | up | gate | up of 128 features
+    } else if (MODE == LP_GEMM_SWIGLU_WIDE) {
         const int row = cta * 256;
         tma_load_2d(stage, map_w, k, row, bar);                  // gate, features 128 cta ..
         tma_load_2d(stage + 8192, map_w, k, row + 128, bar);     // gate, features 128 cta + 64 ..
@@ -678,15 +681,17 @@ static bool fewtok_enabled() {
 // norm fusion: this form serves steps with hundreds of tokens.
 template <int BLOCK_TOK, int MODE>
 struct PersistentTile {
+    static constexpr bool TOKM = MODE == LP_GEMM_SWIGLU_TOKM;
     static constexpr int W_TILES = MODE == LP_GEMM_SWIGLU_WIDE ? 2 : 1;
-    static constexpr int W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
+    static constexpr int W_BYTES = (TOKM ? 256 : BLOCK_FEAT) * BLOCK_K * 2;
     static constexpr int X_BYTES = BLOCK_TOK * BLOCK_K * 2;
     static constexpr int STAGE_BYTES = W_TILES * W_BYTES + X_BYTES;
     static constexpr int STAGES = (196 * 1024) / STAGE_BYTES;
-    static constexpr int ACC_COLS = BLOCK_TOK * W_TILES;
-    static constexpr int TMEM_COLS = 2 * ACC_COLS;                // 512 for both uses below
+    static constexpr int ACC_COLS = TOKM ? 256 : BLOCK_TOK * W_TILES;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS;                // 512 for all uses below
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
     static_assert(TMEM_COLS == 512 || TMEM_COLS == 256, "two accumulators must fit tensor memory");
+    static_assert(!TOKM || BLOCK_TOK == 128, "tokens are the MMA's M");
 };
 
 template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
@@ -749,8 +754,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer: alternating accumulators
         if (lane == 0) {
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_TOK >> 3) << 17) |
-                                       ((uint32_t)(BLOCK_FEAT >> 4) << 24);
+            // TOKM: M = 128 tokens (A = the activation tile), N = 256 weight rows (B = the weight tile)
+            constexpr uint32_t idesc = T::TOKM
+                ? ((1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24))
+                : ((1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_TOK >> 3) << 17) |
+                   ((uint32_t)(BLOCK_FEAT >> 4) << 24));
             int it = 0, j = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++j) {
@@ -768,7 +776,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
                         const uint64_t step = (uint64_t)((k * UMMA_K * 2) >> 4);
-                        tcgen05_mma(acc, dw + step, dx + step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        if (T::TOKM) tcgen05_mma(acc, dx + step, dw + step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                        else tcgen05_mma(acc, dw + step, dx + step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
                         if (MODE == LP_GEMM_SWIGLU_WIDE) {
                             const uint64_t du = smem_desc(w_addr + T::W_BYTES);
                             tcgen05_mma(acc + BLOCK_TOK, du + step, dx + step, idesc, (kb > 0 || k > 0) ? 1u : 0u);
@@ -792,7 +801,50 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             if (ok && !mbar_wait(&acc_full[ab], (j >> 1) & 1)) { if (lane == 0) atomicExch(status, 24); *failed = 1; ok = false; }
             tcgen05_fence_after();
             const bool go = __all_sync(0xffffffffu, ok && *failed == 0);
-            if (go) {
+            if (go && T::TOKM) {
+                // lanes are tokens; columns 0..63 gate, 64..127 up of features 128 ft .. + 63, columns 128..255 the
+                // same for the next 64 features: a thread forms 32 outputs of its token at a time
+                const uint32_t lane_addr = tmem_base + ab * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+                const int t = tt * BLOCK_TOK + quarter * 32 + lane;
+#pragma unroll 1
+                for (int part = 0; part < 4; ++part) {
+                    const int half = part >> 1, c0 = (part & 1) * 32;
+                    uint32_t g[CHUNK], u[CHUNK];
+                    tmem_ld32(lane_addr + half * 128 + c0, g);
+                    tmem_ld32(lane_addr + half * 128 + 64 + c0, u);
+                    tmem_ld_wait();
+                    const int f0 = ft * 128 + half * 64 + c0;
+                    if (t < tokens && f0 < features) {
+                        uint32_t packed[CHUNK / 2];
+                        float vals[CHUNK];
+#pragma unroll
+                        for (int jj = 0; jj < CHUNK; ++jj) {
+                            const float gate = __uint_as_float(g[jj]);
+                            vals[jj] = __fdividef(gate, 1.0f + __expf(-gate)) * __uint_as_float(u[jj]);
+                        }
+                        const size_t at = (size_t)t * ldc + f0;
+                        if (OUT_BF16 && f0 + CHUNK <= features && (ldc & 7) == 0) {
+#pragma unroll
+                            for (int jj = 0; jj < CHUNK / 2; ++jj) {
+                                __nv_bfloat162 p = __floats2bfloat162_rn(vals[2 * jj], vals[2 * jj + 1]);
+                                packed[jj] = *reinterpret_cast<uint32_t*>(&p);
+                            }
+                            uint4* dst = reinterpret_cast<uint4*>((__nv_bfloat16*)out + at);
+#pragma unroll
+                            for (int q = 0; q < CHUNK / 8; ++q)
+                                dst[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                        } else {
+#pragma unroll
+                            for (int jj = 0; jj < CHUNK; ++jj) {
+                                if (f0 + jj < features) {
+                                    if (OUT_BF16) ((__nv_bfloat16*)out)[at + jj] = __float2bfloat16_rn(vals[jj]);
+                                    else ((float*)out)[at + jj] = vals[jj];
+                                }
+                            }
+                        }
+                    }
+                }
+            } else if (go) {
                 const uint32_t lane_addr = tmem_base + ab * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
                 const int f = ft * BLOCK_FEAT + quarter * 32 + lane;
                 const int tok0 = tt * BLOCK_TOK;
@@ -930,14 +982,14 @@ extern "C" int lp_gemm_persistent(const void* X, const void* W, void* out, int o
     const bool gated = mode == LP_GEMM_SWIGLU;
     const long long w_rows = gated ? 128LL * ((features + 63) / 64) : features;
     CUtensorMap mw, mx;
-    int rc = make_map(&mw, W, w_rows, K, ldw, gated ? 64 : BLOCK_FEAT);
+    int rc = make_map(&mw, W, w_rows, K, ldw, gated ? 256 : BLOCK_FEAT);
     if (rc) return rc;
     rc = make_map(&mx, X, tokens, K, ldx, gated ? 128 : 256);
     if (rc) return rc;
     const bool bf = out_dtype == LP_BF16;
     if (gated) {
-        if (bf) return launch_persistent<128, LP_GEMM_SWIGLU_WIDE, true, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
-        return launch_persistent<128, LP_GEMM_SWIGLU_WIDE, false, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+        if (bf) return launch_persistent<128, LP_GEMM_SWIGLU_TOKM, true, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+        return launch_persistent<128, LP_GEMM_SWIGLU_TOKM, false, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
     }
     if (mode == LP_GEMM_ACCUMULATE)
         return launch_persistent<256, LP_GEMM_STORE, false, true>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);

@@ -328,7 +328,9 @@ def _persistent_pays(tokens: int, features: int, k: int, mode: int) -> bool:
     separate_ctas = feat_tiles * -(-tokens // 128)
     fill_p = persistent_tiles / (-(-persistent_tiles // NUM_SMS) * NUM_SMS)
     fill_s = separate_ctas / (-(-separate_ctas // (2 * NUM_SMS)) * 2 * NUM_SMS)
-    return fill_p > fill_s + 0.02 or (k >= 4096 and fill_p >= fill_s)
+    # at equal fill the persistent form wins when the SMs are well filled (its tiles are twice as large and one
+    # tile's epilogue hides under the next one's MMAs) or the K loop is long
+    return fill_p > fill_s + 0.02 or (fill_p >= fill_s and (fill_p >= 0.8 or k >= 4096))
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, block_tok: int = 0,
