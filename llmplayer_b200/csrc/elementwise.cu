@@ -170,28 +170,47 @@ rope_cache_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
     }
     const int head_begin = blockIdx.y * heads_per_block;
     const int head_end = min(heads, head_begin + heads_per_block);
-    // a warp takes whole heads, its lanes the features: no division in the loop
+    // A warp takes whole heads. Rotated heads go pair by pair (each value is read once, both results of a
+    // pair are written by the lane that read them); several heads are in flight per lane.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    for (int head = head_begin + warp; head < head_end; head += nwarps) {
-        const bool is_q = head < H, is_v = head >= H + G;
-        const float* hsrc = src + (long long)head * hd;
-        for (int e = lane; e < hd; e += 32) {
-            float val = hsrc[e];
-            if (!is_v && e < rd) {
-                int pair, partner;
-                bool first;
-                if (interleaved) { pair = e >> 1; first = (e & 1) == 0; partner = e ^ 1; }
-                else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
-                const float other = hsrc[partner];
-                val = first ? val * cs[pair] - other * sn[pair] : other * sn[pair] + val * cs[pair];
-            }
-            if (is_q) {
-                q_out[((long long)t * H + head) * hd + e] = lp_from_float<TQ>(val);
+    const int rot_end = min(head_end, pages ? H + G : H);          // queries and keys are rotated, values are not
+    auto dest = [&](int head, int e) -> long long {
+        if (head < H) return ((long long)t * H + head) * hd + e;
+        const bool is_v = head >= H + G;
+        const int g = is_v ? head - H - G : head - H;
+        return page_base + ((long long)(is_v ? G : 0) + g) * page_size * hd + e;
+    };
+    for (int p = lane; p < half; p += 32) {
+        const int a = interleaved ? 2 * p : p, b = interleaved ? 2 * p + 1 : p + half;
+        const float c = cs[p], sv = sn[p];
+#pragma unroll 4
+        for (int head = head_begin + warp; head < rot_end; head += nwarps) {
+            const float* hsrc = src + (long long)head * hd;
+            const float xa = hsrc[a], xb = hsrc[b];
+            const float ra = xa * c - xb * sv, rb = xa * sv + xb * c;
+            if (head < H) {
+                q_out[dest(head, a)] = lp_from_float<TQ>(ra);
+                q_out[dest(head, b)] = lp_from_float<TQ>(rb);
             } else {
-                const int g = is_v ? head - H - G : head - H;
-                pages[page_base + ((long long)(is_v ? G : 0) + g) * page_size * hd + e] = lp_from_float<TKV>(val);
+                pages[dest(head, a)] = lp_from_float<TKV>(ra);
+                pages[dest(head, b)] = lp_from_float<TKV>(rb);
             }
         }
+    }
+    // what lies beyond the rotary width passes through
+    for (int e = rd + lane; e < hd; e += 32) {
+#pragma unroll 4
+        for (int head = head_begin + warp; head < rot_end; head += nwarps) {
+            const float val = src[(long long)head * hd + e];
+            if (head < H) q_out[dest(head, e)] = lp_from_float<TQ>(val);
+            else pages[dest(head, e)] = lp_from_float<TKV>(val);
+        }
+    }
+    // values
+    const int v_first = max(head_begin, H + G);
+    for (int head = v_first + warp; head < head_end; head += nwarps) {
+#pragma unroll 4
+        for (int e = lane; e < hd; e += 32) pages[dest(head, e)] = lp_from_float<TKV>(src[(long long)head * hd + e]);
     }
 }
 
