@@ -698,8 +698,19 @@ template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                        void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int feat_tiles,
-                       int num_tiles, int* __restrict__ status) {
+                       int num_tiles, int group_tok, int* __restrict__ status) {
     using T = PersistentTile<BLOCK_TOK, MODE>;
+    // Tiles are numbered in bands of `group_tok` token tiles, token tile first within a band: the CTAs that run
+    // at the same time then share a few weight tiles and a few activation tiles, which stay in L2 (feature
+    // tile first has every CTA on a weight tile of its own).
+    const int tok_tiles = num_tiles / feat_tiles;
+    auto tile_at = [&](int tile, int& ft, int& tt) {
+        const int per_band = group_tok * feat_tiles;
+        const int band = tile / per_band, r = tile - band * per_band;
+        const int rows = min(group_tok, tok_tiles - band * group_tok);     // token tiles of this band
+        ft = r / rows;
+        tt = band * group_tok + (r - ft * rows);
+    };
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + T::STAGES * T::STAGE_BYTES);
@@ -736,7 +747,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             int it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int ft = tile % feat_tiles, tt = tile / feat_tiles;
+                int ft, tt;
+                tile_at(tile, ft, tt);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % T::STAGES;
                     if (!mbar_wait(&empty[s], ((it / T::STAGES) & 1) ^ 1)) { atomicExch(status, 21); *failed = 1; ok = false; break; }
@@ -797,7 +809,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++j) {
             const int ab = j & 1;
-            const int ft = tile % feat_tiles, tt = tile / feat_tiles;
+            int ft, tt;
+            tile_at(tile, ft, tt);
             if (ok && !mbar_wait(&acc_full[ab], (j >> 1) & 1)) { if (lane == 0) atomicExch(status, 24); *failed = 1; ok = false; }
             tcgen05_fence_after();
             const bool go = __all_sync(0xffffffffu, ok && *failed == 0);
@@ -903,10 +916,20 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, i
         if (sms <= 0) sms = 148;
     }
     const int feat_tiles = (features + BLOCK_FEAT - 1) / BLOCK_FEAT;
-    const int num_tiles = feat_tiles * ((tokens + BLOCK_TOK - 1) / BLOCK_TOK);
+    const int tok_tiles = (tokens + BLOCK_TOK - 1) / BLOCK_TOK;
+    const int num_tiles = feat_tiles * tok_tiles;
     const int grid = num_tiles < sms ? num_tiles : sms;
+    // how many token tiles a band has: the CTAs of one wave should touch as few distinct rows of X and W as possible
+    const int w_rows = T::TOKM ? 256 : BLOCK_FEAT * T::W_TILES;
+    int group_tok = 1;
+    long long best = -1;
+    for (int gt = 1; gt <= tok_tiles; ++gt) {
+        const int gf = (grid + gt - 1) / gt;
+        const long long cost = (long long)gt * BLOCK_TOK + (long long)(gf < feat_tiles ? gf : feat_tiles) * w_rows;
+        if (best < 0 || cost <= best) { best = cost; group_tok = gt; }       // ties: the larger band
+    }
     cudaError_t err = lp_launch(kernel, dim3(grid), THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
-                                k_blocks, feat_tiles, num_tiles, status);
+                                k_blocks, feat_tiles, num_tiles, group_tok, status);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_persistent: %s", cudaGetErrorString(err));
         return (int)err;
