@@ -357,14 +357,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // applies the factor. `zero` (optional) is cleared on the side, a slice by every CTA.
 constexpr int FEW_THREADS = 160;          // warp 0: TMA; warps 1-4: consumers; XNORM adds warp 5, which makes the operand
 constexpr int FEW_W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
-template <bool XNORM, int NT> struct FewTile {
+// DEEP: the whole shared memory for one CTA's ring (ten stages at most): for grids of no more than one CTA
+// per SM with long K ranges, where the bytes in flight per SM, not the CTAs' number, keep HBM busy.
+template <bool XNORM, int NT, bool DEEP = false> struct FewTile {
     static constexpr int X_ROWS = NT <= 2 ? 16 : 8 * NT;          // rows of the activation tile (tokens, padded)
     static constexpr int X_BOX_BYTES = X_ROWS * 128;              // one box: X_ROWS x 128 bytes
     static constexpr int X_BYTES = XNORM ? 2 * X_BOX_BYTES : X_BOX_BYTES;
     static constexpr int GAIN_BYTES = XNORM ? 1024 : 0;           // 64 floats of gain per k-block, padded to the tiles' alignment
     static constexpr int STAGE_BYTES = FEW_W_BYTES + X_BYTES + GAIN_BYTES;
-    static constexpr int FIT = (110 * 1024) / STAGE_BYTES;        // two CTAs fit an SM
-    static constexpr int STAGES = FIT > 6 ? 6 : FIT;
+    static constexpr int FIT = ((DEEP ? 224 : 110) * 1024) / STAGE_BYTES;        // 110 KB: two CTAs fit an SM
+    static constexpr int CAP = DEEP ? 10 : 6;
+    static constexpr int STAGES = FIT > CAP ? CAP : FIT;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512;
 };
 
@@ -390,12 +393,12 @@ __device__ __forceinline__ void mma_m16n8k16(float* c, const uint32_t* a, uint32
 }
 
 // NT: n-tiles of 8 tokens (1, 2, 4 or 8). MODE: STORE or SWIGLU (interleaved rows). out as in the tcgen05 kernel.
-template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
-__global__ void __launch_bounds__(FEW_THREADS + (XNORM ? 32 : 0), 2)
+template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM, bool DEEP>
+__global__ void __launch_bounds__(FEW_THREADS + (XNORM ? 32 : 0), DEEP ? 1 : 2)
 gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
                    int* __restrict__ status, NormAfter norm, NormBefore before) {
-    using FT = FewTile<XNORM, NT>;
+    using FT = FewTile<XNORM, NT, DEEP>;
     constexpr int FEW_STAGES = FT::STAGES;
     constexpr int FEW_STAGE_BYTES = FT::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
@@ -624,11 +627,12 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (ATOMIC) norm_after_tail<NTHREADS>(norm, out, tokens, features, ldc);
 }
 
-template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
-int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
-                  int splits, int* status, const NormAfter& norm, const NormBefore& before, cudaStream_t stream) {
-    auto kernel = gemm_fewtok_kernel<NT, MODE, OUT_BF16, ATOMIC, XNORM>;
-    constexpr int FEW_SMEM_BYTES = FewTile<XNORM, NT>::SMEM_BYTES;
+template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM, bool DEEP>
+int launch_fewtok_as(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc,
+                     int k_blocks, int per_split, dim3 grid, int* status, const NormAfter& norm, const NormBefore& before,
+                     cudaStream_t stream) {
+    auto kernel = gemm_fewtok_kernel<NT, MODE, OUT_BF16, ATOMIC, XNORM, DEEP>;
+    constexpr int FEW_SMEM_BYTES = FewTile<XNORM, NT, DEEP>::SMEM_BYTES;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FEW_SMEM_BYTES);
@@ -636,10 +640,6 @@ int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int t
                                         cudaGetErrorString(e));
         configured = true;
     }
-    const int per_split = (k_blocks + splits - 1) / splits;
-    const int grid_z = (k_blocks + per_split - 1) / per_split;
-    const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;
-    dim3 grid((features + per_cta - 1) / per_cta, 1, grid_z);
     cudaError_t err = lp_launch(kernel, grid, FEW_THREADS + (XNORM ? 32 : 0), FEW_SMEM_BYTES, stream, mw, mx, out, tokens,
                                 features, ldc, k_blocks, per_split, status, norm, before);
     if (err != cudaSuccess) {
@@ -647,6 +647,24 @@ int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int t
         return (int)err;
     }
     return lp_check_launch("gemm_fewtok");
+}
+
+template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
+int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
+                  int splits, int* status, const NormAfter& norm, const NormBefore& before, cudaStream_t stream) {
+    const int per_split = (k_blocks + splits - 1) / splits;
+    const int grid_z = (k_blocks + per_split - 1) / per_split;
+    const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;
+    dim3 grid((features + per_cta - 1) / per_cta, 1, grid_z);
+    // at most one CTA per SM and a K range longer than the ordinary ring: the deep ring
+    static int deep_enabled = -1;
+    if (deep_enabled < 0) { const char* v = getenv("LLMPLAYER_B200_DEEP_RING"); deep_enabled = (v && v[0] == '0') ? 0 : 1; }
+    const bool deep = deep_enabled && NT <= 2 && (long long)grid.x * grid.z <= 148 && per_split > FewTile<XNORM, NT>::STAGES + 2;
+    if (deep)
+        return launch_fewtok_as<NT, MODE, OUT_BF16, ATOMIC, XNORM, (NT <= 2)>(mw, mx, out, tokens, features, ldc, k_blocks,
+                                                                             per_split, grid, status, norm, before, stream);
+    return launch_fewtok_as<NT, MODE, OUT_BF16, ATOMIC, XNORM, false>(mw, mx, out, tokens, features, ldc, k_blocks, per_split,
+                                                                      grid, status, norm, before, stream);
 }
 
 template <int NT, bool XNORM>
