@@ -357,18 +357,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // applies the factor. `zero` (optional) is cleared on the side, a slice by every CTA.
 constexpr int FEW_THREADS = 160;          // warp 0: TMA; warps 1-4: consumers; XNORM adds warp 5, which makes the operand
 constexpr int FEW_W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
-// DEEP: the whole shared memory for one CTA's ring (ten stages at most): for grids of no more than one CTA
-// per SM with long K ranges, where the bytes in flight per SM, not the CTAs' number, keep HBM busy.
-template <bool XNORM, int NT, bool DEEP = false> struct FewTile {
+// The ring has as many stages as the launch gives it (`stages`): what lets two CTAs share an SM (up to six,
+// LLMPLAYER_B200_RING_SHARED), or, for a grid of no more than one CTA per SM whose K range is longer than that,
+// up to ten (LLMPLAYER_B200_RING_ALONE): such a CTA requests that much more of its weights before it waits
+// for the previous kernel. The shared size also leaves room for the next kernel's CTAs to start beside it.
+template <bool XNORM, int NT> struct FewTile {
     static constexpr int X_ROWS = NT <= 2 ? 16 : 8 * NT;          // rows of the activation tile (tokens, padded)
     static constexpr int X_BOX_BYTES = X_ROWS * 128;              // one box: X_ROWS x 128 bytes
     static constexpr int X_BYTES = XNORM ? 2 * X_BOX_BYTES : X_BOX_BYTES;
     static constexpr int GAIN_BYTES = XNORM ? 1024 : 0;           // 64 floats of gain per k-block, padded to the tiles' alignment
     static constexpr int STAGE_BYTES = FEW_W_BYTES + X_BYTES + GAIN_BYTES;
-    static constexpr int FIT = ((DEEP ? 224 : 110) * 1024) / STAGE_BYTES;        // 110 KB: two CTAs fit an SM
-    static constexpr int CAP = DEEP ? 10 : 6;
-    static constexpr int STAGES = FIT > CAP ? CAP : FIT;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 512;
+    static constexpr int TAIL_BYTES = 1024 + 512;                 // alignment slack, barriers, row factors
+    static constexpr int MAX_SHARED = (110 * 1024 - TAIL_BYTES) / STAGE_BYTES;      // two CTAs per SM
+    static constexpr int MAX_ALONE = (224 * 1024 - TAIL_BYTES) / STAGE_BYTES;
 };
 
 struct NormBefore {
@@ -393,13 +394,12 @@ __device__ __forceinline__ void mma_m16n8k16(float* c, const uint32_t* a, uint32
 }
 
 // NT: n-tiles of 8 tokens (1, 2, 4 or 8). MODE: STORE or SWIGLU (interleaved rows). out as in the tcgen05 kernel.
-template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM, bool DEEP>
-__global__ void __launch_bounds__(FEW_THREADS + (XNORM ? 32 : 0), DEEP ? 1 : 2)
+template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
+__global__ void __launch_bounds__(FEW_THREADS + (XNORM ? 32 : 0), 2)
 gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
-                   int* __restrict__ status, NormAfter norm, NormBefore before) {
-    using FT = FewTile<XNORM, NT, DEEP>;
-    constexpr int FEW_STAGES = FT::STAGES;
+                   int FEW_STAGES, int* __restrict__ status, NormAfter norm, NormBefore before) {
+    using FT = FewTile<XNORM, NT>;
     constexpr int FEW_STAGE_BYTES = FT::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -435,9 +435,9 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 #pragma unroll
         for (int it = 0; it < PASSES; ++it) ss[it] = 0.f;
         bool ok = true;
-        for (int i = 0; i < nkb && ok; ++i) {
-            const int s = i % FEW_STAGES;
-            const uint32_t phase = (i / FEW_STAGES) & 1;
+        int s = 0;
+        uint32_t phase = 0;
+        for (int i = 0; i < nkb && ok; ++i, s = (s + 1 == FEW_STAGES ? 0 : s + 1), phase ^= (s == 0)) {
             if (!mbar_wait(&full[s], phase)) { if (lane == 0) atomicExch(status, 4); *failed = 1; ok = false; break; }
             uint8_t* x_tile = smem + s * FEW_STAGE_BYTES + FEW_W_BYTES;
             const float* gain_tile = reinterpret_cast<const float*>(x_tile + FT::X_BYTES);
@@ -511,9 +511,10 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             for (int i = 0; i < early; ++i) load_activations(i, i);
             int issued = early;
             bool ok = true;
-            for (int i = early; i < nkb; ++i) {
-                const int s = i % FEW_STAGES;
-                const uint32_t phase = (i / FEW_STAGES) & 1;
+            // stage and phase of k-block i: i mod stages, (i / stages) & 1, kept by counting
+            int s = early == FEW_STAGES ? 0 : early;
+            uint32_t phase = early == FEW_STAGES ? 1 : 0;
+            for (int i = early; i < nkb; ++i, s = (s + 1 == FEW_STAGES ? 0 : s + 1), phase ^= (s == 0)) {
                 if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
                 load_constants(i, s);
                 load_activations(i, s);
@@ -542,9 +543,9 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8;
         const int a_chunk = lane >> 4;
         bool ok = true;
-        for (int i = 0; i < nkb; ++i) {
-            const int s = i % FEW_STAGES;
-            const uint32_t phase = (i / FEW_STAGES) & 1;
+        int s = 0;
+        uint32_t phase = 0;
+        for (int i = 0; i < nkb; ++i, s = (s + 1 == FEW_STAGES ? 0 : s + 1), phase ^= (s == 0)) {
             if (!mbar_wait(&full[s], phase)) { if (lane == 0) atomicExch(status, 2); *failed = 1; ok = false; }
             const uint32_t w_tile = smem_u32(smem + s * FEW_STAGE_BYTES);
             const uint8_t* x_tile = smem + s * FEW_STAGE_BYTES + FEW_W_BYTES;
@@ -627,44 +628,45 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (ATOMIC) norm_after_tail<NTHREADS>(norm, out, tokens, features, ldc);
 }
 
-template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM, bool DEEP>
-int launch_fewtok_as(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc,
-                     int k_blocks, int per_split, dim3 grid, int* status, const NormAfter& norm, const NormBefore& before,
-                     cudaStream_t stream) {
-    auto kernel = gemm_fewtok_kernel<NT, MODE, OUT_BF16, ATOMIC, XNORM, DEEP>;
-    constexpr int FEW_SMEM_BYTES = FewTile<XNORM, NT, DEEP>::SMEM_BYTES;
+template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
+int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
+                  int splits, int* status, const NormAfter& norm, const NormBefore& before, cudaStream_t stream) {
+    using FT = FewTile<XNORM, NT>;
+    auto kernel = gemm_fewtok_kernel<NT, MODE, OUT_BF16, ATOMIC, XNORM>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FEW_SMEM_BYTES);
-        if (e != cudaSuccess) LP_REFUSE("gemm: cannot reserve %d bytes of shared memory: %s", FEW_SMEM_BYTES,
-                                        cudaGetErrorString(e));
+        const int most = FT::MAX_ALONE * FT::STAGE_BYTES + FT::TAIL_BYTES;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        if (e != cudaSuccess) LP_REFUSE("gemm: cannot reserve %d bytes of shared memory: %s", most, cudaGetErrorString(e));
         configured = true;
     }
-    cudaError_t err = lp_launch(kernel, grid, FEW_THREADS + (XNORM ? 32 : 0), FEW_SMEM_BYTES, stream, mw, mx, out, tokens,
-                                features, ldc, k_blocks, per_split, status, norm, before);
+    const int per_split = (k_blocks + splits - 1) / splits;
+    const int grid_z = (k_blocks + per_split - 1) / per_split;
+    const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;
+    dim3 grid((features + per_cta - 1) / per_cta, 1, grid_z);
+    static int ring_alone = 0, ring_shared = 0;
+    if (!ring_alone) {
+        const char* v = getenv("LLMPLAYER_B200_RING_ALONE");
+        ring_alone = v ? atoi(v) : 10;
+        v = getenv("LLMPLAYER_B200_RING_SHARED");
+        ring_shared = v ? atoi(v) : 6;
+        if (ring_alone < 2) ring_alone = 2;
+        if (ring_shared < 2) ring_shared = 2;
+    }
+    const int shared_stages = ring_shared < FT::MAX_SHARED ? ring_shared : FT::MAX_SHARED;
+    const bool alone = (long long)grid.x * grid.z <= 148 && per_split > shared_stages + 2;
+    int stages = alone ? (ring_alone < FT::MAX_ALONE ? ring_alone : FT::MAX_ALONE) : shared_stages;
+    // (measured at the 1B shape, 8 tokens: 0.73 ms per step with 7 to 10 stages for the two long products, 0.80 ms
+    // with 6; giving the short products no more stages than they have k-blocks changed nothing; a q|k|v product
+    // with more than the shared ring keeps the attention kernel's CTAs from starting beside it: 0.81 ms)
+    const int smem = stages * FT::STAGE_BYTES + FT::TAIL_BYTES;
+    cudaError_t err = lp_launch(kernel, grid, FEW_THREADS + (XNORM ? 32 : 0), smem, stream, mw, mx, out, tokens, features,
+                                ldc, k_blocks, per_split, stages, status, norm, before);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_fewtok: %s", cudaGetErrorString(err));
         return (int)err;
     }
     return lp_check_launch("gemm_fewtok");
-}
-
-template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
-int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
-                  int splits, int* status, const NormAfter& norm, const NormBefore& before, cudaStream_t stream) {
-    const int per_split = (k_blocks + splits - 1) / splits;
-    const int grid_z = (k_blocks + per_split - 1) / per_split;
-    const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;
-    dim3 grid((features + per_cta - 1) / per_cta, 1, grid_z);
-    // at most one CTA per SM and a K range longer than the ordinary ring: the deep ring
-    static int deep_enabled = -1;
-    if (deep_enabled < 0) { const char* v = getenv("LLMPLAYER_B200_DEEP_RING"); deep_enabled = (v && v[0] == '0') ? 0 : 1; }
-    const bool deep = deep_enabled && NT <= 2 && (long long)grid.x * grid.z <= 148 && per_split > FewTile<XNORM, NT>::STAGES + 2;
-    if (deep)
-        return launch_fewtok_as<NT, MODE, OUT_BF16, ATOMIC, XNORM, (NT <= 2)>(mw, mx, out, tokens, features, ldc, k_blocks,
-                                                                             per_split, grid, status, norm, before, stream);
-    return launch_fewtok_as<NT, MODE, OUT_BF16, ATOMIC, XNORM, false>(mw, mx, out, tokens, features, ldc, k_blocks, per_split,
-                                                                      grid, status, norm, before, stream);
 }
 
 template <int NT, bool XNORM>
