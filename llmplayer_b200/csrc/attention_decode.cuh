@@ -129,6 +129,20 @@ struct FusedDecodeArgs {
     int norm_width;
 };
 
+// The same in two steps, for callers that want the loads of several elements in flight before they combine them.
+__device__ __forceinline__ int rotation_partner(int e, int rd, int interleaved) {
+    const int half = rd >> 1;
+    return interleaved ? (e ^ 1) : (e < half ? e + half : e - half);
+}
+__device__ __forceinline__ float rotate_value(float val, float other, int e, int rd, int interleaved, const float* cs,
+                                              const float* sn) {
+    if (e >= rd) return val;
+    const int half = rd >> 1;
+    const bool first = interleaved ? (e & 1) == 0 : e < half;
+    const int pair = interleaved ? e >> 1 : (first ? e : e - half);
+    return first ? val * cs[pair] - other * sn[pair] : other * sn[pair] + val * cs[pair];
+}
+
 __device__ __forceinline__ float rotated(const float* head, int e, int rd, int interleaved, const float* cs,
                                          const float* sn) {
     float val = __ldcg(head + e);
@@ -147,20 +161,23 @@ __device__ __forceinline__ float rotated(const float* head, int e, int rd, int i
 // HD_EXACT > 0: the head size is that constant (index arithmetic of the copies and of ldmatrix folds
 // into shifts and masks); 0: any multiple of 16 up to HD_MAX, taken from `hd_arg`.
 // One unit of the decode kernel: share `split` of the pages of sequence `b` for key/value head and head
-// group `by` (= g * head_groups + hg), run by 128 threads numbered `tid`, with `smem` as their scratch.
-// NAMED: the 128 threads are part of a larger CTA and meet at named barrier 1 instead of __syncthreads.
-template <bool NAMED> __device__ __forceinline__ void unit_sync() {
-    if (NAMED) asm volatile("bar.sync 1, 128;" ::: "memory");
+// group `by` (= g * head_groups + hg), run by 32 NW threads numbered `tid`, with `smem` as their scratch.
+// NAMED: the threads are part of a larger CTA and meet at named barrier 1 instead of __syncthreads.
+template <bool NAMED, int NT> __device__ __forceinline__ void unit_sync() {
+    if (NAMED) asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory");
     else __syncthreads();
 }
 
-// STAGES: pages in flight (the scratch holds STAGES key and value tiles).
+// STAGES: pages in flight (the scratch holds STAGES key and value tiles). NW: warps (a multiple of 4): four
+// warps share a page, 16 keys each, so NW / 4 pages are worked on at a time and the CTA meets twice per such
+// group of pages. With few CTAs on the GPU more warps per CTA hide the latency of a page's short chain
+// of dependent steps (copy, scores, softmax, values).
 // `before_inputs()` is called once the unit has requested its first pages and computed its angles, right
 // before it reads what the step itself produced (the projection output): a caller whose inputs come
 // from an earlier operation of the same kernel waits for that operation there, so that the page
 // copies (the cache holds nothing the step writes, except the new row this unit patches in itself)
 // are already in flight.
-template <int HD_MAX, bool FUSED, int HD_EXACT, bool NAMED, int STAGES, typename Before>
+template <int HD_MAX, bool FUSED, int HD_EXACT, bool NAMED, int STAGES, int NW, typename Before>
 __device__ __forceinline__ void attention_decode_unit(
     uint8_t* smem, const int tid, const int split, const int by, const int b, const __nv_bfloat16* __restrict__ q,
     const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table, int pt_stride,
@@ -168,12 +185,15 @@ __device__ __forceinline__ void attention_decode_unit(
     __nv_bfloat16* __restrict__ out, int H, int G, int hd_arg, float scale_log2, int window, int pages_per_split,
     int num_splits, int head_groups, const FusedDecodeArgs& fused, Before&& before_inputs) {
     constexpr int KSTEPS = HD_MAX / 16;
+    constexpr int NT = 32 * NW, PG = NW / 4, GROUPS = STAGES / PG;
+    static_assert(NW % 4 == 0 && STAGES % PG == 0 && GROUPS >= 1, "whole groups of pages in the ring");
     const int hd = HD_EXACT > 0 ? HD_EXACT : hd_arg;
     const int g = by / head_groups, hg = by - g * head_groups;
     const int R = H / G;
     const int head0 = g * R + hg * 16;
     const int nrows = min(16, R - hg * 16);
     const int warp = tid >> 5, lane = tid & 31;
+    const int kw = warp & 3, pg = warp >> 2;       // this warp's quarter of a page's keys, and its page of a group
     const int len = kv_len[b];
     const int pos = len - 1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
@@ -185,8 +205,12 @@ __device__ __forceinline__ void attention_decode_unit(
 
     // the ring is requested first; what follows overlaps with the copies
 #pragma unroll
-    for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < npages) load_page(smem + s * stage_bytes, pages, table[page_lo + s], G, g, hd, tid, 128);
+    for (int gi = 0; gi < GROUPS; ++gi) {          // one group of copies per group of pages
+#pragma unroll
+        for (int j = 0; j < PG; ++j) {
+            const int p = gi * PG + j;
+            if (p < npages) load_page(smem + p * stage_bytes, pages, table[page_lo + p], G, g, hd, tid, NT);
+        }
         cp_async_commit();
     }
 
@@ -201,27 +225,47 @@ __device__ __forceinline__ void attention_decode_unit(
     const bool holds_new = FUSED && fused.pages_rw != nullptr && pos / PAGE >= page_lo && pos / PAGE <= page_hi;
     if (FUSED) {
         const int half = fused.rd >> 1;
-        for (int i = tid; i < half; i += 128) sincosf((float)pos * fused.inv_freq[i], &sn[i], &cs[i]);
-        unit_sync<NAMED>();
+        for (int i = tid; i < half; i += NT) sincosf((float)pos * fused.inv_freq[i], &sn[i], &cs[i]);
+        unit_sync<NAMED, NT>();
         before_inputs();
         const float in_scale = fused.row_sumsq
             ? 1.0f / sqrtf(__ldcg(fused.row_sumsq + b) / (float)fused.norm_width + fused.norm_eps) : 1.0f;
         const float* row = fused.qkv + (size_t)b * fused.ld;
-        for (int idx = tid; idx < 16 * hd; idx += 128) {
-            const int r = idx / hd, e = idx - r * hd;
-            const float v = r < nrows ? rotated(row + (size_t)(head0 + r) * hd, e, fused.rd, fused.interleaved, cs, sn) : 0.f;
-            q_s[idx] = __float2bfloat16_rn(v * in_scale);
+        // the queries: the loads of four elements (each with its partner of the rotation) are in flight together
+        for (int idx0 = tid; idx0 < 16 * hd; idx0 += 4 * NT) {
+            float val[4], other[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = idx0 + u * NT;
+                val[u] = other[u] = 0.f;
+                if (idx < 16 * hd) {
+                    const int r = idx / hd, e = idx - r * hd;
+                    if (r < nrows) {
+                        const float* head = row + (size_t)(head0 + r) * hd;
+                        val[u] = __ldcg(head + e);
+                        if (e < fused.rd) other[u] = __ldcg(head + rotation_partner(e, fused.rd, fused.interleaved));
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int idx = idx0 + u * NT;
+                if (idx < 16 * hd) {
+                    const int e = idx % hd;
+                    q_s[idx] = __float2bfloat16_rn(rotate_value(val[u], other[u], e, fused.rd, fused.interleaved, cs, sn) * in_scale);
+                }
+            }
         }
         if (holds_new) {
-            for (int e = tid; e < hd; e += 128) {
+            for (int e = tid; e < hd; e += NT) {
                 new_k[e] = __float2bfloat16_rn(rotated(row + (size_t)(H + g) * hd, e, fused.rd, fused.interleaved, cs, sn) * in_scale);
                 new_v[e] = __float2bfloat16_rn(__ldcg(row + (size_t)(H + G + g) * hd + e) * in_scale);
             }
         }
-        unit_sync<NAMED>();
+        unit_sync<NAMED, NT>();
         if (holds_new && hg == 0) {           // one CTA per (sequence, kv head) stores the new row
             const size_t base = ((size_t)table[pos / PAGE] * 2 * G + g) * PAGE * hd + (size_t)(pos % PAGE) * hd;
-            for (int e = tid; e < hd; e += 128) {
+            for (int e = tid; e < hd; e += NT) {
                 fused.pages_rw[base + e] = new_k[e];
                 fused.pages_rw[base + (size_t)G * PAGE * hd + e] = new_v[e];
             }
@@ -256,78 +300,87 @@ __device__ __forceinline__ void attention_decode_unit(
     for (int i = 0; i < KSTEPS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
 
-    for (int i = 0; i < npages; ++i) {
-        const int nxt = i + STAGES - 1;
-        if (nxt < npages)
-            load_page(smem + (nxt % STAGES) * stage_bytes, pages, table[page_lo + nxt], G, g, hd, tid, 128);
-        cp_async_commit();
-        cp_async_wait<STAGES - 1>();
-        unit_sync<NAMED>();
-        const int key_base = (page_lo + i) * PAGE;
-        const uint32_t k_tile = smem_u32(smem + (i % STAGES) * stage_bytes);
-        const uint32_t v_tile = k_tile + PAGE * hd * 2;
-        if (FUSED && holds_new && page_lo + i == pos / PAGE) {
+    const int ngroups = (npages + PG - 1) / PG;
+    const int new_at = pos / PAGE - page_lo;         // which of the share's pages holds the new token
+    for (int gi = 0; gi < ngroups; ++gi) {
+        cp_async_wait<GROUPS - 1>();                 // all but the newest groups of copies: this group's pages are there
+        unit_sync<NAMED, NT>();
+        if (FUSED && holds_new && new_at >= gi * PG && new_at < (gi + 1) * PG) {
             // the copy of this page predates the new token: put its key and value in place
             const int cpr = hd >> 3, row = pos % PAGE;
-            uint8_t* tile = smem + (i % STAGES) * stage_bytes;
-            for (int c = tid; c < 2 * cpr; c += 128) {
+            uint8_t* tile = smem + (new_at % STAGES) * stage_bytes;
+            for (int c = tid; c < 2 * cpr; c += NT) {
                 const int which = c >= cpr, cc = which ? c - cpr : c;
                 const uint4 v = *reinterpret_cast<const uint4*>((which ? new_v : new_k) + cc * 8);
                 *reinterpret_cast<uint4*>(tile + which * (PAGE * hd * 2) + row * (hd * 2) + swz(row, cc, cpr) * 16) = v;
             }
-            unit_sync<NAMED>();
+            unit_sync<NAMED, NT>();
         }
-        const int key0 = warp * 16;                  // this warp's 16 keys of the page
-        if (key_base + key0 <= pos && key_base + key0 + 15 >= lo) {
-            float s[2][4];
-            s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
-            scores_16keys<KSTEPS>(s, qf, k_tile, key0, hd, lane);
-            float mx_lo = NEG_BIG, mx_hi = NEG_BIG;
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key_base + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    float v = s[nt][e] * scale_log2;
-                    if (key > pos || key < lo) v = NEG_BIG;
-                    s[nt][e] = v;
-                    if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+        const int i = gi * PG + pg;                  // this warp's page
+        if (i < npages) {
+            const int key_base = (page_lo + i) * PAGE;
+            const uint32_t k_tile = smem_u32(smem + (i % STAGES) * stage_bytes);
+            const uint32_t v_tile = k_tile + PAGE * hd * 2;
+            const int key0 = kw * 16;                    // this warp's 16 keys of its page
+            if (key_base + key0 <= pos && key_base + key0 + 15 >= lo) {
+                float s[2][4];
+                s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
+                scores_16keys<KSTEPS>(s, qf, k_tile, key0, hd, lane);
+                float mx_lo = NEG_BIG, mx_hi = NEG_BIG;
+    #pragma unroll
+                for (int nt = 0; nt < 2; ++nt)
+    #pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key_base + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        float v = s[nt][e] * scale_log2;
+                        if (key > pos || key < lo) v = NEG_BIG;
+                        s[nt][e] = v;
+                        if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+                    }
+                mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+                mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+                mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+                mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+                const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+                const float a_lo = fast_exp2(m_lo - mn_lo), a_hi = fast_exp2(m_hi - mn_hi);
+                m_lo = mn_lo; m_hi = mn_hi;
+                uint32_t pf[4];
+                float sum_lo = 0.f, sum_hi = 0.f;
+    #pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    float e0 = s[nt][0] <= NEG_BIG ? 0.f : fast_exp2(s[nt][0] - mn_lo);
+                    float e1 = s[nt][1] <= NEG_BIG ? 0.f : fast_exp2(s[nt][1] - mn_lo);
+                    float e2 = s[nt][2] <= NEG_BIG ? 0.f : fast_exp2(s[nt][2] - mn_hi);
+                    float e3 = s[nt][3] <= NEG_BIG ? 0.f : fast_exp2(s[nt][3] - mn_hi);
+                    sum_lo += e0 + e1; sum_hi += e2 + e3;
+                    pf[nt * 2] = pack_bf16(e0, e1);
+                    pf[nt * 2 + 1] = pack_bf16(e2, e3);
                 }
-            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-            const float a_lo = fast_exp2(m_lo - mn_lo), a_hi = fast_exp2(m_hi - mn_hi);
-            m_lo = mn_lo; m_hi = mn_hi;
-            uint32_t pf[4];
-            float sum_lo = 0.f, sum_hi = 0.f;
-#pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                float e0 = s[nt][0] <= NEG_BIG ? 0.f : fast_exp2(s[nt][0] - mn_lo);
-                float e1 = s[nt][1] <= NEG_BIG ? 0.f : fast_exp2(s[nt][1] - mn_lo);
-                float e2 = s[nt][2] <= NEG_BIG ? 0.f : fast_exp2(s[nt][2] - mn_hi);
-                float e3 = s[nt][3] <= NEG_BIG ? 0.f : fast_exp2(s[nt][3] - mn_hi);
-                sum_lo += e0 + e1; sum_hi += e2 + e3;
-                pf[nt * 2] = pack_bf16(e0, e1);
-                pf[nt * 2 + 1] = pack_bf16(e2, e3);
+                l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
+    #pragma unroll
+                for (int j = 0; j < KSTEPS * 2; ++j) { o[j][0] *= a_lo; o[j][1] *= a_lo; o[j][2] *= a_hi; o[j][3] *= a_hi; }
+                values_16keys<KSTEPS>(o, pf, v_tile, key0, hd, lane);
             }
-            l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
-#pragma unroll
-            for (int j = 0; j < KSTEPS * 2; ++j) { o[j][0] *= a_lo; o[j][1] *= a_lo; o[j][2] *= a_hi; o[j][3] *= a_hi; }
-            values_16keys<KSTEPS>(o, pf, v_tile, key0, hd, lane);
         }
-        unit_sync<NAMED>();
+        unit_sync<NAMED, NT>();
+        // the group's stages are free: the group that comes GROUPS later goes there
+#pragma unroll
+        for (int j = 0; j < PG; ++j) {
+            const int nxt = (gi + GROUPS) * PG + j;
+            if (nxt < npages)
+                load_page(smem + (nxt % STAGES) * stage_bytes, pages, table[page_lo + nxt], G, g, hd, tid, NT);
+        }
+        cp_async_commit();
     }
     cp_async_wait<0>();
-    unit_sync<NAMED>();
+    unit_sync<NAMED, NT>();
 
-    // merge the four warps (each saw a quarter of every page) through shared memory
+    // merge the warps (each saw a quarter of some pages) through shared memory
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    float* sm_m = reinterpret_cast<float*>(smem);            // [4][16]
-    float* sm_l = sm_m + 64;                                 // [4][16]
-    float* sm_o = sm_l + 64;                                 // [4][16][hd]
+    float* sm_m = reinterpret_cast<float*>(smem);            // [NW][16]
+    float* sm_l = sm_m + NW * 16;                            // [NW][16]
+    float* sm_o = sm_l + NW * 16;                            // [NW][16][hd]
     if ((lane & 3) == 0) {
         sm_m[warp * 16 + r_lo] = m_lo; sm_m[warp * 16 + r_hi] = m_hi;
         sm_l[warp * 16 + r_lo] = l_lo; sm_l[warp * 16 + r_hi] = l_hi;
@@ -342,13 +395,15 @@ __device__ __forceinline__ void attention_decode_unit(
             hi_row[0] = o[dt][2]; hi_row[1] = o[dt][3];
         }
     }
-    unit_sync<NAMED>();
-    for (int idx = tid; idx < nrows * hd; idx += 128) {
+    unit_sync<NAMED, NT>();
+    for (int idx = tid; idx < nrows * hd; idx += NT) {
         const int r = idx / hd, d = idx - r * hd;
-        float m = fmaxf(fmaxf(sm_m[r], sm_m[16 + r]), fmaxf(sm_m[32 + r], sm_m[48 + r]));
+        float m = NEG_BIG;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) m = fmaxf(m, sm_m[w * 16 + r]);
         float acc = 0.f, l = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
+        for (int w = 0; w < NW; ++w) {
             const float f = fast_exp2(sm_m[w * 16 + r] - m);
             acc += sm_o[((size_t)w * 16 + r) * hd + d] * f;
             l += sm_l[w * 16 + r] * f;
@@ -365,17 +420,17 @@ __device__ __forceinline__ void attention_decode_unit(
         // the last share of this (sequence, kv head, head group) to arrive merges them all
         __shared__ int last;
         __threadfence();
-        unit_sync<NAMED>();
+        unit_sync<NAMED, NT>();
         int* counter = fused.counters + ((size_t)b * G + g) * head_groups + hg;
         if (tid == 0) {
             const int ticket = atomicAdd(counter, 1);
             last = ticket == num_splits - 1;
             if (last) *counter = 0;                 // ready for the next launch
         }
-        unit_sync<NAMED>();
+        unit_sync<NAMED, NT>();
         if (last) {
             __threadfence();
-            for (int idx = tid; idx < nrows * hd; idx += 128) {
+            for (int idx = tid; idx < nrows * hd; idx += NT) {
                 const int r = idx / hd, d = idx - r * hd;
                 const size_t base = ((size_t)b * H + head0 + r) * num_splits;
                 // the shares' (max, sum, output) are requested eight shares at a time, then combined
@@ -410,7 +465,7 @@ __device__ __forceinline__ void attention_decode_unit(
             }
         }
     }
-    unit_sync<NAMED>();          // the scratch may be reused by the caller's next unit
+    unit_sync<NAMED, NT>();          // the scratch may be reused by the caller's next unit
 }
 
 }  // namespace

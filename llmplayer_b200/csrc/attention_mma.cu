@@ -327,8 +327,8 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
 // for the previous kernel: within a step nothing else writes lengths, page tables or these pages, and
 // the new row is put into the unit's own copy of the page. Every other form waits first (the pages
 // may hold a row that the previous kernel wrote).
-template <int HD_MAX, bool FUSED, int HD_EXACT, int STAGES>
-__global__ void __launch_bounds__(128)
+template <int HD_MAX, bool FUSED, int HD_EXACT, int STAGES, int NW = 4>
+__global__ void __launch_bounds__(32 * NW)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
                         const int* __restrict__ page_table, int pt_stride, const int* __restrict__ kv_len,
                         float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
@@ -338,7 +338,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     lp_grid_release();
     const bool early = FUSED && fused.pages_rw != nullptr;
     if (!early) lp_grid_wait();
-    attention_decode_unit<HD_MAX, FUSED, HD_EXACT, false, STAGES>(
+    attention_decode_unit<HD_MAX, FUSED, HD_EXACT, false, STAGES, NW>(
         smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, q, pages, page_table, pt_stride, kv_len, part_o, part_ml,
         out, H, G, hd_arg, scale_log2, window, pages_per_split, num_splits, head_groups, fused,
         [early] { if (early) lp_grid_wait(); });
@@ -500,10 +500,11 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
     if (G * head_groups > 65535 || B > 65535) LP_REFUSE("attention_decode_fused: grid too large");
     const int stage = 2 * PAGE * hd * 2;
     const int extra = (16 * hd + 2 * hd) * 2 + 256 * 4;
-    const int merge = (128 + 64 * hd) * 4;
-    // long shares of small heads keep six pages in flight instead of three, unless there are CTAs enough
-    // to hide the latency by their number (the deeper ring halves how many fit an SM)
-    const int stages = (hd <= 64 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= 2 * 148) ? 6 : 3;
+    // With few CTAs altogether (at most two per SM) and small heads a CTA has 16 warps, four pages at a time and
+    // eight pages in shared memory; with CTAs enough to hide a page's latency by their number, 4 warps and 3 pages.
+    const bool wide = hd <= 64 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= 2 * 148;
+    const int stages = wide ? 8 : 3, nw = wide ? 16 : 4;
+    const int merge = (2 * nw * 16 + nw * 16 * hd) * 4;
     const int smem = (stages * stage > merge ? stages * stage : merge) + extra;
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)B * H * num_splits * hd;
@@ -511,21 +512,21 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
     const float scale_log2 = scale * 1.4426950408889634f;
     FusedDecodeArgs fused{qkv, ld, inv_freq, rd, interleaved, write_kv ? (__nv_bfloat16*)pages : nullptr, counters,
                           row_sumsq, norm_eps, norm_width};
-#define LP_DECODE_FUSED(HDM, EXACT, ST)                                                                          \
+#define LP_DECODE_FUSED(HDM, EXACT, ST, NWARPS)                                                                  \
     do {                                                                                                         \
-        rc = set_smem<3000 + HDM + EXACT + 7 * ST>(attention_decode_kernel<HDM, true, EXACT, ST>, smem,          \
+        rc = set_smem<3000 + HDM + EXACT + 7 * ST>(attention_decode_kernel<HDM, true, EXACT, ST, NWARPS>, smem,  \
                                                    "attention_decode_fused");                                    \
         if (rc) return rc;                                                                                       \
-        lp_launch(attention_decode_kernel<HDM, true, EXACT, ST>, grid, 128, smem, stream,                        \
+        lp_launch(attention_decode_kernel<HDM, true, EXACT, ST, NWARPS>, grid, 32 * NWARPS, smem, stream,        \
                   (const __nv_bfloat16*)nullptr, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len,     \
                   part_o, part_ml, (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split,           \
                   num_splits, head_groups, fused);                                                               \
     } while (0)
-    if (hd == 64) { if (stages == 6) LP_DECODE_FUSED(64, 64, 6); else LP_DECODE_FUSED(64, 64, 3); }
-    else if (hd == 128) LP_DECODE_FUSED(128, 128, 3);
-    else if (hd <= 64) { if (stages == 6) LP_DECODE_FUSED(64, 0, 6); else LP_DECODE_FUSED(64, 0, 3); }
-    else if (hd <= 128) LP_DECODE_FUSED(128, 0, 3);
-    else LP_DECODE_FUSED(256, 0, 3);
+    if (hd == 64) { if (wide) LP_DECODE_FUSED(64, 64, 8, 16); else LP_DECODE_FUSED(64, 64, 3, 4); }
+    else if (hd == 128) LP_DECODE_FUSED(128, 128, 3, 4);
+    else if (hd <= 64) { if (wide) LP_DECODE_FUSED(64, 0, 8, 16); else LP_DECODE_FUSED(64, 0, 3, 4); }
+    else if (hd <= 128) LP_DECODE_FUSED(128, 0, 3, 4);
+    else LP_DECODE_FUSED(256, 0, 3, 4);
 #undef LP_DECODE_FUSED
     return lp_check_launch("attention_decode_fused");
 }

@@ -326,7 +326,7 @@ __device__ __forceinline__ void grid_arrive(uint32_t* counter, int tid) {
 template <int HD, int STAGES, typename Before>
 __device__ __noinline__ void attention_unit(uint8_t* scratch, int tid, int split, int by, int b, const AttentionOp& a,
                                             Before& before_inputs) {
-    attention_decode_unit<HD, true, HD, true, STAGES>(
+    attention_decode_unit<HD, true, HD, true, STAGES, 4>(
         scratch, tid, split, by, b, nullptr, a.pages, a.page_table, a.pt_stride, a.kv_len, a.part_o, a.part_ml, a.out, a.H,
         a.G, a.hd, a.scale_log2, a.window, a.pages_per_split, a.num_splits, a.head_groups, a.fused, before_inputs);
 }
