@@ -138,7 +138,7 @@ class Engine:
             self._run_captured(ctx, logits)
         else:
             self.model.forward(ctx, self.cache, ctx.rows, logits)
-        self.cache.commit([s.slot for s in ctx.sequences], [s.num_new for s in ctx.sequences])
+        self.cache.commit(ctx.slot_list, ctx.new_counts)
         return logits
 
     def _run_captured(self, ctx: StepContext, logits: torch.Tensor) -> None:
@@ -147,7 +147,10 @@ class Engine:
         second is captured, later ones are replayed; the step's integers were copied to the
         device beforehand, and the graph reads them there (the reference replays its captured
         forward pass the same way: java21 inference/CudaForwardPass.java:1760-1812)."""
-        key = (ctx.num_sequences, tuple(t.shape[1] for t in ctx.page_tables), ctx.num_wanted, ctx.meta.data_ptr())
+        key = ctx.graph_key
+        if key is None:
+            key = ctx.graph_key = (ctx.num_sequences, tuple(t.shape[1] for t in ctx.page_tables), ctx.num_wanted,
+                                   ctx.meta.data_ptr())
         entry = self._graphs.get(key)
         if entry is not None and entry[1] != self.workspace.version:
             entry = None                                  # a buffer moved since the capture
@@ -185,24 +188,21 @@ class Engine:
         """The previous step's description moved on by one token, when this step brings one token
         for each of the same sequences and wants the same rows (the usual decode step); else None."""
         last = self._last_ctx
-        if last is None or len(entries) != last.num_sequences:
+        if last is None or len(entries) != last.num_sequences or not last.continues_all:
             return None
         tokens: List[int] = []
-        for (slot, toks), places, seq in zip(entries, want, last.sequences):
-            if slot != seq.slot or len(toks) != 1 or list(places) != [0]:
+        vocab, limit, cache = self.vocab_size, self.context_length, self.cache
+        for (slot, toks), places, held, pos in zip(entries, want, last.slot_list, last.first_positions):
+            if slot != held or len(toks) != 1 or len(places) != 1 or places[0] != 0:
                 return None
             tok = int(toks[0])
-            if not 0 <= tok < self.vocab_size:
+            if not 0 <= tok < vocab:
                 return None                     # the full check in plan() raises the error
-            tokens.append(tok)
-        if last.wanted_rows != list(range(last.num_sequences)):
-            return None
-        slots = [s.slot for s in last.sequences]
-        for s in slots:
-            if not self.cache.slots.is_held(s) or self.cache.length(s) + 1 > self.context_length:
+            # the slot is still held, has room, and nothing else ran on it meanwhile
+            if not cache.slots.is_held(slot) or cache.length(slot) != pos + 1 or pos + 2 > limit:
                 return None
-        if any(self.cache.length(s.slot) != s.first_position + 1 for s in last.sequences):
-            return None                         # something else ran on these slots meanwhile
+            tokens.append(tok)
+        slots = last.slot_list
         prepared, self._prepared = self._prepared, None
         if prepared is not None and prepared[0] is last:
             tables = prepared[1]                # reserved while the device was still busy with the last step
@@ -220,10 +220,9 @@ class Engine:
         last = self._last_ctx
         if last is None:
             return
-        slots = [s.slot for s in last.sequences]
-        for s in last.sequences:
-            if (not self.cache.slots.is_held(s.slot) or self.cache.length(s.slot) != s.first_position + 1
-                    or s.first_position + 2 > self.context_length):
+        slots = last.slot_list
+        for slot, pos in zip(slots, last.first_positions):
+            if not self.cache.slots.is_held(slot) or self.cache.length(slot) != pos + 1 or pos + 2 > self.context_length:
                 return
         try:
             self.cache.reserve(slots, [1] * len(slots))

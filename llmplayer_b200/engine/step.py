@@ -104,7 +104,10 @@ class StepContext:
                  page_tables: List[List[List[int]]], wanted_rows: Sequence[int], *,
                  min_table_width: int = 1, meta_name: str = "step_meta"):
         self.workspace = workspace
-        self.sequences = sequences
+        self._sequences: Optional[List[SequenceStep]] = sequences
+        self.slot_list = [s.slot for s in sequences]
+        self.first_positions = [s.first_position for s in sequences]
+        self.new_counts = [s.num_new for s in sequences]
         self.num_tokens = T = len(tokens)
         self.num_sequences = B = len(sequences)
         self.max_new = max((s.num_new for s in sequences), default=0)
@@ -112,6 +115,8 @@ class StepContext:
         self.max_kv_len = max((s.first_position + s.num_new for s in sequences), default=0)
         self.num_wanted = W = len(wanted_rows)
         self.wanted_rows = list(wanted_rows)
+        # one token for each sequence and every sequence's logits wanted: the shape a decode step continues in
+        self.continues_all = self.all_single and self.wanted_rows == list(range(B))
 
         widths = [max([min_table_width] + [len(t) for t in group]) for group in page_tables]
         self._widths = widths
@@ -145,6 +150,9 @@ class StepContext:
         meta = workspace.get(meta_name, (total,), torch.int32)
         self._total = total
         self.meta = meta
+        self._upload_views: Dict[int, tuple] = {}
+        self._pinned = host.is_pinned()
+        self.graph_key = None                          # set by the engine: what a captured graph of this step depends on
         self._upload(total)
         self.tokens = meta[o[0]:o[0] + T]
         self.positions = meta[o[1]:o[1] + T]
@@ -155,15 +163,26 @@ class StepContext:
         self.page_tables = [meta[o[6 + g]:o[6 + g] + B * w].view(B, w) for g, w in enumerate(widths)]
         self.rows = meta[o[-1]:o[-1] + W]
 
+    @property
+    def sequences(self) -> List[SequenceStep]:
+        """The step's sequences (rebuilt on demand after :meth:`advance`, which only moves the positions on)."""
+        if self._sequences is None:
+            self._sequences = [SequenceStep(slot, i, 1, pos)
+                               for i, (slot, pos) in enumerate(zip(self.slot_list, self.first_positions))]
+        return self._sequences
+
     def _upload(self, count: int) -> None:
         """Copy the first ``count`` integers of the pinned host image to the device, asynchronously;
         the event lets the next writer of the host image wait until the copy has read it."""
         self.h2d_bytes = count * 4
-        if self._host.is_pinned():
-            self.meta[:count].copy_(self._host[:count], non_blocking=True)
+        views = self._upload_views.get(count)
+        if views is None:
+            views = self._upload_views[count] = (self.meta[:count], self._host[:count])
+        if self._pinned:
+            views[0].copy_(views[1], non_blocking=True)
             self._copied.record()
         else:
-            self.meta[:count].copy_(self._host[:count])
+            views[0].copy_(views[1])
 
     def advance(self, tokens: Sequence[int], page_tables: List[List[List[int]]]) -> bool:
         """Move a context of one token per sequence on by one step: new tokens, positions and
@@ -188,7 +207,8 @@ class StepContext:
                 for i, table in enumerate(group):
                     view[base + i * w:base + i * w + len(table)] = table
                     self._table_lengths[g][i] = len(table)
-        self.sequences = [SequenceStep(s.slot, s.start, 1, s.first_position + 1) for s in self.sequences]
+        self.first_positions = [p + 1 for p in self.first_positions]
+        self._sequences = None
         self.max_kv_len += 1
         self._cleared = False
         self._upload(self._total if grown else self._moving)
