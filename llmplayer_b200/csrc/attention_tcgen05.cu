@@ -35,6 +35,39 @@ constexpr int STAGE_BYTES = 2 * KV_BYTES;
 constexpr int P_BYTES = ROWS * PAGE * 2;          // 16 KB
 constexpr int XCHG_BYTES = 2 * 2 * ROWS * 4;      // row maxima of the two halves, double-buffered
 constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + XCHG_BYTES + 1024 + 256;
+// Two float32 operations in one instruction (Blackwell's packed f32x2 forms): the softmax warps are bound by
+// how many instructions they issue.
+__device__ __forceinline__ void fma2(float& x0, float& x1, float a, float b) {            // x = x * a + b
+    uint64_t vx, va, vb;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(vx) : "f"(x0), "f"(x1));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(va) : "f"(a));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(vb) : "f"(b));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(vx) : "l"(vx), "l"(va), "l"(vb));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(vx));
+}
+__device__ __forceinline__ void addmul2(float& x0, float& x1, float y0, float y1, float a) {   // x = (x + y) * a
+    uint64_t vx, vy, va;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(vx) : "f"(x0), "f"(x1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(vy) : "f"(y0), "f"(y1));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(va) : "f"(a));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(vx) : "l"(vx), "l"(vy));
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(vx) : "l"(vx), "l"(va));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(vx));
+}
+
+__device__ __forceinline__ void add2(float& x0, float& x1, float y0, float y1) {              // x += y
+    uint64_t vx, vy;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(vx) : "f"(x0), "f"(x1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(vy) : "f"(y0), "f"(y1));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(vx) : "l"(vx), "l"(vy));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(vx));
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
 constexpr int THREADS = 320;       // warp 0: loader, warp 1: MMA, warps 2-9: softmax
 constexpr int TMEM_COLS = 256;     // S[2]: 0..127, O_page[2]: 128..255
 
@@ -204,12 +237,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // operations would cost its full latency on a warp that has little else to issue
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int j = 0; j < HALF; ++j) mx4[j & 3] = fmaxf(mx4[j & 3], __uint_as_float(sreg[j]));
+            for (int j = 0; j < HALF; j += 8) {             // three-input maximum: two scores per instruction
+                mx4[0] = max3(mx4[0], __uint_as_float(sreg[j]), __uint_as_float(sreg[j + 1]));
+                mx4[1] = max3(mx4[1], __uint_as_float(sreg[j + 2]), __uint_as_float(sreg[j + 3]));
+                mx4[2] = max3(mx4[2], __uint_as_float(sreg[j + 4]), __uint_as_float(sreg[j + 5]));
+                mx4[3] = max3(mx4[3], __uint_as_float(sreg[j + 6]), __uint_as_float(sreg[j + 7]));
+            }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             float* mine = xchg + ((i & 1) * 2 + half) * ROWS;
             const float* other = xchg + ((i & 1) * 2 + (half ^ 1)) * ROWS;
             mine[r] = mx;
-            asm volatile("bar.sync 2, 256;" ::: "memory");   // the eight softmax warps
+            // the two warps that share these 32 rows (each has half of the keys) meet; the other six go on
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
             mx = fmaxf(mx, other[r]);
             const float m_new = fmaxf(m, mx * scale_log2);
             const float alpha = ex2(m - m_new);
@@ -220,10 +259,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int c = 0; c < HALF / 8; ++c) {
                 float e[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    e[j] = ex2(fmaf(__uint_as_float(sreg[c * 8 + j]), scale_log2, -m_new));
-                    sum4[j & 3] += e[j];
+                for (int j = 0; j < 8; j += 2) {
+                    e[j] = __uint_as_float(sreg[c * 8 + j]);
+                    e[j + 1] = __uint_as_float(sreg[c * 8 + j + 1]);
+                    fma2(e[j], e[j + 1], scale_log2, -m_new);
                 }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) e[j] = ex2(e[j]);
+                add2(sum4[0], sum4[1], e[0], e[1]);
+                add2(sum4[2], sum4[3], e[2], e[3]);
+                add2(sum4[0], sum4[1], e[4], e[5]);
+                add2(sum4[2], sum4[3], e[6], e[7]);
                 uint4 packed;
                 __nv_bfloat162 t0 = __floats2bfloat162_rn(e[0], e[1]), t1 = __floats2bfloat162_rn(e[2], e[3]);
                 __nv_bfloat162 t2 = __floats2bfloat162_rn(e[4], e[5]), t3 = __floats2bfloat162_rn(e[6], e[7]);
@@ -247,7 +293,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     tmem_ld32(lane_addr + 2 * PAGE + (pi & 1) * HD + half * HALF, oreg);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int d = 0; d < HALF; ++d) o[d] = (o[d] + __uint_as_float(oreg[d])) * alpha;
+                    for (int d = 0; d < HALF; d += 2)
+                        addmul2(o[d], o[d + 1], __uint_as_float(oreg[d]), __uint_as_float(oreg[d + 1]), alpha);
                 }
                 tcgen05_fence_before();
             }
@@ -268,9 +315,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // the two halves of a row add their sums
         float* mine = xchg + half * ROWS;
         const float* other = xchg + (half ^ 1) * ROWS;
-        asm volatile("bar.sync 2, 256;" ::: "memory");       // everyone is past the last maximum exchange
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");       // both are past the last maximum exchange
         mine[r] = l;
-        asm volatile("bar.sync 2, 256;" ::: "memory");
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
         l += other[r];
         if (ok && *failed == 0 && r < rows) {
             const float inv = 1.0f / l;
