@@ -402,11 +402,10 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
 
 import os as _os
 FEW_TOKENS_MAX = 64                  # what the few-token kernel takes
-# Up to where the parts choose it with the norm inside. Measured at the 1B shape: at 8 tokens the step
-# takes 0.79 ms against 0.85 ms with separate norm kernels; from 9 tokens on the float32 rows of x that every
-# CTA then reads (twice the bytes of the normed bfloat16 rows, the same lines for all CTAs) cost more than the
-# norm kernels they save (16 tokens: 0.92 ms against 0.88 ms).
-FEW_TOKENS = int(_os.environ.get("LLMPLAYER_B200_FEW_TOKENS", "8"))
+# Up to where the parts choose it with the norm inside. Measured at the 1B shape (ms per step, norm inside
+# against separate norm kernels): 8 tokens 0.70 / 0.76, 12 tokens 0.84 / 0.87, 16 tokens 0.85 / 0.88; at 32 tokens
+# the mma.sync kernel itself loses to the tcgen05 one (1.34 against 1.02).
+FEW_TOKENS = int(_os.environ.get("LLMPLAYER_B200_FEW_TOKENS", "16"))
 
 
 def gemm_few(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, norm=None,
