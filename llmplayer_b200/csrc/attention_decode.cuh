@@ -130,6 +130,8 @@ struct FusedDecodeArgs {
 };
 
 // The same in two steps, for callers that want the loads of several elements in flight before they combine them.
+// (products and sums are rounded one by one, as in the rotation kernels of elementwise.cu: a key must get the
+// same bits whichever kernel stores it)
 __device__ __forceinline__ int rotation_partner(int e, int rd, int interleaved) {
     const int half = rd >> 1;
     return interleaved ? (e ^ 1) : (e < half ? e + half : e - half);
@@ -140,7 +142,8 @@ __device__ __forceinline__ float rotate_value(float val, float other, int e, int
     const int half = rd >> 1;
     const bool first = interleaved ? (e & 1) == 0 : e < half;
     const int pair = interleaved ? e >> 1 : (first ? e : e - half);
-    return first ? val * cs[pair] - other * sn[pair] : other * sn[pair] + val * cs[pair];
+    return first ? __fsub_rn(__fmul_rn(val, cs[pair]), __fmul_rn(other, sn[pair]))
+                 : __fadd_rn(__fmul_rn(other, sn[pair]), __fmul_rn(val, cs[pair]));
 }
 
 __device__ __forceinline__ float rotated(const float* head, int e, int rd, int interleaved, const float* cs,
@@ -153,7 +156,8 @@ __device__ __forceinline__ float rotated(const float* head, int e, int rd, int i
         if (interleaved) { pair = e >> 1; first = (e & 1) == 0; partner = e ^ 1; }
         else { first = e < half; pair = first ? e : e - half; partner = first ? e + half : e - half; }
         const float other = __ldcg(head + partner);
-        val = first ? val * cs[pair] - other * sn[pair] : other * sn[pair] + val * cs[pair];
+        val = first ? __fsub_rn(__fmul_rn(val, cs[pair]), __fmul_rn(other, sn[pair]))
+                 : __fadd_rn(__fmul_rn(other, sn[pair]), __fmul_rn(val, cs[pair]));
     }
     return val;
 }

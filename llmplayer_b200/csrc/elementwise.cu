@@ -86,6 +86,52 @@ rmsnorm_kernel(float* __restrict__ x, const TAdd* __restrict__ add, const int* _
     }
 }
 
+// The same for rows of a multiple of 4 values without a residual add: four values per load and store.
+constexpr int NORM_VEC_PER = 4;          // float4 per thread: rows up to 256 * 4 * 4 = 4096 values
+template <typename TOut>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_vec4_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ w,
+                    TOut* __restrict__ out, int d, float eps, float* __restrict__ zero, long long zero_count) {
+    __shared__ float scratch[32];
+    lp_grid_release();
+    lp_grid_wait();
+    const int r = blockIdx.x;
+    const long long src = rows ? rows[r] : r;
+    const float4* xr = reinterpret_cast<const float4*>(x + src * d);
+    const int quads = d >> 2;
+    float4 v[NORM_VEC_PER];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_PER; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < quads) v[k] = xr[i];
+    }
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_PER; ++k) ss += (v[k].x * v[k].x + v[k].y * v[k].y) + (v[k].z * v[k].z + v[k].w * v[k].w);
+    clear_on_the_side(zero, zero_count);
+    ss = lp_block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+    const float4* wq = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int k = 0; k < NORM_VEC_PER; ++k) {
+        const int i = threadIdx.x + k * NORM_THREADS;
+        if (i < quads) {
+            const float4 g = wq[i];
+            const float a = v[k].x * scale * g.x, b = v[k].y * scale * g.y, c = v[k].z * scale * g.z, e = v[k].w * scale * g.w;
+            if (sizeof(TOut) == 2) {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, e);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(out + (long long)r * d)[i] = packed;
+            } else {
+                reinterpret_cast<float4*>(out + (long long)r * d)[i] = make_float4(a, b, c, e);
+            }
+        }
+    }
+}
+
 template <typename TOut, typename TAdd>
 __global__ void rmsnorm_wide_kernel(float* __restrict__ x, const TAdd* __restrict__ add,
                                     const int* __restrict__ rows, const float* __restrict__ w,
@@ -117,6 +163,17 @@ extern "C" int lp_rmsnorm(float* x, const void* add, int add_dtype, const int* r
     if (d <= 0) LP_REFUSE("rmsnorm: width %d", d);
     if (add && rows) LP_REFUSE("rmsnorm: a fused residual add cannot be combined with a row selection");
     const bool wide = d > NORM_THREADS * NORM_PER;
+    if (!add && d % 4 == 0 && d <= NORM_THREADS * 4 * NORM_VEC_PER &&
+        ((((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) == 0)) {
+        if (out_dtype == LP_BF16)
+            lp_launch(rmsnorm_vec4_kernel<__nv_bfloat16>, R, NORM_THREADS, 0, stream, (const float*)x, rows, w,
+                      (__nv_bfloat16*)out, d, eps, zero, zero_count);
+        else if (out_dtype == LP_F32)
+            lp_launch(rmsnorm_vec4_kernel<float>, R, NORM_THREADS, 0, stream, (const float*)x, rows, w, (float*)out, d,
+                      eps, zero, zero_count);
+        else LP_REFUSE("rmsnorm: dtype code out=%d", out_dtype);
+        return lp_check_launch("rmsnorm");
+    }
 #define LP_LAUNCH_NORM(TOUT, TADD)                                                                              \
     do {                                                                                                        \
         if (wide)                                                                                               \
@@ -187,7 +244,8 @@ rope_cache_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
         for (int head = head_begin + warp; head < rot_end; head += nwarps) {
             const float* hsrc = src + (long long)head * hd;
             const float xa = hsrc[a], xb = hsrc[b];
-            const float ra = xa * c - xb * sv, rb = xa * sv + xb * c;
+            // products and sums rounded one by one (no contraction into FMAs): the same bits as the kernel in fours
+            const float ra = __fsub_rn(__fmul_rn(xa, c), __fmul_rn(xb, sv)), rb = __fadd_rn(__fmul_rn(xa, sv), __fmul_rn(xb, c));
             if (head < H) {
                 q_out[dest(head, a)] = lp_from_float<TQ>(ra);
                 q_out[dest(head, b)] = lp_from_float<TQ>(rb);
@@ -214,6 +272,77 @@ rope_cache_kernel(const float* __restrict__ qkv, int ld, const float* __restrict
     }
 }
 
+// The common case in fours: split-half pairs over the whole head (rd == hd, hd a multiple of 8). An item is four
+// neighbouring pairs of one head: two float4 loads, one float4 of cosines and of sines, two stores of four values.
+template <typename T> __device__ __forceinline__ void store4(T* dst, float a, float b, float c, float d);
+template <> __device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <typename TQ, typename TKV>
+__global__ void __launch_bounds__(256)
+rope_cache_vec_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ inv_freq,
+                      const int* __restrict__ positions, const int* __restrict__ seq_ids,
+                      const int* __restrict__ page_table, int pt_stride, TQ* __restrict__ q_out,
+                      TKV* __restrict__ pages, int H, int G, int hd, int page_size) {
+    __shared__ __align__(16) float cs[128], sn[128];
+    lp_grid_release();
+    lp_grid_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = hd >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    __syncthreads();
+    const float* src = qkv + (long long)t * ld;
+    long long page_base = 0;
+    if (pages) {
+        const int page = page_table[(long long)seq_ids[t] * pt_stride + pos / page_size];
+        page_base = (long long)page * 2 * G * page_size * hd + (long long)(pos % page_size) * hd;
+    }
+    const int qph = half >> 2;                                   // items per rotated head
+    const int rot_heads = pages ? H + G : H;
+    for (int it = threadIdx.x; it < rot_heads * qph; it += blockDim.x) {
+        const int head = it / qph, a = (it - head * qph) * 4;
+        const float* hsrc = src + (long long)head * hd;
+        const float4 xa = *reinterpret_cast<const float4*>(hsrc + a);
+        const float4 xb = *reinterpret_cast<const float4*>(hsrc + a + half);
+        const float4 c = *reinterpret_cast<const float4*>(cs + a);
+        const float4 sv = *reinterpret_cast<const float4*>(sn + a);
+        // products and sums rounded one by one (no contraction into FMAs): the same bits as the kernel above,
+        // whichever of the two a step's size selects
+#define LP_ROT_A(u) __fsub_rn(__fmul_rn(xa.u, c.u), __fmul_rn(xb.u, sv.u))
+#define LP_ROT_B(u) __fadd_rn(__fmul_rn(xa.u, sv.u), __fmul_rn(xb.u, c.u))
+        const float ra0 = LP_ROT_A(x), ra1 = LP_ROT_A(y), ra2 = LP_ROT_A(z), ra3 = LP_ROT_A(w);
+        const float rb0 = LP_ROT_B(x), rb1 = LP_ROT_B(y), rb2 = LP_ROT_B(z), rb3 = LP_ROT_B(w);
+#undef LP_ROT_A
+#undef LP_ROT_B
+        if (head < H) {
+            TQ* dst = q_out + ((long long)t * H + head) * hd + a;
+            store4<TQ>(dst, ra0, ra1, ra2, ra3);
+            store4<TQ>(dst + half, rb0, rb1, rb2, rb3);
+        } else {
+            TKV* dst = pages + page_base + (long long)(head - H) * page_size * hd + a;
+            store4<TKV>(dst, ra0, ra1, ra2, ra3);
+            store4<TKV>(dst + half, rb0, rb1, rb2, rb3);
+        }
+    }
+    if (pages) {                                                 // values: copied as they are
+        const int per = hd >> 2;
+        for (int it = threadIdx.x; it < G * per; it += blockDim.x) {
+            const int g = it / per, e = (it - g * per) * 4;
+            const float4 v = *reinterpret_cast<const float4*>(src + (long long)(H + G + g) * hd + e);
+            store4<TKV>(pages + page_base + ((long long)G + g) * page_size * hd + e, v.x, v.y, v.z, v.w);
+        }
+    }
+}
+
 extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_freq, const int* positions,
                                    const int* seq_ids, const int* page_table, int pt_stride, void* q_out,
                                    int q_dtype, void* pages, int kv_dtype, int T, int H, int G, int hd, int rd,
@@ -226,6 +355,20 @@ extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_fr
     const int heads = pages ? H + 2 * G : H;
     if (ld < heads * hd) LP_REFUSE("rope_cache_write: row of %d values for %d heads of %d", ld, heads, hd);
     if (pages && page_size <= 0) LP_REFUSE("rope_cache_write: page size %d", page_size);
+    // many tokens, split-half pairs over whole heads of a multiple of 8, everything 16-byte aligned: in fours
+    if (T >= 256 && !interleaved && rd == hd && hd % 8 == 0 && ld % 4 == 0 &&
+        ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)pages) & 15) == 0)) {
+#define LP_LAUNCH_ROPE_VEC(TQ, TKV)                                                                         \
+    lp_launch(rope_cache_vec_kernel<TQ, TKV>, T, 256, 0, stream, qkv, ld, inv_freq, positions, seq_ids,      \
+              page_table, pt_stride, (TQ*)q_out, (TKV*)pages, H, G, hd, page_size)
+        if (q_dtype == LP_F32 && kv_dtype == LP_F32) LP_LAUNCH_ROPE_VEC(float, float);
+        else if (q_dtype == LP_BF16 && kv_dtype == LP_BF16) LP_LAUNCH_ROPE_VEC(__nv_bfloat16, __nv_bfloat16);
+        else if (q_dtype == LP_F32 && kv_dtype == LP_BF16) LP_LAUNCH_ROPE_VEC(float, __nv_bfloat16);
+        else if (q_dtype == LP_BF16 && kv_dtype == LP_F32) LP_LAUNCH_ROPE_VEC(__nv_bfloat16, float);
+        else LP_REFUSE("rope_cache_write: dtype codes q=%d kv=%d", q_dtype, kv_dtype);
+#undef LP_LAUNCH_ROPE_VEC
+        return lp_check_launch("rope_cache_write");
+    }
     // many tokens: one block per token takes all its heads; few tokens: the heads are shared out
     int heads_per_block = heads;
     if (T < 256) {

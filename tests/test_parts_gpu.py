@@ -235,3 +235,55 @@ def test_block_part(dtype):
     r = r + plain_attention_part(P.rms_norm(r, hw["n1"], 1e-5), hw, H, G, hd, 10000.0, torch.arange(T), None)
     r = r + P.swiglu(P.rms_norm(r, hw["n2"], 1e-5), hw["g"], hw["u"], hw["dn"])
     assert rel(x, r) < TOL[dtype]
+
+
+@pytest.mark.parametrize("hd,dtype", [(16, torch.float32), (64, torch.bfloat16), (48, torch.bfloat16)])
+def test_rotation_and_cache_write_of_a_long_prompt(hd, dtype):
+    """A prompt of some hundred tokens takes the kernel that works in fours (whole heads, split halves)."""
+    from llmplayer_b200.cache import KVRequest, SequenceCache
+    from llmplayer_b200.engine.step import Workspace
+    from llmplayer_b200.kernels import ops
+    from llmplayer_b200.parts import POSITIONS
+    from llmplayer_b200.parts.specs import PositionSpec
+    H, G, T = 5, 2, 333
+    rope = POSITIONS.build(PositionSpec(kind="rope", head_dim=hd, rotary_dim=hd, theta=50000.0, pairing="split_half"))
+    rope.load({}, runtime("float32"))
+    cache = SequenceCache([KVRequest(G, hd)], max_tokens=1024, max_slots=2, kv_dtype=dtype, device=DEV)
+    ws = Workspace(DEV)
+    a = cache.acquire()
+    ctx = make_context(cache, ws, [a], [T])
+    qkv = torch.randn(T, (H + 2 * G) * hd, generator=torch.Generator().manual_seed(hd))
+    q_out = torch.empty(T, H * hd, device=DEV, dtype=dtype)
+    view = cache.view(0)
+    ops.rope_cache_write(qkv.to(DEV), rope.inv_freq, ctx.positions, ctx.seq_ids, ctx.page_tables[0], q_out,
+                         view.pages, num_heads=H, num_kv_heads=G, head_dim=hd, rotary_dim=hd, interleaved=False)
+    pos = torch.arange(T)
+    inv = P.rope_inverse_frequencies(hd, 50000.0)
+    q_ref = P.rope_rotate(qkv[:, :H * hd].reshape(T, H, hd).double(), pos, inv, "split_half")
+    k_ref = P.rope_rotate(qkv[:, H * hd:(H + G) * hd].reshape(T, G, hd).double(), pos, inv, "split_half")
+    v_ref = qkv[:, (H + G) * hd:].reshape(T, G, hd).double()
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    assert rel(q_out.float().reshape(T, H, hd), q_ref) < tol
+    table = cache.page_tables([a])[0][0]
+    stored = torch.cat([view.pages[p].float().cpu() for p in table], dim=2)[:, :, :T]      # [2, G, T, hd]
+    assert rel(stored[0].transpose(0, 1), k_ref) < tol
+    assert rel(stored[1].transpose(0, 1), v_ref) < tol
+
+
+@pytest.mark.parametrize("d,dtype", [(2048, torch.bfloat16), (264, torch.float32), (4096, torch.bfloat16)])
+def test_rms_norm_of_rows_of_a_multiple_of_four(d, dtype):
+    """Rows of a multiple of 4 values without a residual add take the kernel that loads four values at a time."""
+    from llmplayer_b200.kernels import ops
+    g = torch.Generator().manual_seed(d)
+    x = (torch.randn(37, d, generator=g) * 3).to(DEV)
+    w = (1 + 0.2 * torch.randn(d, generator=g)).to(DEV)
+    out = torch.empty(37, d, device=DEV, dtype=dtype)
+    junk = torch.full((1000,), 5.0, device=DEV)
+    ops.rmsnorm(x, w, 3e-6, out, clear=junk)
+    assert rel(out.float(), P.rms_norm(x.double().cpu(), w.double().cpu(), 3e-6)) < (1e-6 if dtype == torch.float32 else 1e-2)
+    assert float(junk.abs().sum()) == 0.0
+    rows = torch.tensor([5, 0, 36], dtype=torch.int32, device=DEV)
+    sel = torch.empty(3, d, device=DEV, dtype=dtype)
+    ops.rmsnorm(x, w, 3e-6, sel, rows=rows)
+    assert rel(sel.float(), P.rms_norm(x[rows.long()].double().cpu(), w.double().cpu(), 3e-6)) < (1e-6 if dtype == torch.float32 else 1e-2)
+
