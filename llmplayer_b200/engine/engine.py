@@ -134,10 +134,19 @@ class Engine:
         """Run a planned step; returns float32 logits [wanted, vocab] (valid until the next step)."""
         logits = self.workspace.get("logits", (ctx.num_wanted, self.vocab_size), torch.float32)
         self.last_step_h2d_bytes = ctx.h2d_bytes
-        if self.use_graphs and self.runtime.fast and ctx.all_single:
-            self._run_captured(ctx, logits)
-        else:
-            self.model.forward(ctx, self.cache, ctx.rows, logits)
+        try:
+            if self.use_graphs and self.runtime.fast and ctx.all_single:
+                self._run_captured(ctx, logits)
+            else:
+                self.model.forward(ctx, self.cache, ctx.rows, logits)
+        except BaseException:
+            # a step that broke off may have left partial sums behind in buffers that are zero between uses
+            self._last_ctx = None
+            try:
+                self.workspace.restore_zeroes()
+            except Exception:
+                pass
+            raise
         self.cache.commit(ctx.slot_list, ctx.new_counts)
         return logits
 

@@ -42,6 +42,7 @@ class Workspace:
         self.device = device
         self._buffers: Dict[Tuple[str, torch.dtype], torch.Tensor] = {}
         self._pinned: Dict[str, tuple] = {}
+        self._kept_zero = set()
         self.version = 0      # bumped whenever a buffer moved (captured graphs are stale then)
 
     def pinned(self, name: str, count: int):
@@ -80,8 +81,14 @@ class Workspace:
         if buf is None or buf.numel() < count:
             buf = torch.zeros(max(count, 1), dtype=torch.float32, device=self.device)
             self._buffers[key] = buf
+            self._kept_zero.add(key)
             self.version += 1
         return buf[:count]
+
+    def restore_zeroes(self) -> None:
+        """After a step that broke off half-way: the buffers that are zero between uses are made zero again."""
+        for key in self._kept_zero:
+            self._buffers[key].zero_()
 
 
 def _round_up(n: int, m: int) -> int:

@@ -43,3 +43,18 @@ def test_block_hands_pending_norm_only_to_parts_that_ask_for_it():
     class Plain:
         pass
     assert not getattr(Plain(), "takes_pending_norm", False)
+
+
+def test_buffers_kept_zero_are_restored_after_a_broken_step():
+    from llmplayer_b200.engine.step import Workspace
+    ws = Workspace("cpu")
+    a = ws.get_zeroed("sums", 10)
+    assert float(a.abs().sum()) == 0.0
+    a += 3.0                                   # a step left partial sums behind
+    other = ws.get("plain", (4,), torch.float32)
+    other.fill_(7.0)
+    ws.restore_zeroes()
+    assert float(ws.get_zeroed("sums", 10).abs().sum()) == 0.0
+    assert float(other.sum()) == 28.0          # ordinary scratch is left alone
+    bigger = ws.get_zeroed("sums", 100)        # growing hands out zeroes again
+    assert bigger.numel() == 100 and float(bigger.abs().sum()) == 0.0
