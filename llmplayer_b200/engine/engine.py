@@ -279,7 +279,18 @@ class Engine:
                               default_stop_ids=self.config.stop_token_ids())
         out = loop.run(requests, on_token=on_token)
         self.last_generation_stats = loop.stats
+        self.check()
         return out
+
+    def check(self) -> None:
+        """Raise if a kernel with bounded waits reported that one of them ran out since the last check
+        (reads one word back from the device, which synchronises)."""
+        try:
+            ops.check_kernel_status()
+        except BaseException:
+            self._last_ctx = None
+            self.workspace.restore_zeroes()
+            raise
 
     # ------------------------------------------------------------------ reporting
     def info(self) -> str:

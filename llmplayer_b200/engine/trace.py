@@ -46,6 +46,7 @@ def main(argv=None) -> int:
             want.append(entry.get("want", []))
         if entries:
             logits = engine.step(entries, want)
+            engine.check()                     # a kernel that gave up waiting must not pass as a result
             if logits.shape[0]:
                 arr = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
                 path = os.path.join(args.out, f"{step['step']}.f32")
