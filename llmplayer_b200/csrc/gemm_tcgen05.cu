@@ -18,6 +18,16 @@
 // gate and an up accumulator of 128 features each, filled from 64-row boxes of the same
 // layout, so that the activation needs no exchange.
 //
+// Three forms live in this file, chosen by the number of tokens of a step:
+//   * gemm_tcgen05_kernel: one output tile per CTA, token tiles of 16..256 (what is described above);
+//     serves 17 to some hundred tokens.
+//   * gemm_fewtok_kernel: at most 64 tokens (chosen up to 16). The same TMA ring, but four warps of
+//     ldmatrix + mma.sync consume it: one tcgen05.mma takes about 142 cycles whatever its shape, and with
+//     weights as its 128-row operand that is too few weight bytes per instruction to keep up with HBM.
+//     Can apply the RMS norm of its input itself.
+//   * gemm_persistent_kernel: prompts. One CTA per SM walks over the tiles with two accumulators in tensor
+//     memory; for the gated product the tokens are the MMA's M and 256 weight rows its N.
+//
 // Counterparts in the reference are its one-warp-per-row SIMT kernels
 // (src/main/resources/kernels/cuda/matmul_bf16.cu:6-37, silu_mul.cu:6-15).
 //
