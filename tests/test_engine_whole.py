@@ -99,6 +99,41 @@ def test_full_width_layers_bfloat16_against_float32(tmp_path):
     assert_close(logits["bfloat16"][1], ref_tail, "bfloat16", "1B widths, decoded")
 
 
+@pytest.mark.parametrize("batch", [12, 20])
+def test_full_width_decode_batches(tmp_path, batch):
+    """Sequences of unequal lengths decoding together at the Llama-3.2-1B widths, against the float32 engine.
+    Twelve: the few-token products with two tiles of 8 tokens, the norm inside them and the row factor left to
+    the attention kernel. Twenty: the tcgen05 products with a 32-token tile and norm kernels of their own."""
+    from llmplayer_b200 import Engine
+    from llmplayer_b200.config import config_from_dict
+    from llmplayer_b200.weights import write_random_model
+    raw = {
+        "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 2048, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 64, "intermediate_size": 8192, "vocab_size": 128256,
+        "rope_theta": 500000.0, "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+        "max_position_embeddings": 4096,
+    }
+    model_dir = str(tmp_path / "wide12")
+    write_random_model(config_from_dict(raw), 7, model_dir, dtype="bfloat16")
+    lengths = [5 + 11 * (i % 12) + i // 12 for i in range(batch)]    # 5 .. 126: some cross a page boundary
+    steps = 3
+    seqs = [random_tokens(n + steps, 128256, seed=30 + i) for i, n in enumerate(lengths)]
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.load(model_dir, dtype=dtype, max_tokens=batch * 192, max_slots=batch)
+        slots = [eng.acquire() for _ in seqs]
+        eng.step([(s, q[:n]) for s, q, n in zip(slots, seqs, lengths)], [[] for _ in seqs])
+        outs = []
+        for k in range(steps):
+            outs.append(eng.step([(s, [q[n + k]]) for s, q, n in zip(slots, seqs, lengths)], [[0]] * batch).cpu().clone())
+        eng.check()
+        got[dtype] = torch.stack(outs)
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+    assert_close(got["bfloat16"], got["float32"], "bfloat16", f"1B widths, {batch} sequences")
+
+
 @pytest.mark.parametrize("stored,dtype", [("float32", "bfloat16"), ("bfloat16", "float32")])
 def test_stored_and_compute_dtypes_may_differ(tmp_path, stored, dtype):
     """A folder stored in 32 bits run in bfloat16 keeps its float32 matrices (plain products with
