@@ -134,6 +134,41 @@ def test_full_width_decode_batches(tmp_path, batch):
     assert_close(got["bfloat16"], got["float32"], "bfloat16", f"1B widths, {batch} sequences")
 
 
+def test_wider_layers_with_heads_of_128(tmp_path):
+    """Two layers at the widths of a larger model of the family (4096 wide, 32/8 heads of 128, 14336, an odd
+    vocabulary, untied head): prompts of unequal lengths in one step, then three decode steps of the batch of
+    eight, bfloat16 against float32."""
+    from helpers import relative_error
+    from llmplayer_b200 import Engine
+    from llmplayer_b200.config import config_from_dict
+    from llmplayer_b200.weights import write_random_model
+    raw = {
+        "architectures": ["LlamaForCausalLM"], "num_hidden_layers": 2, "hidden_size": 4096, "num_attention_heads": 32,
+        "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 14336, "vocab_size": 32003,
+        "rope_theta": 500000.0, "rope_scaling": None, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+        "max_position_embeddings": 8192,
+    }
+    model_dir = str(tmp_path / "wider")
+    write_random_model(config_from_dict(raw), 3, model_dir, dtype="bfloat16")
+    lengths = [700, 40, 333, 64, 65, 129, 1, 512]
+    steps = 3
+    seqs = [random_tokens(n + steps, 32003, seed=50 + i) for i, n in enumerate(lengths)]
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.load(model_dir, dtype=dtype, max_tokens=8 * 768, max_slots=8)
+        slots = [eng.acquire() for _ in seqs]
+        outs = [eng.step([(s, q[:n]) for s, q, n in zip(slots, seqs, lengths)], [[n - 1] for n in lengths]).cpu().clone()]
+        for k in range(steps):
+            outs.append(eng.step([(s, [q[n + k]]) for s, q, n in zip(slots, seqs, lengths)], [[0]] * 8).cpu().clone())
+        eng.check()
+        got[dtype] = torch.stack(outs)
+        eng.close()
+        del eng
+        torch.cuda.empty_cache()
+    for k in range(steps + 1):
+        assert_close(got["bfloat16"][k], got["float32"][k], "bfloat16", f"wider layers, step {k}")
+
+
 @pytest.mark.parametrize("stored,dtype", [("float32", "bfloat16"), ("bfloat16", "float32")])
 def test_stored_and_compute_dtypes_may_differ(tmp_path, stored, dtype):
     """A folder stored in 32 bits run in bfloat16 keeps its float32 matrices (plain products with
