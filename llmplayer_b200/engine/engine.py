@@ -8,7 +8,6 @@ then one token for each sequence, always from the cache that earlier steps left.
 """
 from __future__ import annotations
 
-import os
 from typing import List, Optional, Sequence, Tuple
 
 import torch

@@ -23,7 +23,6 @@ from typing import List, Optional, Tuple
 
 import torch
 
-from ..errors import KernelError
 from ..kernels import ops
 
 X_BF16, X_RMSNORM = 0, 1
