@@ -507,7 +507,9 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
     // up to two CTAs per SM: 8 warps, two pages at a time, six in shared memory (batch 32: 0.96 ms per step against
     // 1.02 with 4 warps; with more CTAs than that, batch 64, the 4-warp form wins: 1.19 against 1.28)
     const bool mid = !wide && hd <= 64 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= 296;
-    const int stages = wide ? 8 : mid ? 6 : 3, nw = wide ? 16 : mid ? 8 : 4;
+    // heads of 128 (pages of 32 KB): 8 warps, two pages at a time, four in shared memory, one CTA per SM
+    const bool wide128 = hd > 64 && hd <= 128 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= 148;
+    const int stages = wide ? 8 : mid ? 6 : wide128 ? 4 : 3, nw = wide ? 16 : (mid || wide128) ? 8 : 4;
     const int merge = (2 * nw * 16 + nw * 16 * hd) * 4;
     const int smem = (stages * stage > merge ? stages * stage : merge) + extra;
     float* part_o = scratch;
@@ -527,9 +529,9 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
                   num_splits, head_groups, fused);                                                               \
     } while (0)
     if (hd == 64) { if (wide) LP_DECODE_FUSED(64, 64, 8, 16); else if (mid) LP_DECODE_FUSED(64, 64, 6, 8); else LP_DECODE_FUSED(64, 64, 3, 4); }
-    else if (hd == 128) LP_DECODE_FUSED(128, 128, 3, 4);
+    else if (hd == 128) { if (wide128) LP_DECODE_FUSED(128, 128, 4, 8); else LP_DECODE_FUSED(128, 128, 3, 4); }
     else if (hd <= 64) { if (wide) LP_DECODE_FUSED(64, 0, 8, 16); else if (mid) LP_DECODE_FUSED(64, 0, 6, 8); else LP_DECODE_FUSED(64, 0, 3, 4); }
-    else if (hd <= 128) LP_DECODE_FUSED(128, 0, 3, 4);
+    else if (hd <= 128) { if (wide128) LP_DECODE_FUSED(128, 0, 4, 8); else LP_DECODE_FUSED(128, 0, 3, 4); }
     else LP_DECODE_FUSED(256, 0, 3, 4);
 #undef LP_DECODE_FUSED
     return lp_check_launch("attention_decode_fused");
