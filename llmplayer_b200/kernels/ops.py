@@ -62,8 +62,10 @@ _SIGNATURES = {
         "lp_program_launch": [_P, _I, _I, _I, _P, _P, _P, _P],
     },
     "sampling": {
-        "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P],
+        "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P],
         "lp_sample_params_size": [],
+        "lp_sample_select_words": [],
+        "lp_sample_slice_capacity": [_I],
         "lp_argmax": [_P, ctypes.c_longlong, _I, _I, _P, _P, _P],
     },
 }
@@ -617,10 +619,22 @@ def attention(ctx, q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, page
 
 
 # --------------------------------------------------------------------------- sampling
+def sample_select_words() -> int:
+    """4-byte words of scratch per row that ``sample`` wants for finding top-k candidates with several blocks."""
+    return library("sampling").lp_sample_select_words()
+
+
+def sample_slice_capacity(vocab: int) -> int:
+    """The largest top-k whose candidates several blocks per row find together (0: none at this vocabulary)."""
+    return library("sampling").lp_sample_slice_capacity(int(vocab))
+
+
 def sample(logits: torch.Tensor, work: torch.Tensor, params: torch.Tensor, edit_token: torch.Tensor,
            edit_subtract: torch.Tensor, edit_factor: torch.Tensor, out_token: torch.Tensor,
-           out_prob: torch.Tensor) -> None:
-    """One token per row of ``params`` (packed LpSampleParams records) from the float32 ``logits``."""
+           out_prob: torch.Tensor, select: Optional[torch.Tensor] = None) -> None:
+    """One token per row of ``params`` (packed LpSampleParams records) from the float32 ``logits``.
+    ``select``: int32 scratch of ``sample_select_words()`` per row; with it, rows whose top-k is at most
+    ``sample_slice_capacity(vocab)`` have their candidates found by several blocks each."""
     _want(logits, "sample logits", torch.float32, 2)
     _want(work, "sample work", torch.float32, 2)
     _want(params, "sample params", torch.uint8, 1)
@@ -635,8 +649,14 @@ def sample(logits: torch.Tensor, work: torch.Tensor, params: torch.Tensor, edit_
     V = logits.shape[1]
     if params.numel() != B * record or work.shape != (B, V) or out_prob.numel() != B:
         raise KernelError(f"sample: {params.numel()} parameter bytes, work {tuple(work.shape)} for {B} rows of {V}")
+    select_ptr = 0
+    if select is not None:
+        _want(select, "sample select scratch", torch.int32, 1)
+        if select.numel() < B * lib.lp_sample_select_words():
+            raise KernelError(f"sample: select scratch of {select.numel()} words for {B} rows")
+        select_ptr = select.data_ptr()
     _check(lib, lib.lp_sample(logits.data_ptr(), V, work.data_ptr(), V, params.data_ptr(), B, edit_token.data_ptr(),
-                              edit_subtract.data_ptr(), edit_factor.data_ptr(), out_token.data_ptr(),
+                              edit_subtract.data_ptr(), edit_factor.data_ptr(), select_ptr, out_token.data_ptr(),
                               out_prob.data_ptr(), _stream()))
 
 

@@ -96,6 +96,8 @@ class BatchSampler:
         self._done = None
         self._constant = {}          # greedy batches without logit edits: parameters stay on the device
         self._dummy = None
+        self._select = None          # scratch of the two-stage top-k
+        self._slice_capacity = None
         self.last_h2d_bytes = 0
         self.last_d2h_bytes = 0
 
@@ -121,6 +123,8 @@ class BatchSampler:
             self._work = torch.empty((B, self.vocab_size), dtype=torch.float32, device=dev)
             self._out = torch.empty(2 * B, dtype=torch.int32, device=dev)
             self._dummy = (torch.zeros(1, dtype=torch.int32, device=dev), torch.ones(1, dtype=torch.float32, device=dev))
+            self._select = torch.empty(B * ops.sample_select_words(), dtype=torch.int32, device=dev)
+            self._slice_capacity = ops.sample_slice_capacity(self.vocab_size)
         out_tok = self._out[:B]
         out_prob = self._out[B:2 * B].view(torch.float32)
         all_edits = [s.logit_edits() for s in samplers]
@@ -169,7 +173,10 @@ class BatchSampler:
                 if len(self._constant) > 256:
                     self._constant.clear()
                 self._constant[key] = params_dev
-        ops.sample(logits, self._work[:B], params_dev, edit_tok, edit_sub, edit_fac, out_tok, out_prob)
+        # a small top-k: several blocks per row find the candidates before one block draws among them
+        sliced = any(not s.config.is_greedy and 0 < s.config.top_k <= self._slice_capacity for s in samplers)
+        ops.sample(logits, self._work[:B], params_dev, edit_tok, edit_sub, edit_fac, out_tok, out_prob,
+                   select=self._select if sliced else None)
         host = self._read_back(2 * B, while_waiting)         # one copy back: tokens, then probabilities
         self.last_d2h_bytes = 8 * B
         chosen = host[:B].tolist()

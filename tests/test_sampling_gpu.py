@@ -19,6 +19,8 @@ CONFIGS = [
     dict(temperature=1.0, top_k=0, top_p=1.0, mirostat=2, repetition_penalty=1.0),
     dict(temperature=0.8, top_k=20, top_p=0.9, repetition_penalty=1.1, dry_multiplier=0.8, dry_allowed_length=1,
          dry_range=16),
+    dict(temperature=1.1, top_k=900, top_p=0.97, repetition_penalty=1.0),        # many candidates on chip
+    dict(temperature=1.2, top_k=700, top_p=1.0, mirostat=2, mirostat_tau=6.0, repetition_penalty=1.0),
 ]
 
 
@@ -51,6 +53,34 @@ def test_batched_sampler_follows_the_plain_one(V, spread):
             if a != b:
                 mismatches.append((t, i, a, b))
                 # keep both histories alike so that later steps stay comparable
+                ours[i].recent[-1] = b
+    assert not mismatches, mismatches
+
+
+@pytest.mark.parametrize("V", [5003, 40000])
+def test_top_k_among_many_equal_values(V):
+    """Rows whose values repeat: the k-th largest has many equals, in one slice of the row or in all of them,
+    up to a row of one value only, where top-k keeps the whole vocabulary."""
+    dev = torch.device("cuda:0")
+    steps = 6
+    g = torch.Generator().manual_seed(77)
+    base = torch.randn(steps, V, generator=g) * 2.0
+    rows = [torch.round(base), torch.round(base * 4) / 4, torch.full((steps, V), 0.5),
+            torch.where(torch.arange(V) < V // 7, torch.round(base) + 2.0, base)]
+    configs = [dict(temperature=0.9, top_k=40, top_p=0.9, repetition_penalty=1.1),
+               dict(temperature=1.0, top_k=64, top_p=1.0, repetition_penalty=1.0),
+               dict(temperature=0.8, top_k=30, top_p=0.95, repetition_penalty=1.2),
+               dict(temperature=1.1, top_k=50, top_p=0.9, mirostat=2, repetition_penalty=1.0)]
+    plain = [P.PlainSampler(seed=7 + i, **c) for i, c in enumerate(configs)]
+    ours = [SequenceSampler(SamplerConfig(seed=7 + i, **c)) for i, c in enumerate(configs)]
+    batch = BatchSampler(V, dev)
+    mismatches = []
+    for t in range(steps):
+        got = batch.sample(torch.stack([x[t] for x in rows]).to(dev), list(range(len(rows))), ours)
+        want = [p.sample(x[t]) for p, x in zip(plain, rows)]
+        for i, (a, b) in enumerate(zip(got, want)):
+            if a != b:
+                mismatches.append((t, i, a, b))
                 ours[i].recent[-1] = b
     assert not mismatches, mismatches
 
