@@ -571,9 +571,13 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
 
     // softmax
     const float m = reduce_max(vals, n, sh);
-    for (int i = tid; i < n; i += THREADS) vals[i] = (vals[i] == -INFINITY) ? 0.f : expf(vals[i] - m);
-    __syncthreads();
-    float s = reduce_sum(vals, n, sh);
+    float part = 0.f;
+    for (int i = tid; i < n; i += THREADS) {
+        const float e = (vals[i] == -INFINITY) ? 0.f : expf(vals[i] - m);
+        vals[i] = e;
+        part += e;
+    }
+    float s = lp_block_sum(part, sh.fscratch);
     if (s > 0.f) {
         const float inv = 1.0f / s;
         for (int i = tid; i < n; i += THREADS) vals[i] *= inv;
