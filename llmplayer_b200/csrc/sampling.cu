@@ -30,6 +30,7 @@ namespace {
 
 constexpr int THREADS = 1024;
 constexpr int CAP = THREADS;   // candidates kept in shared memory after top-k: one per thread
+constexpr int TOP_P_TRY = 256; // top-p without top-k looks for its cut among this many largest values first
 constexpr int STAGE = 2048;    // values that the slices of a row may hand over together
 constexpr int SLICE_MAX = 8192;   // values of a row that one block of the first stage takes
 constexpr int SLICES_MAX = 32;
@@ -51,6 +52,7 @@ struct Shared {
     float stage_val[STAGE];    // what the first stage handed over ...
     int stage_idx[STAGE];      // ... with the places in the vocabulary
     int slice_at[SLICES_MAX + 1];
+    float many[16][32];        // 15 sums at a time: per warp, and (row 15) over the block
     Select select;
     int bcast_i;
     float bcast_f;
@@ -152,19 +154,25 @@ __device__ unsigned kth_largest_key(const float* vals, int n, int k, Select& sel
         if (threadIdx.x < 256) sel.hist[threadIdx.x] = 0;
         __syncthreads();
         const unsigned settled = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-        for (int base = 0; base < n; base += THREADS) {
-            const int i = base + threadIdx.x;
-            unsigned key = 0;
-            bool in = false;
-            if (i < n) {
-                key = ordered_key(vals[i]);
-                in = (key & settled) == prefix;
+        // eight values per thread are fetched before any is counted, so that their latencies overlap
+        for (int base = 0; base < n; base += 8 * THREADS) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * THREADS + (int)threadIdx.x;
+                v[u] = i < n ? vals[i] : 0.f;
             }
-            const unsigned takers = __ballot_sync(0xffffffffu, in);
-            if (in) {
-                const unsigned digit = (key >> shift) & 0xffu;
-                const unsigned same = __match_any_sync(takers, digit);
-                if ((int)(threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&sel.hist[digit], __popc(same));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = base + u * THREADS + (int)threadIdx.x;
+                const unsigned key = ordered_key(v[u]);
+                const bool in = i < n && (key & settled) == prefix;
+                const unsigned takers = __ballot_sync(0xffffffffu, in);
+                if (in) {
+                    const unsigned digit = (key >> shift) & 0xffu;
+                    const unsigned same = __match_any_sync(takers, digit);
+                    if ((int)(threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&sel.hist[digit], __popc(same));
+                }
             }
         }
         __syncthreads();
@@ -283,16 +291,47 @@ __device__ int walk_until(const float* list, int n, float target, float floor_va
 // and including that point.
 __device__ bool descending_cut(const float* vals, int n, float target, float floor_value, unsigned* cut_key,
                                int* ties_kept, Shared& sh) {
+    // The key is settled four bits at a time: for each of the 15 non-zero digits d, the sum of the values
+    // whose key is >= prefix | d << shift, and the largest digit whose sum still exceeds the target. Each
+    // sum is formed in the order in which a search bit by bit would form it.
     unsigned prefix = 0;
     bool any = false;
-    for (int bit = 31; bit >= 0; --bit) {
-        const unsigned cand = prefix | (1u << bit);
-        float s = 0.f;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int shift = 28; shift >= 0; shift -= 4) {
+        const unsigned settled = shift == 28 ? 0u : (0xffffffffu << (shift + 4));
+        float acc[15];
+#pragma unroll
+        for (int j = 0; j < 15; ++j) acc[j] = 0.f;
         for (int i = threadIdx.x; i < n; i += THREADS) {
             const float v = vals[i];
-            if (v >= floor_value && v > 0.f && ordered_key(v) >= cand) s += v;
+            if (v >= floor_value && v > 0.f) {
+                const unsigned key = ordered_key(v);
+                const unsigned high = key & settled;
+                // how many of the 15 candidates this key reaches
+                const int reaches = high > prefix ? 15 : high < prefix ? 0 : (int)((key >> shift) & 15u);
+#pragma unroll
+                for (int j = 0; j < 15; ++j) acc[j] += reaches > j ? v : 0.f;
+            }
         }
-        if (lp_block_sum(s, sh.fscratch) > target) { prefix = cand; any = true; }
+#pragma unroll
+        for (int j = 0; j < 15; ++j) acc[j] = lp_warp_sum(acc[j]);
+        __syncthreads();
+        if (lane == 0) {
+#pragma unroll
+            for (int j = 0; j < 15; ++j) sh.many[j][warp] = acc[j];
+        }
+        __syncthreads();
+        if (threadIdx.x < 15) {
+            float total = 0.f;
+            for (int w = 0; w < THREADS / 32; ++w) total += sh.many[threadIdx.x][w];
+            sh.many[15][threadIdx.x] = total;
+        }
+        __syncthreads();
+        int digit = 0;
+#pragma unroll
+        for (int j = 0; j < 15; ++j)
+            if (sh.many[15][j] > target) digit = j + 1;
+        if (digit > 0) { prefix |= (unsigned)digit << shift; any = true; }
     }
     if (!any) {
         // no bit could be set: either the whole mass stays below the target, or the cut lies at key 0
@@ -481,7 +520,7 @@ __device__ bool take_slices(const int* __restrict__ row_select, int slices, int 
     return true;
 }
 
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 sample_kernel(const float* __restrict__ logits, long long logits_stride, float* __restrict__ work, int V,
               const LpSampleParams* __restrict__ params, const int* __restrict__ edit_token,
               const float* __restrict__ edit_subtract, const float* __restrict__ edit_factor,
@@ -567,7 +606,7 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
             __syncthreads();
         }
     }
-    const bool small = n <= CAP;      // ranked and walked by one thread, else searched by all
+    bool small = n <= CAP;            // ranked and walked by one thread, else searched by all
 
     // softmax
     const float m = reduce_max(vals, n, sh);
@@ -578,9 +617,11 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
         part += e;
     }
     float s = lp_block_sum(part, sh.fscratch);
+    float largest = 1.f;
     if (s > 0.f) {
         const float inv = 1.0f / s;
         for (int i = tid; i < n; i += THREADS) vals[i] *= inv;
+        largest = inv;
     }
     __syncthreads();
 
@@ -602,7 +643,28 @@ sample_kernel(const float* __restrict__ logits, long long logits_stride, float* 
     if (p.top_p < 1.0f) {
         int c = 0;
         for (int i = tid; i < n; i += THREADS) c += vals[i] > 0.f;
-        if (block_sum_int(c, sh.iscratch) > 1) {
+        const int positives = block_sum_int(c, sh.iscratch);
+        if (positives > 1) {
+            // The cut mostly lies among the largest few values: if the TOP_P_TRY largest together exceed
+            // top-p, everything else goes, and the candidates alone are carried on. (Before min-p the largest
+            // probability is the softmax's exp(0) / sum: that many times it bounds what they hold.)
+            if (!small && (p.min_p > 0.f || (float)TOP_P_TRY * largest > p.top_p)) {
+                int reach;
+                const unsigned thr = kth_largest_key(vals, n, min(TOP_P_TRY, positives), sh.select, &reach);
+                if (reach <= CAP) {
+                    gather_candidates(vals, nullptr, n, thr, reach, sh);
+                    sort_descending(sh.cand_val, reach, sh);
+                    if (tid == 0) {
+                        int walked;
+                        float sum;
+                        sh.bcast_i = walk_until(sh.sorted, reach, p.top_p, 0.f, true, &walked, &sum);
+                    }
+                    __syncthreads();
+                    const bool inside = sh.bcast_i >= 0;
+                    __syncthreads();
+                    if (inside) { vals = sh.cand_val; ids = sh.cand_idx; n = reach; small = true; }
+                }
+            }
             if (small) {
                 sort_descending(vals, n, sh);
                 if (tid == 0) {

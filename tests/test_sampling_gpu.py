@@ -85,6 +85,32 @@ def test_top_k_among_many_equal_values(V):
     assert not mismatches, mismatches
 
 
+@pytest.mark.parametrize("V,spread", [(5003, 6.0), (128256, 5.0), (128256, 9.0)])
+def test_top_p_without_top_k_on_peaked_rows(V, spread):
+    """Rows as a trained model gives them, with most of the mass on a few tokens: the cut of top-p lies among
+    the largest values, which are then carried on alone. The widest spread leaves probabilities of zero."""
+    dev = torch.device("cuda:0")
+    steps = 8
+    configs = [dict(temperature=1.0, top_k=0, top_p=0.9, repetition_penalty=1.0),
+               dict(temperature=0.7, top_k=0, top_p=0.95, repetition_penalty=1.1),
+               dict(temperature=1.2, top_k=0, top_p=0.6, min_p=0.001, repetition_penalty=1.0),
+               dict(temperature=1.0, top_k=0, top_p=0.9, mirostat=2, mirostat_tau=4.0, repetition_penalty=1.0),
+               dict(temperature=1.0, top_k=5000, top_p=0.9, repetition_penalty=1.0)]
+    logits = [make_logits(V, steps, seed=40 + i, spread=spread) for i in range(len(configs))]
+    plain = [P.PlainSampler(seed=3 + i, **c) for i, c in enumerate(configs)]
+    ours = [SequenceSampler(SamplerConfig(seed=3 + i, **c)) for i, c in enumerate(configs)]
+    batch = BatchSampler(V, dev)
+    mismatches = []
+    for t in range(steps):
+        got = batch.sample(torch.stack([x[t] for x in logits]).to(dev), list(range(len(configs))), ours)
+        want = [p.sample(x[t]) for p, x in zip(plain, logits)]
+        for i, (a, b) in enumerate(zip(got, want)):
+            if a != b:
+                mismatches.append((t, i, a, b))
+                ours[i].recent[-1] = b
+    assert not mismatches, mismatches
+
+
 def test_draws_do_not_depend_on_the_batch():
     dev = torch.device("cuda:0")
     V = 777
