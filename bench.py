@@ -255,6 +255,11 @@ def main() -> int:
         for b in (1, 64):
             steps = max(16, args.steps // 2)
             points[f"decode_b{b}"] = timed_decode(b, steps, max(3, args.warmup // 2))["tok_s"]
+        # the same entry point with the reference's default sampler (temperature 0.7, top-k 40, top-p 0.9,
+        # repetition penalty 1.1) instead of the greedy choice
+        engine.generate(e2e_prompts, SamplerConfig(seed=1), max_tokens=max(3, args.warmup // 2), stop_token_ids=())
+        engine.generate(e2e_prompts, SamplerConfig(seed=1), max_tokens=max(16, args.steps // 2), stop_token_ids=())
+        points["e2e_reference_sampler"] = engine.last_generation_stats.decode_tokens_per_second
         result["points"] = points
     print(json.dumps(result))
     return 0
