@@ -1,5 +1,6 @@
 """Each part alone, built from its specification, against the plain functions."""
 import math
+import zlib
 
 import pytest
 import torch
@@ -10,6 +11,16 @@ pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
 TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+# The cache keeps keys and values, and the attention kernels take queries, in the activation type. With
+# queries and keys made large on purpose (sharp attention shows a wrong key), that one rounding alone moves a
+# bfloat16 result by 1-2 % of its largest value, so the plain attention below rounds the same three tensors.
+STORED = {"float32": None, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(autouse=True)
+def own_random_numbers(request):
+    """Every test draws from its own seed, so that no result depends on which tests ran before it."""
+    torch.manual_seed(zlib.crc32(request.node.name.encode()))
 
 
 def runtime(dtype):
@@ -106,12 +117,14 @@ def attention_tensors(d, H, G, hd, seed):
             "v": torch.randn(G * hd, d, generator=g) * s, "o": torch.randn(d, H * hd, generator=g) * s}
 
 
-def plain_attention_part(x, w, H, G, hd, theta, positions, window):
+def plain_attention_part(x, w, H, G, hd, theta, positions, window, stored=None):
     T = x.shape[0]
     inv = P.rope_inverse_frequencies(hd, theta)
     q = P.rope_rotate((x @ w["q"].T).reshape(T, H, hd), positions, inv)
     k = P.rope_rotate((x @ w["k"].T).reshape(T, G, hd), positions, inv)
     v = (x @ w["v"].T).reshape(T, G, hd)
+    if stored is not None:
+        q, k, v = (t.to(stored).to(x.dtype) for t in (q, k, v))
     return P.attention(q, k, v, 1.0 / math.sqrt(hd), window=window, q_positions=positions).reshape(T, H * hd) @ w["o"].T
 
 
@@ -138,7 +151,7 @@ def test_attention_part_in_steps(dtype, H, G, hd, window):
     ws = Workspace(DEV)
     x = torch.randn(T, d).to(rt.act_dtype)
     ref = plain_attention_part(x.double(), {n: t.double() for n, t in held.items()}, H, G, hd, 5000.0,
-                               torch.arange(T), window)
+                               torch.arange(T), window, stored=STORED[dtype])
     slot = cache.acquire()
     got = []
     for n in [90, 30] + [1] * 30:
@@ -232,7 +245,8 @@ def test_block_part(dtype):
     block.forward(ctx, cache.view(0), x)
     hw = {n: t.double() for n, t in held.items()}
     r = x0.double()
-    r = r + plain_attention_part(P.rms_norm(r, hw["n1"], 1e-5), hw, H, G, hd, 10000.0, torch.arange(T), None)
+    r = r + plain_attention_part(P.rms_norm(r, hw["n1"], 1e-5), hw, H, G, hd, 10000.0, torch.arange(T), None,
+                                 stored=STORED[dtype])
     r = r + P.swiglu(P.rms_norm(r, hw["n2"], 1e-5), hw["g"], hw["u"], hw["dn"])
     assert rel(x, r) < TOL[dtype]
 
