@@ -15,6 +15,13 @@ TOL = {"float32": 2e-5, "bfloat16": 2e-2}
 # queries and keys made large on purpose (sharp attention shows a wrong key), that one rounding alone moves a
 # bfloat16 result by 1-2 % of its largest value, so the plain attention below rounds the same three tensors.
 STORED = {"float32": None, "bfloat16": torch.bfloat16}
+# ... and a block hands its parts the normed stream in the activation type.
+ACTIVATION = {"float32": None, "bfloat16": torch.bfloat16}
+
+
+def kept_as(t, dtype):
+    """``t`` after a round trip through ``dtype`` (None: unchanged)."""
+    return t if dtype is None else t.to(dtype).to(t.dtype)
 
 
 @pytest.fixture(autouse=True)
@@ -245,9 +252,10 @@ def test_block_part(dtype):
     block.forward(ctx, cache.view(0), x)
     hw = {n: t.double() for n, t in held.items()}
     r = x0.double()
-    r = r + plain_attention_part(P.rms_norm(r, hw["n1"], 1e-5), hw, H, G, hd, 10000.0, torch.arange(T), None,
-                                 stored=STORED[dtype])
-    r = r + P.swiglu(P.rms_norm(r, hw["n2"], 1e-5), hw["g"], hw["u"], hw["dn"])
+    act = ACTIVATION[dtype]
+    r = r + plain_attention_part(kept_as(P.rms_norm(r, hw["n1"], 1e-5), act), hw, H, G, hd, 10000.0, torch.arange(T),
+                                 None, stored=STORED[dtype])
+    r = r + P.swiglu(kept_as(P.rms_norm(r, hw["n2"], 1e-5), act), hw["g"], hw["u"], hw["dn"])
     assert rel(x, r) < TOL[dtype]
 
 
