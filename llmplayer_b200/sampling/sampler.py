@@ -9,6 +9,7 @@ block per sequence (csrc/sampling.cu).
 from __future__ import annotations
 
 import math
+from collections import Counter
 from typing import Dict, List, Sequence, Tuple
 
 import numpy as np
@@ -32,20 +33,39 @@ class SequenceSampler:
         self.recent: List[int] = []
         self.max_recent = max(64, config.dry_range)
         self.mu = 2.0 * config.mirostat_tau
+        self._powers = [1.0]         # powers of the repetition penalty, by number of occurrences
 
     # ------------------------------------------------------------------ before a draw
-    def logit_edits(self) -> List[Tuple[int, float, float]]:
-        """(token, amount to subtract, penalty factor) for every token whose logit changes."""
+    def edit_lists(self) -> Tuple[List[int], List[float], List[float]]:
+        """The tokens whose logit changes, in ascending order, with the amount to subtract from each (DRY)
+        and the factor of its repetition penalty: the penalty once per occurrence among the recent
+        tokens (sampler/CompositeSampler.java:45-55), so the factor is the penalty multiplied up that often."""
         c = self.config
-        subtract: Dict[int, float] = {}
+        counts = Counter(self.recent) if c.repetition_penalty != 1.0 else {}
         if c.dry_multiplier > 0:
+            subtract: Dict[int, float] = {}
             for tok, pen in self._dry_penalties():
                 subtract[tok] = subtract.get(tok, 0.0) + pen
-        factor: Dict[int, float] = {}
-        if c.repetition_penalty != 1.0:
-            for tok in self.recent:            # once per occurrence (sampler/CompositeSampler.java:45-55)
-                factor[tok] = factor.get(tok, 1.0) * c.repetition_penalty
-        return [(tok, subtract.get(tok, 0.0), factor.get(tok, 1.0)) for tok in sorted(set(subtract) | set(factor))]
+            tokens = sorted(set(subtract) | set(counts))
+            return (tokens, [subtract.get(tok, 0.0) for tok in tokens],
+                    [self._penalty_power(counts.get(tok, 0)) for tok in tokens])
+        if not counts:
+            return [], [], []
+        tokens = sorted(counts)
+        self._penalty_power(max(counts.values()))
+        powers = self._powers
+        return tokens, [0.0] * len(tokens), [powers[counts[tok]] for tok in tokens]
+
+    def logit_edits(self) -> List[Tuple[int, float, float]]:
+        """(token, amount to subtract, penalty factor) for every token whose logit changes."""
+        return list(zip(*self.edit_lists()))
+
+    def _penalty_power(self, times: int) -> float:
+        """1 * penalty * penalty ... (``times`` factors), multiplied up in that order."""
+        powers = self._powers
+        while len(powers) <= times:
+            powers.append(powers[-1] * self.config.repetition_penalty)
+        return powers[times]
 
     def _dry_penalties(self):
         """sampler/CompositeSampler.java:150-192: for each earlier occurrence of the last token,
@@ -127,8 +147,8 @@ class BatchSampler:
             self._slice_capacity = ops.sample_slice_capacity(self.vocab_size)
         out_tok = self._out[:B]
         out_prob = self._out[B:2 * B].view(torch.float32)
-        all_edits = [s.logit_edits() for s in samplers]
-        plain_greedy = all(s.config.is_greedy for s in samplers) and not any(all_edits)
+        all_edits = [s.edit_lists() for s in samplers]
+        plain_greedy = all(s.config.is_greedy for s in samplers) and not any(e[0] for e in all_edits)
         key = tuple(rows)
         if plain_greedy and list(rows) == list(range(B)) and logits.shape[0] == B:
             # first-maximum argmax of every row, spread over many blocks
@@ -145,14 +165,13 @@ class BatchSampler:
         else:
             params = np.zeros(B, dtype=PARAMS_DTYPE)
             tokens, subs, facs = [], [], []
-            for i, (row, s, edits) in enumerate(zip(rows, samplers, all_edits)):
+            for i, (row, s, (edit_tokens, edit_subs, edit_facs)) in enumerate(zip(rows, samplers, all_edits)):
                 c = s.config
                 params[i] = (0.0 if c.is_greedy else 1.0 / np.float32(c.temperature), c.top_k, c.top_p, c.min_p,
-                             s.mirostat_threshold(), s.draw(), len(tokens), len(edits), row)
-                for tok, sub, fac in edits:
-                    tokens.append(tok)
-                    subs.append(sub)
-                    facs.append(fac)
+                             s.mirostat_threshold(), s.draw(), len(tokens), len(edit_tokens), row)
+                tokens.extend(edit_tokens)
+                subs.extend(edit_subs)
+                facs.extend(edit_facs)
             # one upload: parameter records, then the edits' tokens, amounts and factors (4-byte units)
             n = max(1, len(tokens))
             packed = np.zeros(B * PARAMS_DTYPE.itemsize // 4 + 3 * n, dtype=np.int32)
