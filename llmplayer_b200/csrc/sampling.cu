@@ -1,4 +1,5 @@
-// Sampling on the device: one block per sequence turns a row of float32 logits into a token.
+// Sampling on the device: a row of float32 logits becomes a token; one block per sequence draws it,
+// several blocks per sequence find the candidates of a small top-k beforehand.
 //
 // Stages, in the reference's order (sampler/CompositeSampler.java:33-120):
 //   logit edits (DRY subtraction, then repetition penalty: positive / r, else * r)
@@ -12,7 +13,9 @@
 // survivors are gathered into shared memory. A set of at most 1024 candidates is then ranked in
 // descending order (equal values in index order, as a stable sort would) and one thread walks
 // it, adding the probabilities one by one as the reference does. Larger sets (no top-k, or a very
-// wide one) stay in global memory, and their cut-offs are found by a bitwise search over the keys.
+// wide one) stay in global memory: top-p first looks for its cut among the largest 256 values and
+// carries only those on when it lies there; else the key at the cut is searched over the whole row,
+// four bits per pass.
 #include "common.cuh"
 
 struct LpSampleParams {
