@@ -16,6 +16,7 @@ USAGE = """Usage: python -m llmplayer_b200 [options]
 Options:
   --model, -m <dir>        Model folder (config.json + model.safetensors)
   --prompt, -p <ids>       Prompt as token ids, e.g. "1 15 7" (repeat for a batch)
+  --prompt-file <path>     One prompt of token ids per line (a batch)
   --interactive, -i        Read one prompt (token ids) per line from standard input
   --max-tokens, -n <num>   Max tokens to generate (default: 256)
   --temperature, -t <num>  Sampling temperature, 0 = greedy (default: 0.7)
@@ -34,6 +35,10 @@ Options:
   --context-length, -c <n> Max context length (default: 2048)
   --stop-ids <ids>         Token ids that end a sequence (default: the model's eos_token_id)
   --dtype <name>           bfloat16 (default) or float32
+  --max-slots <num>        Sequences held at once (default: one per prompt)
+  --no-graph               Run every step directly instead of replaying captured CUDA graphs
+  --profile                Time each section of the model walk (disables graphs) and print ms per step
+  --plain-kernels          Use the plain twin of every kernel
   --gpu-device <id>        CUDA device index (default: 0)
   --random <seed>          Write random weights for the config.json in --model first
   --info                   Show model info and exit
@@ -65,6 +70,11 @@ class CLIOptions:
         self.dtype = "bfloat16"
         self.gpu_device = 0
         self.random_seed: Optional[int] = None
+        self.prompt_file: Optional[str] = None
+        self.max_slots: Optional[int] = None
+        self.no_graph = False
+        self.profile = False
+        self.plain_kernels = False
         self.show_info = False
         self.help = False
         self.unknown: List[str] = []
@@ -81,7 +91,9 @@ class CLIOptions:
         "--dry-range": ("dry_range", int), "--seed": ("seed", int),
         "--context-length": ("context_length", int), "-c": ("context_length", int),
         "--dtype": ("dtype", str), "--gpu-device": ("gpu_device", int), "--random": ("random_seed", int),
+        "--prompt-file": ("prompt_file", str), "--max-slots": ("max_slots", int),
     }
+    _SWITCHES = {"--no-graph": "no_graph", "--profile": "profile", "--plain-kernels": "plain_kernels"}
     # flags of the reference that place work on devices or threads; accepted, without effect here
     _IGNORED_WITH_VALUE = ("--threads", "--gpu-layers", "--gpu-backend", "--gpu-memory")
     _IGNORED = ("--gpu", "--gpu-chain", "--no-gpu-chain")
@@ -104,6 +116,8 @@ class CLIOptions:
             elif a == "--stop-ids":
                 i += 1
                 o.stop_ids = parse_ids(args[i])
+            elif a in cls._SWITCHES:
+                setattr(o, cls._SWITCHES[a], True)
             elif a in ("--interactive", "-i"):
                 o.interactive = True
             elif a == "--info":
@@ -123,6 +137,14 @@ class CLIOptions:
                 o.unknown.append(a)
             i += 1
         return o
+
+    def to_engine_options(self, batch: int):
+        """The engine's options that this command line asks for (engine/options.py)."""
+        from .engine.options import EngineOptions
+        return EngineOptions(
+            dtype=self.dtype, kernels="plain" if self.plain_kernels else "fast", context_length=self.context_length,
+            max_batch=batch, max_slots=self.max_slots, device=f"cuda:{self.gpu_device}", graphs=not self.no_graph,
+            profile=self.profile)
 
     def to_sampler_config(self):
         from .sampling.params import SamplerConfig
@@ -158,9 +180,12 @@ def run(argv: Optional[List[str]] = None) -> int:
         from .weights import write_random_model
         write_random_model(load_config(opts.model_path), opts.random_seed, opts.model_path, dtype=opts.dtype)
     from .engine import Engine
-    batch = max(1, len(opts.prompts))
-    engine = Engine.load(opts.model_path, dtype=opts.dtype, context_length=opts.context_length, max_batch=batch,
-                         device=f"cuda:{opts.gpu_device}")
+    prompts = [parse_ids(p) for p in opts.prompts]
+    if opts.prompt_file is not None:
+        with open(opts.prompt_file) as fh:
+            prompts += [parse_ids(line) for line in fh if line.strip()]
+    batch = max(1, len(prompts))
+    engine = Engine.load(opts.model_path, opts.to_engine_options(batch))
     if opts.show_info:
         print(engine.info())
         return 0
@@ -178,9 +203,16 @@ def run(argv: Optional[List[str]] = None) -> int:
         print("Tokens: %d prompt + %d generated in %dms (%.1f tok/s)" % (
             sum(r.prompt_token_count for r in responses), sum(r.token_count for r in responses),
             elapsed_ms, stats.decode_tokens_per_second))
+        if opts.profile:
+            # as the reference's -Dcuda.profile=true prints: milliseconds per section (java21
+            # inference/CudaForwardPass.java:1431-1456)
+            report = engine.profile_report(reset=True)
+            print("--- Profile (%d steps, ms per step) ---" % report["steps"])
+            for name, row in report["sections"].items():
+                print("  %-20s %8.3f  (%d calls)" % (name, row["ms_per_step"], row["calls"]))
 
-    if opts.prompts:
-        generate([parse_ids(p) for p in opts.prompts])
+    if prompts:
+        generate(prompts)
     if opts.interactive:
         print("Interactive mode: one prompt of token ids per line, 'quit' to leave.")
         for line in sys.stdin:
@@ -189,7 +221,7 @@ def run(argv: Optional[List[str]] = None) -> int:
                 break
             if line:
                 generate([parse_ids(line)])
-    elif not opts.prompts:
+    elif not prompts:
         print("No prompt given: use --prompt or --interactive.", file=sys.stderr)
         return 2
     return 0

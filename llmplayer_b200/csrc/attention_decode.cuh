@@ -1,6 +1,6 @@
 // The decode-step attention unit and the mma.sync / cp.async helpers it shares with the prompt
 // kernels: one (sequence, key/value head, share of the pages) handled by 128 threads. Used by the
-// stand-alone decode kernels and by the persistent step program.
+// stand-alone decode kernels (plain entry, fused entry, entry without allocation).
 #pragma once
 
 #include "common.cuh"
@@ -187,7 +187,7 @@ __device__ __forceinline__ void attention_decode_unit(
     const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table, int pt_stride,
     const int* __restrict__ kv_len, float* __restrict__ part_o, float* __restrict__ part_ml,
     __nv_bfloat16* __restrict__ out, int H, int G, int hd_arg, float scale_log2, int window, int pages_per_split,
-    int num_splits, int head_groups, const FusedDecodeArgs& fused, Before&& before_inputs) {
+    int num_splits, int min_share_pages, int head_groups, const FusedDecodeArgs& fused, Before&& before_inputs) {
     constexpr int KSTEPS = HD_MAX / 16;
     constexpr int NT = 32 * NW, PG = NW / 4, GROUPS = STAGES / PG;
     static_assert(NW % 4 == 0 && STAGES % PG == 0 && GROUPS >= 1, "whole groups of pages in the ring");
@@ -199,10 +199,36 @@ __device__ __forceinline__ void attention_decode_unit(
     const int warp = tid >> 5, lane = tid & 31;
     const int kw = warp & 3, pg = warp >> 2;       // this warp's quarter of a page's keys, and its page of a group
     const int len = kv_len[b];
-    const int pos = len - 1;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int page_lo = max(lo / PAGE, split * pages_per_split);
-    const int page_hi = min(pos / PAGE, (split + 1) * pages_per_split - 1);
+    const int pos = len - 1;                       // a length of zero or less is an empty sequence: no page is
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;      // read, nothing is stored, the output is zero
+    // Which pages this share takes. Fixed (min_share_pages == 0): share s takes pages s * pages_per_split ... of the
+    // table. Fitted to the sequence (min_share_pages > 0): the pages that the sequence really has (within its
+    // window) are cut into as many shares as leaves each at least min_share_pages, at most num_splits; the other
+    // CTAs of the grid have nothing to do. A share and the merge of shares cost several dependent round trips
+    // to memory, so a short sequence is better served by one CTA however wide its page table is.
+    int shares = num_splits, page_lo, page_hi;
+    if (min_share_pages > 0) {
+        const int first = lo / PAGE, last = len > 0 ? pos / PAGE : first - 1;
+        const int total = last - first + 1;
+        shares = max(1, min(num_splits, total / min_share_pages));
+        const int per = (max(total, 1) + shares - 1) / shares;
+        page_lo = first + split * per;
+        page_hi = min(last, page_lo + per - 1);
+        if (split >= shares) {
+            if (!FUSED) {                          // the separate merge kernel reads every share: leave an empty one
+                const int R0 = H / G, rows0 = min(16, R0 - (by % head_groups) * 16);
+                for (int r = tid; r < rows0; r += 32 * NW) {
+                    const size_t slot = ((size_t)b * H + (by / head_groups) * R0 + (by % head_groups) * 16 + r) * num_splits + split;
+                    part_ml[slot * 2] = NEG_BIG;
+                    part_ml[slot * 2 + 1] = 0.f;
+                }
+            }
+            return;
+        }
+    } else {
+        page_lo = max(lo / PAGE, split * pages_per_split);
+        page_hi = len > 0 ? min(pos / PAGE, (split + 1) * pages_per_split - 1) : page_lo - 1;
+    }
     const int* table = page_table + (size_t)b * pt_stride;
     const int stage_bytes = 2 * PAGE * hd * 2;
     const int npages = page_hi - page_lo + 1;      // may be <= 0: this share holds nothing of the sequence
@@ -226,7 +252,7 @@ __device__ __forceinline__ void attention_decode_unit(
     __nv_bfloat16* new_v = new_k + hd;
     float* cs = reinterpret_cast<float*>(new_v + hd);
     float* sn = cs + 128;
-    const bool holds_new = FUSED && fused.pages_rw != nullptr && pos / PAGE >= page_lo && pos / PAGE <= page_hi;
+    const bool holds_new = FUSED && fused.pages_rw != nullptr && len > 0 && pos / PAGE >= page_lo && pos / PAGE <= page_hi;
     if (FUSED) {
         const int half = fused.rd >> 1;
         for (int i = tid; i < half; i += NT) sincosf((float)pos * fused.inv_freq[i], &sn[i], &cs[i]);
@@ -412,15 +438,15 @@ __device__ __forceinline__ void attention_decode_unit(
             acc += sm_o[((size_t)w * 16 + r) * hd + d] * f;
             l += sm_l[w * 16 + r] * f;
         }
-        if (num_splits == 1) {                      // the only share: this is the result
-            out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(acc / l);
+        if ((FUSED ? shares : num_splits) == 1) {   // the only share: this is the result
+            out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
         } else {
             const size_t slot = ((size_t)b * H + head0 + r) * num_splits + split;
             part_o[slot * hd + d] = acc;
             if (d == 0) { part_ml[slot * 2] = m; part_ml[slot * 2 + 1] = l; }
         }
     }
-    if (FUSED && num_splits > 1) {
+    if (FUSED && shares > 1) {
         // the last share of this (sequence, kv head, head group) to arrive merges them all
         __shared__ int last;
         __threadfence();
@@ -428,7 +454,7 @@ __device__ __forceinline__ void attention_decode_unit(
         int* counter = fused.counters + ((size_t)b * G + g) * head_groups + hg;
         if (tid == 0) {
             const int ticket = atomicAdd(counter, 1);
-            last = ticket == num_splits - 1;
+            last = ticket == shares - 1;
             if (last) *counter = 0;                 // ready for the next launch
         }
         unit_sync<NAMED, NT>();
@@ -439,19 +465,19 @@ __device__ __forceinline__ void attention_decode_unit(
                 const size_t base = ((size_t)b * H + head0 + r) * num_splits;
                 // the shares' (max, sum, output) are requested eight shares at a time, then combined
                 float m = NEG_BIG;
-                for (int s0 = 0; s0 < num_splits; s0 += 8) {
+                for (int s0 = 0; s0 < shares; s0 += 8) {
                     float mm[8];
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) mm[u] = s0 + u < num_splits ? __ldcg(part_ml + (base + s0 + u) * 2) : NEG_BIG;
+                    for (int u = 0; u < 8; ++u) mm[u] = s0 + u < shares ? __ldcg(part_ml + (base + s0 + u) * 2) : NEG_BIG;
 #pragma unroll
                     for (int u = 0; u < 8; ++u) m = fmaxf(m, mm[u]);
                 }
                 float acc = 0.f, l = 0.f;
-                for (int s0 = 0; s0 < num_splits; s0 += 8) {
+                for (int s0 = 0; s0 < shares; s0 += 8) {
                     float mm[8], ll[8], oo[8];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
-                        const bool in = s0 + u < num_splits;
+                        const bool in = s0 + u < shares;
                         mm[u] = in ? __ldcg(part_ml + (base + s0 + u) * 2) : NEG_BIG;
                         ll[u] = in ? __ldcg(part_ml + (base + s0 + u) * 2 + 1) : 0.f;
                         oo[u] = in ? __ldcg(part_o + (base + s0 + u) * hd + d) : 0.f;
@@ -465,7 +491,7 @@ __device__ __forceinline__ void attention_decode_unit(
                         }
                     }
                 }
-                out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(acc / l);
+                out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
             }
         }
     }

@@ -324,23 +324,24 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
 // ============================================================================ decode
 // grid: (splits, G * head_groups, B); 128 threads; one new token per sequence (attention_decode.cuh).
 // The fused form that writes the new key and value itself requests its first pages before it waits
-// for the previous kernel: within a step nothing else writes lengths, page tables or these pages, and
-// the new row is put into the unit's own copy of the page. Every other form waits first (the pages
-// may hold a row that the previous kernel wrote).
+// for the previous kernel: within a step nothing writes lengths, page tables or these pages (a kernel that
+// moves lengths on belongs to the end of the previous step, and the step's first kernel is launched without
+// the early start, so it has finished), and the new row is put into the unit's own copy of the page. Every
+// other form waits first (the pages may hold a row that the previous kernel wrote).
 template <int HD_MAX, bool FUSED, int HD_EXACT, int STAGES, int NW = 4>
 __global__ void __launch_bounds__(32 * NW)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ pages,
                         const int* __restrict__ page_table, int pt_stride, const int* __restrict__ kv_len,
                         float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
                         int H, int G, int hd_arg, float scale_log2, int window, int pages_per_split, int num_splits,
-                        int head_groups, FusedDecodeArgs fused) {
+                        int min_share_pages, int head_groups, FusedDecodeArgs fused) {
     extern __shared__ __align__(128) uint8_t smem[];
     lp_grid_release();
     const bool early = FUSED && fused.pages_rw != nullptr;
     if (!early) lp_grid_wait();
     attention_decode_unit<HD_MAX, FUSED, HD_EXACT, false, STAGES, NW>(
         smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, q, pages, page_table, pt_stride, kv_len, part_o, part_ml,
-        out, H, G, hd_arg, scale_log2, window, pages_per_split, num_splits, head_groups, fused,
+        out, H, G, hd_arg, scale_log2, window, pages_per_split, num_splits, min_share_pages, head_groups, fused,
         [early] { if (early) lp_grid_wait(); });
 }
 
@@ -362,21 +363,28 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
             if (d < hd) acc += part_o[(base + s) * hd + d] * f;
         }
     }
-    if (d < hd) out[((size_t)b * H + h) * hd + d] = __float2bfloat16_rn(acc / l);
+    if (d < hd) out[((size_t)b * H + h) * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
 }
 
 // Opt in to `bytes` of dynamic shared memory; remembered per kernel so that later calls
 // (also those recorded into a CUDA graph) make no runtime call.
-template <int TAG, typename K> int set_smem(K kernel, int bytes, const char* what) {
-    static int granted = 0;          // one copy per TAG: every kernel instantiation gets its own
-    if (bytes <= granted) return 0;
+template <typename K> int set_smem(K kernel, int bytes, const char* what) {
+    // what each kernel (by its address) has been granted so far; a handful of instantiations are ever used
+    constexpr int SLOTS = 64;
+    static const void* known[SLOTS];
+    static int granted[SLOTS];
+    static int used = 0;
+    int at = 0;
+    while (at < used && known[at] != (const void*)kernel) ++at;
+    if (at < used && bytes <= granted[at]) return 0;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
     if (e != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "%s: cannot reserve %d bytes of shared memory: %s", what, bytes,
                  cudaGetErrorString(e));
         return (int)e;
     }
-    granted = bytes;
+    if (at == used && used < SLOTS) { known[at] = (const void*)kernel; ++used; }
+    if (at < used) granted[at] = bytes;
     return 0;
 }
 
@@ -403,7 +411,7 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LP_PREFILL(HDM)                                                                                          \
     do {                                                                                                         \
-        rc = set_smem<HDM>(attention_prefill_kernel<HDM>, smem, "attention_prefill");                                 \
+        rc = set_smem(attention_prefill_kernel<HDM>, smem, "attention_prefill");                                 \
         if (rc) return rc;                                                                                       \
         lp_launch(attention_prefill_kernel<HDM>, grid, 128, smem, stream,                                        \
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)pages, page_table, pt_stride,     \
@@ -411,7 +419,7 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
     } while (0)
 #define LP_PREFILL_EXACT(HD, ROWS)                                                                               \
     do {                                                                                                         \
-        rc = set_smem<2000 + HD + ROWS>(attention_prefill_exact_kernel<HD, ROWS>, smem, "attention_prefill");    \
+        rc = set_smem(attention_prefill_exact_kernel<HD, ROWS>, smem, "attention_prefill");    \
         if (rc) return rc;                                                                                       \
         dim3 grid_exact((max_new + ROWS - 1) / ROWS, H, B);                                                      \
         lp_launch(attention_prefill_exact_kernel<HD, ROWS>, grid_exact, ROWS * 2, smem, stream,                  \
@@ -419,7 +427,7 @@ extern "C" int lp_attention_prefill(const void* q, void* out, const void* pages,
                   pt_stride, q_start, kv_len, H, G, scale_log2, window);                                         \
     } while (0)
     // long prompts: 128 query rows share each page of keys; short ones keep 64 rows for more CTAs
-    const bool tall = (long long)((max_new + 127) / 128) * H * B >= 1184;
+    const bool tall = (long long)((max_new + 127) / 128) * H * B >= 8LL * lp_sm_count();
     if (hd == 64 && tall) LP_PREFILL_EXACT(64, 128);
     else if (hd == 64) LP_PREFILL_EXACT(64, 64);
     else if (hd == 128 && tall) LP_PREFILL_EXACT(128, 128);
@@ -437,9 +445,11 @@ extern "C" long long lp_attention_decode_scratch(int B, int H, int hd, int num_s
 
 // q, out: [B, H, hd] bf16 (one token per sequence); kv_len: [B] (after the step). The pages of a sequence
 // are shared out over `num_splits` CTAs, `pages_per_split` each; scratch as sized above.
-extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
+// lp_attention_decode_fitted: the same with `min_share_pages` > 0: each sequence's pages are cut into as many
+// shares (at most num_splits) as leaves each share that many pages (see attention_decode.cuh).
+static int attention_decode_launch(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
                                    const int* kv_len, float* scratch, int B, int H, int G, int hd, int page_size,
-                                   float scale, int window, int pages_per_split, int num_splits,
+                                   float scale, int window, int pages_per_split, int num_splits, int min_share_pages,
                                    cudaStream_t stream) {
     if (B <= 0) return 0;
     int rc = check_geometry("attention_decode", H, G, hd);
@@ -457,12 +467,12 @@ extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, 
     const float scale_log2 = scale * 1.4426950408889634f;
 #define LP_DECODE(HDM, EXACT)                                                                                    \
     do {                                                                                                         \
-        rc = set_smem<1000 + HDM + EXACT>(attention_decode_kernel<HDM, false, EXACT, 3>, smem, "attention_decode"); \
+        rc = set_smem(attention_decode_kernel<HDM, false, EXACT, 3>, smem, "attention_decode"); \
         if (rc) return rc;                                                                                       \
         lp_launch(attention_decode_kernel<HDM, false, EXACT, 3>, grid, 128, smem, stream,                           \
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml, \
-            (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, head_groups,         \
-            FusedDecodeArgs{});                                                                                  \
+            (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split, num_splits, min_share_pages,     \
+            head_groups, FusedDecodeArgs{});                                                                     \
     } while (0)
     if (hd == 64) LP_DECODE(64, 64); else if (hd == 128) LP_DECODE(128, 128);
     else if (hd <= 64) LP_DECODE(64, 0); else if (hd <= 128) LP_DECODE(128, 0); else LP_DECODE(256, 0);
@@ -474,19 +484,37 @@ extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, 
     return lp_check_launch("attention_merge");
 }
 
+extern "C" int lp_attention_decode(const void* q, void* out, const void* pages, const int* page_table, int pt_stride,
+                                   const int* kv_len, float* scratch, int B, int H, int G, int hd, int page_size,
+                                   float scale, int window, int pages_per_split, int num_splits,
+                                   cudaStream_t stream) {
+    return attention_decode_launch(q, out, pages, page_table, pt_stride, kv_len, scratch, B, H, G, hd, page_size, scale,
+                                   window, pages_per_split, num_splits, 0, stream);
+}
+
+extern "C" int lp_attention_decode_fitted(const void* q, void* out, const void* pages, const int* page_table,
+                                          int pt_stride, const int* kv_len, float* scratch, int B, int H, int G, int hd,
+                                          int page_size, float scale, int window, int num_splits, int min_share_pages,
+                                          cudaStream_t stream) {
+    if (min_share_pages <= 0) LP_REFUSE("attention_decode_fitted: shares of at least %d pages", min_share_pages);
+    return attention_decode_launch(q, out, pages, page_table, pt_stride, kv_len, scratch, B, H, G, hd, page_size, scale,
+                                   window, pt_stride > 0 ? pt_stride : 1, num_splits, min_share_pages, stream);
+}
+
 // Decode attention that starts from the fused projection output: rotation of queries and of the new key,
 // the cache write of the new key and value, attention over the pages and the merge of the shares in one
 // kernel. qkv: [B, ld] float32 = [H query heads | G key heads | G value heads] x hd (keys and values only
 // if `pages_rw` is given: a layer that attends over another run's cache has none). counters: int32
 // [B * G * head_groups], zero before the first call; the kernel leaves them zero. row_sumsq (optional, [B]):
 // the projection left out the factor of its input's RMS norm; the kernel applies 1 / sqrt(row_sumsq[b] /
-// norm_width + norm_eps) to the queries, the key and the value it reads.
+// norm_width + norm_eps) to the queries, the key and the value it reads. min_share_pages > 0: shares fitted to each
+// sequence's own length (see attention_decode.cuh); pages_per_split then only says how long a share can get.
 extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* inv_freq, int rd, int interleaved,
                                          void* out, void* pages, int write_kv, const int* page_table, int pt_stride,
                                          const int* kv_len, float* scratch, int* counters, int B, int H, int G,
                                          int hd, int page_size, float scale, int window, int pages_per_split,
-                                         int num_splits, const float* row_sumsq, float norm_eps, int norm_width,
-                                         cudaStream_t stream) {
+                                         int num_splits, int min_share_pages, const float* row_sumsq, float norm_eps,
+                                         int norm_width, cudaStream_t stream) {
     if (B <= 0) return 0;
     int rc = check_geometry("attention_decode_fused", H, G, hd);
     if (row_sumsq && norm_width <= 0) LP_REFUSE("attention_decode_fused: a row factor over %d values", norm_width);
@@ -500,15 +528,16 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
     if (G * head_groups > 65535 || B > 65535) LP_REFUSE("attention_decode_fused: grid too large");
     const int stage = 2 * PAGE * hd * 2;
     const int extra = (16 * hd + 2 * hd) * 2 + 256 * 4;
+    const int sms = lp_sm_count();
     // With few CTAs altogether (no more than one per SM: measured, batch 24 / 32: 1.01 / 1.02 ms per step against
     // 1.07 / 1.08 when up to two per SM count as few) and small heads a CTA has 16 warps, four pages at a time and
     // eight pages in shared memory; with CTAs enough to hide a page's latency by their number, 4 warps and 3 pages.
-    const bool wide = hd <= 64 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= 148;
+    const bool wide = hd <= 64 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= sms;
     // up to two CTAs per SM: 8 warps, two pages at a time, six in shared memory (batch 32: 0.96 ms per step against
     // 1.02 with 4 warps; with more CTAs than that, batch 64, the 4-warp form wins: 1.19 against 1.28)
-    const bool mid = !wide && hd <= 64 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= 296;
+    const bool mid = !wide && hd <= 64 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= 2 * sms;
     // heads of 128 (pages of 32 KB): 8 warps, two pages at a time, four in shared memory, one CTA per SM
-    const bool wide128 = hd > 64 && hd <= 128 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= 148;
+    const bool wide128 = hd > 64 && hd <= 128 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= sms;
     const int stages = wide ? 8 : mid ? 6 : wide128 ? 4 : 3, nw = wide ? 16 : (mid || wide128) ? 8 : 4;
     const int merge = (2 * nw * 16 + nw * 16 * hd) * 4;
     const int smem = (stages * stage > merge ? stages * stage : merge) + extra;
@@ -520,13 +549,13 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
                           row_sumsq, norm_eps, norm_width};
 #define LP_DECODE_FUSED(HDM, EXACT, ST, NWARPS)                                                                  \
     do {                                                                                                         \
-        rc = set_smem<3000 + HDM + EXACT + 7 * ST>(attention_decode_kernel<HDM, true, EXACT, ST, NWARPS>, smem,  \
+        rc = set_smem(attention_decode_kernel<HDM, true, EXACT, ST, NWARPS>, smem,  \
                                                    "attention_decode_fused");                                    \
         if (rc) return rc;                                                                                       \
         lp_launch(attention_decode_kernel<HDM, true, EXACT, ST, NWARPS>, grid, 32 * NWARPS, smem, stream,        \
                   (const __nv_bfloat16*)nullptr, (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len,     \
                   part_o, part_ml, (__nv_bfloat16*)out, H, G, hd, scale_log2, window, pages_per_split,           \
-                  num_splits, head_groups, fused);                                                               \
+                  num_splits, min_share_pages, head_groups, fused);                                              \
     } while (0)
     if (hd == 64) { if (wide) LP_DECODE_FUSED(64, 64, 8, 16); else if (mid) LP_DECODE_FUSED(64, 64, 6, 8); else LP_DECODE_FUSED(64, 64, 3, 4); }
     else if (hd == 128) { if (wide128) LP_DECODE_FUSED(128, 128, 4, 8); else LP_DECODE_FUSED(128, 128, 3, 4); }

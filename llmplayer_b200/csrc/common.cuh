@@ -41,22 +41,27 @@ static inline int lp_check_launch(const char* what) {
 // predecessor still runs; it must call lp_grid_wait() before it touches anything an earlier
 // kernel wrote or read-modifies, and calls lp_grid_release() so that its own successor may
 // start early. Every kernel waits, so completion stays transitive along the stream.
-// LLMPLAYER_B200_PDL=0 in the environment turns the early start off.
+// lp_set_pdl(0), or LLMPLAYER_B200_PDL=0 in the environment when nothing was set, turns the early start off.
 __device__ __forceinline__ void lp_grid_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void lp_grid_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <stdlib.h>
 #include <utility>
+#ifndef LP_PDL_DEFINED
+#define LP_PDL_DEFINED
+static int lp_pdl_state = -1;      // -1: not decided yet (then the environment decides), 0: off, 1: on
+// Switch the early start on or off for the launches of this library (the engine's options call this).
+extern "C" void lp_set_pdl(int on) { lp_pdl_state = on ? 1 : 0; }
+#endif
 static inline bool lp_pdl_enabled() {
-    static int state = -1;
-    if (state < 0) {
+    if (lp_pdl_state < 0) {
         const char* v = getenv("LLMPLAYER_B200_PDL");
-        state = (v && v[0] == '0') ? 0 : 1;
+        lp_pdl_state = (v && v[0] == '0') ? 0 : 1;
     }
-    return state == 1;
+    return lp_pdl_state == 1;
 }
 
-template <typename... KArgs, typename... Args>
+template <bool EARLY = true, typename... KArgs, typename... Args>
 static inline cudaError_t lp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                     Args&&... args) {
     cudaLaunchConfig_t cfg = {};
@@ -68,8 +73,28 @@ static inline cudaError_t lp_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = lp_pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = (EARLY && lp_pdl_enabled()) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+// The first kernel of a step starts only when everything before it on the stream has finished: kernels
+// later in the step read the step's integers (lengths, page tables) before their own lp_grid_wait(), and
+// those may have been written by the last kernel of the previous step.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t lp_launch_first(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                          cudaStream_t stream, Args&&... args) {
+    return lp_launch<false>(kernel, grid, block, smem, stream, std::forward<Args>(args)...);
+}
+
+// Streaming multiprocessors of the current device (asked once per process).
+static inline int lp_sm_count() {
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            sms <= 0)
+            sms = 1;
+    }
+    return sms;
 }
 
 __device__ __forceinline__ float lp_to_float(float v) { return v; }

@@ -25,10 +25,11 @@ extern "C" int lp_embed(const void* table, int table_dtype, const int* tokens, f
     if (T <= 0) return 0;
     if (d <= 0) LP_REFUSE("embed: width %d", d);
     const int threads = d >= 1024 ? 256 : 128;
+    // the embedding opens a step: it is launched without the early start (see lp_launch_first)
     if (table_dtype == LP_F32)
-        lp_launch(embed_kernel<float>, T, threads, 0, stream, (const float*)table, tokens, out, d);
+        lp_launch_first(embed_kernel<float>, T, threads, 0, stream, (const float*)table, tokens, out, d);
     else if (table_dtype == LP_BF16)
-        lp_launch(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, d);
+        lp_launch_first(embed_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)table, tokens, out, d);
     else
         LP_REFUSE("embed: table dtype code %d", table_dtype);
     return lp_check_launch("embed");

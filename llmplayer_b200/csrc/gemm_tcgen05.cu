@@ -157,8 +157,11 @@ template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
-                    int up_row_offset, int* __restrict__ status, NormAfter norm) {
+                    int withheld_kblock, int* __restrict__ status, NormAfter norm) {
+    // withheld_kblock >= 0 (tests of the bounded waits only, see lp_gemm_withhold_next): the loader never brings
+    // that k-block, so the waits for it run out, the roles report through *status and the CTA winds down.
     using T = Tile<BLOCK_TOK, MODE>;
+    const uint32_t wait_limit = withheld_kblock >= 0 ? (1u << 14) : SPIN_LIMIT;     // a test need not wait long
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + T::STAGES * T::STAGE_BYTES);
@@ -203,31 +206,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             // before waiting for the previous kernel, the activation tiles only after it.
             const int early = min(nkb, T::STAGES);
             for (int i = 0; i < early; ++i) {
+                if (kb_begin + i == withheld_kblock) continue;
                 uint8_t* stage = smem + i * T::STAGE_BYTES;
                 mbar_expect_tx(&full[i], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BLOCK_K;
                 load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[i]);
             }
             lp_grid_wait();
-            for (int i = 0; i < early; ++i)
+            for (int i = 0; i < early; ++i) {
+                if (kb_begin + i == withheld_kblock) continue;
                 tma_load_2d(smem + i * T::STAGE_BYTES + T::W_TILES * T::W_BYTES, &map_x, (kb_begin + i) * BLOCK_K, tok0,
                             &full[i]);
+            }
             issued = early;
             for (int i = early; i < nkb && ok; ++i) {
                 const int s = i % T::STAGES;
                 const uint32_t phase = (i / T::STAGES) & 1;
-                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
+                if (!mbar_wait(&empty[s], phase ^ 1, wait_limit)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
+                issued = i + 1;
+                if (kb_begin + i == withheld_kblock) continue;
                 uint8_t* stage = smem + s * T::STAGE_BYTES;
                 mbar_expect_tx(&full[s], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BLOCK_K;
                 load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[s]);
                 tma_load_2d(stage + T::W_TILES * T::W_BYTES, &map_x, k, tok0, &full[s]);
-                issued = i + 1;
             }
-            if (!ok) {
+            if (!ok || *failed) {
                 // consumers may be gone: await the copies still in flight before the CTA's memory is released
+                // (a withheld k-block has no copy in flight and is not waited for)
                 for (int i = max(0, issued - T::STAGES); i < issued; ++i)
-                    mbar_wait(&full[i % T::STAGES], (i / T::STAGES) & 1);
+                    if (kb_begin + i != withheld_kblock) mbar_wait(&full[i % T::STAGES], (i / T::STAGES) & 1, wait_limit);
             }
         }
         __syncwarp();
@@ -240,7 +248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % T::STAGES;
                 const uint32_t phase = (i / T::STAGES) & 1;
-                if (!mbar_wait(&full[s], phase)) { atomicExch(status, 2); *failed = 1; ok = false; break; }
+                if (!mbar_wait(&full[s], phase, wait_limit)) { atomicExch(status, 2); *failed = 1; ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t w_addr = smem_u32(smem + s * T::STAGE_BYTES);
                 const uint32_t x_addr = w_addr + T::W_TILES * T::W_BYTES;
@@ -263,7 +271,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5)
         const int quarter = warp & 3;             // TMEM lanes 32*quarter .. +31 belong to this warp
-        const bool ready = mbar_wait(acc_ready, 0);
+        const bool ready = mbar_wait(acc_ready, 0, wait_limit);
         if (!ready && lane == 0) atomicExch(status, 3);
         tcgen05_fence_after();
         const bool go = __all_sync(0xffffffffu, ready && *failed == 0);
@@ -638,6 +646,25 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (ATOMIC) norm_after_tail<NTHREADS>(norm, out, tokens, features, ldc);
 }
 
+// Settings of the few-token product (lp_gemm_configure; until that is called, the environment's
+// LLMPLAYER_B200_FEWTOK / _RING_SHARED / _RING_ALONE or the defaults 1 / 6 / 10).
+struct FewSettings { int enabled, ring_shared, ring_alone; bool decided; };
+static FewSettings& few_settings() {
+    static FewSettings st = {1, 6, 10, false};
+    if (!st.decided) {
+        const char* v = getenv("LLMPLAYER_B200_FEWTOK");
+        st.enabled = (v && v[0] == '0') ? 0 : 1;
+        v = getenv("LLMPLAYER_B200_RING_ALONE");
+        st.ring_alone = v ? atoi(v) : 10;
+        v = getenv("LLMPLAYER_B200_RING_SHARED");
+        st.ring_shared = v ? atoi(v) : 6;
+        if (st.ring_alone < 2) st.ring_alone = 2;
+        if (st.ring_shared < 2) st.ring_shared = 2;
+        st.decided = true;
+    }
+    return st;
+}
+
 template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
 int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
                   int splits, int* status, const NormAfter& norm, const NormBefore& before, cudaStream_t stream) {
@@ -654,17 +681,9 @@ int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int t
     const int grid_z = (k_blocks + per_split - 1) / per_split;
     const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;
     dim3 grid((features + per_cta - 1) / per_cta, 1, grid_z);
-    static int ring_alone = 0, ring_shared = 0;
-    if (!ring_alone) {
-        const char* v = getenv("LLMPLAYER_B200_RING_ALONE");
-        ring_alone = v ? atoi(v) : 10;
-        v = getenv("LLMPLAYER_B200_RING_SHARED");
-        ring_shared = v ? atoi(v) : 6;
-        if (ring_alone < 2) ring_alone = 2;
-        if (ring_shared < 2) ring_shared = 2;
-    }
+    const int ring_alone = few_settings().ring_alone, ring_shared = few_settings().ring_shared;
     const int shared_stages = ring_shared < FT::MAX_SHARED ? ring_shared : FT::MAX_SHARED;
-    const bool alone = (long long)grid.x * grid.z <= 148 && per_split > shared_stages + 2;
+    const bool alone = (long long)grid.x * grid.z <= lp_sm_count() && per_split > shared_stages + 2;
     int stages = alone ? (ring_alone < FT::MAX_ALONE ? ring_alone : FT::MAX_ALONE) : shared_stages;
     // (measured at the 1B shape, 8 tokens: 0.73 ms per step with 7 to 10 stages for the two long products, 0.80 ms
     // with 6; giving the short products no more stages than they have k-blocks changed nothing; a q|k|v product
@@ -695,14 +714,7 @@ int dispatch_fewtok(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw,
 #undef LP_GO
 }
 
-static bool fewtok_enabled() {
-    static int state = -1;
-    if (state < 0) {
-        const char* v = getenv("LLMPLAYER_B200_FEWTOK");
-        state = (v && v[0] == '0') ? 0 : 1;
-    }
-    return state == 1;
-}
+static bool fewtok_enabled() { return few_settings().enabled != 0; }
 
 // ------------------------------------------------------------------ persistent form for prompts
 // One CTA per SM walks over output tiles (tile = blockIdx.x, + gridDim.x, ...). Tensor memory holds two
@@ -938,13 +950,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, i
                                         cudaGetErrorString(e));
         configured = true;
     }
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
-    }
+    const int sms = lp_sm_count();
     const int feat_tiles = (features + BLOCK_FEAT - 1) / BLOCK_FEAT;
     const int tok_tiles = (tokens + BLOCK_TOK - 1) / BLOCK_TOK;
     const int num_tiles = feat_tiles * tok_tiles;
@@ -967,9 +973,15 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, i
     return lp_check_launch("gemm_persistent");
 }
 
+// For tests of the bounded waits: the next launch of the one-tile kernel gets this k-block withheld (then -1 again).
+static int withhold_next_kblock = -1;
+
 template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
            int splits, int up_offset, int* status, const NormAfter& norm, cudaStream_t stream) {
+    (void)up_offset;
+    const int withheld = withhold_next_kblock;
+    withhold_next_kblock = -1;
     using T = Tile<BLOCK_TOK, MODE>;
     auto kernel = gemm_tcgen05_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC>;
     static bool configured = false;
@@ -984,7 +996,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
     const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;     // output features per CTA
     dim3 grid((features + per_cta - 1) / per_cta, (tokens + BLOCK_TOK - 1) / BLOCK_TOK, grid_z);
     cudaError_t err = lp_launch(kernel, grid, THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
-                                k_blocks, per_split, up_offset, status, norm);
+                                k_blocks, per_split, withheld, status, norm);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_tcgen05: %s", cudaGetErrorString(err));
         return (int)err;
@@ -1014,6 +1026,24 @@ int dispatch(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const 
 }
 
 }  // namespace
+
+// Tests only: the next launch of the one-tile tcgen05 kernel (lp_gemm_tcgen05 with more than 16 tokens) never loads
+// k-block `kblock`. The waits for it run out after their limit, the kernel sets *status and returns by itself
+// with nothing left in flight; its output is not written. Exercises what the host does after such a report.
+extern "C" int lp_gemm_withhold_next(int kblock) {
+    withhold_next_kblock = kblock;
+    return 0;
+}
+
+// fewtok: whether lp_gemm_tcgen05 hands 16-token tiles to the few-token kernel; ring_shared / ring_alone: stages of
+// that kernel's ring when two CTAs share an SM / when a CTA has an SM to itself (at least 2 each).
+extern "C" int lp_gemm_configure(int fewtok, int ring_shared, int ring_alone) {
+    FewSettings& st = few_settings();
+    st.enabled = fewtok ? 1 : 0;
+    st.ring_shared = ring_shared < 2 ? 2 : ring_shared;
+    st.ring_alone = ring_alone < 2 ? 2 : ring_alone;
+    return 0;
+}
 
 // X: [tokens, K] bf16 (row stride ldx); W: [features, K] bf16 (row stride ldw); for SWIGLU, W holds
 // 128 rows per 64 output features (64 gate rows, then the 64 up rows), features rounded up to 64;

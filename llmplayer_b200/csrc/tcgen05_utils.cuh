@@ -31,9 +31,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait: false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+// Bounded wait: false when the limit (a number of polls) ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = SPIN_LIMIT) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_test(bar, parity)) return true;
         if (i > 64) __nanosleep(40);
     }

@@ -8,8 +8,10 @@ then one token for each sequence, always from the cache that earlier steps left.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.pages import PAGE_SIZE
@@ -20,6 +22,7 @@ from ..kernels import ops
 from ..parts.base import Runtime
 from ..weights.loader import load_tensors
 from .model import Model
+from .options import EngineOptions
 from .step import SequenceStep, StepContext, Workspace
 
 
@@ -29,10 +32,12 @@ def _round_up(n: int, m: int) -> int:
 
 class Engine:
     def __init__(self, config: ArchitectureConfig, model: Model, runtime: Runtime, *, max_tokens: int,
-                 max_slots: Optional[int] = None, context_length: Optional[int] = None):
+                 max_slots: Optional[int] = None, context_length: Optional[int] = None,
+                 options: Optional[EngineOptions] = None):
         self.config = config
         self.model = model
         self.runtime = runtime
+        self.options = options if options is not None else EngineOptions(dtype=runtime.dtype, kernels=runtime.kernels)
         self.vocab_size = model.layout.head.vocab_size
         self.context_length = context_length if context_length is not None else config.max_positions()
         self.cache = SequenceCache(model.cache_requests(), max_tokens=max_tokens, max_slots=max_slots,
@@ -41,37 +46,50 @@ class Engine:
         self._sampler = None
         self.last_generation_stats = None
         self.last_step_h2d_bytes = 0
-        self.use_graphs = True
+        self.last_step_d2h_bytes = 0
+        self.profiler: Optional[ops.StepProfiler] = ops.StepProfiler() if self.options.profile else None
+        self.use_graphs = bool(self.options.graphs) and not self.options.profile
         self._graphs = {}
+        self._fused = {}               # captured decode steps with upload, argmax and read-back inside
         self._last_ctx: Optional[StepContext] = None
         self._prepared = None          # (context, page tables): the next decode step's pages, reserved ahead
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def load(cls, model_dir: str, *, dtype: str = "bfloat16", context_length: Optional[int] = None,
-             max_batch: int = 1, max_tokens: Optional[int] = None, max_slots: Optional[int] = None,
-             device: str = "cuda:0", kernels: str = "fast") -> "Engine":
+    def load(cls, model_dir: str, options: Optional[EngineOptions] = None, **changes) -> "Engine":
         """Load ``config.json`` and ``model.safetensors`` from ``model_dir``.
 
-        ``context_length`` caps each sequence (default and upper bound: the model's
-        ``max_position_embeddings``, as api/LLMEngine.java:348 takes the smaller of
-        the two); the cache holds ``max_tokens`` positions in all, by default
-        ``max_batch`` sequences of that length.
+        ``options`` (an :class:`EngineOptions`) and/or its fields as keyword arguments: ``dtype``,
+        ``kernels``, ``context_length``, ``max_batch``, ``max_tokens``, ``max_slots``, ``device``,
+        ``graphs``, ``profile``, kernel switches. ``context_length`` caps each sequence (default and
+        upper bound: the model's ``max_position_embeddings``, as api/LLMEngine.java:348 takes the
+        smaller of the two; ``beyond_model_context=True`` lifts the upper bound); the cache holds
+        ``max_tokens`` positions in all, by default ``max_batch`` sequences of that length.
         """
         ops.require_gpu()
+        opts = (options if options is not None else EngineOptions()).with_changes(**changes)
+        if opts.kernel_settings():
+            ops.configure(**opts.kernel_settings())
         config = load_config(model_dir)
-        dev = torch.device(device)
+        dev = torch.device(opts.device)
         torch.cuda.set_device(dev)
-        runtime = Runtime(device=dev, dtype=dtype, kernels=kernels)
+        runtime = Runtime(device=dev, dtype=opts.dtype, kernels=opts.kernels)
         model = Model(config.layout())
         tensors = load_tensors(model_dir, model.tensor_specs())
         model.load(tensors, runtime)
         del tensors
         limit = config.max_positions()
-        ctx_len = limit if context_length is None else min(int(context_length), limit)
+        if opts.context_length is None:
+            ctx_len = limit
+        elif opts.beyond_model_context:
+            ctx_len = int(opts.context_length)
+        else:
+            ctx_len = min(int(opts.context_length), limit)
+        max_tokens = opts.max_tokens
         if max_tokens is None:
-            max_tokens = max(1, max_batch) * _round_up(ctx_len, PAGE_SIZE)
-        return cls(config, model, runtime, max_tokens=max_tokens, max_slots=max_slots, context_length=ctx_len)
+            max_tokens = max(1, opts.max_batch) * _round_up(ctx_len, PAGE_SIZE)
+        return cls(config, model, runtime, max_tokens=max_tokens, max_slots=opts.max_slots, context_length=ctx_len,
+                   options=opts)
 
     def close(self) -> None:
         self.cache = None
@@ -134,7 +152,14 @@ class Engine:
         logits = self.workspace.get("logits", (ctx.num_wanted, self.vocab_size), torch.float32)
         self.last_step_h2d_bytes = ctx.h2d_bytes
         try:
-            if self.use_graphs and self.runtime.fast and ctx.all_single:
+            if self.profiler is not None:
+                ops.set_profiler(self.profiler)
+                try:
+                    self.model.forward(ctx, self.cache, ctx.rows, logits)
+                    self.profiler.steps += 1
+                finally:
+                    ops.set_profiler(None)
+            elif self.use_graphs and self.runtime.fast and ctx.all_single and self.model.capture_safe:
                 self._run_captured(ctx, logits)
             else:
                 self.model.forward(ctx, self.cache, ctx.rows, logits)
@@ -192,9 +217,10 @@ class Engine:
         self._last_ctx = ctx if ctx.all_single else None
         return self.run(ctx)
 
-    def _continue(self, entries, want) -> Optional[StepContext]:
+    def _continue(self, entries, want, advance: bool = True) -> Optional[StepContext]:
         """The previous step's description moved on by one token, when this step brings one token
-        for each of the same sequences and wants the same rows (the usual decode step); else None."""
+        for each of the same sequences and wants the same rows (the usual decode step); else None.
+        ``advance=False``: only say whether it applies (the context is returned as it is)."""
         last = self._last_ctx
         if last is None or len(entries) != last.num_sequences or not last.continues_all:
             return None
@@ -210,6 +236,8 @@ class Engine:
             if not cache.slots.is_held(slot) or cache.length(slot) != pos + 1 or pos + 2 > limit:
                 return None
             tokens.append(tok)
+        if not advance:
+            return last
         slots = last.slot_list
         prepared, self._prepared = self._prepared, None
         if prepared is not None and prepared[0] is last:
@@ -217,7 +245,7 @@ class Engine:
         else:
             self.cache.reserve(slots, [1] * len(slots))
             tables = self.cache.page_tables(slots)
-        if not last.advance(tokens, tables):
+        if last.advance(tokens, tables) is None:
             return None
         return last
 
@@ -244,7 +272,159 @@ class Engine:
         if self._sampler is None:
             from ..sampling.sampler import BatchSampler
             self._sampler = BatchSampler(self.vocab_size, self.runtime.device)
-        return self._sampler.sample(logits, rows, samplers, while_waiting=self._prepare_continue)
+        if self.profiler is not None:
+            ops.set_profiler(self.profiler)
+        try:
+            chosen = self._sampler.sample(logits, rows, samplers, while_waiting=self._prepare_continue)
+        finally:
+            ops.set_profiler(None)
+        self.last_step_d2h_bytes = self._sampler.last_d2h_bytes
+        self.last_step_h2d_bytes += self._sampler.last_h2d_bytes
+        return chosen
+
+    def decode_steps(self, entries: Sequence[Tuple[int, int]], samplers, *, quiet: Optional[Sequence[int]] = None,
+                     stops: Optional[Sequence[Sequence[int]]] = None, max_steps: int = 256) -> List[List[int]]:
+        """Decode: feed one token to each sequence (``entries``: ``(slot, token)``), sample each one's next
+        token, and go on doing so while nothing has to be decided. Returns the chosen tokens of every step
+        that ran (at least one step), oldest first.
+
+        ``quiet[i]``: how many of sequence i's next chosen tokens are certain to need no decision other than
+        "is it one of ``stops[i]``" (the generation loop knows: token budget, context). Given these, and
+        when every sampler is a plain greedy choice, the steps run from the native host loop: one captured
+        graph per step that holds the upload of the step's integers from page-locked memory, the model
+        walk, the argmax and the read-back of the chosen tokens (csrc/host_loop.cu), until a step is not
+        quiet. Otherwise one step runs through :meth:`step` and :meth:`sample`.
+        """
+        if (quiet is not None and self.options.host_loop and self.use_graphs and self.runtime.fast
+                and self.model.capture_safe and all(s.plain_greedy for s in samplers)):
+            out = self._decode_fused(entries, quiet, stops, max_steps)
+            if out is not None:
+                return out
+        logits = self.step([(slot, [tok]) for slot, tok in entries], [[0]] * len(entries))
+        return [self.sample(logits, list(range(len(entries))), samplers)]
+
+    def _decode_fused(self, entries, quiet, stops, max_steps) -> Optional[List[List[int]]]:
+        B = len(entries)
+        want = [[0]] * B
+        step_entries = [(slot, [tok]) for slot, tok in entries]
+        last = self._continue(step_entries, want, advance=False)     # None: the first step after the prompts
+        slots = [slot for slot, _ in entries]
+        try:
+            lengths = [self.cache.length(slot) for slot in slots]
+        except LLMPlayerError:
+            return None                                   # the plain way reports it
+        # how many steps at most: while all stay quiet, within the context, and within the pages that can be had
+        room = min(self.context_length - n for n in lengths)
+        if room < 1 or len(set(slots)) != B:
+            return None
+        steps = max(1, min(int(max_steps), min(int(q) for q in quiet) + 1, room))
+        self._prepared = None
+        while True:
+            try:
+                self.cache.reserve(slots, [steps] * B)
+                break
+            except LLMPlayerError:
+                if steps == 1:
+                    return None                           # the plain way reports it
+                steps = max(1, steps // 2)
+        tables = self.cache.page_tables(slots)
+        moved = None if last is None else last.advance([tok for _, tok in entries], tables, upload=False)
+        if moved is None:                  # no context to move on, or the tables outgrew its shape: describe the step anew
+            ctx = self.plan(step_entries, want)
+        else:
+            ctx = last
+            if moved:                                     # page tables changed: they are not part of the graph's own copy
+                ctx.upload_all()
+        self._last_ctx = ctx
+        key = ctx.fused_key
+        if key is None:
+            key = ctx.fused_key = (B, tuple(t.shape[1] for t in ctx.page_tables), ctx.meta.data_ptr(), ctx.host_pointer)
+        entry = self._fused.get(key)
+        if entry is not None and entry["version"] != self.workspace.version:
+            entry = None
+        logits = self.workspace.get("logits", (B, self.vocab_size), torch.float32)
+        sampled = self.workspace.get("sampled", (B,), torch.int32)
+        work = self.workspace.get("argmax_work", (64 * B,), torch.float32)
+        landing, _ = self.workspace.pinned("sampled_host", B)
+
+        def one_step(upload: bool, captured: bool = False):
+            if upload:
+                ctx.upload_moving(record=not captured)
+            self.model.forward(ctx, self.cache, ctx.rows, logits)
+            ops.argmax(logits, work, sampled)
+            landing[:B].copy_(sampled, non_blocking=True)
+
+        try:
+            if entry is None:
+                # the first step of a shape runs directly (it sizes every buffer), the second is captured
+                one_step(upload=moved is not None)
+                torch.cuda.current_stream().synchronize()
+                self._fused[key] = {"graph": None, "version": self.workspace.version}
+                chosen = [landing[:B].tolist()]
+            else:
+                if entry["graph"] is None:
+                    graph = torch.cuda.CUDAGraph()
+                    before = ops.launch_count()
+                    with torch.cuda.graph(graph):
+                        one_step(upload=True, captured=True)
+                    if entry["version"] != self.workspace.version:
+                        raise LLMPlayerError("a buffer moved while a decode step was captured")
+                    if len(self._fused) > 64:
+                        self._fused.clear()
+                    entry = self._fused[key] = {"graph": graph, "version": entry["version"],
+                                                "exec": graph.raw_cuda_graph_exec(),
+                                                "launches": ops.launch_count() - before}
+                chosen = self._host_loop(ctx, entry, landing, B, steps, quiet, stops)
+                ops.count_launches(entry["launches"] * len(chosen))
+        except BaseException:
+            self._last_ctx = None
+            try:
+                self.workspace.restore_zeroes()
+            except Exception:
+                pass
+            raise
+        k = len(chosen)
+        ctx.moved_on(k - 1)
+        self.cache.commit(slots, [k] * B)
+        self.last_step_h2d_bytes = ctx.moving_bytes
+        self.last_step_d2h_bytes = 4 * B
+        return chosen
+
+    def _host_loop(self, ctx, entry, landing, B, steps, quiet, stops) -> List[List[int]]:
+        lib = ops.library("host_loop")
+        quiet_arr = np.asarray([int(q) for q in quiet], dtype=np.int32)
+        begin = np.zeros(B + 1, dtype=np.int32)
+        flat: List[int] = []
+        for i in range(B):
+            if stops is not None:
+                flat.extend(int(t) for t in stops[i])
+            begin[i + 1] = len(flat)
+        stop_arr = np.asarray(flat or [0], dtype=np.int32)
+        out = np.empty((steps, B), dtype=np.int32)
+        ran = ctypes.c_int(0)
+        tokens_at, positions_at, lengths_at = ctx.moving_offsets
+        code = lib.lp_decode_loop(entry["exec"], ops.current_stream(), ctx.host_pointer, tokens_at, positions_at,
+                                  lengths_at, landing.data_ptr(), B, steps, quiet_arr.ctypes.data, stop_arr.ctypes.data,
+                                  begin.ctypes.data, out.ctypes.data, ctypes.byref(ran))
+        if code != 0:
+            raise LLMPlayerError(lib.lp_last_error().decode("utf-8", "replace") or f"decode loop failed ({code})")
+        return out[:ran.value].tolist()
+
+    @staticmethod
+    def launch_count() -> int:
+        """Kernels of this library launched so far by this process (replays of captured steps included)."""
+        return ops.launch_count()
+
+    def mark(self):
+        """A timing event on the current stream (for the generation loop's device-side clock)."""
+        event = torch.cuda.Event(enable_timing=True)
+        event.record()
+        return event
+
+    @staticmethod
+    def elapsed_ms(start, end) -> float:
+        end.synchronize()
+        return float(start.elapsed_time(end))
 
     def fits(self, token_counts: Sequence[int]) -> bool:
         """Whether sequences of these final lengths can be held at once, beside what is held now."""
@@ -253,14 +433,15 @@ class Engine:
                 and all(need <= free for free in self.cache.free_pages()))
 
     def generate(self, prompts, sampler_config=None, *, max_tokens: int = 256, stop_token_ids=None,
-                 on_token=None, max_batch: Optional[int] = None):
+                 on_token=None, max_batch: Optional[int] = None, laps=None):
         """Generate for a batch of prompts (lists of token ids) or of
         :class:`GenerationRequest`; returns one :class:`GenerationResponse` each, in order.
 
         Mirrors ``engine.generate(request[, callback])`` (api/LLMEngine.java:356-468):
         a prompt, a token budget, sampler options; ``on_token(request_index, token_id)``
         may return False to stop that request. ``stats`` of the last call are kept in
-        ``last_generation_stats``.
+        ``last_generation_stats``; ``laps=(skip, every)`` times the decode steps in laps (see
+        :meth:`GenerationLoop.run`).
         """
         from ..sampling.params import SamplerConfig
         from .generate import GenerationLoop, GenerationRequest
@@ -276,7 +457,7 @@ class Engine:
         loop = GenerationLoop(self, max_batch=max_batch or self.cache.max_slots,
                               context_length=self.context_length,
                               default_stop_ids=self.config.stop_token_ids())
-        out = loop.run(requests, on_token=on_token)
+        out = loop.run(requests, on_token=on_token, laps=laps)
         self.last_generation_stats = loop.stats
         self.check()
         return out
@@ -292,6 +473,16 @@ class Engine:
             raise
 
     # ------------------------------------------------------------------ reporting
+    def profile_report(self, reset: bool = False) -> dict:
+        """Device time per section of the model walk since the engine was loaded with ``profile=True`` (or since
+        the last reset): ``{"steps", "total_ms", "sections": {name: {"ms", "calls", "ms_per_step"}}}``."""
+        if self.profiler is None:
+            raise RequestError("this engine was not loaded with profile=True")
+        report = self.profiler.report()
+        if reset:
+            self.profiler.reset()
+        return report
+
     def info(self) -> str:
         lines = [self.config.describe() if hasattr(self.config, "describe") else repr(self.config)]
         lines.append(f"dtype: {self.runtime.dtype} ({self.runtime.kernels} kernels), device {self.runtime.device}")

@@ -55,10 +55,25 @@ class GenerationStats:
     prefill_ms: float = 0.0
     decode_ms: float = 0.0
     decode_steps: int = 0
+    step_tokens: int = 0              # tokens chosen from the logits of decode steps (not of the prompts)
+    decode_device_ms: float = 0.0     # the decode steps' time on the device's own clock, when the backend has one
+    decode_launches: int = 0          # kernels launched for the decode steps, when the backend counts them
+    laps: List[dict] = field(default_factory=list)   # see GenerationLoop.run(laps=...)
 
     @property
     def decode_tokens_per_second(self) -> float:
+        """The reference's figure: all generated tokens over the time since the prompts' logits were there
+        (api/LLMEngine.java:481, :772-775), the first token of each sequence included."""
         return self.generated_tokens / (self.decode_ms / 1e3) if self.decode_ms > 0 else 0.0
+
+    @property
+    def step_tokens_per_second(self) -> float:
+        """Tokens that decode steps produced over the same time: the rate of the steps themselves."""
+        return self.step_tokens / (self.decode_ms / 1e3) if self.decode_ms > 0 else 0.0
+
+    @property
+    def device_step_tokens_per_second(self) -> float:
+        return self.step_tokens / (self.decode_device_ms / 1e3) if self.decode_device_ms > 0 else 0.0
 
 
 class _Live:
@@ -80,14 +95,22 @@ class GenerationLoop:
         self.context_length = int(context_length)
         self.default_stop_ids = tuple(default_stop_ids)
         self.stats = GenerationStats()
+        self._laps = None
 
     # ------------------------------------------------------------------ batches
     def _need(self, request: GenerationRequest) -> int:
         return min(len(request.prompt_ids) + max(0, request.max_tokens), self.context_length)
 
     def run(self, requests: Sequence[GenerationRequest],
-            on_token: Optional[Callable[[int, int], Optional[bool]]] = None) -> List[GenerationResponse]:
-        """Generate for every request; responses come in request order."""
+            on_token: Optional[Callable[[int, int], Optional[bool]]] = None,
+            laps: Optional[Sequence[int]] = None) -> List[GenerationResponse]:
+        """Generate for every request; responses come in request order.
+
+        ``laps = (skip, every)``: for measurements. After the first ``skip`` decode steps of a batch, the
+        decode steps are timed in laps of ``every`` steps each; ``stats.laps`` gets one entry per full lap:
+        ``{"steps", "tokens", "host_ms", "device_ms", "launches"}`` (the device's clock and the launch count
+        when the backend has them)."""
+        self._laps = (max(0, int(laps[0])), max(1, int(laps[1]))) if laps else None
         responses: List[Optional[GenerationResponse]] = [None] * len(requests)
         pending: List[int] = []
         for i, req in enumerate(requests):
@@ -118,6 +141,31 @@ class GenerationLoop:
         return responses  # type: ignore[return-value]
 
     # ------------------------------------------------------------------ one batch
+    def _decide(self, s: _Live, tok: int, step_index: int, on_token) -> None:
+        """What becomes of sequence ``s`` after ``tok`` was chosen for it (the reference's order of decisions)."""
+        if tok in s.stop_ids:
+            s.finish = "stop"
+            return
+        s.tokens.append(tok)
+        self.stats.generated_tokens += 1
+        if on_token is not None and on_token(s.index, tok) is False:
+            s.finish = "callback"
+            return
+        position = len(s.request.prompt_ids) + step_index
+        if position >= self.context_length - 1:
+            s.finish = "context"
+        elif len(s.tokens) >= s.request.max_tokens:
+            s.finish = "length"
+        else:
+            s.next_token = tok
+
+    def _quiet(self, s: _Live, step_index: int) -> int:
+        """How many of the sequence's next chosen tokens can only be continued or be a stop token: neither the
+        token budget nor the context ends the sequence at them."""
+        by_context = self.context_length - 1 - len(s.request.prompt_ids) - step_index
+        by_budget = s.request.max_tokens - len(s.tokens) - 1
+        return max(0, min(by_context, by_budget))
+
     def _run_batch(self, batch, requests, responses, on_token) -> None:
         be = self.backend
         live: List[_Live] = []
@@ -126,38 +174,38 @@ class GenerationLoop:
             stop = self.default_stop_ids if req.stop_token_ids is None else tuple(req.stop_token_ids)
             live.append(_Live(i, req, frozenset(int(t) for t in stop), be.acquire()))
         self.stats.batches += 1
+        several = getattr(be, "decode_steps", None)       # a backend that can run several quiet steps per call
+        mark = getattr(be, "mark", None)
+        count = getattr(be, "launch_count", None)
+        launched = None
         t0 = time.perf_counter()
+        t_decode = None
+        started = None
         try:
             logits = be.step([(s.slot, list(s.request.prompt_ids)) for s in live],
                              [[len(s.request.prompt_ids) - 1] for s in live])
+            pending = [be.sample(logits, list(range(len(live))), [s.sampler for s in live])]
+            # the prompt is processed once its logits are there: decode time starts here
+            t_decode = time.perf_counter()
+            started = mark() if mark is not None else None
+            launched = count() if count is not None else None
+            self.stats.prefill_ms += (t_decode - t0) * 1e3
+            self.stats.prompt_tokens += sum(len(s.request.prompt_ids) for s in live)
             step_index = 0
-            first = True
-            t_decode = None
+            steps_done = 0
+            boundary = None                       # the decode step count at which the current lap ends
+            lap_start = None                      # (host time, device mark, launches, tokens) at its beginning
+            if self._laps is not None:
+                boundary = self._laps[0] if self._laps[0] > 0 else self._laps[1]
+                if self._laps[0] == 0:
+                    lap_start = (t_decode, started, launched, 0)
             while live:
-                chosen = be.sample(logits, list(range(len(live))), [s.sampler for s in live])
-                if first:
-                    # the prompt is processed once its logits are there: decode time starts here
-                    t_decode = time.perf_counter()
-                    self.stats.prefill_ms += (t_decode - t0) * 1e3
-                    self.stats.prompt_tokens += sum(len(s.request.prompt_ids) for s in live)
-                    first = False
-                for s, tok in zip(live, chosen):
-                    tok = int(tok)
-                    if tok in s.stop_ids:
-                        s.finish = "stop"
-                        continue
-                    s.tokens.append(tok)
-                    self.stats.generated_tokens += 1
-                    if on_token is not None and on_token(s.index, tok) is False:
-                        s.finish = "callback"
-                        continue
-                    position = len(s.request.prompt_ids) + step_index
-                    if position >= self.context_length - 1:
-                        s.finish = "context"
-                    elif len(s.tokens) >= s.request.max_tokens:
-                        s.finish = "length"
-                    else:
-                        s.next_token = tok
+                for n, chosen in enumerate(pending):
+                    for s, tok in zip(live, chosen):
+                        self._decide(s, int(tok), step_index, on_token)
+                    step_index += 1
+                    if n + 1 < len(pending) and any(s.finish is not None for s in live):
+                        raise RuntimeError("the backend ran on past a step that ended a sequence")
                 now = time.perf_counter()
                 for s in live:
                     if s.finish is not None:
@@ -171,12 +219,40 @@ class GenerationLoop:
                 live = [s for s in live if s.finish is None]
                 if not live:
                     break
-                logits = be.step([(s.slot, [s.next_token]) for s in live], [[0] for _ in live])
-                self.stats.decode_steps += 1
-                step_index += 1
+                if several is not None:
+                    quiet = [0 if on_token is not None else self._quiet(s, step_index) for s in live]
+                    most = 256 if boundary is None else max(1, min(256, boundary - steps_done))
+                    pending = several([(s.slot, s.next_token) for s in live], [s.sampler for s in live],
+                                      quiet=quiet, stops=[s.stop_ids for s in live], max_steps=most)
+                else:
+                    logits = be.step([(s.slot, [s.next_token]) for s in live], [[0] for _ in live])
+                    pending = [be.sample(logits, list(range(len(live))), [s.sampler for s in live])]
+                self.stats.decode_steps += len(pending)
+                self.stats.step_tokens += len(live) * len(pending)
+                steps_done += len(pending)
+                if boundary is not None and steps_done >= boundary:
+                    here = (time.perf_counter(), mark() if mark is not None else None,
+                            count() if count is not None else None, self.stats.step_tokens)
+                    if lap_start is not None and steps_done == boundary:
+                        lap = {"steps": self._laps[1], "tokens": here[3] - lap_start[3],
+                               "host_ms": (here[0] - lap_start[0]) * 1e3}
+                        if here[1] is not None and lap_start[1] is not None:
+                            lap["device_ms"] = be.elapsed_ms(lap_start[1], here[1])
+                        if here[2] is not None and lap_start[2] is not None:
+                            lap["launches"] = here[2] - lap_start[2]
+                        self.stats.laps.append(lap)
+                    lap_start = here
+                    boundary = steps_done + self._laps[1]
+        finally:
             if t_decode is not None:
                 self.stats.decode_ms += (time.perf_counter() - t_decode) * 1e3
-        finally:
+                if launched is not None:
+                    self.stats.decode_launches += count() - launched
+                if started is not None:
+                    try:
+                        self.stats.decode_device_ms += be.elapsed_ms(started, mark())
+                    except Exception:
+                        pass
             for s in live:
                 if s.slot is not None:
                     be.release(s.slot)

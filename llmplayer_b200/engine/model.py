@@ -8,7 +8,6 @@ layout's list of runs (a layer may run twice, or attend over an earlier run's ca
 from __future__ import annotations
 
 import inspect
-import os
 from typing import Dict, List, Mapping, Optional
 
 import torch
@@ -35,10 +34,12 @@ class Model:
         self.runtime: Optional[Runtime] = None
         # blocks whose forward takes (normed_ready, next_block) can hand a fused norm to the next block
         self._chains = ["next_block" in inspect.signature(b.forward).parameters for b in self.blocks]
-        # steps of one token per sequence can run as one persistent kernel when every part can emit its
-        # operations; measured slower than the chain of kernels so far, so it is opt-in
-        self.use_program = os.environ.get("LLMPLAYER_B200_PROGRAM", "0") == "1"
-        self._programs: Dict[tuple, object] = {}
+
+    @property
+    def capture_safe(self) -> bool:
+        """Whether a captured graph of a one-token step may be replayed for other sequences: every part
+        must read the step from device tensors only (``Part.capture_safe``)."""
+        return all(bool(getattr(p, "capture_safe", False)) for p in [self.embedding, self.head] + self.blocks)
 
     # ------------------------------------------------------------------ tensors
     def tensor_specs(self) -> Dict[str, TensorSpec]:
@@ -73,10 +74,6 @@ class Model:
     # ------------------------------------------------------------------ a step
     def forward(self, ctx, cache, rows: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         """Run the step's tokens through every run and fill ``logits[i]`` for token ``rows[i]``."""
-        program = self._program(ctx, cache, rows, logits)
-        if program is not None:
-            program.run()
-            return logits
         d = self.layout.embedding.hidden_size
         x = ctx.buffer("residual", (ctx.num_tokens, d), torch.float32)
         self.embedding.forward(ctx.tokens, x)
@@ -93,42 +90,6 @@ class Model:
         if rows.numel():
             self.head.forward(ctx, x, rows, logits)
         return logits
-
-
-    # ------------------------------------------------------------------ the step as one kernel
-    def _program(self, ctx, cache, rows: torch.Tensor, logits: torch.Tensor):
-        """The step program for a step of this shape, or None if the step runs as a chain of kernels
-        (several tokens per sequence, float32, a part that cannot emit, sizes the kernel refuses)."""
-        from .program import ProgramRefused, StepProgram, max_tokens
-        rt = self.runtime
-        if not (self.use_program and rt is not None and rt.fast and ctx.all_single and rows.numel() > 0):
-            return None
-        if not all(hasattr(p, "emit") for p in [self.embedding, self.head] + self.blocks):
-            return None
-        if ctx.num_tokens > max_tokens():
-            return None
-        for _ in range(3):
-            key = (ctx.num_tokens, tuple(t.shape[1] for t in ctx.page_tables), ctx.meta.data_ptr(), rows.data_ptr(),
-                   rows.numel(), logits.data_ptr(), ctx.workspace.version)
-            if key in self._programs:
-                return self._programs[key]
-            try:
-                program = StepProgram(rt.device, ctx.num_tokens)
-                x = ctx.buffer("residual", (ctx.num_tokens, self.layout.embedding.hidden_size), torch.float32)
-                self.embedding.emit(program, ctx.tokens, x)
-                for i, run in enumerate(self.runs):
-                    self.blocks[run.layer].emit(program, ctx, cache.view(self.cache_owner(i)), x)
-                self.head.emit(program, x, rows, logits)
-                program.finish()
-            except ProgramRefused:
-                program = None
-            if ctx.workspace.version != key[-1]:
-                continue                 # a buffer grew (and moved) while the list was written: write it again
-            if len(self._programs) > 64:
-                self._programs.clear()
-            self._programs[key] = program
-            return program
-        return None
 
 
 def expected_tensors(layout: ModelLayout) -> Dict[str, TensorSpec]:

@@ -85,8 +85,21 @@ class Workspace:
             self.version += 1
         return buf[:count]
 
+    def get_counters(self, name: str, count: int) -> torch.Tensor:
+        """An int32 buffer of ``count`` counters that is zero when first handed out and that its users leave
+        zero again after each use (CTAs that count themselves; the last one sets the counter back)."""
+        key = (name, torch.int32)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < count:
+            buf = torch.zeros(max(count, 1024), dtype=torch.int32, device=self.device)
+            self._buffers[key] = buf
+            self._kept_zero.add(key)
+            self.version += 1
+        return buf[:count]
+
     def restore_zeroes(self) -> None:
-        """After a step that broke off half-way: the buffers that are zero between uses are made zero again."""
+        """After a step that broke off half-way: the buffers and counters that are zero between uses are
+        made zero again."""
         for key in self._kept_zero:
             self._buffers[key].zero_()
 
@@ -160,6 +173,10 @@ class StepContext:
         self._upload_views: Dict[int, tuple] = {}
         self._pinned = host.is_pinned()
         self.graph_key = None                          # set by the engine: what a captured graph of this step depends on
+        self.fused_key = None
+        self.host_pointer = host.data_ptr()
+        self.moving_offsets = (o[0], o[1], o[2])
+        self.moving_bytes = self._moving * 4
         self._upload(total)
         self.tokens = meta[o[0]:o[0] + T]
         self.positions = meta[o[1]:o[1] + T]
@@ -178,29 +195,47 @@ class StepContext:
                                for i, (slot, pos) in enumerate(zip(self.slot_list, self.first_positions))]
         return self._sequences
 
-    def _upload(self, count: int) -> None:
+    def _upload(self, count: int, record: bool = True) -> None:
         """Copy the first ``count`` integers of the pinned host image to the device, asynchronously;
-        the event lets the next writer of the host image wait until the copy has read it."""
+        the event lets the next writer of the host image wait until the copy has read it
+        (``record=False`` while a graph is being captured: the graph's user waits for the whole step)."""
         self.h2d_bytes = count * 4
         views = self._upload_views.get(count)
         if views is None:
             views = self._upload_views[count] = (self.meta[:count], self._host[:count])
         if self._pinned:
             views[0].copy_(views[1], non_blocking=True)
-            self._copied.record()
+            if record:
+                self._copied.record()
         else:
             views[0].copy_(views[1])
 
-    def advance(self, tokens: Sequence[int], page_tables: List[List[List[int]]]) -> bool:
+    def upload_all(self) -> None:
+        self._upload(self._total)
+
+    def upload_moving(self, record: bool = True) -> None:
+        """Copy tokens, positions and lengths (what changes from one decode step to the next) to the device."""
+        self._upload(self._moving, record)
+
+    def moved_on(self, steps: int) -> None:
+        """The host image was moved on by ``steps`` further decode steps outside this object (the native
+        host loop): bring the host-side counters along."""
+        if steps:
+            self.first_positions = [p + steps for p in self.first_positions]
+            self._sequences = None
+            self.max_kv_len += steps
+
+    def advance(self, tokens: Sequence[int], page_tables: List[List[List[int]]], upload: bool = True):
         """Move a context of one token per sequence on by one step: new tokens, positions and
-        lengths one further, page tables as they are now. False if the tables outgrew the
-        context's shape (the caller then builds a new context)."""
+        lengths one further, page tables as they are now. None if the tables outgrew the
+        context's shape (the caller then builds a new context); else whether the page tables changed.
+        ``upload=False``: only the host image is written; the caller copies it to the device."""
         o, B = self._offsets, self.num_sequences
         grown = False
         for g, group in enumerate(page_tables):
             for i, table in enumerate(group):
                 if len(table) > self._widths[g]:
-                    return False
+                    return None
                 if len(table) != self._table_lengths[g][i]:
                     grown = True
         self._copied.synchronize()                     # the previous copy has read the host image
@@ -218,11 +253,15 @@ class StepContext:
         self._sequences = None
         self.max_kv_len += 1
         self._cleared = False
-        self._upload(self._total if grown else self._moving)
-        return True
+        if upload:
+            self._upload(self._total if grown else self._moving)
+        return grown
 
     def buffer(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)
+
+    def counters(self, name: str, count: int) -> torch.Tensor:
+        return self.workspace.get_counters(name, count)
 
     # A norm can zero, on the side, the buffer that the product after it sums into. The
     # block says so here, and the product picks the note up (once).

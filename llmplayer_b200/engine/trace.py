@@ -23,14 +23,16 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--context-length", type=int, default=None,
+                    help="longest request; default: the model's max_position_embeddings. A larger value is taken "
+                         "as given (positions beyond what the model was made for)")
     args = ap.parse_args(argv)
 
     from .engine import Engine
 
     os.makedirs(args.out, exist_ok=True)
     engine = Engine.load(args.model, dtype=args.dtype, max_tokens=max(args.max_tokens, 64), device=args.device,
-                         context_length=None)
-    engine.context_length = max(engine.context_length, args.max_tokens)
+                         context_length=args.context_length, beyond_model_context=args.context_length is not None)
     slots: Dict[str, int] = {}
     for line in sys.stdin:
         line = line.strip()

@@ -33,7 +33,7 @@ LIBRARIES: Dict[str, str] = {
     "gemm_tcgen05": "gemm_tcgen05.cu",
     "attention_mma": "attention_mma.cu",
     "attention_tcgen05": "attention_tcgen05.cu",
-    "decode_program": "decode_program.cu",
+    "host_loop": "host_loop.cu",
 }
 HEADERS = ("common.cuh", "attention_noalloc.h", "tcgen05_utils.cuh", "attention_decode.cuh")
 

@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_void_p
+from dataclasses import dataclass
 from typing import Dict, Optional
 
 import torch
@@ -38,28 +39,21 @@ _SIGNATURES = {
                             ctypes.c_longlong, _P, _P],
         "lp_gemm_persistent": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "lp_gemm_fewtok": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _I, _P],
+        "lp_gemm_configure": [_I, _I, _I],
     },
     "attention_mma": {
         "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
         "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
+        "lp_attention_decode_fitted": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
         "lp_attention_decode_fused": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
-                                      _I, _I, _P, _F, _I, _P],
+                                      _I, _I, _I, _P, _F, _I, _P],
     },
     "attention_tcgen05": {
         "lp_attention_prefill_tc": [_P, _P, _P, ctypes.c_longlong, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I,
                                     _P, _P],
     },
-    "decode_program": {
-        "lp_program_op_bytes": [],
-        "lp_program_max_tokens": [],
-        "lp_program_operand_bytes": [_I],
-        "lp_program_attention_bytes": [_I],
-        "lp_program_product": [_P, _P, ctypes.c_longlong, _I, ctypes.c_longlong, _I, _I, _I, _P, _I, _P, _P, _F, _I, _I,
-                               _P, _I, _P, _I],
-        "lp_program_attention": [_P, _P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
-                                 _I, _I],
-        "lp_program_prologue": [_P, _I, _P, _P, _I, _I, _I, _P, _I, _P, _P],
-        "lp_program_launch": [_P, _I, _I, _I, _P, _P, _P, _P],
+    "host_loop": {
+        "lp_decode_loop": [_P, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P],
     },
     "sampling": {
         "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P],
@@ -71,6 +65,66 @@ _SIGNATURES = {
 }
 
 _libs: Dict[str, ctypes.CDLL] = {}
+
+
+def _env_int(name: str, default: int) -> int:
+    import os
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+@dataclass
+class KernelSettings:
+    """Switches of the kernels, one set per process (the compiled libraries are shared by every engine of the
+    process). The defaults are what was measured best; the environment variables of the same meaning
+    (``LLMPLAYER_B200_PDL``, ``_FEW_TOKENS``, ``_FEWTOK``, ``_RING_SHARED``, ``_RING_ALONE``) set the initial
+    values, :func:`configure` (which the engine's options call) changes them.
+
+    ``pdl``: programmatic dependent launch between the kernels of a step. ``few_tokens``: up to how many tokens
+    the parts put the RMS norm inside the consuming product and use the few-token kernel. ``fewtok_kernel``:
+    whether 16-token tiles of the general product go to the mma.sync few-token kernel. ``ring_shared`` /
+    ``ring_alone``: stages of that kernel's ring when two CTAs share an SM / when a CTA has one to itself."""
+    pdl: bool = True
+    few_tokens: int = 16
+    fewtok_kernel: bool = True
+    ring_shared: int = 6
+    ring_alone: int = 10
+
+    @classmethod
+    def from_env(cls) -> "KernelSettings":
+        return cls(pdl=_env_int("LLMPLAYER_B200_PDL", 1) != 0, few_tokens=_env_int("LLMPLAYER_B200_FEW_TOKENS", 16),
+                   fewtok_kernel=_env_int("LLMPLAYER_B200_FEWTOK", 1) != 0,
+                   ring_shared=_env_int("LLMPLAYER_B200_RING_SHARED", 6),
+                   ring_alone=_env_int("LLMPLAYER_B200_RING_ALONE", 10))
+
+
+settings = KernelSettings.from_env()
+
+
+def _apply_settings(name: str, lib: ctypes.CDLL) -> None:
+    lib.lp_set_pdl.argtypes = [c_int]
+    lib.lp_set_pdl.restype = None
+    lib.lp_set_pdl(1 if settings.pdl else 0)
+    if name == "gemm_tcgen05":
+        lib.lp_gemm_configure(1 if settings.fewtok_kernel else 0, int(settings.ring_shared), int(settings.ring_alone))
+
+
+def configure(**changes) -> KernelSettings:
+    """Change kernel settings (fields of :class:`KernelSettings`) for this process, now and for libraries
+    loaded later. Graphs captured before the change keep what they were captured with."""
+    global FEW_TOKENS
+    for key, value in changes.items():
+        if value is None:
+            continue
+        if not hasattr(settings, key):
+            raise KernelError(f"unknown kernel setting {key!r}")
+        setattr(settings, key, type(getattr(settings, key))(value))
+    FEW_TOKENS = max(0, min(int(settings.few_tokens), FEW_TOKENS_MAX))
+    for name, lib in _libs.items():
+        _apply_settings(name, lib)
+    return settings
 
 
 def library(name: str) -> ctypes.CDLL:
@@ -88,6 +142,7 @@ def library(name: str) -> ctypes.CDLL:
         f.argtypes = args
         f.restype = c_int
     lib.lp_last_error.restype = ctypes.c_char_p
+    _apply_settings(name, lib)
     _libs[name] = lib
     return lib
 
@@ -95,6 +150,87 @@ def library(name: str) -> ctypes.CDLL:
 def require_gpu() -> None:
     if not torch.cuda.is_available():
         raise ExtensionMissing("no CUDA device: this library runs on the GPU only and has no CPU path")
+
+
+# --------------------------------------------------------------------------- profile mode
+class _NoSection:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SECTION = _NoSection()
+
+
+class StepProfiler:
+    """Device time per section of the model walk, from CUDA-event pairs around each section.
+
+    The reference's ``-Dcuda.profile=true`` puts stream barriers between the sections of a token's forward
+    pass and prints milliseconds per section (java21 inference/CudaForwardPass.java:1431-1456, :1646-1737);
+    graph replay is off meanwhile (:1761). Here a section is a ``with ops.section(name):`` block in a part;
+    the events between sections also keep neighbouring kernels from overlapping, so the times add up to
+    the step's, and steps run directly instead of from captured graphs."""
+
+    def __init__(self):
+        self._pairs = []            # (name, start event, end event), resolved when a report is asked for
+        self._totals: Dict[str, list] = {}
+        self.steps = 0
+
+    class _Section:
+        def __init__(self, owner, name):
+            self.owner, self.name = owner, name
+
+        def __enter__(self):
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+            return self
+
+        def __exit__(self, *exc):
+            end = torch.cuda.Event(enable_timing=True)
+            end.record()
+            self.owner._pairs.append((self.name, self.start, end))
+            return False
+
+    def section(self, name: str):
+        return StepProfiler._Section(self, name)
+
+    def _resolve(self) -> None:
+        if self._pairs:
+            torch.cuda.synchronize()
+            for name, start, end in self._pairs:
+                entry = self._totals.setdefault(name, [0.0, 0])
+                entry[0] += start.elapsed_time(end)
+                entry[1] += 1
+            self._pairs = []
+
+    def report(self) -> dict:
+        """{"steps": n, "total_ms": t, "sections": {name: {"ms": total, "calls": c, "ms_per_step": m}}}"""
+        self._resolve()
+        steps = max(1, self.steps)
+        sections = {name: {"ms": ms, "calls": calls, "ms_per_step": ms / steps}
+                    for name, (ms, calls) in sorted(self._totals.items(), key=lambda kv: -kv[1][0])}
+        return {"steps": self.steps, "total_ms": sum(v["ms"] for v in sections.values()), "sections": sections}
+
+    def reset(self) -> None:
+        self._resolve()
+        self._totals = {}
+        self.steps = 0
+
+
+_profiler: Optional[StepProfiler] = None
+
+
+def set_profiler(profiler: Optional[StepProfiler]) -> None:
+    global _profiler
+    _profiler = profiler
+
+
+def section(name: str):
+    """``with ops.section("attention.qkv"):`` around the launches of one section of the model walk; costs
+    nothing unless a profiler is set."""
+    return _NO_SECTION if _profiler is None else _profiler.section(name)
 
 
 _launches = 0
@@ -105,6 +241,12 @@ def launch_count() -> int:
     return _launches
 
 
+def count_launches(n: int) -> None:
+    """Kernels launched by replaying captured graphs from native code (the host loop) are counted here."""
+    global _launches
+    _launches += int(n)
+
+
 def _check(lib: ctypes.CDLL, code: int) -> None:
     global _launches
     _launches += 1
@@ -113,6 +255,10 @@ def _check(lib: ctypes.CDLL, code: int) -> None:
 
 
 _device_index = None
+
+
+def current_stream() -> int:
+    return _stream()
 
 
 def _stream() -> int:
@@ -204,10 +350,33 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 
 
 # --------------------------------------------------------------------------- rotation + cache write
-def rope_cache_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
+@dataclass(frozen=True)
+class Rotation:
+    """What the kernels that prepare queries and keys can do to them on the way: rotate the first
+    ``rotary_dim`` features of every head by ``position * inv_freq[pair]``, the pairs being
+    (i, i + rotary_dim / 2) or, ``interleaved``, (2i, 2i + 1). ``rotary_dim == 0``: nothing.
+    A position encoding that is such a rotation hands this to the kernels; any other rule is
+    applied by its own part before they run."""
+    inv_freq: Optional[torch.Tensor] = None      # float32 [rotary_dim / 2] on the device
+    rotary_dim: int = 0
+    interleaved: bool = False
+
+    def checked(self, what: str):
+        """(pointer or None, rotary_dim, interleaved as int) after checking the frequencies."""
+        if self.rotary_dim <= 0:
+            return None, 0, 0
+        _want(self.inv_freq, f"{what} inv_freq", torch.float32, 1)
+        if self.inv_freq.numel() != self.rotary_dim // 2:
+            raise KernelError(f"{what}: {self.inv_freq.numel()} frequencies for a rotary width of {self.rotary_dim}")
+        return self.inv_freq.data_ptr(), int(self.rotary_dim), 1 if self.interleaved else 0
+
+
+NO_ROTATION = Rotation()
+
+
+def rope_cache_write(qkv: torch.Tensor, rotation: Rotation, positions: torch.Tensor,
                      seq_ids: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor,
-                     pages: Optional[torch.Tensor], *, num_heads: int, num_kv_heads: int, head_dim: int,
-                     rotary_dim: int, interleaved: bool) -> None:
+                     pages: Optional[torch.Tensor], *, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
     """Rotate queries (and keys), write queries to ``q_out`` [T, H*hd] and keys and
     values into ``pages`` [num_pages, 2, G, page_size, hd]. ``pages=None``: queries only."""
     _want(qkv, "rope qkv", torch.float32, 2)
@@ -225,15 +394,12 @@ def rope_cache_write(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], positi
         if pages.shape[1] != 2 or pages.shape[2] != G or pages.shape[4] != hd:
             raise KernelError(f"rope: pages {tuple(pages.shape)} do not fit {G} key heads of {hd}")
         page_size, kv_code = pages.shape[3], _code(pages, "rope pages")
-    if rotary_dim > 0:
-        _want(inv_freq, "rope inv_freq", torch.float32, 1)
-        if inv_freq.numel() != rotary_dim // 2:
-            raise KernelError(f"rope: {inv_freq.numel()} frequencies for a rotary width of {rotary_dim}")
+    freq_ptr, rotary_dim, interleaved = rotation.checked("rope")
     lib = library("elementwise")
     _check(lib, lib.lp_rope_cache_write(
-        qkv.data_ptr(), qkv.shape[1], _ptr(inv_freq) if rotary_dim > 0 else None, positions.data_ptr(),
+        qkv.data_ptr(), qkv.shape[1], freq_ptr, positions.data_ptr(),
         seq_ids.data_ptr(), page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(), _code(q_out, "rope q_out"),
-        _ptr(pages), kv_code, T, H, G, hd, rotary_dim, 1 if interleaved else 0, page_size, _stream()))
+        _ptr(pages), kv_code, T, H, G, hd, rotary_dim, interleaved, page_size, _stream()))
 
 
 # --------------------------------------------------------------------------- matrix products
@@ -256,11 +422,18 @@ def gemm_plain(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = 
     return out
 
 
-def fast_gemm_available() -> bool:
-    return True
+_num_sms = None
 
 
-NUM_SMS = 148
+def num_sms() -> int:
+    """Streaming multiprocessors of the current device (asked once)."""
+    global _num_sms
+    if _num_sms is None:
+        require_gpu()
+        _num_sms = int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
+    return _num_sms
+
+
 _status = None
 
 
@@ -278,8 +451,8 @@ def check_kernel_status() -> None:
         code = int(_status.item())
         _status.zero_()
         raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}: "
-                          "1 = loader, 2 = MMA issuer, 3 = epilogue; 2x the same in the persistent product; "
-                          "31-34 = roles of the step program, 40 = its barrier between operations)")
+                          "1 = loader, 2 = MMA issuer, 3 = epilogue, 4-5 = operand maker; 2x the same in the "
+                          "persistent product)")
 
 
 def _token_tile(tokens: int, gated: bool) -> int:
@@ -312,14 +485,14 @@ def gemm_plan(tokens: int, features: int, k: int, mode: int):
     if mode == SWIGLU:
         return tile, 1
     ctas = -(-features // 128) * -(-tokens // tile)
-    if ctas >= NUM_SMS // 2 or k_blocks < 8:
+    sms = num_sms()
+    if ctas >= sms // 2 or k_blocks < 8:
         return tile, 1
-    return tile, max(1, min(NUM_SMS // ctas, k_blocks // 4))
+    return tile, max(1, min(sms // ctas, k_blocks // 4))
 
 
 FUSED_NORM_MAX_TOKENS = 4
 PERSISTENT_MIN_TOKENS = 512
-_gemm_counter = None
 
 
 def _persistent_pays(tokens: int, features: int, k: int, mode: int) -> bool:
@@ -328,8 +501,9 @@ def _persistent_pays(tokens: int, features: int, k: int, mode: int) -> bool:
     feat_tiles = -(-features // 128)
     persistent_tiles = feat_tiles * -(-tokens // (128 if mode == SWIGLU else 256))
     separate_ctas = feat_tiles * -(-tokens // 128)
-    fill_p = persistent_tiles / (-(-persistent_tiles // NUM_SMS) * NUM_SMS)
-    fill_s = separate_ctas / (-(-separate_ctas // (2 * NUM_SMS)) * 2 * NUM_SMS)
+    sms = num_sms()
+    fill_p = persistent_tiles / (-(-persistent_tiles // sms) * sms)
+    fill_s = separate_ctas / (-(-separate_ctas // (2 * sms)) * 2 * sms)
     # at equal fill the persistent form wins when the SMs are well filled (its tiles are twice as large and one
     # tile's epilogue hides under the next one's MMAs) or the K loop is long
     return fill_p > fill_s + 0.02 or (fill_p >= fill_s and (fill_p >= 0.8 or k >= 4096))
@@ -345,12 +519,12 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
     them and the partial sums meet in float32 atomics; ``cleared`` says that ``out`` is already
     zero for that. ``block_tok`` / ``splits`` override the plan (tests).
 
-    ``norm_after = (gain, eps, normed_out, clear)`` (``ACCUMULATE`` only, at most
+    ``norm_after = (gain, eps, normed_out, clear, counter)`` (``ACCUMULATE`` only, at most
     ``FUSED_NORM_MAX_TOKENS`` rows): once all CTAs have added their parts, the last one writes
     the RMS norm of every row of ``out`` to ``normed_out`` (bfloat16) and zeroes ``clear``
-    (a float32 tensor or None).
+    (a float32 tensor or None). ``counter``: one int32 on the device that is zero between uses
+    (the CTAs count themselves there; the last one sets it back).
     """
-    global _gemm_counter
     _want(a, "gemm a", torch.bfloat16, 2)
     _want(w, "gemm w", torch.bfloat16, 2)
     _want(out, "gemm out", ndim=2)
@@ -384,7 +558,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
             out.zero_()
     norm_args = (None, 0.0, None, None, 0, None)
     if norm_after is not None:
-        gain, eps, normed, clear = norm_after
+        gain, eps, normed, clear, counter = norm_after
         if mode != ACCUMULATE or M > FUSED_NORM_MAX_TOKENS:
             raise KernelError("gemm: a following norm needs an accumulating product of few rows")
         _want(gain, "gemm norm gain", torch.float32, 1)
@@ -393,21 +567,19 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
             raise KernelError(f"gemm: norm gain {tuple(gain.shape)}, normed out {tuple(normed.shape)} for [{M}, {N}]")
         if clear is not None:
             _want(clear, "gemm norm clear", torch.float32)
-        if _gemm_counter is None or _gemm_counter.device != a.device:
-            _gemm_counter = torch.zeros(1, dtype=torch.int32, device=a.device)
+        _want(counter, "gemm norm counter", torch.int32, 1)
         norm_args = (gain.data_ptr(), float(eps), normed.data_ptr(), _ptr(clear),
-                     clear.numel() if clear is not None else 0, _gemm_counter.data_ptr())
+                     clear.numel() if clear is not None else 0, counter.data_ptr())
     _check(lib, lib.lp_gemm_tcgen05(a.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out, "gemm out"), M, N, K,
                                     K, K, N, mode, tile, n_splits, status.data_ptr(), *norm_args, _stream()))
     return out
 
 
-import os as _os
 FEW_TOKENS_MAX = 64                  # what the few-token kernel takes
-# Up to where the parts choose it with the norm inside. Measured at the 1B shape (ms per step, norm inside
-# against separate norm kernels): 8 tokens 0.70 / 0.76, 12 tokens 0.84 / 0.87, 16 tokens 0.85 / 0.88; at 32 tokens
-# the mma.sync kernel itself loses to the tcgen05 one (1.34 against 1.02).
-FEW_TOKENS = int(_os.environ.get("LLMPLAYER_B200_FEW_TOKENS", "16"))
+# Up to where the parts choose it with the norm inside (``settings.few_tokens``). Measured at the 1B shape (ms per
+# step, norm inside against separate norm kernels): 8 tokens 0.70 / 0.76, 12 tokens 0.84 / 0.87, 16 tokens
+# 0.85 / 0.88; at 32 tokens the mma.sync kernel itself loses to the tcgen05 one (1.34 against 1.02).
+FEW_TOKENS = max(0, min(int(settings.few_tokens), FEW_TOKENS_MAX))
 
 
 def gemm_few(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, norm=None,
@@ -522,13 +694,19 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
     return out
 
 
+MIN_SHARE_PAGES = 8
+
+
 def decode_split(batch: int, num_kv_heads: int, num_heads: int, table_width: int):
-    """How a decode step's pages are shared out over CTAs: (pages per share, shares). A share and the
-    merge of shares cost several dependent round trips to memory, so a sequence is cut only into shares
-    of at least 8 pages, and into no more CTAs than there are SMs (the kernel then gives each CTA 16 warps;
-    measured at batch 8, context 1.9 k / 3.9 k: 0.82 / 0.96 ms per step against 0.92 / 1.01 with twice the CTAs)."""
+    """How a decode step's pages are shared out over CTAs: (pages per share, shares) for page tables of
+    ``table_width`` entries. A share and the merge of shares cost several dependent round trips to memory, so a
+    sequence is cut only into shares of at least ``MIN_SHARE_PAGES`` pages, and into no more CTAs than there are SMs
+    (the kernel then gives each CTA 16 warps; measured at batch 8, context 1.9 k / 3.9 k: 0.82 / 0.96 ms per step
+    against 0.92 / 1.01 with twice the CTAs). This is the most shares a sequence can get; the kernels fit the
+    number to each sequence's own length (at batch 8 and a context of 600 in a table of 16 pages: one share,
+    0.69 ms per step, against 0.75 with two shares of 8 pages)."""
     groups = batch * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
-    shares = max(1, min(table_width // 8, NUM_SMS // groups))
+    shares = max(1, min(table_width // MIN_SHARE_PAGES, num_sms() // groups))
     per = -(-table_width // shares)
     return per, -(-table_width // per)
 
@@ -543,10 +721,17 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pa
     B = kv_len.numel()
     if q.shape[0] != B or page_table.shape[0] != B:
         raise KernelError(f"attention_decode: {B} sequences, q {tuple(q.shape)}, table {tuple(page_table.shape)}")
-    if not pages_per_split or not num_splits:
+    fitted = not pages_per_split or not num_splits
+    if fitted:
         pages_per_split, num_splits = decode_split(B, num_kv_heads, num_heads, page_table.shape[1])
     buf = scratch("attention_partials", (B * num_heads * num_splits * (head_dim + 2),), torch.float32)
     lib = library("attention_mma")
+    if fitted:
+        _check(lib, lib.lp_attention_decode_fitted(
+            q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+            kv_len.data_ptr(), buf.data_ptr(), B, num_heads, num_kv_heads, head_dim, pages.shape[3], float(scale),
+            int(window) if window else 0, num_splits, MIN_SHARE_PAGES, _stream()))
+        return out
     _check(lib, lib.lp_attention_decode(
         q.data_ptr(), out.data_ptr(), pages.data_ptr(), page_table.data_ptr(), page_table.shape[1], kv_len.data_ptr(),
         buf.data_ptr(), B, num_heads, num_kv_heads, head_dim, pages.shape[3], float(scale),
@@ -554,26 +739,33 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pa
     return out
 
 
-_decode_counters = None
+def decode_groups(batch: int, num_heads: int, num_kv_heads: int) -> int:
+    """How many groups of CTAs a fused decode step has (each merges its own shares and counts them in a
+    counter of its own)."""
+    return batch * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
 
 
-def attention_decode_fused(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], out: torch.Tensor,
-                           pages: torch.Tensor, page_table: torch.Tensor, kv_len: torch.Tensor, scratch, *,
-                           num_heads: int, num_kv_heads: int, head_dim: int, rotary_dim: int, interleaved: bool,
+def attention_decode_fused(qkv: torch.Tensor, rotation: Rotation, out: torch.Tensor,
+                           pages: torch.Tensor, page_table: torch.Tensor, kv_len: torch.Tensor, scratch,
+                           counters: torch.Tensor, *,
+                           num_heads: int, num_kv_heads: int, head_dim: int,
                            write_kv: bool, scale: float, window: Optional[int], pages_per_split: int = 0,
                            num_splits: int = 0, row_sumsq: Optional[torch.Tensor] = None, norm_eps: float = 0.0,
                            norm_width: int = 0) -> torch.Tensor:
     """A decode step's attention from the float32 fused projection ``qkv`` [B, (H + 2G) * hd]
     (``[B, H * hd]`` when ``write_kv`` is false): rotates the queries, rotates and stores the new
     key, stores the new value, attends over the pages and merges the shares, in one kernel.
+    ``counters``: int32, at least ``decode_groups(B, H, G)`` entries, zero between uses (the shares of a
+    group count themselves there and the last one sets the counter back).
+    Without ``pages_per_split`` / ``num_splits`` the shares are fitted to each sequence's own length.
     ``row_sumsq`` [B]: ``qkv`` still lacks the factor of the RMS norm of its input; row b is scaled by
     ``1 / sqrt(row_sumsq[b] / norm_width + norm_eps)`` as it is read."""
-    global _decode_counters
     _want(qkv, "attention_decode_fused qkv", torch.float32, 2)
     _want(out, "attention_decode_fused out", torch.bfloat16, 2)
     _want(pages, "attention_decode_fused pages", torch.bfloat16, 5)
     _want(page_table, "attention_decode_fused page_table", torch.int32, 2)
     _want(kv_len, "attention_decode_fused kv_len", torch.int32, 1)
+    _want(counters, "attention_decode_fused counters", torch.int32, 1)
     H, G, hd = num_heads, num_kv_heads, head_dim
     B = kv_len.numel()
     heads = H + 2 * G if write_kv else H
@@ -581,23 +773,21 @@ def attention_decode_fused(qkv: torch.Tensor, inv_freq: Optional[torch.Tensor], 
         raise KernelError(f"attention_decode_fused: qkv {tuple(qkv.shape)}, out {tuple(out.shape)}, {B} sequences")
     if pages.shape[1] != 2 or pages.shape[2] != G or pages.shape[4] != hd:
         raise KernelError(f"attention_decode_fused: pages {tuple(pages.shape)} do not fit {G} key heads of {hd}")
-    if rotary_dim > 0:
-        _want(inv_freq, "attention_decode_fused inv_freq", torch.float32, 1)
-        if inv_freq.numel() != rotary_dim // 2:
-            raise KernelError(f"attention_decode_fused: {inv_freq.numel()} frequencies for a rotary width of {rotary_dim}")
-    if not pages_per_split or not num_splits:
-        pages_per_split, num_splits = decode_split(B, G, H, page_table.shape[1])
-    groups = B * G * (-(-(H // G) // 16))
-    if _decode_counters is None or _decode_counters.numel() < groups or _decode_counters.device != qkv.device:
-        _decode_counters = torch.zeros(max(groups, 1 << 14), dtype=torch.int32, device=qkv.device)
+    freq_ptr, rotary_dim, interleaved = rotation.checked("attention_decode_fused")
+    fitted = not pages_per_split or not num_splits
+    if fitted:                       # as many shares as the tables allow; the kernel fits them to each sequence
+        _, num_splits = decode_split(B, G, H, page_table.shape[1])
+        pages_per_split = page_table.shape[1]
+    if counters.numel() < decode_groups(B, H, G):
+        raise KernelError(f"attention_decode_fused: {counters.numel()} counters for {decode_groups(B, H, G)} groups")
     buf = scratch("attention_partials", (B * H * num_splits * (hd + 2),), torch.float32)
     lib = library("attention_mma")
     _check(lib, lib.lp_attention_decode_fused(
-        qkv.data_ptr(), qkv.shape[1], _ptr(inv_freq) if rotary_dim > 0 else None, rotary_dim, 1 if interleaved else 0,
+        qkv.data_ptr(), qkv.shape[1], freq_ptr, rotary_dim, interleaved,
         out.data_ptr(), pages.data_ptr(), 1 if write_kv else 0, page_table.data_ptr(), page_table.shape[1],
-        kv_len.data_ptr(), buf.data_ptr(), _decode_counters.data_ptr(), B, H, G, hd, pages.shape[3], float(scale),
-        int(window) if window else 0, pages_per_split, num_splits, _ptr(row_sumsq), float(norm_eps), int(norm_width),
-        _stream()))
+        kv_len.data_ptr(), buf.data_ptr(), counters.data_ptr(), B, H, G, hd, pages.shape[3], float(scale),
+        int(window) if window else 0, pages_per_split, num_splits, MIN_SHARE_PAGES if fitted else 0, _ptr(row_sumsq),
+        float(norm_eps), int(norm_width), _stream()))
     return out
 
 

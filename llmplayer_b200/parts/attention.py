@@ -39,6 +39,11 @@ class Attention(Part):
         self.qkv: Optional[Linear] = None
         self.out: Optional[Linear] = None
 
+    @property
+    def capture_safe(self) -> bool:
+        # slots reach the kernels as page tables on the device; the position part must be safe as well
+        return bool(getattr(self.position, "capture_safe", False))
+
     # ------------------------------------------------------------------ tensors
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         s = self.spec
@@ -68,28 +73,9 @@ class Attention(Part):
     def buffer_to_clear(self, ctx, tokens: int):
         return self.qkv.sums_into(ctx, tokens, "qkv", ops.STORE)
 
-    def emit(self, program, ctx, cache, residual: torch.Tensor, norm) -> None:
-        """The layer as operations of a step program: projection of the normed stream, rotation +
-        cache write + attention, output projection added into the stream."""
-        from ..engine.program import ProgramRefused
-        s = self.spec
-        if cache is None or cache.pages.dtype != torch.bfloat16:
-            raise ProgramRefused("attention without a bfloat16 cache")
-        T = residual.shape[0]
-        H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim
-        qkv = ctx.buffer("qkv", (T, self.qkv.out_features), torch.float32)
-        self.qkv.emit(program, residual, qkv, ops.STORE, norm=norm)
-        o = ctx.buffer("attn_out", (T, H * hd), torch.bfloat16)
-        program.attention(
-            qkv=qkv, inv_freq=self.position.inv_freq, rotary_dim=self.position.rotary_dim,
-            interleaved=self.position.interleaved, out=o, pages=cache.pages, write_kv=not s.shares_kv,
-            page_table=ctx.page_tables[cache.group_index], kv_len=ctx.kv_len, scratch=ctx.buffer, num_heads=H,
-            num_kv_heads=G, head_dim=hd, scale=s.scale, window=s.window)
-        self.out.emit(program, o, residual, ops.ACCUMULATE)
-
     takes_pending_norm = True     # the projection applies the norm of its input itself when a step is small
 
-    def _forward_few(self, ctx, cache, pending: PendingNorm, residual: torch.Tensor) -> None:
+    def _forward_few(self, ctx, cache, pending: PendingNorm, residual: torch.Tensor, rotation) -> None:
         """A step of one token for each of a handful of sequences, in three kernels: projection of the
         normed stream (norm applied on the way in), rotation + cache write + attention, output projection.
         The projection's partial sums meet in a buffer that is zero between uses; it leaves each row's
@@ -100,14 +86,17 @@ class Attention(Part):
         F = self.qkv.out_features
         sums = ctx.workspace.get_zeroed("qkv_partial_sums", ops.FEW_TOKENS + ops.FEW_TOKENS * F)
         sumsq, qkv = sums[:ops.FEW_TOKENS], sums[ops.FEW_TOKENS:ops.FEW_TOKENS + T * F].view(T, F)
-        deferred = self.qkv.few(pending.source, qkv, ops.STORE, norm=pending.norm, sumsq=sumsq)
+        with ops.section("attention.qkv"):
+            deferred = self.qkv.few(pending.source, qkv, ops.STORE, norm=pending.norm, sumsq=sumsq)
         o = ctx.buffer("attn_out", (T, H * hd), torch.bfloat16)
-        ops.attention_decode_fused(
-            qkv, self.position.inv_freq, o, cache.pages, ctx.page_tables[cache.group_index], ctx.kv_len, ctx.buffer,
-            num_heads=H, num_kv_heads=G, head_dim=hd, rotary_dim=self.position.rotary_dim,
-            interleaved=self.position.interleaved, write_kv=not s.shares_kv, scale=s.scale, window=s.window,
-            row_sumsq=sumsq if deferred else None, norm_eps=pending.norm.spec.eps, norm_width=residual.shape[1])
-        self.out.few(o, residual, ops.ACCUMULATE, zero=sums[:ops.FEW_TOKENS + T * F])
+        with ops.section("attention.scores"):
+            ops.attention_decode_fused(
+                qkv, rotation, o, cache.pages, ctx.page_tables[cache.group_index], ctx.kv_len, ctx.buffer,
+                ctx.counters("decode_shares", ops.decode_groups(T, H, G)),
+                num_heads=H, num_kv_heads=G, head_dim=hd, write_kv=not s.shares_kv, scale=s.scale, window=s.window,
+                row_sumsq=sumsq if deferred else None, norm_eps=pending.norm.spec.eps, norm_width=residual.shape[1])
+        with ops.section("attention.out"):
+            self.out.few(o, residual, ops.ACCUMULATE, zero=sums[:ops.FEW_TOKENS + T * F])
 
     def forward(self, ctx, cache, x, residual: torch.Tensor, then_norm=None) -> bool:
         """Adds the layer's output into ``residual``; returns whether ``then_norm`` was fused.
@@ -116,35 +105,47 @@ class Attention(Part):
         if cache is None:
             raise ConfigError("attention needs a key/value cache (its own or another run's)")
         H, G, hd = s.num_heads, s.num_kv_heads, s.head_dim
+        # the position encoding as something the kernels do on the way (a rotation), or None: then the
+        # encoding's own part changes queries and keys in the projection's output before the kernels run
+        rotation = self.position.rotation()
         if isinstance(x, PendingNorm):
             T = residual.shape[0]
             if (rt.fast and ctx.all_single and x.fusable and cache.pages.dtype == torch.bfloat16 and hd % 16 == 0
                     and hd <= 256 and self.qkv.can_few(T, ops.STORE) and self.out.can_few(T, ops.ACCUMULATE)
-                    and residual.dtype == torch.float32):
-                self._forward_few(ctx, cache, x, residual)
+                    and residual.dtype == torch.float32 and rotation is not None):
+                self._forward_few(ctx, cache, x, residual, rotation)
                 return False
             x = x.tensor()
         T = x.shape[0]
         table = ctx.page_tables[cache.group_index]
         qkv = ctx.buffer("qkv", (T, self.qkv.out_features), torch.float32)
-        self.qkv.store(x, qkv, ctx)
+        with ops.section("attention.qkv"):
+            self.qkv.store(x, qkv, ctx)
+        if rotation is None:
+            with ops.section("attention.position"):
+                self.position.apply(ctx, qkv, num_heads=H, num_kv_heads=0 if s.shares_kv else G, head_dim=hd)
+            rotation = ops.NO_ROTATION
         o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
         if rt.fast and ctx.all_single and cache.pages.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256:
             # one token per sequence: rotation, cache write, attention and the merge of its shares in one kernel
-            ops.attention_decode_fused(
-                qkv, self.position.inv_freq, o, cache.pages, table, ctx.kv_len, ctx.buffer, num_heads=H,
-                num_kv_heads=G, head_dim=hd, rotary_dim=self.position.rotary_dim,
-                interleaved=self.position.interleaved, write_kv=not s.shares_kv, scale=s.scale, window=s.window)
-            return self.out.accumulate(o, residual, ctx, then_norm)
+            with ops.section("attention.scores"):
+                ops.attention_decode_fused(
+                    qkv, rotation, o, cache.pages, table, ctx.kv_len, ctx.buffer,
+                    ctx.counters("decode_shares", ops.decode_groups(T, H, G)), num_heads=H,
+                    num_kv_heads=G, head_dim=hd, write_kv=not s.shares_kv, scale=s.scale, window=s.window)
+            with ops.section("attention.out"):
+                return self.out.accumulate(o, residual, ctx, then_norm)
         q = ctx.buffer("q", (T, H * hd), rt.act_dtype)
-        ops.rope_cache_write(
-            qkv, self.position.inv_freq, ctx.positions, ctx.seq_ids, table, q,
-            None if s.shares_kv else cache.pages,
-            num_heads=H, num_kv_heads=G, head_dim=hd, rotary_dim=self.position.rotary_dim,
-            interleaved=self.position.interleaved)
-        ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd,
-                      scale=s.scale, window=s.window, fast=rt.fast)
-        return self.out.accumulate(o, residual, ctx, then_norm)
+        with ops.section("attention.position"):
+            ops.rope_cache_write(
+                qkv, rotation, ctx.positions, ctx.seq_ids, table, q,
+                None if s.shares_kv else cache.pages,
+                num_heads=H, num_kv_heads=G, head_dim=hd)
+        with ops.section("attention.scores"):
+            ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd,
+                          scale=s.scale, window=s.window, fast=rt.fast)
+        with ops.section("attention.out"):
+            return self.out.accumulate(o, residual, ctx, then_norm)
 
 
 MIXERS.register("attention", Attention)

@@ -5,7 +5,8 @@ A part is built from its specification alone, says which tensors it needs
 step. No part knows which model it is in.
 
 * Norm:          ``apply(x[T, d] float32, out[T, d]) -> out`` (optionally on chosen rows)
-* Position:      owned by a mixer; offers what the mixer's kernels need (frequencies)
+* Position:      owned by a mixer: ``rotation()`` (a rule the kernels apply on the way) or
+                 ``apply(ctx, qkv, ...)`` (any other rule, applied to the projection in place)
 * Mixer:         ``cache_request()`` and ``forward(ctx, cache_view, x[T, d], residual[T, d])``:
                  adds its output into the float32 residual stream
 * Feed-forward:  ``forward(ctx, x[T, d], residual[T, d])``: adds into the residual stream
@@ -114,6 +115,14 @@ class PendingNorm:
 
 
 class Part:
+    # Steps of one token per sequence are replayed from CUDA graphs that were captured on an earlier step of
+    # the same shape, possibly for other sequences. A part whose ``forward`` depends on the step only through
+    # the device tensors of ``ctx`` (``tokens``, ``positions``, ``slots``, ``kv_len``, ``page_tables``...) and
+    # through what the graph's key holds (batch, page-table widths, wanted rows) may say so; a part that reads
+    # the step on the host (``ctx.sequences``, ``ctx.slot_list``: which rows of a state it updates, say)
+    # leaves this False, and a model with such a part runs every step directly.
+    capture_safe = False
+
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}
 

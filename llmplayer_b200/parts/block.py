@@ -10,6 +10,7 @@ from typing import Dict, Mapping
 
 import torch
 
+from ..kernels import ops
 from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, FollowingNorm, Part, PendingNorm, Runtime
 from .specs import BlockSpec, TensorSpec
 
@@ -27,6 +28,10 @@ class PreNormBlock(Part):
 
     def children(self):
         return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+
+    @property
+    def capture_safe(self) -> bool:
+        return all(bool(getattr(part, "capture_safe", False)) for part in self.children())
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         out: Dict[str, TensorSpec] = {}
@@ -97,15 +102,6 @@ class PreNormBlock(Part):
 
     kind_prenorm = True
 
-    def emit(self, program, ctx, cache, residual: torch.Tensor) -> None:
-        """The layer as operations of a step program: each half's norm is applied by the half's
-        first product on the way in, so the parts must be able to emit and the norms to be fused."""
-        from ..engine.program import ProgramRefused
-        if not hasattr(self.mixer, "emit") or not hasattr(self.ffn, "emit"):
-            raise ProgramRefused("a part that only runs as kernels of its own")
-        self.mixer.emit(program, ctx, cache, residual, self.mixer_norm)
-        self.ffn.emit(program, ctx, residual, self.ffn_norm)
-
     @staticmethod
     def _clear_for(ctx, consumer, tokens):
         ask = getattr(consumer, "buffer_to_clear", None)
@@ -116,11 +112,12 @@ class PreNormBlock(Part):
         """Norm the residual stream for ``consumer``; if the consumer's first product wants a
         zeroed buffer (``buffer_to_clear(ctx, tokens)``), the norm clears it on the side."""
         clear = PreNormBlock._clear_for(ctx, consumer, residual.shape[0])
-        if clear is not None:
-            norm.apply(residual, h, clear=clear)
-            ctx.note_cleared()
-        else:
-            norm.apply(residual, h)
+        with ops.section("norm"):
+            if clear is not None:
+                norm.apply(residual, h, clear=clear)
+                ctx.note_cleared()
+            else:
+                norm.apply(residual, h)
 
 
 BLOCKS.register("prenorm", PreNormBlock)

@@ -19,6 +19,7 @@ from .specs import MATRIX, EmbeddingSpec, HeadSpec, TensorSpec
 
 
 class Embedding(Part):
+    capture_safe = True
     def __init__(self, spec: EmbeddingSpec):
         self.spec = spec
         self.table: Optional[torch.Tensor] = None
@@ -31,17 +32,18 @@ class Embedding(Part):
         self.table = shared if shared is not None else runtime.matrix(tensors[self.spec.weight])
 
     def forward(self, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        return ops.embed(self.table, tokens, out)
-
-    def emit(self, program, tokens: torch.Tensor, out: torch.Tensor) -> None:
-        program.embed(self.table, tokens, out)
-
+        with ops.section("embedding"):
+            return ops.embed(self.table, tokens, out)
 
 class LinearHead(Part):
     def __init__(self, spec: HeadSpec):
         self.spec = spec
         self.norm = NORMS.build(spec.norm)
         self.proj: Optional[Linear] = None
+
+    @property
+    def capture_safe(self) -> bool:
+        return bool(getattr(self.norm, "capture_safe", False))
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         out = dict(self.norm.tensor_specs())
@@ -56,8 +58,7 @@ class LinearHead(Part):
     def forward(self, ctx, residual: torch.Tensor, rows: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         """logits[i] = head(norm(residual[rows[i]])), float32."""
         h = ctx.buffer("head_in", (rows.numel(), self.spec.hidden_size), self.runtime.act_dtype)
-        self.norm.apply(residual, h, rows=rows)
-        return self.proj.store(h, logits, ctx)
-
-    def emit(self, program, residual: torch.Tensor, rows: torch.Tensor, logits: torch.Tensor) -> None:
-        self.proj.emit(program, residual, logits, ops.STORE, norm=self.norm, x_rows=rows, tokens=rows.numel())
+        with ops.section("head.norm"):
+            self.norm.apply(residual, h, rows=rows)
+        with ops.section("head.proj"):
+            return self.proj.store(h, logits, ctx)

@@ -18,6 +18,7 @@ from .specs import MATRIX, SwiGLUSpec, TensorSpec
 
 
 class SwiGLU(Part):
+    capture_safe = True
     def __init__(self, spec: SwiGLUSpec):
         self.spec = spec
         self.gate_up: Optional[Linear] = None
@@ -37,13 +38,6 @@ class SwiGLU(Part):
         self.gate_up = Linear([tensors[s.gate], tensors[s.up]], runtime, gated=True)
         self.down = Linear([tensors[s.down]], runtime)
 
-    def emit(self, program, ctx, residual: torch.Tensor, norm) -> None:
-        """The layer as operations of a step program (engine/program.py)."""
-        from ..kernels import ops
-        h = ctx.buffer("ffn_hidden", (residual.shape[0], self.spec.intermediate_size), torch.bfloat16)
-        self.gate_up.emit(program, residual, h, ops.SWIGLU, norm=norm)
-        self.down.emit(program, h, residual, ops.ACCUMULATE)
-
     takes_pending_norm = True     # the gated product applies the norm of its input itself when a step is small
 
     def forward(self, ctx, x, residual: torch.Tensor, then_norm=None) -> bool:
@@ -55,13 +49,17 @@ class SwiGLU(Part):
             if (self.runtime.fast and x.fusable and residual.dtype == torch.float32
                     and self.gate_up.can_few(T, ops.SWIGLU) and self.down.can_few(T, ops.ACCUMULATE)):
                 h = ctx.buffer("ffn_hidden", (T, self.spec.intermediate_size), torch.bfloat16)
-                self.gate_up.few(x.source, h, ops.SWIGLU, norm=x.norm)
-                self.down.few(h, residual, ops.ACCUMULATE)
+                with ops.section("ffn.gate_up"):
+                    self.gate_up.few(x.source, h, ops.SWIGLU, norm=x.norm)
+                with ops.section("ffn.down"):
+                    self.down.few(h, residual, ops.ACCUMULATE)
                 return False
             x = x.tensor()
         h = ctx.buffer("ffn_hidden", (x.shape[0], self.spec.intermediate_size), self.runtime.act_dtype)
-        self.gate_up.swiglu(x, h, ctx)
-        return self.down.accumulate(h, residual, ctx, then_norm)
+        with ops.section("ffn.gate_up"):
+            self.gate_up.swiglu(x, h, ctx)
+        with ops.section("ffn.down"):
+            return self.down.accumulate(h, residual, ctx, then_norm)
 
 
 FEED_FORWARDS.register("swiglu", SwiGLU)

@@ -31,8 +31,7 @@ class Linear:
             if len(mats) != 2 or mats[0].shape != mats[1].shape:
                 raise ValueError("a gated product takes a gate and an up matrix of equal shape")
             self.out_features = mats[0].shape[0]
-            self.interleaved = (runtime.fast and mats[0].dtype == torch.bfloat16 and self.in_features % 8 == 0
-                                and ops.fast_gemm_available())
+            self.interleaved = runtime.fast and mats[0].dtype == torch.bfloat16 and self.in_features % 8 == 0
         if self.interleaved:
             # the tensor-core kernel wants gate and up rows of the same features side by side
             self.weight = ops.interleave_gate_up(mats[0], mats[1])
@@ -41,8 +40,7 @@ class Linear:
 
     def _fast(self) -> bool:
         # the tensor-core kernel wants bfloat16 operands and rows of a multiple of 8 elements (TMA strides)
-        return (self.runtime.fast and self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
-                and ops.fast_gemm_available())
+        return self.runtime.fast and self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
 
     def store(self, x: torch.Tensor, out: torch.Tensor, ctx=None) -> torch.Tensor:
         return self._run(x, out, ops.STORE, ctx)
@@ -51,15 +49,15 @@ class Linear:
         """out += x @ W^T. ``then_norm`` (a :class:`FollowingNorm`): if this product runs on the
         tensor cores for a few rows and the norm is an RMS norm over whole rows, the product's
         last CTA also writes the norm; returns whether it did."""
-        if (then_norm is not None and self._fast() and x.dtype == torch.bfloat16
+        if (then_norm is not None and ctx is not None and self._fast() and x.dtype == torch.bfloat16
                 and x.shape[0] <= ops.FUSED_NORM_MAX_TOKENS and getattr(then_norm.norm, "fusable_rms", False)
                 and then_norm.out.dtype == torch.bfloat16 and out.shape[1] == self.out_features
                 and self.out_features % 128 == 0):
-            if ctx is not None:
-                ctx.take_cleared()
+            ctx.take_cleared()
             norm = then_norm.norm
             ops.gemm(x, self.weight, out, ops.ACCUMULATE,
-                     norm_after=(norm.weight, norm.spec.eps, then_norm.out, then_norm.clear))
+                     norm_after=(norm.weight, norm.spec.eps, then_norm.out, then_norm.clear,
+                                 ctx.counters("product_ctas", 1)))
             return True
         self._run(x, out, ops.ACCUMULATE, ctx)
         return False
@@ -88,19 +86,6 @@ class Linear:
         Returns whether ``out`` still lacks the rows' factors (then ``sumsq`` holds their sums of squares)."""
         return ops.gemm_few(x, self.weight, out, mode, norm=None if norm is None else (norm.weight, norm.spec.eps),
                             sumsq=sumsq, zero=zero)
-
-    def emit(self, program, x: torch.Tensor, out: torch.Tensor, mode: int, *, norm=None, x_rows=None,
-             tokens=None) -> None:
-        """Append this product to a step program (engine/program.py); ``norm``: the RMS norm part
-        whose output the product takes, applied to the float32 ``x`` on the way in."""
-        from ..engine.program import ADD, STORE as P_STORE, SWIGLU as P_SWIGLU, ProgramRefused
-        if not self._fast() or (mode == ops.SWIGLU and not self.interleaved):
-            raise ProgramRefused("a product outside the tensor-core path")
-        if norm is not None and not getattr(norm, "fusable_rms", False):
-            raise ProgramRefused("a norm that the product cannot apply to its input")
-        epilogue = {ops.STORE: P_STORE, ops.ACCUMULATE: ADD, ops.SWIGLU: P_SWIGLU}[mode]
-        program.product(self.weight, x=x, out=out, epilogue=epilogue, features=self.out_features,
-                        norm=None if norm is None else (norm.weight, norm.spec.eps), x_rows=x_rows, tokens=tokens)
 
     def _run(self, x, out, mode, ctx):
         if self._fast() and x.dtype == torch.bfloat16 and (mode != ops.SWIGLU or self.interleaved):

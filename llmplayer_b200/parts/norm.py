@@ -15,6 +15,7 @@ from .specs import GAIN, NormSpec, TensorSpec
 
 
 class RMSNorm(Part):
+    capture_safe = True
     fusable_rms = True      # a product that adds into the residual stream may write this norm on the way
 
     def __init__(self, spec: NormSpec):

@@ -1,4 +1,14 @@
-"""Rotary position encoding: the per-pair frequencies a mixer's kernels rotate by.
+"""Position encodings of a mixer's queries and keys.
+
+A position part owns the rule. It offers it in one of two forms: ``rotation()`` returns an
+:class:`llmplayer_b200.kernels.ops.Rotation` when the rule is a rotation of feature pairs by
+position x frequency, which the kernels that prepare queries and keys apply on the way; a part
+whose rule is anything else returns None there and implements ``apply(ctx, qkv, num_heads=,
+num_kv_heads=, head_dim=)``, which changes the query and key heads of the float32 projection
+``qkv`` [T, (H + 2G) * hd] (or [T, H * hd] for a layer without keys of its own) in place, reading
+the tokens' positions from ``ctx.positions``; the mixer then runs its kernels without rotation.
+
+Rotary encoding: the per-pair frequencies the kernels rotate by.
 
 Reference: inference/RoPE.java:80-105. f_i = 1 / theta^(2i / rotary_dim) is
 computed in double and rounded to float32 (:83); a per-pair divisor may follow
@@ -14,6 +24,7 @@ from typing import Optional
 import torch
 
 from ..errors import ConfigError
+from ..kernels import ops
 from .base import POSITIONS, Part, Runtime
 from .specs import PositionSpec
 
@@ -42,27 +53,39 @@ def inverse_frequencies(spec: PositionSpec) -> torch.Tensor:
 
 
 class Rotary(Part):
+    """Rotation of query and key pairs by position x frequency: a rule the kernels apply themselves."""
+    capture_safe = True
+
     def __init__(self, spec: PositionSpec):
         if spec.pairing not in ("split_half", "interleaved"):
             raise ConfigError(f"unknown rotary pairing {spec.pairing!r}")
         self.spec = spec
-        self.rotary_dim = spec.rotary_dim
-        self.interleaved = spec.pairing == "interleaved"
-        self.inv_freq: Optional[torch.Tensor] = None
+        self._rotation: Optional[ops.Rotation] = None
 
     def load(self, tensors, runtime: Runtime) -> None:
         super().load(tensors, runtime)
-        self.inv_freq = inverse_frequencies(self.spec).to(runtime.device)
+        self._rotation = ops.Rotation(inverse_frequencies(self.spec).to(runtime.device), self.spec.rotary_dim,
+                                      self.spec.pairing == "interleaved")
+
+    def rotation(self) -> Optional[ops.Rotation]:
+        return self._rotation
+
+    def apply(self, ctx, qkv, *, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+        raise ConfigError("a rotary encoding is applied by the kernels that take its rotation()")
 
 
 class NoPosition(Part):
     """Queries and keys are used as projected."""
+    capture_safe = True
 
     def __init__(self, spec: PositionSpec):
         self.spec = spec
-        self.rotary_dim = 0
-        self.interleaved = False
-        self.inv_freq = None
+
+    def rotation(self) -> Optional[ops.Rotation]:
+        return ops.NO_ROTATION
+
+    def apply(self, ctx, qkv, *, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+        pass
 
 
 POSITIONS.register("rope", Rotary)

@@ -34,6 +34,8 @@ class SequenceSampler:
         self.max_recent = max(64, config.dry_range)
         self.mu = 2.0 * config.mirostat_tau
         self._powers = [1.0]         # powers of the repetition penalty, by number of occurrences
+        # the first maximum of the logits as they are: nothing of this state enters the choice
+        self.plain_greedy = config.is_greedy and config.repetition_penalty == 1.0 and config.dry_multiplier <= 0
 
     # ------------------------------------------------------------------ before a draw
     def edit_lists(self) -> Tuple[List[int], List[float], List[float]]:
@@ -113,6 +115,7 @@ class BatchSampler:
         self._work = None
         self._out = None
         self._host = None            # page-locked landing place of the results
+        self._staging = None         # page-locked staging of the parameters and logit edits
         self._done = None
         self._constant = {}          # greedy batches without logit edits: parameters stay on the device
         self._dummy = None
@@ -120,6 +123,15 @@ class BatchSampler:
         self._slice_capacity = None
         self.last_h2d_bytes = 0
         self.last_d2h_bytes = 0
+
+    def _stage(self, packed: np.ndarray) -> torch.Tensor:
+        """``packed`` in page-locked memory that is kept from call to call (the previous call's copy out of it
+        has finished: every call ends by waiting for its results)."""
+        n = packed.size
+        if self._staging is None or self._staging.numel() < n:
+            self._staging = torch.empty(max(2 * n, 4096), dtype=torch.int32).pin_memory()
+        self._staging[:n].numpy()[:] = packed
+        return self._staging[:n]
 
     def _read_back(self, count: int, while_waiting) -> torch.Tensor:
         """The first ``count`` result words on the host. The copy is asynchronous into page-locked memory;
@@ -152,7 +164,8 @@ class BatchSampler:
         key = tuple(rows)
         if plain_greedy and list(rows) == list(range(B)) and logits.shape[0] == B:
             # first-maximum argmax of every row, spread over many blocks
-            ops.argmax(logits, self._work.view(-1), out_tok)
+            with ops.section("sample"):
+                ops.argmax(logits, self._work.view(-1), out_tok)
             self.last_h2d_bytes = 0
             self.last_d2h_bytes = 4 * B
             chosen = self._read_back(B, while_waiting).tolist()
@@ -182,7 +195,7 @@ class BatchSampler:
             fac_arr = np.ones(n, dtype=np.float32)
             fac_arr[:len(tokens)] = np.asarray(facs, dtype=np.float32)
             packed[head + 2 * n:head + 3 * n] = fac_arr.view(np.int32)
-            blob = torch.from_numpy(packed).pin_memory().to(dev, non_blocking=True)
+            blob = self._stage(packed).to(dev, non_blocking=True)
             self.last_h2d_bytes = packed.nbytes
             params_dev = blob[:head].view(torch.uint8)
             edit_tok = blob[head:head + n]
@@ -194,8 +207,9 @@ class BatchSampler:
                 self._constant[key] = params_dev
         # a small top-k: several blocks per row find the candidates before one block draws among them
         sliced = any(not s.config.is_greedy and 0 < s.config.top_k <= self._slice_capacity for s in samplers)
-        ops.sample(logits, self._work[:B], params_dev, edit_tok, edit_sub, edit_fac, out_tok, out_prob,
-                   select=self._select if sliced else None)
+        with ops.section("sample"):
+            ops.sample(logits, self._work[:B], params_dev, edit_tok, edit_sub, edit_fac, out_tok, out_prob,
+                       select=self._select if sliced else None)
         host = self._read_back(2 * B, while_waiting)         # one copy back: tokens, then probabilities
         self.last_d2h_bytes = 8 * B
         chosen = host[:B].tolist()

@@ -152,8 +152,9 @@ def attention_block(x, w, prefix, cfg, inv_freq, positions, window=None):
     return o.reshape(T, H * hd) @ w[prefix + "self_attn.o_proj.weight"].T
 
 
-def forward(cfg, tensors, tokens, dtype=torch.float64, layers=None):
-    """Logits [T, vocab] of one whole sequence: embedding row without scaling
+def forward(cfg, tensors, tokens, dtype=torch.float64, layers=None, rows=None):
+    """Logits [T, vocab] of one whole sequence (or of its positions ``rows`` only, which spares
+    a large vocabulary's head for the others): embedding row without scaling
     (inference/InferenceEngine.java:199-208), for each layer x += attention(norm(x)),
     x += ffn(norm(x)) (inference/TransformerBlock.java:73-149), final norm and head,
     which is the embedding table when tied (inference/InferenceEngine.java:225-262,
@@ -172,6 +173,8 @@ def forward(cfg, tensors, tokens, dtype=torch.float64, layers=None):
         x = x + attention_block(rms_norm(x, w[p + "input_layernorm.weight"], eps), w, p, cfg, inv_freq, positions)
         h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
         x = x + swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long)]
     x = rms_norm(x, w["model.norm.weight"], eps)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return x @ head.T

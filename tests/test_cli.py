@@ -35,6 +35,30 @@ def test_flags_and_short_forms():
     assert c.is_greedy and c.mirostat == 2 and c.dry_range == 64 and c.seed == 9 and c.min_p == 0.05
 
 
+def test_engine_switches_become_engine_options(tmp_path):
+    o = CLIOptions.parse(["-m", "x", "--prompt-file", "p.txt", "--max-slots", "5", "--no-graph", "--profile",
+                          "--plain-kernels", "--dtype", "float32", "-c", "300", "--gpu-device", "1"])
+    assert o.prompt_file == "p.txt" and o.max_slots == 5 and o.no_graph and o.profile and o.plain_kernels
+    e = o.to_engine_options(batch=3)
+    assert (e.dtype, e.kernels, e.context_length, e.max_batch, e.max_slots) == ("float32", "plain", 300, 3, 5)
+    assert e.device == "cuda:1" and e.graphs is False and e.profile is True
+    d = CLIOptions.parse(["x"]).to_engine_options(batch=1)
+    assert d.graphs and not d.profile and d.kernels == "fast" and d.max_slots is None
+
+
+def test_engine_options_are_checked():
+    from llmplayer_b200.engine.options import EngineOptions
+    from llmplayer_b200.errors import ConfigError
+    with pytest.raises(ConfigError, match="dtype"):
+        EngineOptions(dtype="float16")
+    with pytest.raises(ConfigError, match="max_tokens"):
+        EngineOptions(max_tokens=0)
+    with pytest.raises(ConfigError, match="unknown engine option.*warp_speed"):
+        EngineOptions().with_changes(warp_speed=9)
+    o = EngineOptions().with_changes(few_tokens=8, pdl=False)
+    assert o.kernel_settings() == {"few_tokens": 8, "pdl": False}
+
+
 def test_help_runs_without_a_gpu():
     out = subprocess.run([sys.executable, "-m", "llmplayer_b200", "--help"], cwd=ROOT, capture_output=True, text=True)
     assert out.returncode == 0 and "--max-tokens, -n" in out.stdout and "--repetition-penalty" in out.stdout
@@ -52,6 +76,16 @@ def test_cli_generates_and_prints_the_stats_line(tmp_path):
     assert lines[-1].startswith("Tokens: 5 prompt + 10 generated in ") and lines[-1].endswith("tok/s)")
     rows = [l for l in lines if l.startswith("[0] ") or l.startswith("[1] ")]
     assert len(rows) == 2 and all(len(r.split()) == 6 for r in rows)
+    # prompts from a file, sections timed: the profile lines follow the stats line
+    prompt_file = tmp_path / "prompts.txt"
+    prompt_file.write_text("5 17 3\n\n9,1\n")
+    prof = subprocess.run([sys.executable, "-m", "llmplayer_b200", "-m", model_dir, "--prompt-file", str(prompt_file),
+                           "-n", "4", "-t", "0", "--repetition-penalty", "1.0", "-c", "64", "--profile"],
+                          cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert prof.returncode == 0, prof.stderr
+    assert "Tokens: 5 prompt + 8 generated in " in prof.stdout
+    tail = prof.stdout.split("--- Profile (")[1]
+    assert tail.startswith("4 steps") and "attention.scores" in tail and "ffn.gate_up" in tail and "head.proj" in tail
     info = subprocess.run([sys.executable, "-m", "llmplayer_b200", model_dir, "--info"], cwd=ROOT, capture_output=True,
                           text=True, timeout=300)
     assert info.returncode == 0 and "LlamaForCausalLM" in info.stdout and "num_hidden_layers" in info.stdout

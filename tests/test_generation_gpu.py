@@ -106,26 +106,41 @@ def test_prompt_too_long_is_an_error_response(tmp_path):
     assert out[1].finish_reason == "context" and out[1].token_count == 16 - 1 - 3 + 1
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_device_resident_decoding_equals_the_generation_loop(tmp_path, dtype):
-    """Decode steps that follow one another on the device (captured once, replayed) must
-    produce the tokens that the host-driven loop produces, across page boundaries."""
+def test_native_host_loop_equals_stepping_from_python(tmp_path):
+    """Greedy decoding through the native host loop (a captured graph per step with upload, argmax and
+    read-back inside, several quiet steps per call) must give what the loop gives when every step goes
+    through ``Engine.step`` and ``Engine.sample``: across page boundaries, with a stop token that ends one
+    sequence in the middle of a run, with unequal budgets, and with a callback (one step per call)."""
     from llmplayer_b200 import Engine, SamplerConfig
-    from llmplayer_b200.engine.decode import DecodeSession
-    model_dir = make_model(tmp_path, "C", dtype=dtype)
+    from llmplayer_b200.engine.generate import GenerationRequest
+    model_dir = make_model(tmp_path, "C", dtype="bfloat16")
     prompts = prompts_for("C", [50, 3, 61], seed=80)
-    eng = Engine.load(model_dir, dtype=dtype, context_length=512, max_batch=3)
+    fast = Engine.load(model_dir, dtype="bfloat16", context_length=512, max_batch=3)
+    slow = Engine.load(model_dir, dtype="bfloat16", context_length=512, max_batch=3, host_loop=False, graphs=False)
     steps = 90
-    ref = eng.generate(prompts, SamplerConfig.greedy(), max_tokens=steps + 1, stop_token_ids=())
-    session = DecodeSession(eng, prompts, reserve=61 + steps + 2)
-    try:
-        session.run(steps, keep_tokens=True)
-        got = session.tokens()
-    finally:
-        session.close()
-    if dtype == "float32":
-        assert got == [r.token_ids for r in ref]
-    else:
-        for p, g in zip(prompts, got):
-            check_greedy_chain(model_dir, p, g, dtype)
-    assert eng.cache.slots.num_held == 0
+    ref = slow.generate(prompts, SamplerConfig.greedy(), max_tokens=steps + 1, stop_token_ids=())
+    got = fast.generate(prompts, SamplerConfig.greedy(), max_tokens=steps + 1, stop_token_ids=())
+    assert fast.last_generation_stats.decode_steps == steps
+    assert any(e.get("graph") is not None for e in fast._fused.values()), "the captured step never ran"
+    for p, r, g in zip(prompts, ref, got):
+        assert g.finish_reason == "length" and g.token_count == steps + 1
+        check_greedy_chain(model_dir, p, g.token_ids, "bfloat16")
+        check_greedy_chain(model_dir, p, r.token_ids, "bfloat16")
+    # a stop token in the middle: the 30th token of the second sequence; budgets differ per request
+    stop = got[1].token_ids[29]
+    first_hit = [r.token_ids.index(stop) if stop in r.token_ids else None for r in got]
+    requests = [GenerationRequest(p, max_tokens=m, sampler_config=SamplerConfig.greedy(), stop_token_ids=(stop,))
+                for p, m in zip(prompts, (70, 91, 20))]
+    again = fast.generate(requests)
+    for r, full, hit, budget in zip(again, got, first_hit, (70, 91, 20)):
+        if hit is not None and hit < budget:
+            assert r.finish_reason == "stop" and r.token_ids == full.token_ids[:hit]
+        else:
+            assert r.finish_reason == "length" and r.token_ids == full.token_ids[:budget]
+    # with a callback every token passes through the interpreter before the next step
+    seen = []
+    called = fast.generate(prompts, SamplerConfig.greedy(), max_tokens=40, stop_token_ids=(),
+                           on_token=lambda i, t: seen.append((i, t)))
+    assert [r.token_ids for r in called] == [g.token_ids[:40] for g in got]
+    assert len(seen) == 3 * 40
+    assert fast.cache.slots.num_held == 0 and slow.cache.slots.num_held == 0

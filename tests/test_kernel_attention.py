@@ -51,8 +51,10 @@ def reference(q, k, v, positions, scale, window):
     return out
 
 
-def run_case(kind, lengths, new, H, G, hd, window, dtype, seed=0, crafted=False):
-    """``new[b]`` tokens of sequence b are the step's queries (the last ``new[b]`` positions)."""
+def run_case(kind, lengths, new, H, G, hd, window, dtype, seed=0, crafted=False, shares=None):
+    """``new[b]`` tokens of sequence b are the step's queries (the last ``new[b]`` positions).
+    ``shares``: into how many shares a decode kernel cuts the page tables (None: its own choice);
+    ``kind="fused"`` runs the decode kernel that starts from the projection (no rotation, no cache write)."""
     from llmplayer_b200.kernels import ops
     dev = "cuda:0"
     dense, pages, table = build_cache(lengths, G, hd, dtype, seed)
@@ -98,11 +100,26 @@ def run_case(kind, lengths, new, H, G, hd, window, dtype, seed=0, crafted=False)
         def buf(name, shape, dt):
             scratch[name] = torch.full(shape, float("nan"), dtype=dt, device=dev)
             return scratch[name]
-        ops.attention_decode(qd, out, pages_d, table_d, kv_len, buf, **kw)
+        split = {}
+        if shares:
+            per = -(-table.shape[1] // shares)
+            split = dict(pages_per_split=per, num_splits=-(-table.shape[1] // per))
+        if kind == "fused":
+            # the queries as the float32 projection would deliver them; this layer keeps no keys of its own, so
+            # the kernel attends over the pages as they are
+            counters = torch.zeros(ops.decode_groups(len(lengths), H, G), dtype=torch.int32, device=dev)
+            ops.attention_decode_fused(qd.float(), ops.NO_ROTATION, out, pages_d, table_d, kv_len, buf, counters,
+                                       write_kv=False, **kw, **split)
+            assert int(counters.abs().sum()) == 0
+        else:
+            ops.attention_decode(qd, out, pages_d, table_d, kv_len, buf, **kw, **split)
     torch.cuda.synchronize()
     got = out.reshape(T, H, hd).double().cpu()
     assert torch.isfinite(got).all()
     err = float((got - ref).abs().max())
+    from helpers import record_error
+    record_error(f"attention kernel ({kind}), {str(dtype).split('.')[-1]}", f"H{H} G{G} hd{hd} window {window}", err,
+                 2e-5 if dtype == torch.float32 else 2e-2)
     if crafted:
         for b in range(len(lengths)):
             row = q_start[b + 1] - 1
@@ -153,6 +170,88 @@ def test_tensor_core_decode(H, G, hd, window):
     assert err < 2e-2, err
 
 
+@pytest.mark.parametrize("kind", ["decode", "fused"])
+@pytest.mark.parametrize("shares", [2, 3, 5])
+@pytest.mark.parametrize("window", [None, 70, 200])
+def test_decode_in_several_shares_against_float64(kind, shares, window):
+    """The pages of a sequence cut into shares: with a window some shares lie wholly before it, one share may
+    hold nothing but the newest page, short sequences leave most shares empty. Compared with the float64
+    attention (not with another entry point of the same kernel), random and with one far key made to win."""
+    lengths = [1, 64, 65, 700, 129, 17, 641]
+    err = run_case(kind, lengths, [1] * len(lengths), 8, 2, 64, window, torch.bfloat16, seed=11, shares=shares)
+    assert err < 2e-2, err
+    err = run_case(kind, lengths, [1] * len(lengths), 6, 3, 48, window, torch.bfloat16, seed=12, shares=shares)
+    assert err < 2e-2, err
+    run_case(kind, [900, 333, 70], [1, 1, 1], 8, 2, 64, window, torch.bfloat16, seed=3, crafted=True, shares=shares)
+
+
+@pytest.mark.parametrize("kind", ["decode", "fused"])
+@pytest.mark.parametrize("window", [None, 300, 1000])
+def test_shares_fitted_to_each_sequence(kind, window):
+    """Left to themselves the decode kernels cut every sequence into as many shares as its own length (within the
+    window) gives pages for: here four, two, one and one shares in one grid, some CTAs with nothing to do."""
+    lengths = [2000, 70, 1100, 513]
+    err = run_case(kind, lengths, [1] * 4, 8, 2, 64, window, torch.bfloat16, seed=31)
+    assert err < 2e-2, err
+    run_case(kind, lengths, [1] * 4, 4, 2, 128, window, torch.bfloat16, seed=32, crafted=True)
+
+
+def test_a_sequence_of_length_zero_reads_and_writes_nothing():
+    """A row whose length is zero is an empty sequence: its output is zero, and neither its neighbours'
+    results nor any page changes (the fused kernel stores no key for it)."""
+    from llmplayer_b200.kernels import ops
+    dev = "cuda:0"
+    H, G, hd = 8, 2, 64
+    lengths = [130, 0, 65]
+    _, pages, table = build_cache([130, 1, 65], G, hd, torch.bfloat16, seed=21)
+    g = torch.Generator().manual_seed(22)
+    qkv = torch.randn(3, (H + 2 * G) * hd, generator=g).to(dev)
+    table_d = table.to(dev)
+    kw = dict(num_heads=H, num_kv_heads=G, head_dim=hd, scale=hd ** -0.5, window=None)
+
+    def scratch(name, shape, dt):
+        return torch.full(shape, float("nan"), dtype=dt, device=dev)
+
+    def run(lens, shares):
+        p = pages.to(dev).clone()
+        out = torch.full((3, H * hd), 5.0, dtype=torch.bfloat16, device=dev)
+        counters = torch.zeros(ops.decode_groups(3, H, G), dtype=torch.int32, device=dev)
+        per = -(-table.shape[1] // shares)
+        ops.attention_decode_fused(qkv, ops.NO_ROTATION, out, p, table_d,
+                                   torch.tensor(lens, dtype=torch.int32, device=dev), scratch, counters,
+                                   write_kv=True, pages_per_split=per, num_splits=-(-table.shape[1] // per), **kw)
+        torch.cuda.synchronize()
+        return out, p
+
+    for shares in (1, 3):
+        with_empty, pages_empty = run(lengths, shares)
+        with_one, pages_one = run([130, 1, 65], shares)
+        assert torch.isfinite(with_empty.float()).all()
+        assert float(with_empty[1].float().abs().max()) == 0.0
+        assert torch.equal(with_empty[0], with_one[0]) and torch.equal(with_empty[2], with_one[2])
+        # only the page of the middle sequence may differ between the two runs, and with a length of zero
+        # it is exactly what it was
+        middle = int(table[1, 0])
+        assert torch.equal(pages_empty[middle], pages.to(dev)[middle])
+        others = [i for i in range(pages.shape[0]) if i != middle]
+        assert torch.equal(pages_empty[others], pages_one[others])
+    q = torch.randn(3, H * hd, generator=g).to(torch.bfloat16).to(dev)
+    out = torch.full_like(q, 5.0)
+    ops.attention_decode(q, out, pages.to(dev), table_d, torch.tensor(lengths, dtype=torch.int32, device=dev), scratch,
+                         pages_per_split=1, num_splits=table.shape[1], **kw)
+    torch.cuda.synchronize()
+    assert float(out[1].float().abs().max()) == 0.0 and torch.isfinite(out.float()).all()
+
+
+def test_shared_memory_grants_do_not_cross_between_head_sizes():
+    """Each kernel instantiation remembers its own grant of dynamic shared memory: a decode step at a head
+    size of 96 (which needs a large grant) must not make the kernel for heads of 64 skip asking for its own."""
+    for hd in (96, 64, 112, 128, 64):
+        for kind in ("decode", "fused"):
+            err = run_case(kind, [700, 65], [1, 1], 4, 2, hd, None, torch.bfloat16, seed=hd, shares=2)
+            assert err < 2e-2, (hd, kind, err)
+
+
 @pytest.mark.parametrize("kind", ["plain", "prefill", "decode"])
 @pytest.mark.parametrize("window", [None, 200])
 def test_a_far_key_among_hundreds_is_found(kind, window):
@@ -188,18 +287,19 @@ def test_fused_decode_equals_rotation_then_attention(H, G, hd, rd, pairing, wind
 
     pages_a = pages.to(dev).clone()
     q = torch.empty(B, H * hd, dtype=torch.bfloat16, device=dev)
-    ops.rope_cache_write(qkv, inv, positions, seq_ids, table_d, q, pages_a, rotary_dim=rd,
-                         interleaved=(pairing == "interleaved"), **kw)
+    rotation = ops.Rotation(inv, rd, pairing == "interleaved") if rd else ops.NO_ROTATION
+    ops.rope_cache_write(qkv, rotation, positions, seq_ids, table_d, q, pages_a, **kw)
     want = torch.zeros_like(q)
     ops.attention_decode(q, want, pages_a, table_d, kv_len, scratch, scale=hd ** -0.5, window=window,
                          pages_per_split=per, num_splits=n_splits, **kw)
 
     pages_b = pages.to(dev).clone()
     got = torch.full_like(q, 3.0)
+    counters = torch.zeros(ops.decode_groups(B, H, G), dtype=torch.int32, device=dev)
     for _ in range(2):                       # twice: the share counters must be back at zero
-        ops.attention_decode_fused(qkv, inv, got, pages_b, table_d, kv_len, scratch, rotary_dim=rd,
-                                   interleaved=(pairing == "interleaved"), write_kv=True, scale=hd ** -0.5,
-                                   window=window, pages_per_split=per, num_splits=n_splits, **kw)
+        ops.attention_decode_fused(qkv, rotation, got, pages_b, table_d, kv_len, scratch, counters, write_kv=True,
+                                   scale=hd ** -0.5, window=window, pages_per_split=per, num_splits=n_splits, **kw)
+    assert int(counters.abs().sum()) == 0
     torch.cuda.synchronize()
     assert torch.equal(pages_a, pages_b)                      # the same keys and values were stored
     assert float((got.float() - want.float()).abs().max()) <= 2e-2

@@ -125,12 +125,13 @@ def test_accumulate_with_the_following_norm(M, N, K):
     a = torch.randn(M, K, device=dev).to(torch.bfloat16)
     w = (torch.randn(N, K, device=dev) / K ** 0.5).to(torch.bfloat16)
     gain = (1 + 0.1 * torch.randn(N, device=dev))
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
     for _ in range(2):
         out0 = torch.randn(M, N, device=dev)
         out = out0.clone()
         normed = torch.full((M, N), 9.0, device=dev, dtype=torch.bfloat16)
         junk = torch.full((3000,), 4.0, device=dev)
-        ops.gemm(a, w, out, ops.ACCUMULATE, norm_after=(gain, 1e-5, normed, junk))
+        ops.gemm(a, w, out, ops.ACCUMULATE, norm_after=(gain, 1e-5, normed, junk, counter))
         torch.cuda.synchronize()
         ops.check_kernel_status()
         ref = reference(a, w, ops.ACCUMULATE, out0)

@@ -100,9 +100,8 @@ def test_rotation_and_cache_write(pairing, hd, rd):
     qkv = torch.randn(T, (H + 2 * G) * hd)
     q_out = torch.empty(T, H * hd, device=DEV)
     view = cache.view(0)
-    ops.rope_cache_write(qkv.to(DEV), rope.inv_freq, ctx2.positions, ctx2.seq_ids, ctx2.page_tables[0], q_out,
-                         view.pages, num_heads=H, num_kv_heads=G, head_dim=hd, rotary_dim=rd,
-                         interleaved=(pairing == "interleaved"))
+    ops.rope_cache_write(qkv.to(DEV), rope.rotation(), ctx2.positions, ctx2.seq_ids, ctx2.page_tables[0], q_out,
+                         view.pages, num_heads=H, num_kv_heads=G, head_dim=hd)
     pos = torch.tensor([5, 6, 7])
     inv = P.rope_inverse_frequencies(rd, 777.0)
     q_ref = P.rope_rotate(qkv[:, :H * hd].reshape(T, H, hd).double(), pos, inv, pairing)
@@ -277,8 +276,8 @@ def test_rotation_and_cache_write_of_a_long_prompt(hd, dtype):
     qkv = torch.randn(T, (H + 2 * G) * hd, generator=torch.Generator().manual_seed(hd))
     q_out = torch.empty(T, H * hd, device=DEV, dtype=dtype)
     view = cache.view(0)
-    ops.rope_cache_write(qkv.to(DEV), rope.inv_freq, ctx.positions, ctx.seq_ids, ctx.page_tables[0], q_out,
-                         view.pages, num_heads=H, num_kv_heads=G, head_dim=hd, rotary_dim=hd, interleaved=False)
+    ops.rope_cache_write(qkv.to(DEV), rope.rotation(), ctx.positions, ctx.seq_ids, ctx.page_tables[0], q_out,
+                         view.pages, num_heads=H, num_kv_heads=G, head_dim=hd)
     pos = torch.arange(T)
     inv = P.rope_inverse_frequencies(hd, 50000.0)
     q_ref = P.rope_rotate(qkv[:, :H * hd].reshape(T, H, hd).double(), pos, inv, "split_half")

@@ -118,22 +118,26 @@ def steps_batches(reqs, batch, prompt_frac=0.5):
     return steps
 
 
-CASES = [("A", [5, 9, 13, 40, 70]), ("B", [1, 7, 16, 30, 65, 129])]
+# tiny-D has heads of 64: its prompts of more than 64 tokens take the tcgen05 prompt attention, the request of
+# 600 tokens spans ten pages, and batches of 20 decode with the products' 32-token tiles
+CASES = [("A", [5, 9, 13, 40, 70], 3), ("B", [1, 7, 16, 30, 65, 129], 3),
+         ("D", [600, 130, 70, 33, 200, 66, 129, 90] + [3 + 5 * i for i in range(32)], 20)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,lengths", CASES)
-def test_replay_whole_tail_batches(tmp_path, name, lengths, dtype):
+@pytest.mark.parametrize("name,lengths,batch", CASES)
+def test_replay_whole_tail_batches(tmp_path, name, lengths, batch, dtype):
     model_dir = make_model(tmp_path, name, dtype=dtype)
     vocab = TINY[name][0]["vocab_size"]
     reqs = requests_for(name, lengths)
     longest = -(-max(lengths) // 64) * 64
+    by_need = sorted((-(-n // 64) * 64 for n in lengths), reverse=True)
     for what, steps, max_tokens in [
         ("whole", steps_whole(reqs), longest),
         ("tail32", steps_tail(reqs), longest),
-        # three requests at a time: the cache is sized for the largest batch only, so slots
+        # `batch` requests at a time: the cache is sized for the largest batch only, so slots
         # and pages of finished requests must be used again by the next batch
-        ("batches", steps_batches(reqs, 3), 3 * longest),
+        ("batches", steps_batches(reqs, batch), sum(by_need[:batch])),
     ]:
         out_dir = str(tmp_path / f"{what}_{dtype}")
         run_trace(model_dir, dtype, steps, out_dir, max_tokens)
