@@ -35,8 +35,19 @@ TINY_D = {
 }
 TINY = {"A": (TINY_A, 0, 0.02), "B": (TINY_B, 1, 0.05), "C": (TINY_C, 5, 0.08), "D": (TINY_D, 8, 0.06)}
 
-# Largest |engine - plain| allowed, as a fraction of the largest |plain| logit.
+# Largest |engine - plain| allowed, as a fraction of the largest |plain| logit. float32: 2e-5 everywhere. bfloat16:
+# the error grows with a model's depth and widths, so each configuration has its own bound, set to at most four
+# times the worst error that the comparisons of that configuration achieved on a B200 (tiny-A 1.8e-3, tiny-B 6.7e-3,
+# tiny-C 6.3e-3, tiny-D 9.0e-3, the toy architecture 5.2e-3, two layers at the Llama-3.2-1B widths 9.2e-3, two
+# layers 4096 / 14336 wide 1.2e-2); the session prints the achieved errors at its end (conftest.py).
 TOLERANCE = {"float32": 2e-5, "bfloat16": 4e-2}
+BFLOAT16_BOUND = {"A": 7e-3, "B": 2.5e-2, "C": 2.5e-2, "D": 3.5e-2, "toy": 2e-2, "1B": 3.5e-2, "wider": 4e-2}
+
+
+def tolerance(dtype, config=None):
+    if dtype == "float32":
+        return TOLERANCE["float32"]
+    return BFLOAT16_BOUND.get(config, TOLERANCE["bfloat16"])
 
 
 def make_model(tmp_path, name, dtype="bfloat16"):
@@ -82,5 +93,6 @@ def relative_error(got, ref):
     return float((got - ref).abs().max() / ref.abs().max())
 
 
-def assert_close(got, ref, dtype, what=""):
-    return check_error(f"model logits, {dtype}", what, relative_error(got, ref), TOLERANCE[dtype])
+def assert_close(got, ref, dtype, what="", config=None):
+    """``config``: which configuration's bfloat16 bound applies (a key of ``BFLOAT16_BOUND``)."""
+    return check_error(f"model logits, {dtype}", what, relative_error(got, ref), tolerance(dtype, config))

@@ -84,6 +84,6 @@ def test_the_engine_goes_on_after_a_step_whose_kernel_gave_up(tmp_path):
     eng.check()
     for i, q in enumerate(seqs):
         got = torch.stack([r[i] for r in rows])
-        assert_close(got, plain_logits(model_dir, q)[-3:], "bfloat16", f"after a kernel gave up, request {i}")
+        assert_close(got, plain_logits(model_dir, q)[-3:], "bfloat16", f"after a kernel gave up, request {i}", config="D")
     for s in slots:
         eng.release(s)

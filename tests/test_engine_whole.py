@@ -17,7 +17,7 @@ def test_whole_sequence(tmp_path, name, length, dtype):
     slot = eng.acquire()
     logits = eng.step([(slot, tokens)], [list(range(length))]).cpu()
     eng.release(slot)
-    assert_close(logits, plain_logits(model_dir, tokens), dtype, f"tiny-{name} whole")
+    assert_close(logits, plain_logits(model_dir, tokens), dtype, f"tiny-{name} whole", config=name)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -33,8 +33,8 @@ def test_long_decoding_and_first_tokens(tmp_path, dtype):
     eng.release(slot)
     got = torch.cat(rows)
     ref = plain_logits(model_dir, tokens)
-    assert_close(got[:4], ref[:4], dtype, "first tokens")
-    assert_close(got, ref, dtype, "long decoding")
+    assert_close(got[:4], ref[:4], dtype, "first tokens", config="C")
+    assert_close(got, ref, dtype, "long decoding", config="C")
 
 
 def test_steps_are_checked(tmp_path):
@@ -95,8 +95,8 @@ def test_full_width_layers_bfloat16_against_float32(tmp_path):
         torch.cuda.empty_cache()
     ref_whole, ref_tail = logits["float32"]
     assert torch.equal(ref_whole[3:], ref_tail)                       # float32: cutting into steps changes nothing
-    assert_close(logits["bfloat16"][0], ref_whole, "bfloat16", "1B widths, whole")
-    assert_close(logits["bfloat16"][1], ref_tail, "bfloat16", "1B widths, decoded")
+    assert_close(logits["bfloat16"][0], ref_whole, "bfloat16", "1B widths, whole", config="1B")
+    assert_close(logits["bfloat16"][1], ref_tail, "bfloat16", "1B widths, decoded", config="1B")
 
 
 @pytest.mark.parametrize("batch", [12, 20])
@@ -131,7 +131,7 @@ def test_full_width_decode_batches(tmp_path, batch):
         eng.close()
         del eng
         torch.cuda.empty_cache()
-    assert_close(got["bfloat16"], got["float32"], "bfloat16", f"1B widths, {batch} sequences")
+    assert_close(got["bfloat16"], got["float32"], "bfloat16", f"1B widths, {batch} sequences", config="1B")
 
 
 def test_wider_layers_with_heads_of_128(tmp_path):
@@ -166,7 +166,7 @@ def test_wider_layers_with_heads_of_128(tmp_path):
         del eng
         torch.cuda.empty_cache()
     for k in range(steps + 1):
-        assert_close(got["bfloat16"][k], got["float32"][k], "bfloat16", f"wider layers, step {k}")
+        assert_close(got["bfloat16"][k], got["float32"][k], "bfloat16", f"wider layers, step {k}", config="wider")
 
 
 @pytest.mark.parametrize("stored,dtype", [("float32", "bfloat16"), ("bfloat16", "float32")])
@@ -183,4 +183,4 @@ def test_stored_and_compute_dtypes_may_differ(tmp_path, stored, dtype):
     got = [eng.step([(slot, tokens[:40])], [list(range(40))]).cpu().clone()]
     got += [eng.step([(slot, [t])], [[0]]).cpu().clone() for t in tokens[40:]]
     eng.release(slot)
-    assert_close(torch.cat(got), plain_logits(model_dir, tokens), dtype, f"{stored} folder in {dtype}")
+    assert_close(torch.cat(got), plain_logits(model_dir, tokens), dtype, f"{stored} folder in {dtype}", config="B")

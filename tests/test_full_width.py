@@ -12,7 +12,7 @@ import pytest
 import torch
 
 import plain_llama as P
-from helpers import TOLERANCE, check_error, random_tokens, relative_error
+from helpers import check_error, random_tokens, relative_error, tolerance
 
 pytestmark = pytest.mark.gpu
 
@@ -49,7 +49,7 @@ class Checker:
 
     def check(self, tokens, rows, got, what):
         ref = P.forward(self.cfg, self.weights, tokens, dtype=torch.float64, rows=rows)
-        err = check_error(f"1B-width logits, {self.dtype}", what, relative_error(got, ref), TOLERANCE[self.dtype])
+        err = check_error(f"1B-width logits, {self.dtype}", what, relative_error(got, ref), tolerance(self.dtype, "1B"))
         self.worst = max(self.worst, err)
 
 

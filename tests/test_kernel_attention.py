@@ -8,6 +8,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 PAGE = 64
+# Largest |kernel - float64 attention| allowed in bfloat16, on outputs of order one: at most four times the worst
+# that each kernel achieved on a B200 (decode and fused decode 4.3e-3, prompt kernels 1.0e-2, plain kernel 7.8e-3).
+BOUND = {"decode": 1.5e-2, "fused": 1.5e-2, "prefill": 2e-2, "plain": 2e-2}
 
 
 def build_cache(lengths, G, hd, dtype, seed, extra_pages=5):
@@ -119,7 +122,7 @@ def run_case(kind, lengths, new, H, G, hd, window, dtype, seed=0, crafted=False,
     err = float((got - ref).abs().max())
     from helpers import record_error
     record_error(f"attention kernel ({kind}), {str(dtype).split('.')[-1]}", f"H{H} G{G} hd{hd} window {window}", err,
-                 2e-5 if dtype == torch.float32 else 2e-2)
+                 2e-5 if dtype == torch.float32 else BOUND.get(kind, 2e-2))
     if crafted:
         for b in range(len(lengths)):
             row = q_start[b + 1] - 1
@@ -147,7 +150,7 @@ def test_plain_attention(H, G, hd, window):
 def test_tensor_core_prefill(H, G, hd, window):
     """Heads of 64 with long runs of new tokens take the tcgen05 kernel, everything else mma.sync."""
     err = run_case("prefill", [1, 64, 65, 300, 129], [1, 64, 3, 150, 129], H, G, hd, window, torch.bfloat16)
-    assert err < 2e-2, err
+    assert err < BOUND["prefill"], err
 
 
 @pytest.mark.parametrize("H,G", [(32, 8), (20, 1), (3, 3)])
@@ -158,7 +161,7 @@ def test_both_prefill_kernels_at_head_size_64(H, G, window, tcgen05, monkeypatch
     monkeypatch.setattr(ops, "tcgen05_attention", tcgen05)
     lengths, new = [700, 128, 129, 391, 65], [700, 128, 100, 130, 65]        # whole prompts and continued ones
     err = run_case("prefill", lengths, new, H, G, 64, window, torch.bfloat16, seed=7)
-    assert err < 2e-2, err
+    assert err < BOUND["prefill"], err
     run_case("prefill", [900, 333], [200, 70], H, G, 64, window, torch.bfloat16, seed=3, crafted=True)
 
 
@@ -167,7 +170,7 @@ def test_both_prefill_kernels_at_head_size_64(H, G, window, tcgen05, monkeypatch
 def test_tensor_core_decode(H, G, hd, window):
     lengths = [1, 64, 65, 700, 129, 17]
     err = run_case("decode", lengths, [1] * len(lengths), H, G, hd, window, torch.bfloat16)
-    assert err < 2e-2, err
+    assert err < BOUND["decode"], err
 
 
 @pytest.mark.parametrize("kind", ["decode", "fused"])
@@ -179,9 +182,9 @@ def test_decode_in_several_shares_against_float64(kind, shares, window):
     attention (not with another entry point of the same kernel), random and with one far key made to win."""
     lengths = [1, 64, 65, 700, 129, 17, 641]
     err = run_case(kind, lengths, [1] * len(lengths), 8, 2, 64, window, torch.bfloat16, seed=11, shares=shares)
-    assert err < 2e-2, err
+    assert err < BOUND[kind], err
     err = run_case(kind, lengths, [1] * len(lengths), 6, 3, 48, window, torch.bfloat16, seed=12, shares=shares)
-    assert err < 2e-2, err
+    assert err < BOUND[kind], err
     run_case(kind, [900, 333, 70], [1, 1, 1], 8, 2, 64, window, torch.bfloat16, seed=3, crafted=True, shares=shares)
 
 
@@ -192,7 +195,7 @@ def test_shares_fitted_to_each_sequence(kind, window):
     window) gives pages for: here four, two, one and one shares in one grid, some CTAs with nothing to do."""
     lengths = [2000, 70, 1100, 513]
     err = run_case(kind, lengths, [1] * 4, 8, 2, 64, window, torch.bfloat16, seed=31)
-    assert err < 2e-2, err
+    assert err < BOUND[kind], err
     run_case(kind, lengths, [1] * 4, 4, 2, 128, window, torch.bfloat16, seed=32, crafted=True)
 
 
@@ -249,7 +252,7 @@ def test_shared_memory_grants_do_not_cross_between_head_sizes():
     for hd in (96, 64, 112, 128, 64):
         for kind in ("decode", "fused"):
             err = run_case(kind, [700, 65], [1, 1], 4, 2, hd, None, torch.bfloat16, seed=hd, shares=2)
-            assert err < 2e-2, (hd, kind, err)
+            assert err < BOUND[kind], (hd, kind, err)
 
 
 @pytest.mark.parametrize("kind", ["plain", "prefill", "decode"])

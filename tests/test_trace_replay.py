@@ -66,11 +66,11 @@ def collect(out_dir, steps, vocab):
     return got
 
 
-def check_all(got, reqs, model_dir, dtype, what):
+def check_all(got, reqs, model_dir, dtype, what, config):
     for rid, toks in reqs.items():
         ref = plain_logits(model_dir, toks)
         have = torch.stack([got[rid][p] for p in range(len(toks))])
-        assert_close(have, ref, dtype, f"{what} request {rid}")
+        assert_close(have, ref, dtype, f"{what} request {rid}", config=config)
 
 
 def steps_whole(reqs):
@@ -141,7 +141,7 @@ def test_replay_whole_tail_batches(tmp_path, name, lengths, batch, dtype):
     ]:
         out_dir = str(tmp_path / f"{what}_{dtype}")
         run_trace(model_dir, dtype, steps, out_dir, max_tokens)
-        check_all(collect(out_dir, steps, vocab), reqs, model_dir, dtype, f"tiny-{name} {what}")
+        check_all(collect(out_dir, steps, vocab), reqs, model_dir, dtype, f"tiny-{name} {what}", name)
 
 
 def test_replay_without_wanted_rows_writes_no_file(tmp_path):
