@@ -677,8 +677,8 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
     B = kv_len.numel()
     if q_start.numel() != B + 1 or page_table.shape[0] != B:
         raise KernelError(f"attention_prefill: {B} sequences, {q_start.numel()} offsets, table {tuple(page_table.shape)}")
-    if head_dim == 64 and max_new > 64 and tcgen05_attention:
-        # long runs of new tokens with heads of 64: scores and P V on the tcgen05 tensor cores
+    if head_dim in (64, 128) and max_new > 64 and tcgen05_attention:
+        # long runs of new tokens with heads of 64 or 128: scores and P V on the tcgen05 tensor cores
         lib = library("attention_tcgen05")
         _check(lib, lib.lp_attention_prefill_tc(
             q.data_ptr(), out.data_ptr(), pages.data_ptr(), pages.shape[0], page_table.data_ptr(),

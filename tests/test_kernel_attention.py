@@ -153,16 +153,46 @@ def test_tensor_core_prefill(H, G, hd, window):
     assert err < BOUND["prefill"], err
 
 
-@pytest.mark.parametrize("H,G", [(32, 8), (20, 1), (3, 3)])
+@pytest.mark.parametrize("H,G,hd", [(32, 8, 64), (20, 1, 64), (3, 3, 64), (8, 2, 128), (24, 8, 128), (5, 5, 128)])
 @pytest.mark.parametrize("window", [None, 70, 200])
 @pytest.mark.parametrize("tcgen05", [True, False])
-def test_both_prefill_kernels_at_head_size_64(H, G, window, tcgen05, monkeypatch):
+def test_both_prefill_kernels_at_head_sizes_64_and_128(H, G, hd, window, tcgen05, monkeypatch):
     from llmplayer_b200.kernels import ops
     monkeypatch.setattr(ops, "tcgen05_attention", tcgen05)
     lengths, new = [700, 128, 129, 391, 65], [700, 128, 100, 130, 65]        # whole prompts and continued ones
-    err = run_case("prefill", lengths, new, H, G, 64, window, torch.bfloat16, seed=7)
+    err = run_case("prefill", lengths, new, H, G, hd, window, torch.bfloat16, seed=7)
     assert err < BOUND["prefill"], err
-    run_case("prefill", [900, 333], [200, 70], H, G, 64, window, torch.bfloat16, seed=3, crafted=True)
+    run_case("prefill", [900, 333], [200, 70], H, G, hd, window, torch.bfloat16, seed=3, crafted=True)
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_prefill_whose_maximum_keeps_growing(hd):
+    """The tcgen05 prompt kernel keeps a reference maximum per row that moves only when the row's true maximum
+    has outgrown it by a factor of 256; here every later page holds a key that beats all earlier ones by far more
+    (and by less, in alternation), so the output in tensor memory is brought down again and again."""
+    from llmplayer_b200.kernels import ops
+    dev = "cuda:0"
+    H, G, n = 4, 2, 640
+    dense, pages, table = build_cache([n], G, hd, torch.bfloat16, seed=5)
+    k, v = dense[0]
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn(n, H, hd, generator=g).to(torch.bfloat16)
+    q[:, :, 0] = 4.0
+    for page in range(n // PAGE):                      # one key per page whose score grows page by page
+        at = page * PAGE + 17
+        k[at] = 0
+        k[at, :, 0] = (1.5 if page % 2 else 6.0) * (page + 1)
+        pages[table[0, page], 0, :, 17] = k[at]
+    ref = reference(q, k, v, torch.arange(n), 1.0 / math.sqrt(hd), None)
+    qd = q.reshape(n, H * hd).to(dev)
+    out = torch.zeros_like(qd)
+    ops.attention_prefill(qd, out, pages.to(dev), table.to(dev), torch.tensor([0, n], dtype=torch.int32, device=dev),
+                          torch.tensor([n], dtype=torch.int32, device=dev), n, num_heads=H, num_kv_heads=G, head_dim=hd,
+                          scale=1.0 / math.sqrt(hd), window=None)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    err = float((out.reshape(n, H, hd).double().cpu() - ref).abs().max())
+    assert err < BOUND["prefill"], err
 
 
 @pytest.mark.parametrize("H,G,hd", GEOMETRIES)

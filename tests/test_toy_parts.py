@@ -287,8 +287,8 @@ def make_more_toys():
             return None
 
         def apply(self, ctx, qkv, *, num_heads, num_kv_heads, head_dim):
-            factor = torch.pow(torch.tensor(self.spec.theta, device=qkv.device),
-                               ctx.positions.to(torch.float32) / float(self.spec.rotary_dim))[:, None]
+            # base^(position / span) from device tensors and host scalars only (nothing is copied: capturable)
+            factor = torch.exp2(ctx.positions.to(torch.float32) * (math.log2(self.spec.theta) / self.spec.rotary_dim))[:, None]
             nq = num_heads * head_dim
             qkv[:, :nq] *= factor
             if num_kv_heads:
@@ -296,7 +296,10 @@ def make_more_toys():
 
     class RoutedFeedForward(Part):
         """Each token goes to the one expert with the largest router logit (float32) and gets that expert's gated
-        feed-forward, weighted by the softmax probability of the choice. Plain torch on the device: a toy."""
+        feed-forward, weighted by the softmax probability of the choice. Plain torch on the device: a toy, which
+        runs every expert over every token and keeps the chosen one's result (no shape depends on the routing,
+        so a step can be captured)."""
+        capture_safe = True
 
         def __init__(self, spec):
             self.spec = spec
@@ -320,12 +323,9 @@ def make_more_toys():
             weight, expert = prob.max(dim=-1)
             F, d = s.intermediate_size, s.hidden_size
             for e in range(s.num_experts):
-                rows = torch.nonzero(expert == e).flatten()
-                if rows.numel() == 0:
-                    continue
-                xe = x[rows]
-                h = torch.nn.functional.silu(xe @ w["gate"][e * F:(e + 1) * F].T) * (xe @ w["up"][e * F:(e + 1) * F].T)
-                residual[rows] += weight[rows, None] * (h @ w["down"][e * d:(e + 1) * d].T)
+                h = torch.nn.functional.silu(x @ w["gate"][e * F:(e + 1) * F].T) * (x @ w["up"][e * F:(e + 1) * F].T)
+                chosen = (weight * (expert == e))[:, None]
+                residual += chosen * (h @ w["down"][e * d:(e + 1) * d].T)
 
     class DeviceDecayMixer(Part):
         """The decay mixer again, but a step of one token per sequence finds its rows of the state through
