@@ -740,10 +740,7 @@ template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                        void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int feat_tiles,
-                       int num_tiles, int group_tok, int tile_tok, int* __restrict__ status) {
-    // tile_tok: tokens per tile, a multiple of 16 up to BLOCK_TOK (BLOCK_TOK itself in the form with tokens as M):
-    // the launcher picks the width whose tiles fill whole waves of CTAs best. The stages and the accumulators keep
-    // the room of the widest tile.
+                       int num_tiles, int group_tok, int* __restrict__ status) {
     using T = PersistentTile<BLOCK_TOK, MODE>;
     // Tiles are numbered in bands of `group_tok` token tiles, token tile first within a band: the CTAs that run
     // at the same time then share a few weight tiles and a few activation tiles, which stay in L2 (feature
@@ -798,9 +795,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     const int s = it % T::STAGES;
                     if (!mbar_wait(&empty[s], ((it / T::STAGES) & 1) ^ 1)) { atomicExch(status, 21); *failed = 1; ok = false; break; }
                     uint8_t* stage = smem + s * T::STAGE_BYTES;
-                    mbar_expect_tx(&full[s], T::W_TILES * T::W_BYTES + tile_tok * BLOCK_K * 2);
+                    mbar_expect_tx(&full[s], T::STAGE_BYTES);
                     load_weights<MODE>(stage, &map_w, kb * BLOCK_K, ft, &full[s]);
-                    tma_load_2d(stage + T::W_TILES * T::W_BYTES, &map_x, kb * BLOCK_K, tt * tile_tok, &full[s]);
+                    tma_load_2d(stage + T::W_TILES * T::W_BYTES, &map_x, kb * BLOCK_K, tt * BLOCK_TOK, &full[s]);
                 }
             }
             if (!ok) {
@@ -812,9 +809,9 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         // ------------------------------------------------------------ MMA issuer: alternating accumulators
         if (lane == 0) {
             // TOKM: M = 128 tokens (A = the activation tile), N = 256 weight rows (B = the weight tile)
-            const uint32_t idesc = T::TOKM
+            constexpr uint32_t idesc = T::TOKM
                 ? ((1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24))
-                : ((1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(tile_tok >> 3) << 17) |
+                : ((1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_TOK >> 3) << 17) |
                    ((uint32_t)(BLOCK_FEAT >> 4) << 24));
             int it = 0, j = 0;
             bool ok = true;
@@ -863,7 +860,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 // lanes are tokens; columns 0..63 gate, 64..127 up of features 128 ft .. + 63, columns 128..255 the
                 // same for the next 64 features: a thread forms 32 outputs of its token at a time
                 const uint32_t lane_addr = tmem_base + ab * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-                const int t = tt * tile_tok + quarter * 32 + lane;
+                const int t = tt * BLOCK_TOK + quarter * 32 + lane;
 #pragma unroll 1
                 for (int part = 0; part < 4; ++part) {
                     const int half = part >> 1, c0 = (part & 1) * 32;
@@ -905,20 +902,18 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             } else if (go) {
                 const uint32_t lane_addr = tmem_base + ab * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
                 const int f = ft * BLOCK_FEAT + quarter * 32 + lane;
-                const int tok0 = tt * tile_tok;
+                const int tok0 = tt * BLOCK_TOK;
 #pragma unroll 1
-                for (int c0 = 0; c0 < tile_tok; c0 += CHUNK) {
+                for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
                     uint32_t g[CHUNK], u[MODE == LP_GEMM_SWIGLU_WIDE ? CHUNK : 1];
-                    // the last chunk of a tile whose width is an odd multiple of 16 has 16 columns
-                    const int width = min(CHUNK, tile_tok - c0);
-                    if (width == CHUNK) tmem_ld32(lane_addr + c0, g); else tmem_ld16(lane_addr + c0, g);
+                    tmem_ld32(lane_addr + c0, g);
                     if (MODE == LP_GEMM_SWIGLU_WIDE) tmem_ld32(lane_addr + BLOCK_TOK + c0, u);
                     tmem_ld_wait();
                     if (f < features) {
 #pragma unroll
                         for (int jj = 0; jj < CHUNK; ++jj) {
                             const int t = tok0 + c0 + jj;
-                            if (t >= tokens || jj >= width) break;
+                            if (t >= tokens) break;
                             float v = __uint_as_float(g[jj]);
                             if (MODE == LP_GEMM_SWIGLU_WIDE) v = __fdividef(v, 1.0f + __expf(-v)) * __uint_as_float(u[jj]);
                             const size_t at = (size_t)t * ldc + f;
@@ -944,8 +939,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 }
 
 template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
-int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const void* x_base, int x_cols, int ldx, void* out,
-                      int tokens, int features, int ldc, int k_blocks, int* status, cudaStream_t stream) {
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc,
+                      int k_blocks, int* status, cudaStream_t stream) {
     using T = PersistentTile<BLOCK_TOK, MODE>;
     auto kernel = gemm_persistent_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC>;
     static bool configured = false;
@@ -957,21 +952,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const void* 
     }
     const int sms = lp_sm_count();
     const int feat_tiles = (features + BLOCK_FEAT - 1) / BLOCK_FEAT;
-    // The width of a token tile: with one CTA per SM a product takes as many waves as its tiles need, each as
-    // long as a tile is wide, so the width (a multiple of 16, from half the widest up) with the smallest
-    // waves x width wins; a little is added per wave for what every tile costs beside its MMAs. (2,048 tokens,
-    // 3,072 features: 192 tiles of 256 tokens take two waves of 256; 264 tiles of 192 tokens two waves of 192.)
-    int tile_tok = BLOCK_TOK;
-    if (!T::TOKM && MODE != LP_GEMM_SWIGLU_WIDE) {
-        long long best = -1;
-        for (int w = BLOCK_TOK; w >= BLOCK_TOK / 2; w -= 16) {
-            const long long tiles = (long long)feat_tiles * ((tokens + w - 1) / w);
-            const long long waves = (tiles + sms - 1) / sms;
-            const long long cost = waves * (w + 12);
-            if (best < 0 || cost < best) { best = cost; tile_tok = w; }
-        }
-    }
-    const int tok_tiles = (tokens + tile_tok - 1) / tile_tok;
+    const int tok_tiles = (tokens + BLOCK_TOK - 1) / BLOCK_TOK;
     const int num_tiles = feat_tiles * tok_tiles;
     const int grid = num_tiles < sms ? num_tiles : sms;
     // how many token tiles a band has: the CTAs of one wave should touch as few distinct rows of X and W as possible
@@ -980,17 +961,11 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const void* 
     long long best = -1;
     for (int gt = 1; gt <= tok_tiles; ++gt) {
         const int gf = (grid + gt - 1) / gt;
-        const long long cost = (long long)gt * tile_tok + (long long)(gf < feat_tiles ? gf : feat_tiles) * w_rows;
+        const long long cost = (long long)gt * BLOCK_TOK + (long long)(gf < feat_tiles ? gf : feat_tiles) * w_rows;
         if (best < 0 || cost <= best) { best = cost; group_tok = gt; }       // ties: the larger band
     }
-    // the activation tiles come as boxes of tile_tok rows
-    CUtensorMap mx_tile = mx;
-    if (tile_tok != BLOCK_TOK) {
-        int rc = make_map(&mx_tile, x_base, tokens, x_cols, ldx, tile_tok);
-        if (rc) return rc;
-    }
-    cudaError_t err = lp_launch(kernel, dim3(grid), THREADS, T::SMEM_BYTES, stream, mw, mx_tile, out, tokens, features,
-                                ldc, k_blocks, feat_tiles, num_tiles, group_tok, tile_tok, status);
+    cudaError_t err = lp_launch(kernel, dim3(grid), THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
+                                k_blocks, feat_tiles, num_tiles, group_tok, status);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_persistent: %s", cudaGetErrorString(err));
         return (int)err;
@@ -1096,13 +1071,13 @@ extern "C" int lp_gemm_persistent(const void* X, const void* W, void* out, int o
     if (rc) return rc;
     const bool bf = out_dtype == LP_BF16;
     if (gated) {
-        if (bf) return launch_persistent<128, LP_GEMM_SWIGLU_TOKM, true, false>(mw, mx, X, K, ldx, out, tokens, features, ldc, k_blocks, status, stream);
-        return launch_persistent<128, LP_GEMM_SWIGLU_TOKM, false, false>(mw, mx, X, K, ldx, out, tokens, features, ldc, k_blocks, status, stream);
+        if (bf) return launch_persistent<128, LP_GEMM_SWIGLU_TOKM, true, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+        return launch_persistent<128, LP_GEMM_SWIGLU_TOKM, false, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
     }
     if (mode == LP_GEMM_ACCUMULATE)
-        return launch_persistent<256, LP_GEMM_STORE, false, true>(mw, mx, X, K, ldx, out, tokens, features, ldc, k_blocks, status, stream);
-    if (bf) return launch_persistent<256, LP_GEMM_STORE, true, false>(mw, mx, X, K, ldx, out, tokens, features, ldc, k_blocks, status, stream);
-    return launch_persistent<256, LP_GEMM_STORE, false, false>(mw, mx, X, K, ldx, out, tokens, features, ldc, k_blocks, status, stream);
+        return launch_persistent<256, LP_GEMM_STORE, false, true>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+    if (bf) return launch_persistent<256, LP_GEMM_STORE, true, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+    return launch_persistent<256, LP_GEMM_STORE, false, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
 }
 
 // norm_weight (optional, ACCUMULATE only, ldc == features): after the sums are complete, the last CTA writes

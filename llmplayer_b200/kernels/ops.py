@@ -496,17 +496,17 @@ PERSISTENT_MIN_TOKENS = 512
 
 
 def _persistent_pays(tokens: int, features: int, k: int, mode: int) -> bool:
-    """Whether the persistent form (one CTA per SM walking tiles of 128 features x up to 256 tokens, whose width it
-    fits to whole waves; 128 tokens x 128 features x 2 when gated) takes no longer than separate CTAs of 128 x 128
-    tiles, two to an SM. Both are counted in columns of MMA work per SM: waves x tile width."""
-    sms = num_sms()
+    """Whether the persistent form (one CTA per SM walking 128 x 256 tiles, 128 x 128 x 2 when gated)
+    fills the SMs at least as well as separate CTAs of 128 x 128 tiles, two to an SM."""
     feat_tiles = -(-features // 128)
-    if mode == SWIGLU:
-        persistent = -(-(feat_tiles * -(-tokens // 128)) // sms) * 256
-    else:
-        persistent = min(-(-(feat_tiles * -(-tokens // w)) // sms) * (w + 12) for w in range(256, 127, -16))
-    separate = -(-(feat_tiles * -(-tokens // 128)) // (2 * sms)) * 256
-    return persistent <= separate + 12
+    persistent_tiles = feat_tiles * -(-tokens // (128 if mode == SWIGLU else 256))
+    separate_ctas = feat_tiles * -(-tokens // 128)
+    sms = num_sms()
+    fill_p = persistent_tiles / (-(-persistent_tiles // sms) * sms)
+    fill_s = separate_ctas / (-(-separate_ctas // (2 * sms)) * 2 * sms)
+    # at equal fill the persistent form wins when the SMs are well filled (its tiles are twice as large and one
+    # tile's epilogue hides under the next one's MMAs) or the K loop is long
+    return fill_p > fill_s + 0.02 or (fill_p >= fill_s and (fill_p >= 0.8 or k >= 4096))
 
 
 def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, block_tok: int = 0,
