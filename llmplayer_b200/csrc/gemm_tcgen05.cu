@@ -147,9 +147,13 @@ struct Tile {
     // (prompts) take the whole shared memory for a deeper ring
     static constexpr int BUDGET = BLOCK_TOK <= 128 ? 110 * 1024 : 196 * 1024;
     static constexpr int STAGES = (BUDGET / STAGE_BYTES) > 8 ? 8 : (BUDGET / STAGE_BYTES);
+    // a CTA that has an SM to itself (a grid of no more CTAs than SMs) may take a deeper ring: streaming weights
+    // for a few dozen tokens is bound by how many bytes an SM has in flight
+    static constexpr int STAGES_ALONE = ((196 * 1024) / STAGE_BYTES) > 8 ? 8 : ((196 * 1024) / STAGE_BYTES);
+    static constexpr int TAIL_BYTES = 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr int ACC_COLS = BLOCK_TOK * W_TILES;
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;       // power of two by construction
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TAIL_BYTES;
 };
 
 // out: [tokens, ldc]; OUT_BF16 selects the element type of a STORE / SWIGLU output.
@@ -157,16 +161,16 @@ template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
-                    int withheld_kblock, int* __restrict__ status, NormAfter norm) {
+                    int withheld_kblock, int num_stages, int* __restrict__ status, NormAfter norm) {
     // withheld_kblock >= 0 (tests of the bounded waits only, see lp_gemm_withhold_next): the loader never brings
     // that k-block, so the waits for it run out, the roles report through *status and the CTA winds down.
     using T = Tile<BLOCK_TOK, MODE>;
     const uint32_t wait_limit = withheld_kblock >= 0 ? (1u << 14) : SPIN_LIMIT;     // a test need not wait long
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full = (uint64_t*)(smem + T::STAGES * T::STAGE_BYTES);
-    uint64_t* empty = full + T::STAGES;
-    uint64_t* acc_ready = empty + T::STAGES;
+    uint64_t* full = (uint64_t*)(smem + num_stages * T::STAGE_BYTES);
+    uint64_t* empty = full + num_stages;
+    uint64_t* acc_ready = empty + num_stages;
     uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
     volatile uint32_t* failed = tmem_slot + 1;     // set by a role whose wait ran out; read by the epilogue
 
@@ -183,7 +187,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         *failed = 0;
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-        for (int s = 0; s < T::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < num_stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_ready, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -204,7 +208,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             bool ok = true;
             // Weights are written by no kernel of a step: the first ring of weight tiles is requested
             // before waiting for the previous kernel, the activation tiles only after it.
-            const int early = min(nkb, T::STAGES);
+            const int early = min(nkb, num_stages);
             for (int i = 0; i < early; ++i) {
                 if (kb_begin + i == withheld_kblock) continue;
                 uint8_t* stage = smem + i * T::STAGE_BYTES;
@@ -220,8 +224,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             }
             issued = early;
             for (int i = early; i < nkb && ok; ++i) {
-                const int s = i % T::STAGES;
-                const uint32_t phase = (i / T::STAGES) & 1;
+                const int s = i % num_stages;
+                const uint32_t phase = (i / num_stages) & 1;
                 if (!mbar_wait(&empty[s], phase ^ 1, wait_limit)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
                 issued = i + 1;
                 if (kb_begin + i == withheld_kblock) continue;
@@ -234,8 +238,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             if (!ok || *failed) {
                 // consumers may be gone: await the copies still in flight before the CTA's memory is released
                 // (a withheld k-block has no copy in flight and is not waited for)
-                for (int i = max(0, issued - T::STAGES); i < issued; ++i)
-                    if (kb_begin + i != withheld_kblock) mbar_wait(&full[i % T::STAGES], (i / T::STAGES) & 1, wait_limit);
+                for (int i = max(0, issued - num_stages); i < issued; ++i)
+                    if (kb_begin + i != withheld_kblock) mbar_wait(&full[i % num_stages], (i / num_stages) & 1, wait_limit);
             }
         }
         __syncwarp();
@@ -246,8 +250,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                                        ((uint32_t)(BLOCK_FEAT >> 4) << 24);
             bool ok = true;
             for (int i = 0; i < nkb; ++i) {
-                const int s = i % T::STAGES;
-                const uint32_t phase = (i / T::STAGES) & 1;
+                const int s = i % num_stages;
+                const uint32_t phase = (i / num_stages) & 1;
                 if (!mbar_wait(&full[s], phase, wait_limit)) { atomicExch(status, 2); *failed = 1; ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t w_addr = smem_u32(smem + s * T::STAGE_BYTES);
@@ -648,9 +652,9 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 // Settings of the few-token product (lp_gemm_configure; until that is called, the environment's
 // LLMPLAYER_B200_FEWTOK / _RING_SHARED / _RING_ALONE or the defaults 1 / 6 / 10).
-struct FewSettings { int enabled, ring_shared, ring_alone; bool decided; };
+struct FewSettings { int enabled, ring_shared, ring_alone, ring_alone_tile; bool decided; };
 static FewSettings& few_settings() {
-    static FewSettings st = {1, 6, 10, false};
+    static FewSettings st = {1, 6, 10, 0, false};
     if (!st.decided) {
         const char* v = getenv("LLMPLAYER_B200_FEWTOK");
         st.enabled = (v && v[0] == '0') ? 0 : 1;
@@ -660,6 +664,8 @@ static FewSettings& few_settings() {
         st.ring_shared = v ? atoi(v) : 6;
         if (st.ring_alone < 2) st.ring_alone = 2;
         if (st.ring_shared < 2) st.ring_shared = 2;
+        v = getenv("LLMPLAYER_B200_RING_ALONE_TILE");
+        st.ring_alone_tile = v ? atoi(v) : 0;
         st.decided = true;
     }
     return st;
@@ -986,17 +992,28 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
     auto kernel = gemm_tcgen05_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::SMEM_BYTES);
-        if (e != cudaSuccess) LP_REFUSE("gemm: cannot reserve %d bytes of shared memory: %s", T::SMEM_BYTES,
-                                        cudaGetErrorString(e));
+        const int most = T::STAGES_ALONE * T::STAGE_BYTES + T::TAIL_BYTES;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        if (e != cudaSuccess) LP_REFUSE("gemm: cannot reserve %d bytes of shared memory: %s", most, cudaGetErrorString(e));
         configured = true;
     }
     const int per_split = (k_blocks + splits - 1) / splits;
     const int grid_z = (k_blocks + per_split - 1) / per_split;
     const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;     // output features per CTA
     dim3 grid((features + per_cta - 1) / per_cta, (tokens + BLOCK_TOK - 1) / BLOCK_TOK, grid_z);
-    cudaError_t err = lp_launch(kernel, grid, THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
-                                k_blocks, per_split, withheld, status, norm);
+    // the ring: what lets two CTAs share an SM, or, for a grid of at most one CTA per SM and when lp_gemm_configure's
+    // ring_alone_tile allows it, up to the whole shared memory. Off by default: measured at the 1B shape, batches of
+    // 32 / 64, a ring of 8 stages gave 1.101 / 1.340 ms per step against 1.078 / 1.320 with the shared ring (the
+    // next kernel's CTAs can no longer start beside a CTA that holds the whole shared memory)
+    int stages = T::STAGES;
+    const bool alone = (long long)grid.x * grid.y * grid.z <= lp_sm_count();
+    if (alone && few_settings().ring_alone_tile > stages) {
+        stages = few_settings().ring_alone_tile < T::STAGES_ALONE ? few_settings().ring_alone_tile : T::STAGES_ALONE;
+        if (stages > per_split) stages = per_split > T::STAGES ? per_split : T::STAGES;
+    }
+    const int smem = stages * T::STAGE_BYTES + T::TAIL_BYTES;
+    cudaError_t err = lp_launch(kernel, grid, THREADS, smem, stream, mw, mx, out, tokens, features, ldc,
+                                k_blocks, per_split, withheld, stages, status, norm);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_tcgen05: %s", cudaGetErrorString(err));
         return (int)err;
@@ -1036,12 +1053,15 @@ extern "C" int lp_gemm_withhold_next(int kblock) {
 }
 
 // fewtok: whether lp_gemm_tcgen05 hands 16-token tiles to the few-token kernel; ring_shared / ring_alone: stages of
-// that kernel's ring when two CTAs share an SM / when a CTA has an SM to itself (at least 2 each).
-extern "C" int lp_gemm_configure(int fewtok, int ring_shared, int ring_alone) {
+// that kernel's ring when two CTAs share an SM / when a CTA has an SM to itself (at least 2 each); ring_alone_tile:
+// the most stages the one-tile tcgen05 kernel takes when its grid has no more CTAs than there are SMs (0: never
+// more than what lets two CTAs share an SM).
+extern "C" int lp_gemm_configure(int fewtok, int ring_shared, int ring_alone, int ring_alone_tile) {
     FewSettings& st = few_settings();
     st.enabled = fewtok ? 1 : 0;
     st.ring_shared = ring_shared < 2 ? 2 : ring_shared;
     st.ring_alone = ring_alone < 2 ? 2 : ring_alone;
+    st.ring_alone_tile = ring_alone_tile;
     return 0;
 }
 

@@ -38,6 +38,7 @@ class EngineOptions:
     fewtok_kernel: Optional[bool] = None
     ring_shared: Optional[int] = None
     ring_alone: Optional[int] = None
+    ring_alone_tile: Optional[int] = None
 
     def __post_init__(self):
         if self.dtype not in ("bfloat16", "float32"):
@@ -52,7 +53,8 @@ class EngineOptions:
             raise ConfigError(f"max_batch must be positive, got {self.max_batch}")
 
     def kernel_settings(self) -> dict:
-        return {name: getattr(self, name) for name in ("pdl", "few_tokens", "fewtok_kernel", "ring_shared", "ring_alone")
+        return {name: getattr(self, name) for name in ("pdl", "few_tokens", "fewtok_kernel", "ring_shared", "ring_alone",
+                                                          "ring_alone_tile")
                 if getattr(self, name) is not None}
 
     def with_changes(self, **changes) -> "EngineOptions":

@@ -39,7 +39,7 @@ _SIGNATURES = {
                             ctypes.c_longlong, _P, _P],
         "lp_gemm_persistent": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "lp_gemm_fewtok": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _I, _P],
-        "lp_gemm_configure": [_I, _I, _I],
+        "lp_gemm_configure": [_I, _I, _I, _I],
     },
     "attention_mma": {
         "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -85,19 +85,23 @@ class KernelSettings:
     ``pdl``: programmatic dependent launch between the kernels of a step. ``few_tokens``: up to how many tokens
     the parts put the RMS norm inside the consuming product and use the few-token kernel. ``fewtok_kernel``:
     whether 16-token tiles of the general product go to the mma.sync few-token kernel. ``ring_shared`` /
-    ``ring_alone``: stages of that kernel's ring when two CTAs share an SM / when a CTA has one to itself."""
+    ``ring_alone``: stages of that kernel's ring when two CTAs share an SM / when a CTA has one to itself.
+    ``ring_alone_tile``: the most stages the one-tile tcgen05 product takes when its grid has no more CTAs than SMs
+    (0, the default: never more than what lets two CTAs share an SM; a deeper ring measured slower)."""
     pdl: bool = True
     few_tokens: int = 16
     fewtok_kernel: bool = True
     ring_shared: int = 6
     ring_alone: int = 10
+    ring_alone_tile: int = 0
 
     @classmethod
     def from_env(cls) -> "KernelSettings":
         return cls(pdl=_env_int("LLMPLAYER_B200_PDL", 1) != 0, few_tokens=_env_int("LLMPLAYER_B200_FEW_TOKENS", 16),
                    fewtok_kernel=_env_int("LLMPLAYER_B200_FEWTOK", 1) != 0,
                    ring_shared=_env_int("LLMPLAYER_B200_RING_SHARED", 6),
-                   ring_alone=_env_int("LLMPLAYER_B200_RING_ALONE", 10))
+                   ring_alone=_env_int("LLMPLAYER_B200_RING_ALONE", 10),
+                   ring_alone_tile=_env_int("LLMPLAYER_B200_RING_ALONE_TILE", 0))
 
 
 settings = KernelSettings.from_env()
@@ -108,7 +112,8 @@ def _apply_settings(name: str, lib: ctypes.CDLL) -> None:
     lib.lp_set_pdl.restype = None
     lib.lp_set_pdl(1 if settings.pdl else 0)
     if name == "gemm_tcgen05":
-        lib.lp_gemm_configure(1 if settings.fewtok_kernel else 0, int(settings.ring_shared), int(settings.ring_alone))
+        lib.lp_gemm_configure(1 if settings.fewtok_kernel else 0, int(settings.ring_shared), int(settings.ring_alone),
+                              int(settings.ring_alone_tile))
 
 
 def configure(**changes) -> KernelSettings:

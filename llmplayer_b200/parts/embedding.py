@@ -57,6 +57,13 @@ class LinearHead(Part):
 
     def forward(self, ctx, residual: torch.Tensor, rows: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
         """logits[i] = head(norm(residual[rows[i]])), float32."""
+        if (self.runtime.fast and ctx.wanted_rows == list(range(residual.shape[0])) and residual.dtype == torch.float32
+                and getattr(self.norm, "fusable_rms", False) and self.proj.can_few(residual.shape[0], ops.STORE)):
+            # every token's logits are wanted and the tokens are few (a decode step): the product applies the
+            # norm to the stream itself on the way in
+            with ops.section("head.proj"):
+                self.proj.few(residual, logits, ops.STORE, norm=self.norm)
+            return logits
         h = ctx.buffer("head_in", (rows.numel(), self.spec.hidden_size), self.runtime.act_dtype)
         with ops.section("head.norm"):
             self.norm.apply(residual, h, rows=rows)
