@@ -105,6 +105,22 @@ __device__ __forceinline__ void values_16keys(float (*o)[4], const uint32_t* p, 
     }
 }
 
+// Transpose an 8 x 8 matrix of 16-bit values held as one register per lane (row lane / 4, columns 2 (lane % 4) and
+// the next): what turns the accumulator layout of one product into the operand layout of the next when the roles
+// of rows and columns swap.
+__device__ __forceinline__ uint32_t transpose_8x8(uint32_t v) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+
+// A decode step has one query per head, and the handful of query heads that share a key/value head are far fewer
+// than the keys. So the keys are the rows (M = 16) of the tensor-core products and the query heads their columns
+// (N = 8): S^T[16 keys x 8 heads] = K Q^T and O^T[head size x 8 heads] += V^T P^T. With the query heads as the rows
+// of 16-row tiles three quarters of every product and of the softmax's work were padding; this way half is, and
+// a page costs half the instructions.
+constexpr int HEAD_ROWS = 8;       // query heads per unit (a key/value head with more query heads takes several units)
+
 // ============================================================================ decode
 // grid: (splits, G * head_groups, B); 128 threads; one new token per sequence.
 // Partial results: part_o[b][head][split][hd] (unnormalised), part_ml[b][head][split][2] = (max, sum),
@@ -194,8 +210,8 @@ __device__ __forceinline__ void attention_decode_unit(
     const int hd = HD_EXACT > 0 ? HD_EXACT : hd_arg;
     const int g = by / head_groups, hg = by - g * head_groups;
     const int R = H / G;
-    const int head0 = g * R + hg * 16;
-    const int nrows = min(16, R - hg * 16);
+    const int head0 = g * R + hg * HEAD_ROWS;
+    const int nrows = min(HEAD_ROWS, R - hg * HEAD_ROWS);
     const int warp = tid >> 5, lane = tid & 31;
     const int kw = warp & 3, pg = warp >> 2;       // this warp's quarter of a page's keys, and its page of a group
     const int len = kv_len[b];
@@ -216,9 +232,8 @@ __device__ __forceinline__ void attention_decode_unit(
         page_hi = min(last, page_lo + per - 1);
         if (split >= shares) {
             if (!FUSED) {                          // the separate merge kernel reads every share: leave an empty one
-                const int R0 = H / G, rows0 = min(16, R0 - (by % head_groups) * 16);
-                for (int r = tid; r < rows0; r += 32 * NW) {
-                    const size_t slot = ((size_t)b * H + (by / head_groups) * R0 + (by % head_groups) * 16 + r) * num_splits + split;
+                for (int r = tid; r < nrows; r += 32 * NW) {
+                    const size_t slot = ((size_t)b * H + head0 + r) * num_splits + split;
                     part_ml[slot * 2] = NEG_BIG;
                     part_ml[slot * 2 + 1] = 0.f;
                 }
@@ -244,11 +259,11 @@ __device__ __forceinline__ void attention_decode_unit(
         cp_async_commit();
     }
 
-    const int r_lo = lane >> 2, r_hi = r_lo + 8;
-    uint32_t qf[KSTEPS][4];
-    // FUSED: extra shared memory behind the ring: rotated queries [16][hd] bf16, the new key and value, cos, sin
+    const int g8 = lane >> 2, t4 = lane & 3;       // the lane's place in a fragment: row / column group
+    uint32_t qf[KSTEPS][2];                        // Q^T as the products' column operand: head g8, features 2 t4 (+8) ...
+    // FUSED: extra shared memory behind the ring: rotated queries [8][hd] bf16, the new key and value, cos, sin
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * stage_bytes);
-    __nv_bfloat16* new_k = q_s + 16 * hd;
+    __nv_bfloat16* new_k = q_s + HEAD_ROWS * hd;
     __nv_bfloat16* new_v = new_k + hd;
     float* cs = reinterpret_cast<float*>(new_v + hd);
     float* sn = cs + 128;
@@ -261,14 +276,15 @@ __device__ __forceinline__ void attention_decode_unit(
         const float in_scale = fused.row_sumsq
             ? 1.0f / sqrtf(__ldcg(fused.row_sumsq + b) / (float)fused.norm_width + fused.norm_eps) : 1.0f;
         const float* row = fused.qkv + (size_t)b * fused.ld;
-        // the queries: the loads of four elements (each with its partner of the rotation) are in flight together
-        for (int idx0 = tid; idx0 < 16 * hd; idx0 += 4 * NT) {
+        // the queries (heads beyond the unit's own are zero): the loads of four elements (each with its partner of
+        // the rotation) are in flight together
+        for (int idx0 = tid; idx0 < HEAD_ROWS * hd; idx0 += 4 * NT) {
             float val[4], other[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int idx = idx0 + u * NT;
                 val[u] = other[u] = 0.f;
-                if (idx < 16 * hd) {
+                if (idx < HEAD_ROWS * hd) {
                     const int r = idx / hd, e = idx - r * hd;
                     if (r < nrows) {
                         const float* head = row + (size_t)(head0 + r) * hd;
@@ -280,7 +296,7 @@ __device__ __forceinline__ void attention_decode_unit(
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int idx = idx0 + u * NT;
-                if (idx < 16 * hd) {
+                if (idx < HEAD_ROWS * hd) {
                     const int e = idx % hd;
                     q_s[idx] = __float2bfloat16_rn(rotate_value(val[u], other[u], e, fused.rd, fused.interleaved, cs, sn) * in_scale);
                 }
@@ -303,41 +319,40 @@ __device__ __forceinline__ void attention_decode_unit(
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
             if (kk * 16 < hd) {
-                const int c = kk * 16 + (lane & 3) * 2;
-                qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_s + r_lo * hd + c);
-                qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_s + r_hi * hd + c);
-                qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_s + r_lo * hd + c + 8);
-                qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_s + r_hi * hd + c + 8);
+                const int c = kk * 16 + t4 * 2;
+                qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_s + g8 * hd + c);
+                qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_s + g8 * hd + c + 8);
             }
         }
     } else {
         before_inputs();
-        const __nv_bfloat16* q_lo = q + ((size_t)b * H + head0 + min(r_lo, nrows - 1)) * hd;
-        const __nv_bfloat16* q_hi = q + ((size_t)b * H + head0 + min(r_hi, nrows - 1)) * hd;
+        // heads beyond the unit's own repeat its last one (finite values; their results are never stored)
+        const __nv_bfloat16* q_row = q + ((size_t)b * H + head0 + min(g8, nrows - 1)) * hd;
 #pragma unroll
         for (int kk = 0; kk < KSTEPS; ++kk) {
             if (kk * 16 < hd) {
-                const int c = kk * 16 + (lane & 3) * 2;
-                qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_lo + c);
-                qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_hi + c);
-                qf[kk][2] = *reinterpret_cast<const uint32_t*>(q_lo + c + 8);
-                qf[kk][3] = *reinterpret_cast<const uint32_t*>(q_hi + c + 8);
+                const int c = kk * 16 + t4 * 2;
+                qf[kk][0] = *reinterpret_cast<const uint32_t*>(q_row + c);
+                qf[kk][1] = *reinterpret_cast<const uint32_t*>(q_row + c + 8);
             }
         }
     }
-    float o[KSTEPS * 2][4];
+    // O^T: tile mt holds features 16 mt + g8 (o[mt][0..1]) and 16 mt + 8 + g8 (o[mt][2..3]) of heads 2 t4, 2 t4 + 1
+    float o[KSTEPS][4];
 #pragma unroll
-    for (int i = 0; i < KSTEPS * 2; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_lo = NEG_BIG, m_hi = NEG_BIG, l_lo = 0.f, l_hi = 0.f;
+    for (int i = 0; i < KSTEPS; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = NEG_BIG, m1 = NEG_BIG, l0 = 0.f, l1 = 0.f;       // running maximum and sum of heads 2 t4 and 2 t4 + 1
 
     const int ngroups = (npages + PG - 1) / PG;
     const int new_at = pos / PAGE - page_lo;         // which of the share's pages holds the new token
+    const int cpr = hd >> 3;
+    const int frag_row = (lane & 7) + ((lane >> 3) & 1) * 8, frag_chunk = lane >> 4;      // ldmatrix.x4 for a 16 x 16 row operand
     for (int gi = 0; gi < ngroups; ++gi) {
         cp_async_wait<GROUPS - 1>();                 // all but the newest groups of copies: this group's pages are there
         unit_sync<NAMED, NT>();
         if (FUSED && holds_new && new_at >= gi * PG && new_at < (gi + 1) * PG) {
             // the copy of this page predates the new token: put its key and value in place
-            const int cpr = hd >> 3, row = pos % PAGE;
+            const int row = pos % PAGE;
             uint8_t* tile = smem + (new_at % STAGES) * stage_bytes;
             for (int c = tid; c < 2 * cpr; c += NT) {
                 const int which = c >= cpr, cc = which ? c - cpr : c;
@@ -353,43 +368,47 @@ __device__ __forceinline__ void attention_decode_unit(
             const uint32_t v_tile = k_tile + PAGE * hd * 2;
             const int key0 = kw * 16;                    // this warp's 16 keys of its page
             if (key_base + key0 <= pos && key_base + key0 + 15 >= lo) {
-                float s[2][4];
-                s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
-                scores_16keys<KSTEPS>(s, qf, k_tile, key0, hd, lane);
-                float mx_lo = NEG_BIG, mx_hi = NEG_BIG;
-    #pragma unroll
-                for (int nt = 0; nt < 2; ++nt)
-    #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const int key = key_base + key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                        float v = s[nt][e] * scale_log2;
-                        if (key > pos || key < lo) v = NEG_BIG;
-                        s[nt][e] = v;
-                        if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
+                // S^T: s[0], s[1] = key g8 with heads 2 t4, 2 t4 + 1; s[2], s[3] = key g8 + 8 with the same heads
+                float s[4] = {0.f, 0.f, 0.f, 0.f};
+                const int k_row = key0 + frag_row;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    if (kk * 16 < hd) {
+                        uint32_t a[4];
+                        ldmatrix_x4(k_tile + k_row * (hd * 2) + swz(k_row, kk * 2 + frag_chunk, cpr) * 16, a[0], a[1], a[2], a[3]);
+                        mma_bf16(s, a, qf[kk][0], qf[kk][1]);
                     }
-                mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
-                mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-                mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
-                mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-                const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-                const float a_lo = fast_exp2(m_lo - mn_lo), a_hi = fast_exp2(m_hi - mn_hi);
-                m_lo = mn_lo; m_hi = mn_hi;
-                uint32_t pf[4];
-                float sum_lo = 0.f, sum_hi = 0.f;
-    #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
-                    float e0 = s[nt][0] <= NEG_BIG ? 0.f : fast_exp2(s[nt][0] - mn_lo);
-                    float e1 = s[nt][1] <= NEG_BIG ? 0.f : fast_exp2(s[nt][1] - mn_lo);
-                    float e2 = s[nt][2] <= NEG_BIG ? 0.f : fast_exp2(s[nt][2] - mn_hi);
-                    float e3 = s[nt][3] <= NEG_BIG ? 0.f : fast_exp2(s[nt][3] - mn_hi);
-                    sum_lo += e0 + e1; sum_hi += e2 + e3;
-                    pf[nt * 2] = pack_bf16(e0, e1);
-                    pf[nt * 2 + 1] = pack_bf16(e2, e3);
                 }
-                l_lo = l_lo * a_lo + sum_lo; l_hi = l_hi * a_hi + sum_hi;
-    #pragma unroll
-                for (int j = 0; j < KSTEPS * 2; ++j) { o[j][0] *= a_lo; o[j][1] *= a_lo; o[j][2] *= a_hi; o[j][3] *= a_hi; }
-                values_16keys<KSTEPS>(o, pf, v_tile, key0, hd, lane);
+                const int key_a = key_base + key0 + g8, key_b = key_a + 8;
+                const bool out_a = key_a > pos || key_a < lo, out_b = key_b > pos || key_b < lo;
+                s[0] = out_a ? NEG_BIG : s[0] * scale_log2; s[1] = out_a ? NEG_BIG : s[1] * scale_log2;
+                s[2] = out_b ? NEG_BIG : s[2] * scale_log2; s[3] = out_b ? NEG_BIG : s[3] * scale_log2;
+                float mx0 = fmaxf(s[0], s[2]), mx1 = fmaxf(s[1], s[3]);        // over the 16 keys: the lanes of equal t4
+#pragma unroll
+                for (int sh = 4; sh < 32; sh <<= 1) {
+                    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, sh));
+                    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, sh));
+                }
+                const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+                const float a0 = fast_exp2(m0 - mn0), a1 = fast_exp2(m1 - mn1);
+                m0 = mn0; m1 = mn1;
+                const float e0 = out_a ? 0.f : fast_exp2(s[0] - mn0), e1 = out_a ? 0.f : fast_exp2(s[1] - mn1);
+                const float e2 = out_b ? 0.f : fast_exp2(s[2] - mn0), e3 = out_b ? 0.f : fast_exp2(s[3] - mn1);
+                l0 = l0 * a0 + (e0 + e2);
+                l1 = l1 * a1 + (e1 + e3);
+                // P^T as the column operand of the second product: (keys 2 t4, 2 t4 + 1 | + 8, head g8)
+                const uint32_t p0 = transpose_8x8(pack_bf16(e0, e1)), p1 = transpose_8x8(pack_bf16(e2, e3));
+                const int v_row = key0 + (lane & 7) + (lane >> 4) * 8;          // ldmatrix.x4.trans for V^T, 16 features x 16 keys
+                const int v_chunk = (lane >> 3) & 1;
+#pragma unroll
+                for (int mt = 0; mt < KSTEPS; ++mt) {
+                    if (mt * 16 < hd) {
+                        o[mt][0] *= a0; o[mt][1] *= a1; o[mt][2] *= a0; o[mt][3] *= a1;
+                        uint32_t a[4];
+                        ldmatrix_x4_trans(v_tile + v_row * (hd * 2) + swz(v_row, mt * 2 + v_chunk, cpr) * 16, a[0], a[1], a[2], a[3]);
+                        mma_bf16(o[mt], a, p0, p1);
+                    }
+                }
             }
         }
         unit_sync<NAMED, NT>();
@@ -405,24 +424,28 @@ __device__ __forceinline__ void attention_decode_unit(
     cp_async_wait<0>();
     unit_sync<NAMED, NT>();
 
-    // merge the warps (each saw a quarter of some pages) through shared memory
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    float* sm_m = reinterpret_cast<float*>(smem);            // [NW][16]
-    float* sm_l = sm_m + NW * 16;                            // [NW][16]
-    float* sm_o = sm_l + NW * 16;                            // [NW][16][hd]
-    if ((lane & 3) == 0) {
-        sm_m[warp * 16 + r_lo] = m_lo; sm_m[warp * 16 + r_hi] = m_hi;
-        sm_l[warp * 16 + r_lo] = l_lo; sm_l[warp * 16 + r_hi] = l_hi;
+    // merge the warps (each saw a quarter of some pages) through shared memory; a head's sum over the keys lies in
+    // the lanes of equal t4
+#pragma unroll
+    for (int sh = 4; sh < 32; sh <<= 1) {
+        l0 += __shfl_xor_sync(0xffffffffu, l0, sh);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, sh);
+    }
+    float* sm_m = reinterpret_cast<float*>(smem);            // [NW][8]
+    float* sm_l = sm_m + NW * HEAD_ROWS;                     // [NW][8]
+    float* sm_o = sm_l + NW * HEAD_ROWS;                     // [NW][8][hd]
+    if (g8 == 0) {
+        sm_m[warp * HEAD_ROWS + 2 * t4] = m0; sm_m[warp * HEAD_ROWS + 2 * t4 + 1] = m1;
+        sm_l[warp * HEAD_ROWS + 2 * t4] = l0; sm_l[warp * HEAD_ROWS + 2 * t4 + 1] = l1;
     }
 #pragma unroll
-    for (int dt = 0; dt < KSTEPS * 2; ++dt) {
-        const int d = dt * 8 + (lane & 3) * 2;
+    for (int mt = 0; mt < KSTEPS; ++mt) {
+        const int d = mt * 16 + g8;
         if (d < hd) {
-            float* lo_row = sm_o + ((size_t)warp * 16 + r_lo) * hd + d;
-            float* hi_row = sm_o + ((size_t)warp * 16 + r_hi) * hd + d;
-            lo_row[0] = o[dt][0]; lo_row[1] = o[dt][1];
-            hi_row[0] = o[dt][2]; hi_row[1] = o[dt][3];
+            float* head_a = sm_o + ((size_t)warp * HEAD_ROWS + 2 * t4) * hd;
+            float* head_b = head_a + hd;
+            head_a[d] = o[mt][0]; head_b[d] = o[mt][1];
+            head_a[d + 8] = o[mt][2]; head_b[d + 8] = o[mt][3];
         }
     }
     unit_sync<NAMED, NT>();
@@ -430,13 +453,13 @@ __device__ __forceinline__ void attention_decode_unit(
         const int r = idx / hd, d = idx - r * hd;
         float m = NEG_BIG;
 #pragma unroll
-        for (int w = 0; w < NW; ++w) m = fmaxf(m, sm_m[w * 16 + r]);
+        for (int w = 0; w < NW; ++w) m = fmaxf(m, sm_m[w * HEAD_ROWS + r]);
         float acc = 0.f, l = 0.f;
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-            const float f = fast_exp2(sm_m[w * 16 + r] - m);
-            acc += sm_o[((size_t)w * 16 + r) * hd + d] * f;
-            l += sm_l[w * 16 + r] * f;
+            const float f = fast_exp2(sm_m[w * HEAD_ROWS + r] - m);
+            acc += sm_o[((size_t)w * HEAD_ROWS + r) * hd + d] * f;
+            l += sm_l[w * HEAD_ROWS + r] * f;
         }
         if ((FUSED ? shares : num_splits) == 1) {   // the only share: this is the result
             out[((size_t)b * H + head0 + r) * hd + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);

@@ -11,10 +11,11 @@
 //
 //  * prefill: a CTA takes 64 consecutive new tokens of one sequence and one query head;
 //    each of its 4 warps owns 16 query rows and visits the pages its rows can see.
-//  * decode:  a CTA takes one sequence, one key/value head and one share of the pages; the
-//    query heads that share the key/value head are the 16 rows of the MMA, so each key and
-//    value is read once for all of them; each warp owns 16 of a page's 64 keys; the CTA
-//    writes an unnormalised partial result (max, sum, output), merged by a second kernel.
+//  * decode:  a CTA takes one sequence, one key/value head and one share of the pages; the keys
+//    are the 16 rows of the MMA and the (up to 8) query heads that share the key/value head its
+//    columns, so each key and value is read once for all of them; each warp owns 16 of a page's
+//    64 keys; the CTA writes an unnormalised partial result (max, sum, output), merged by a
+//    second kernel or, in the fused form, by the last CTA of the group.
 //
 // Reference: src/main/resources/kernels/cuda/attention.cu:10-108 (one block per head,
 // scores of one query in shared memory) and the online-softmax form of
@@ -456,10 +457,10 @@ static int attention_decode_launch(const void* q, void* out, const void* pages, 
     if (rc) return rc;
     if (page_size != PAGE) LP_REFUSE("attention_decode: pages of %d positions (built for %d)", page_size, PAGE);
     if (pages_per_split <= 0 || num_splits <= 0) LP_REFUSE("attention_decode: %d shares of %d pages", num_splits, pages_per_split);
-    const int head_groups = (H / G + 15) / 16;
+    const int head_groups = (H / G + HEAD_ROWS - 1) / HEAD_ROWS;
     if (G * head_groups > 65535 || B > 65535) LP_REFUSE("attention_decode: grid too large");
     const int stage = 2 * PAGE * hd * 2;
-    const int merge = (128 + 64 * hd) * 4;
+    const int merge = (2 * 4 * HEAD_ROWS + 4 * HEAD_ROWS * hd) * 4;
     const int smem = 3 * stage > merge ? 3 * stage : merge;
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)B * H * num_splits * hd;
@@ -524,10 +525,10 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
     if (rd < 0 || rd > hd || (rd & 1) || rd > 256) LP_REFUSE("attention_decode_fused: rotary width %d of a head of %d", rd, hd);
     if (rd > 0 && !inv_freq) LP_REFUSE("attention_decode_fused: rotation without frequencies");
     if (ld < (write_kv ? H + 2 * G : H) * hd) LP_REFUSE("attention_decode_fused: row of %d values", ld);
-    const int head_groups = (H / G + 15) / 16;
+    const int head_groups = (H / G + HEAD_ROWS - 1) / HEAD_ROWS;
     if (G * head_groups > 65535 || B > 65535) LP_REFUSE("attention_decode_fused: grid too large");
     const int stage = 2 * PAGE * hd * 2;
-    const int extra = (16 * hd + 2 * hd) * 2 + 256 * 4;
+    const int extra = (HEAD_ROWS * hd + 2 * hd) * 2 + 256 * 4;
     const int sms = lp_sm_count();
     // With few CTAs altogether (no more than one per SM: measured, batch 24 / 32: 1.01 / 1.02 ms per step against
     // 1.07 / 1.08 when up to two per SM count as few) and small heads a CTA has 16 warps, four pages at a time and
@@ -539,7 +540,7 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
     // heads of 128 (pages of 32 KB): 8 warps, two pages at a time, four in shared memory, one CTA per SM
     const bool wide128 = hd > 64 && hd <= 128 && pages_per_split > 3 && (long long)num_splits * G * head_groups * B <= sms;
     const int stages = wide ? 8 : mid ? 6 : wide128 ? 4 : 3, nw = wide ? 16 : (mid || wide128) ? 8 : 4;
-    const int merge = (2 * nw * 16 + nw * 16 * hd) * 4;
+    const int merge = (2 * nw * HEAD_ROWS + nw * HEAD_ROWS * hd) * 4;
     const int smem = (stages * stage > merge ? stages * stage : merge) + extra;
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)B * H * num_splits * hd;

@@ -710,7 +710,7 @@ def decode_split(batch: int, num_kv_heads: int, num_heads: int, table_width: int
     against 0.92 / 1.01 with twice the CTAs). This is the most shares a sequence can get; the kernels fit the
     number to each sequence's own length (at batch 8 and a context of 600 in a table of 16 pages: one share,
     0.69 ms per step, against 0.75 with two shares of 8 pages)."""
-    groups = batch * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
+    groups = decode_groups(batch, num_heads, num_kv_heads)
     shares = max(1, min(table_width // MIN_SHARE_PAGES, num_sms() // groups))
     per = -(-table_width // shares)
     return per, -(-table_width // per)
@@ -744,10 +744,13 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, pa
     return out
 
 
+DECODE_HEAD_ROWS = 8          # query heads that one CTA of a decode step serves (HEAD_ROWS of the kernels)
+
+
 def decode_groups(batch: int, num_heads: int, num_kv_heads: int) -> int:
     """How many groups of CTAs a fused decode step has (each merges its own shares and counts them in a
     counter of its own)."""
-    return batch * num_kv_heads * (-(-(num_heads // num_kv_heads) // 16))
+    return batch * num_kv_heads * (-(-(num_heads // num_kv_heads) // DECODE_HEAD_ROWS))
 
 
 def attention_decode_fused(qkv: torch.Tensor, rotation: Rotation, out: torch.Tensor,
