@@ -393,6 +393,30 @@ extern "C" int lp_rope_cache_write(const float* qkv, int ld, const float* inv_fr
     return lp_check_launch("rope_cache_write");
 }
 
+// ---------------------------------------------------------------- rotation angles of a step's tokens
+// out[t][i] = (cos, sin) of float(positions[t]) * inv_freq[i]: the same float32 product and the same sincosf as
+// the rotation kernels above, formed once per step for a product whose epilogue rotates (gemm_tcgen05.cu).
+__global__ void __launch_bounds__(128)
+rope_angles_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, float2* __restrict__ out,
+                   int T, int half) {
+    lp_grid_release();
+    lp_grid_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)T * half) return;
+    const int t = (int)(i / half), p = (int)(i - (long long)t * half);
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[p], &sn, &cs);
+    out[i] = make_float2(cs, sn);
+}
+
+extern "C" int lp_rope_angles(const int* positions, const float* inv_freq, float* out, int T, int half,
+                              cudaStream_t stream) {
+    if (T <= 0 || half <= 0) return 0;
+    const long long n = (long long)T * half;
+    lp_launch(rope_angles_kernel, (unsigned)((n + 127) / 128), 128, 0, stream, positions, inv_freq, (float2*)out, T, half);
+    return lp_check_launch("rope_angles");
+}
+
 // ---------------------------------------------------------------- advancing a decoding batch on the device
 // After a decode step whose sampler left one token per sequence: that token becomes the next
 // step's input, and every sequence moves on by one position. Lets decode steps follow one

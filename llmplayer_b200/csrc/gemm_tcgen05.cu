@@ -41,6 +41,8 @@
 #define LP_GEMM_SWIGLU 2
 #define LP_GEMM_SWIGLU_WIDE 3   // same result and weight layout; two accumulators, 128 output features per CTA
 #define LP_GEMM_SWIGLU_TOKM 4   // same again, persistent form only: 128 tokens are the MMA's M, 256 weight rows its N
+#define LP_GEMM_QKV_TOKM 5      // persistent form only: the fused q|k|v projection with tokens as M; the epilogue rotates
+                                // queries and keys and writes queries to their buffer, keys and values into the cache
 
 namespace {
 
@@ -51,8 +53,8 @@ constexpr int THREADS = 192;      // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5:
 // first 128-row tile, their up rows the second (the tensor map's box is 64 rows then).
 template <int MODE>
 __device__ __forceinline__ void load_weights(uint8_t* stage, const CUtensorMap* map_w, int k, int cta, uint64_t* bar) {
-    if (MODE == LP_GEMM_SWIGLU_TOKM) {
-        tma_load_2d(stage, map_w, k, cta * 256, bar);            // one box of 256 rows: gate | up | gate | up of 128 features
+    if (MODE == LP_GEMM_SWIGLU_TOKM || MODE == LP_GEMM_QKV_TOKM) {
+        tma_load_2d(stage, map_w, k, cta * 256, bar);            // one box of 256 rows (gated: gate | up | gate | up of 128 features)
     } else if (MODE == LP_GEMM_SWIGLU_WIDE) {
         const int row = cta * 256;
         tma_load_2d(stage, map_w, k, row, bar);                  // gate, features 128 cta ..
@@ -153,7 +155,6 @@ struct Tile {
     static constexpr int TAIL_BYTES = 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr int ACC_COLS = BLOCK_TOK * W_TILES;
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;       // power of two by construction
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + TAIL_BYTES;
 };
 
 // out: [tokens, ldc]; OUT_BF16 selects the element type of a STORE / SWIGLU output.
@@ -727,9 +728,38 @@ static bool fewtok_enabled() { return few_settings().enabled != 0; }
 // accumulators: while the epilogue warps read tile i out of one, the MMA thread fills the other with
 // tile i + 1, and the loader keeps the ring of stages full across tile boundaries. No split of K, no
 // norm fusion: this form serves steps with hundreds of tokens.
+// What the epilogue of the fused q|k|v projection needs (LP_GEMM_QKV_TOKM): a token is a row of the accumulator, so
+// a thread holds whole heads of its token and a rotation pair never leaves the thread.
+struct QkvEpilogue {
+    const float2* angles;       // [tokens, half] (cos, sin) of position x frequency; null: no rotation
+    int half;                   // rotary width / 2 (the rotary width is the head size, or 0)
+    int interleaved;            // pairs (2i, 2i + 1) instead of (i, i + head size / 2)
+    const int* positions;       // [tokens]
+    const int* seq_ids;         // [tokens]
+    const int* page_table;      // [sequences, pt_stride]
+    int pt_stride;
+    __nv_bfloat16* q_out;       // [tokens, H * hd]
+    __nv_bfloat16* pages;       // [num_pages, 2, G, page_size, hd]; null: this layer keeps no keys of its own
+    int H, G, hd, page_size;
+};
+
+// 32 float32 values of a token -> 32 bfloat16 at dst (16-byte aligned)
+__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float* v) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        uint4 packed;
+        __nv_bfloat162 t0 = __floats2bfloat162_rn(v[q * 8], v[q * 8 + 1]), t1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
+        __nv_bfloat162 t2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]), t3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
+        packed.x = *reinterpret_cast<uint32_t*>(&t0); packed.y = *reinterpret_cast<uint32_t*>(&t1);
+        packed.z = *reinterpret_cast<uint32_t*>(&t2); packed.w = *reinterpret_cast<uint32_t*>(&t3);
+        reinterpret_cast<uint4*>(dst)[q] = packed;
+    }
+}
+
 template <int BLOCK_TOK, int MODE>
 struct PersistentTile {
-    static constexpr bool TOKM = MODE == LP_GEMM_SWIGLU_TOKM;
+    static constexpr bool TOKM = MODE == LP_GEMM_SWIGLU_TOKM || MODE == LP_GEMM_QKV_TOKM;
+    static constexpr int FEAT_PER_TILE = MODE == LP_GEMM_QKV_TOKM ? 256 : BLOCK_FEAT;
     static constexpr int W_TILES = MODE == LP_GEMM_SWIGLU_WIDE ? 2 : 1;
     static constexpr int W_BYTES = (TOKM ? 256 : BLOCK_FEAT) * BLOCK_K * 2;
     static constexpr int X_BYTES = BLOCK_TOK * BLOCK_K * 2;
@@ -746,7 +776,7 @@ template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                        void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int feat_tiles,
-                       int num_tiles, int group_tok, int* __restrict__ status) {
+                       int num_tiles, int group_tok, int* __restrict__ status, QkvEpilogue qkv) {
     using T = PersistentTile<BLOCK_TOK, MODE>;
     // Tiles are numbered in bands of `group_tok` token tiles, token tile first within a band: the CTAs that run
     // at the same time then share a few weight tiles and a few activation tiles, which stay in L2 (feature
@@ -862,7 +892,93 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             if (ok && !mbar_wait(&acc_full[ab], (j >> 1) & 1)) { if (lane == 0) atomicExch(status, 24); *failed = 1; ok = false; }
             tcgen05_fence_after();
             const bool go = __all_sync(0xffffffffu, ok && *failed == 0);
-            if (go && T::TOKM) {
+            if (go && MODE == LP_GEMM_QKV_TOKM) {
+                // lanes are tokens, columns the tile's 256 features = whole heads. Queries and keys: every pair of
+                // a head is rotated by the token's angle (products and sums rounded one by one, as the rotation
+                // kernels do); queries go to their buffer, keys and values to the token's place in the cache.
+                const uint32_t lane_addr = tmem_base + ab * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+                const int t = tt * BLOCK_TOK + quarter * 32 + lane;
+                const bool live = t < tokens;
+                const int hd = qkv.hd, chunks = hd >> 5;             // 32 columns per chunk
+                long long page_base = 0;
+                if (live && qkv.pages) {
+                    const int pos = qkv.positions[t];
+                    const int page = qkv.page_table[(long long)qkv.seq_ids[t] * qkv.pt_stride + pos / qkv.page_size];
+                    page_base = (long long)page * 2 * qkv.G * qkv.page_size * hd + (long long)(pos % qkv.page_size) * hd;
+                }
+                const float2* ang = qkv.angles ? qkv.angles + (size_t)(live ? t : 0) * qkv.half : nullptr;
+                const int heads_per_tile = 256 / hd, total_heads = qkv.pages ? qkv.H + 2 * qkv.G : qkv.H;
+                auto dest = [&](int head) -> __nv_bfloat16* {
+                    if (head < qkv.H) return qkv.q_out + ((size_t)(live ? t : 0) * qkv.H + head) * hd;
+                    const bool is_v = head >= qkv.H + qkv.G;
+                    return qkv.pages + page_base + (size_t)(is_v ? head - qkv.H : head - qkv.H) * qkv.page_size * hd;
+                };
+                const int rotated_heads = ang == nullptr ? 0 : (qkv.pages ? qkv.H + qkv.G : qkv.H);     // heads below this index are rotated
+                const bool split_half = ang != nullptr && !qkv.interleaved;
+                // heads that pass through (values; everything when there is no rotation) and interleaved pairs: chunk by chunk
+#pragma unroll 1
+                for (int hh = 0; hh < heads_per_tile; ++hh) {
+                    const int head = ft * heads_per_tile + hh;
+                    if (head >= total_heads) break;
+                    const bool rotate = head < rotated_heads;
+                    if (rotate && split_half) continue;
+                    __nv_bfloat16* dst = dest(head);
+                    const uint32_t col0 = lane_addr + hh * hd;
+#pragma unroll 1
+                    for (int c = 0; c < chunks; ++c) {
+                        uint32_t g[32];
+                        float v[32];
+                        tmem_ld32(col0 + c * 32, g);
+                        tmem_ld_wait();
+                        if (rotate) {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                const float2 cs = live ? ang[c * 16 + i] : make_float2(1.f, 0.f);
+                                const float xa = __uint_as_float(g[2 * i]), xb = __uint_as_float(g[2 * i + 1]);
+                                v[2 * i] = __fsub_rn(__fmul_rn(xa, cs.x), __fmul_rn(xb, cs.y));
+                                v[2 * i + 1] = __fadd_rn(__fmul_rn(xa, cs.y), __fmul_rn(xb, cs.x));
+                            }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(g[i]);
+                        }
+                        if (live) store_row32(dst + c * 32, v);
+                    }
+                }
+                // pairs (i, i + hd / 2): chunk c of a head with its chunk c + half_chunks; the token's angles of a
+                // chunk are fetched once and serve every rotated head of the tile
+                if (split_half) {
+                    const int half_chunks = chunks >> 1;
+#pragma unroll 1
+                    for (int c = 0; c < half_chunks; ++c) {
+                        float2 cs[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) cs[i] = live ? ang[c * 32 + i] : make_float2(1.f, 0.f);
+#pragma unroll 1
+                        for (int hh = 0; hh < heads_per_tile; ++hh) {
+                            const int head = ft * heads_per_tile + hh;
+                            if (head >= rotated_heads) break;
+                            __nv_bfloat16* dst = dest(head);
+                            const uint32_t col0 = lane_addr + hh * hd;
+                            uint32_t g[32], u[32];
+                            float va[32], vb[32];
+                            tmem_ld32(col0 + c * 32, g);
+                            tmem_ld32(col0 + (c + half_chunks) * 32, u);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                const float xa = __uint_as_float(g[i]), xb = __uint_as_float(u[i]);
+                                va[i] = __fsub_rn(__fmul_rn(xa, cs[i].x), __fmul_rn(xb, cs[i].y));
+                                vb[i] = __fadd_rn(__fmul_rn(xa, cs[i].y), __fmul_rn(xb, cs[i].x));
+                            }
+                            if (live) {
+                                store_row32(dst + c * 32, va);
+                                store_row32(dst + (c + half_chunks) * 32, vb);
+                            }
+                        }
+                    }
+                }
+            } else if (go && T::TOKM) {
                 // lanes are tokens; columns 0..63 gate, 64..127 up of features 128 ft .. + 63, columns 128..255 the
                 // same for the next 64 features: a thread forms 32 outputs of its token at a time
                 const uint32_t lane_addr = tmem_base + ab * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
@@ -946,7 +1062,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 
 template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc,
-                      int k_blocks, int* status, cudaStream_t stream) {
+                      int k_blocks, int* status, cudaStream_t stream, const QkvEpilogue& qkv = QkvEpilogue{}) {
     using T = PersistentTile<BLOCK_TOK, MODE>;
     auto kernel = gemm_persistent_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC>;
     static bool configured = false;
@@ -957,7 +1073,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, i
         configured = true;
     }
     const int sms = lp_sm_count();
-    const int feat_tiles = (features + BLOCK_FEAT - 1) / BLOCK_FEAT;
+    const int feat_tiles = (features + T::FEAT_PER_TILE - 1) / T::FEAT_PER_TILE;
     const int tok_tiles = (tokens + BLOCK_TOK - 1) / BLOCK_TOK;
     const int num_tiles = feat_tiles * tok_tiles;
     const int grid = num_tiles < sms ? num_tiles : sms;
@@ -971,7 +1087,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, i
         if (best < 0 || cost <= best) { best = cost; group_tok = gt; }       // ties: the larger band
     }
     cudaError_t err = lp_launch(kernel, dim3(grid), THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
-                                k_blocks, feat_tiles, num_tiles, group_tok, status);
+                                k_blocks, feat_tiles, num_tiles, group_tok, status, qkv);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_persistent: %s", cudaGetErrorString(err));
         return (int)err;
@@ -1098,6 +1214,38 @@ extern "C" int lp_gemm_persistent(const void* X, const void* W, void* out, int o
         return launch_persistent<256, LP_GEMM_STORE, false, true>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
     if (bf) return launch_persistent<256, LP_GEMM_STORE, true, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
     return launch_persistent<256, LP_GEMM_STORE, false, false>(mw, mx, out, tokens, features, ldc, k_blocks, status, stream);
+}
+
+// The fused q|k|v projection of a step with many tokens: [tokens, K] x W[(H + 2G) * hd, K]^T (or H * hd rows when the
+// layer keeps no keys of its own: pages null), whose epilogue rotates queries and keys by `angles` ([tokens, half]
+// (cos, sin) pairs from lp_rope_angles; half = hd / 2, or 0 with angles null for no rotation), writes the queries to
+// q_out [tokens, H * hd] and keys and values into pages [num_pages, 2, G, page_size, hd] at the tokens' positions,
+// all bfloat16. Head sizes 32 (interleaved pairs or no rotation only), 64, 128, 256.
+extern "C" int lp_gemm_qkv_rope(const void* X, const void* W, int tokens, int K, int ldx, int ldw, const float* angles,
+                                int half, int interleaved, const int* positions, const int* seq_ids,
+                                const int* page_table, int pt_stride, void* q_out, void* pages, int H, int G, int hd,
+                                int page_size, int* status, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (K <= 0 || K % 8) LP_REFUSE("gemm_qkv_rope: inner size %d must be a positive multiple of 8", K);
+    if (ldx % 8 || ldw % 8) LP_REFUSE("gemm_qkv_rope: row strides %d / %d must be multiples of 8 elements", ldx, ldw);
+    if ((((uintptr_t)X | (uintptr_t)W | (uintptr_t)q_out | (uintptr_t)pages) & 15)) LP_REFUSE("gemm_qkv_rope: operands must be 16-byte aligned");
+    if (H <= 0 || G < 0 || hd < 32 || hd > 256 || 256 % hd) LP_REFUSE("gemm_qkv_rope: heads %d/%d of %d (head sizes 32, 64, 128, 256)", H, G, hd);
+    if (half != 0 && half * 2 != hd) LP_REFUSE("gemm_qkv_rope: rotary width %d of a head of %d (all of it, or none)", 2 * half, hd);
+    if (half != 0 && !angles) LP_REFUSE("gemm_qkv_rope: rotation without angles");
+    if (half != 0 && !interleaved && hd < 64) LP_REFUSE("gemm_qkv_rope: split-half pairs need heads of at least 64");
+    if (pages && (page_size <= 0 || !page_table || !seq_ids)) LP_REFUSE("gemm_qkv_rope: a cache without page tables");
+    if (!positions || !q_out) LP_REFUSE("gemm_qkv_rope: a null argument");
+    const int features = (pages ? H + 2 * G : H) * hd;
+    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, features, K, ldw, 256);
+    if (rc) return rc;
+    rc = make_map(&mx, X, tokens, K, ldx, 128);
+    if (rc) return rc;
+    const QkvEpilogue qkv{half ? (const float2*)angles : nullptr, half, interleaved, positions, seq_ids, page_table, pt_stride,
+                          (__nv_bfloat16*)q_out, (__nv_bfloat16*)pages, H, G, hd, page_size};
+    return launch_persistent<128, LP_GEMM_QKV_TOKM, true, false>(mw, mx, nullptr, tokens, features, features, k_blocks,
+                                                                 status, stream, qkv);
 }
 
 // norm_weight (optional, ACCUMULATE only, ldc == features): after the sums are complete, the last CTA writes

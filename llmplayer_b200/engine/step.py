@@ -260,6 +260,19 @@ class StepContext:
     def buffer(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         return self.workspace.get(name, shape, dtype)
 
+    def angles(self, rotation) -> torch.Tensor:
+        """(cos, sin) of every token's position times each of the rotation's frequencies, float32
+        [T, rotary_dim / 2, 2]; formed once per step and table of frequencies."""
+        from ..kernels import ops
+        cache = self.__dict__.setdefault("_angles", {})
+        key = (rotation.inv_freq.data_ptr(), rotation.rotary_dim)
+        table = cache.get(key)
+        if table is None:
+            table = self.workspace.get(f"angles{len(cache)}", (self.num_tokens, rotation.rotary_dim // 2, 2), torch.float32)
+            ops.rope_angles(self.positions, rotation, table)
+            cache[key] = table
+        return table
+
     def counters(self, name: str, count: int) -> torch.Tensor:
         return self.workspace.get_counters(name, count)
 

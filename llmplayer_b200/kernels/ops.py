@@ -27,6 +27,7 @@ _SIGNATURES = {
         "lp_rmsnorm": [_P, _P, _I, _P, _P, _P, _I, _I, _I, _F, _P, ctypes.c_longlong, _P],
         "lp_rope_cache_write": [_P, _I, _P, _P, _P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
         "lp_advance": [_P, _P, _P, _P, _I, _P],
+        "lp_rope_angles": [_P, _P, _P, _I, _I, _P],
     },
     "gemm_plain": {
         "lp_gemm_plain": [_P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -40,6 +41,7 @@ _SIGNATURES = {
         "lp_gemm_persistent": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "lp_gemm_fewtok": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _I, _P],
         "lp_gemm_configure": [_I, _I, _I, _I],
+        "lp_gemm_qkv_rope": [_P, _P, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     },
     "attention_mma": {
         "lp_attention_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _F, _I, _P],
@@ -405,6 +407,68 @@ def rope_cache_write(qkv: torch.Tensor, rotation: Rotation, positions: torch.Ten
         qkv.data_ptr(), qkv.shape[1], freq_ptr, positions.data_ptr(),
         seq_ids.data_ptr(), page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(), _code(q_out, "rope q_out"),
         _ptr(pages), kv_code, T, H, G, hd, rotary_dim, interleaved, page_size, _stream()))
+
+
+def rope_angles(positions: torch.Tensor, rotation: Rotation, out: torch.Tensor) -> torch.Tensor:
+    """out[t, i] = (cos, sin) of float(positions[t]) * inv_freq[i], float32 [T, rotary_dim / 2, 2]: the angles of a
+    step's tokens, formed once for a product whose epilogue rotates (:func:`gemm_qkv_rope`)."""
+    _want(positions, "rope_angles positions", torch.int32, 1)
+    _want(out, "rope_angles out", torch.float32, 3)
+    freq_ptr, rotary_dim, _ = rotation.checked("rope_angles")
+    T, half = positions.numel(), rotary_dim // 2
+    if out.shape != (T, half, 2) or half == 0:
+        raise KernelError(f"rope_angles: out {tuple(out.shape)} for {T} tokens and a rotary width of {rotary_dim}")
+    lib = library("elementwise")
+    _check(lib, lib.lp_rope_angles(positions.data_ptr(), freq_ptr, out.data_ptr(), T, half, _stream()))
+    return out
+
+
+QKV_ROPE_HEAD_SIZES = (32, 64, 128, 256)
+
+
+def qkv_rope_serves(rotation: Rotation, head_dim: int) -> bool:
+    """Whether :func:`gemm_qkv_rope` can apply this rotation to heads of this size in its epilogue."""
+    if head_dim not in QKV_ROPE_HEAD_SIZES or rotation.rotary_dim not in (0, head_dim):
+        return False
+    return rotation.rotary_dim == 0 or rotation.interleaved or head_dim >= 64
+
+
+def gemm_qkv_rope(x: torch.Tensor, w: torch.Tensor, angles: Optional[torch.Tensor], interleaved: bool,
+                  positions: torch.Tensor, seq_ids: torch.Tensor, page_table: torch.Tensor, q_out: torch.Tensor,
+                  pages: Optional[torch.Tensor], *, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """The fused projection of a step with many tokens on the tensor cores, with what follows it in its epilogue:
+    ``x`` [T, K] x ``w`` [(H + 2G) * hd, K]^T (rows of queries, keys, values; ``[H * hd, K]`` and ``pages=None``
+    for a layer without keys of its own), queries and keys rotated by ``angles`` (from :func:`rope_angles`;
+    None: no rotation), queries written to ``q_out`` [T, H * hd], keys and values into ``pages`` at the tokens'
+    positions. All bfloat16."""
+    _want(x, "gemm_qkv_rope x", torch.bfloat16, 2)
+    _want(w, "gemm_qkv_rope w", torch.bfloat16, 2)
+    _want(q_out, "gemm_qkv_rope q_out", torch.bfloat16, 2)
+    _want(positions, "gemm_qkv_rope positions", torch.int32, 1)
+    _want(seq_ids, "gemm_qkv_rope seq_ids", torch.int32, 1)
+    _want(page_table, "gemm_qkv_rope page_table", torch.int32, 2)
+    T, K = x.shape
+    H, G, hd = num_heads, num_kv_heads, head_dim
+    heads = H + 2 * G if pages is not None else H
+    if w.shape != (heads * hd, K) or q_out.shape != (T, H * hd) or positions.numel() != T or seq_ids.numel() != T:
+        raise KernelError(f"gemm_qkv_rope: x {tuple(x.shape)}, w {tuple(w.shape)}, q_out {tuple(q_out.shape)}")
+    page_size = 0
+    if pages is not None:
+        _want(pages, "gemm_qkv_rope pages", torch.bfloat16, 5)
+        if pages.shape[1] != 2 or pages.shape[2] != G or pages.shape[4] != hd:
+            raise KernelError(f"gemm_qkv_rope: pages {tuple(pages.shape)} do not fit {G} key heads of {hd}")
+        page_size = pages.shape[3]
+    half = 0
+    if angles is not None:
+        _want(angles, "gemm_qkv_rope angles", torch.float32, 3)
+        half = angles.shape[1]
+        if angles.shape != (T, half, 2):
+            raise KernelError(f"gemm_qkv_rope: angles {tuple(angles.shape)} for {T} tokens")
+    lib = library("gemm_tcgen05")
+    _check(lib, lib.lp_gemm_qkv_rope(
+        x.data_ptr(), w.data_ptr(), T, K, K, K, _ptr(angles), half, 1 if interleaved else 0, positions.data_ptr(),
+        seq_ids.data_ptr(), page_table.data_ptr(), page_table.shape[1], q_out.data_ptr(), _ptr(pages), H, G, hd,
+        page_size, kernel_status().data_ptr(), _stream()))
 
 
 # --------------------------------------------------------------------------- matrix products

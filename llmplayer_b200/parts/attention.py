@@ -118,6 +118,21 @@ class Attention(Part):
             x = x.tensor()
         T = x.shape[0]
         table = ctx.page_tables[cache.group_index]
+        o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
+        if (rt.fast and T >= ops.PERSISTENT_MIN_TOKENS and not ctx.all_single and rotation is not None
+                and x.dtype == torch.bfloat16 and cache.pages.dtype == torch.bfloat16 and self.qkv.tensor_cores()
+                and ops.qkv_rope_serves(rotation, hd)):
+            # many tokens: the projection's epilogue rotates queries and keys and writes keys and values into the cache
+            q = ctx.buffer("q", (T, H * hd), torch.bfloat16)
+            with ops.section("attention.qkv"):
+                ops.gemm_qkv_rope(x, self.qkv.weight, ctx.angles(rotation) if rotation.rotary_dim else None,
+                                  rotation.interleaved, ctx.positions, ctx.seq_ids, table, q,
+                                  None if s.shares_kv else cache.pages, num_heads=H, num_kv_heads=G, head_dim=hd)
+            with ops.section("attention.scores"):
+                ops.attention(ctx, q, o, cache.pages, table, num_heads=H, num_kv_heads=G, head_dim=hd,
+                              scale=s.scale, window=s.window, fast=True)
+            with ops.section("attention.out"):
+                return self.out.accumulate(o, residual, ctx, then_norm)
         qkv = ctx.buffer("qkv", (T, self.qkv.out_features), torch.float32)
         with ops.section("attention.qkv"):
             self.qkv.store(x, qkv, ctx)
@@ -125,7 +140,6 @@ class Attention(Part):
             with ops.section("attention.position"):
                 self.position.apply(ctx, qkv, num_heads=H, num_kv_heads=0 if s.shares_kv else G, head_dim=hd)
             rotation = ops.NO_ROTATION
-        o = ctx.buffer("attn_out", (T, H * hd), rt.act_dtype)
         if rt.fast and ctx.all_single and cache.pages.dtype == torch.bfloat16 and hd % 16 == 0 and hd <= 256:
             # one token per sequence: rotation, cache write, attention and the merge of its shares in one kernel
             with ops.section("attention.scores"):

@@ -73,6 +73,14 @@ class Runtime:
         memo[id(t)] = (t, dev)
         return dev
 
+    def shared(self, key, make):
+        """One object per key for the whole model (parts of several layers that would otherwise each hold an
+        equal table, such as rotary frequencies, hold the same one)."""
+        memo = self.__dict__.setdefault("_shared", {})
+        if key not in memo:
+            memo[key] = make()
+        return memo[key]
+
     def forget_uploads(self) -> None:
         """Drop the host tensors remembered by :meth:`matrix` (after a model is loaded)."""
         self.__dict__.pop("_uploaded", None)

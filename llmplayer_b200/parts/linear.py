@@ -42,6 +42,10 @@ class Linear:
         # the tensor-core kernel wants bfloat16 operands and rows of a multiple of 8 elements (TMA strides)
         return self.runtime.fast and self.weight.dtype == torch.bfloat16 and self.in_features % 8 == 0
 
+    def tensor_cores(self) -> bool:
+        """Whether this map's products run on the tensor-core kernels (bfloat16 weights, rows of a multiple of 8)."""
+        return self._fast()
+
     def store(self, x: torch.Tensor, out: torch.Tensor, ctx=None) -> torch.Tensor:
         return self._run(x, out, ops.STORE, ctx)
 

@@ -64,8 +64,9 @@ class Rotary(Part):
 
     def load(self, tensors, runtime: Runtime) -> None:
         super().load(tensors, runtime)
-        self._rotation = ops.Rotation(inverse_frequencies(self.spec).to(runtime.device), self.spec.rotary_dim,
-                                      self.spec.pairing == "interleaved")
+        # layers with equal specifications share one table of frequencies (and, per step, one table of angles)
+        inv_freq = runtime.shared(("rotary", self.spec), lambda: inverse_frequencies(self.spec).to(runtime.device))
+        self._rotation = ops.Rotation(inv_freq, self.spec.rotary_dim, self.spec.pairing == "interleaved")
 
     def rotation(self) -> Optional[ops.Rotation]:
         return self._rotation

@@ -210,3 +210,62 @@ def test_few_token_product_applies_the_norm(M, N, K, mode):
     full = reference(normed.float().to(torch.bfloat16), w, code)
     got = out.double() * factor if deferred else out.double()
     assert rel_err(got, full) < 2e-2
+
+
+@pytest.mark.parametrize("H,G,hd,pairing,rotary", [(32, 8, 64, "split_half", True), (6, 4, 64, "split_half", True),
+                                                   (24, 8, 128, "split_half", True), (5, 3, 128, "interleaved", True),
+                                                   (3, 1, 256, "split_half", True), (7, 2, 32, "interleaved", True),
+                                                   (4, 2, 64, "split_half", False)])
+@pytest.mark.parametrize("shares_kv", [False, True])
+def test_projection_with_rotation_and_cache_write_in_its_epilogue(H, G, hd, pairing, rotary, shares_kv):
+    """The fused q|k|v projection of a long step against the separate kernels: the float32 product, then the
+    rotation kernel that writes queries and the cache. Two sequences of unequal lengths, the second continued
+    at a position in the middle of a page, pages scattered."""
+    from llmplayer_b200.kernels import ops
+    dev = "cuda:0"
+    torch.manual_seed(H * 100 + hd)
+    K = 328
+    lengths, starts = [700, 333], [0, 41]                       # new tokens and first positions of the two sequences
+    T = sum(lengths)
+    heads = H if shares_kv else H + 2 * G
+    x = torch.randn(T, K, device=dev).to(torch.bfloat16)
+    w = (torch.randn(heads * hd, K, device=dev) / K ** 0.5).to(torch.bfloat16)
+    positions = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lengths)]).to(torch.int32).to(dev)
+    seq_ids = torch.cat([torch.full((n,), i) for i, n in enumerate(lengths)]).to(torch.int32).to(dev)
+    width = max(-(-(s + n) // 64) for s, n in zip(starts, lengths))
+    num_pages = 2 * width + 3
+    order = torch.randperm(num_pages)[:2 * width].reshape(2, width).to(torch.int32).to(dev)
+    rd = hd if rotary else 0
+    inv = (torch.rand(max(rd // 2, 1), device=dev) * 0.3) if rd else None
+    rotation = ops.Rotation(inv, rd, pairing == "interleaved") if rd else ops.NO_ROTATION
+    assert ops.qkv_rope_serves(rotation, hd)
+
+    def fresh_pages():
+        return torch.full((num_pages, 2, G, 64, hd), 5.0, device=dev, dtype=torch.bfloat16)
+
+    # separate kernels
+    qkv = torch.empty(T, heads * hd, device=dev)
+    ops.gemm(x, w, qkv, ops.STORE)
+    q_ref = torch.empty(T, H * hd, device=dev, dtype=torch.bfloat16)
+    pages_ref = fresh_pages()
+    ops.rope_cache_write(qkv, rotation, positions, seq_ids, order, q_ref, None if shares_kv else pages_ref,
+                         num_heads=H, num_kv_heads=G, head_dim=hd)
+    # fused
+    q_got = torch.full_like(q_ref, 9.0)
+    pages_got = fresh_pages()
+    angles = None
+    if rd:
+        angles = torch.empty(T, rd // 2, 2, device=dev)
+        ops.rope_angles(positions, rotation, angles)
+    ops.gemm_qkv_rope(x, w, angles, pairing == "interleaved", positions, seq_ids, order, q_got,
+                      None if shares_kv else pages_got, num_heads=H, num_kv_heads=G, head_dim=hd)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    scale = float(q_ref.float().abs().max())
+    assert float((q_got.float() - q_ref.float()).abs().max()) <= 8e-3 * scale        # one bfloat16 rounding apart at most
+    if not shares_kv:
+        assert float((pages_got.float() - pages_ref.float()).abs().max()) <= 8e-3 * max(scale, 5.0)
+        untouched = pages_ref == 5.0
+        assert torch.equal(pages_got[untouched], pages_ref[untouched])              # nothing written beside the tokens' rows
+    else:
+        assert torch.equal(pages_got, fresh_pages())
