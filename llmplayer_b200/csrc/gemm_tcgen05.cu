@@ -280,6 +280,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (!ready && lane == 0) atomicExch(status, 3);
         tcgen05_fence_after();
         const bool go = __all_sync(0xffffffffu, ready && *failed == 0);
+        if (norm.weight == nullptr && norm.clear != nullptr && ready) {
+            // no norm to follow, only a buffer to clear on the side: all CTAs share it (the x tiles have arrived,
+            // so the kernel before this one, the buffer's last reader, has ended)
+            const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+            const long long ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
+            for (long long i = cta * 128 + threadIdx.x - 64; i < norm.clear_count; i += ctas * 128) norm.clear[i] = 0.f;
+        }
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         constexpr int CHUNK = BLOCK_TOK >= 32 ? 32 : 16;
         if (MODE != LP_GEMM_SWIGLU) {
@@ -653,9 +660,9 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 // Settings of the few-token product (lp_gemm_configure; until that is called, the environment's
 // LLMPLAYER_B200_FEWTOK / _RING_SHARED / _RING_ALONE or the defaults 1 / 6 / 10).
-struct FewSettings { int enabled, ring_shared, ring_alone, ring_alone_tile; bool decided; };
+struct FewSettings { int enabled, ring_shared, ring_alone, ring_alone_tile, ring_normed; bool decided; };
 static FewSettings& few_settings() {
-    static FewSettings st = {1, 6, 10, 0, false};
+    static FewSettings st = {1, 6, 10, 0, 6, false};
     if (!st.decided) {
         const char* v = getenv("LLMPLAYER_B200_FEWTOK");
         st.enabled = (v && v[0] == '0') ? 0 : 1;
@@ -667,6 +674,8 @@ static FewSettings& few_settings() {
         if (st.ring_shared < 2) st.ring_shared = 2;
         v = getenv("LLMPLAYER_B200_RING_ALONE_TILE");
         st.ring_alone_tile = v ? atoi(v) : 0;
+        v = getenv("LLMPLAYER_B200_RING_NORMED");
+        st.ring_normed = v ? atoi(v) : 6;
         st.decided = true;
     }
     return st;
@@ -722,6 +731,335 @@ int dispatch_fewtok(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw,
 }
 
 static bool fewtok_enabled() { return few_settings().enabled != 0; }
+
+// ------------------------------------------------------------------ 17 to 64 tokens with the norm on the way in
+// The one-tile tcgen05 product for a decode batch beyond what the mma.sync kernel above serves, taking the
+// float32 residual stream and applying an RMS norm on the way in, as that kernel does: the tile of x comes as
+// float32 (two boxes of rows x 32 values per k-block) with the gain's 64 values; four "maker" warps turn it into
+// the bfloat16 operand bfloat16(x * gain) in place of the first box (every value is read before any is written),
+// sum x^2 per row, and hand the stage to the MMA thread through a barrier of their own. The row factor
+// 1 / sqrt(mean x^2 + eps) is applied to the sums in the epilogue when the CTA sees the whole K range; else the
+// CTAs of the first feature tile add their shares of the sums of squares to `sumsq_out` and the reader of the
+// output applies the factor. Saves the norm kernels in front of the q|k|v and the gated products of a layer.
+//
+// Measured at the 1B shape (ms per decode step, this kernel against norm kernels of their own): 24 tokens
+// 0.960 / 1.008, 32 tokens 0.992 / 1.027; with the 64-token tile 48 tokens 1.279 / 1.169 and 64 tokens
+// 1.303 / 1.248: there the float32 tile makes 80 KB of shared-memory traffic per k-block against 48 KB, and the
+// callers keep the norm kernels. A variant whose makers read x from L2 with plain loads, two k-blocks ahead
+// (no float32 tile in shared memory), was slower at every size (1.17 ms at 24 tokens): TMA keeps as many
+// k-blocks of x in flight as the ring has stages, the makers' registers cannot.
+constexpr int NORMED_THREADS = 320;       // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue, warps 6-9: operand makers
+
+template <int BLOCK_TOK> struct NormedTile {
+    static constexpr int W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
+    static constexpr int X_BOX_BYTES = BLOCK_TOK * 128;            // BLOCK_TOK rows x 32 float32
+    static constexpr int X_BYTES = 2 * X_BOX_BYTES;
+    static constexpr int GAIN_BYTES = 1024;                        // 64 float32 of gain, padded to the tiles' alignment
+    static constexpr int STAGE_BYTES = W_BYTES + X_BYTES + GAIN_BYTES;
+    static constexpr int TAIL_BYTES = 1024 + 768;                  // alignment slack, barriers, row factors
+    static constexpr int MAX_STAGES = 8;
+    static constexpr int STAGES_SHARED = (110 * 1024 - TAIL_BYTES) / STAGE_BYTES;          // two CTAs on an SM
+    static constexpr int STAGES_ALONE =
+        (227 * 1024 - TAIL_BYTES) / STAGE_BYTES < MAX_STAGES ? (227 * 1024 - TAIL_BYTES) / STAGE_BYTES : MAX_STAGES;
+    static constexpr int TMEM_COLS = BLOCK_TOK < 32 ? 32 : BLOCK_TOK;
+    static_assert(BLOCK_TOK == 32 || BLOCK_TOK == 64, "token tiles of 32 or 64");
+    static_assert(STAGES_SHARED >= 2, "at least two stages");
+};
+
+// MODE: STORE or SWIGLU (interleaved rows, 64 output features per CTA). tokens <= BLOCK_TOK (one token tile).
+template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
+__global__ void __launch_bounds__(NORMED_THREADS, 1)
+gemm_tcgen05_normed_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                           void* __restrict__ out, int tokens, int features, int ldc, int k_blocks,
+                           int k_blocks_per_split, int num_stages, int* __restrict__ status, NormBefore before) {
+    using T = NormedTile<BLOCK_TOK>;
+    constexpr int MAXS = T::MAX_STAGES;
+    const int STAGES = num_stages;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + STAGES * T::STAGE_BYTES);
+    uint64_t* empty = full + MAXS;
+    uint64_t* made = empty + MAXS;                 // the bfloat16 operand of the stage is ready
+    uint64_t* acc_ready = made + MAXS;
+    uint32_t* tmem_slot = (uint32_t*)(acc_ready + 1);
+    volatile uint32_t* failed = tmem_slot + 1;
+    float* row_scale = (float*)(tmem_slot + 4);    // [BLOCK_TOK]
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int feat0 = blockIdx.x * BLOCK_FEAT;
+    const int kb_begin = blockIdx.z * k_blocks_per_split;
+    const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
+    const int nkb = kb_end - kb_begin;
+    const bool whole_k = gridDim.z == 1;
+
+    lp_grid_release();
+    if (threadIdx.x == 0) {
+        *failed = 0;
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); mbar_init(&made[s], 4); }
+        mbar_init(acc_ready, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)T::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            constexpr int TILE_BYTES = T::W_BYTES + T::X_BYTES;
+            auto load_constants = [&](int i, int s) {            // what nothing in the step writes: weights, gain
+                uint8_t* stage = smem + s * T::STAGE_BYTES;
+                const int k = (kb_begin + i) * BLOCK_K;
+                const uint32_t gain_bytes = (uint32_t)min(BLOCK_K, before.K - k) * 4u;
+                mbar_expect_tx(&full[s], TILE_BYTES + gain_bytes);
+                tma_load_2d(stage, &map_w, k, blockIdx.x * BLOCK_FEAT, &full[s]);
+                bulk_load(stage + TILE_BYTES, before.gain + k, gain_bytes, &full[s]);
+            };
+            auto load_activations = [&](int i, int s) {          // what the previous kernel produced
+                uint8_t* xs = smem + s * T::STAGE_BYTES + T::W_BYTES;
+                const int k = (kb_begin + i) * BLOCK_K;
+                tma_load_2d(xs, &map_x, k, 0, &full[s]);
+                tma_load_2d(xs + T::X_BOX_BYTES, &map_x, k + 32, 0, &full[s]);
+            };
+            const int early = min(nkb, STAGES);
+            for (int i = 0; i < early; ++i) load_constants(i, i);
+            lp_grid_wait();
+            for (int i = 0; i < early; ++i) load_activations(i, i);
+            int issued = early;
+            bool ok = true;
+            for (int i = early; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
+                load_constants(i, s);
+                load_activations(i, s);
+                issued = i + 1;
+            }
+            if (!ok) {
+                for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_TOK >> 3) << 17) |
+                                       ((uint32_t)(BLOCK_FEAT >> 4) << 24);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(&made[s], (i / STAGES) & 1)) { atomicExch(status, 2); *failed = 1; break; }
+                tcgen05_fence_after();
+                const uint32_t w_addr = smem_u32(smem + s * T::STAGE_BYTES);
+                const uint64_t dw = smem_desc(w_addr), dx = smem_desc(w_addr + T::W_BYTES);
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const uint64_t step = (uint64_t)((k * UMMA_K * 2) >> 4);
+                    tcgen05_mma(tmem_base, dw + step, dx + step, idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(&empty[s]);
+            }
+            tcgen05_commit(acc_ready);
+        }
+        __syncwarp();
+    } else if (warp >= 6) {
+        // ------------------------------------------------------------ operand makers (128 threads)
+        // float4 q of the k-block: row q / 16, values 4 (q % 16) ..; thread c takes q = c, c + 128, ...: a fixed
+        // place in the row, rows 8 apart, so sixteen neighbouring threads share a row
+        const int c = threadIdx.x - 192;
+        constexpr int PASSES = BLOCK_TOK / 8;
+        const int kq = c & 15, k = kq * 4;
+        float ss[PASSES];
+#pragma unroll
+        for (int it = 0; it < PASSES; ++it) ss[it] = 0.f;
+        bool ok = true;
+        for (int i = 0; i < nkb && ok; ++i) {
+            const int s = i % STAGES;
+            if (!mbar_wait(&full[s], (i / STAGES) & 1)) { if (lane == 0) atomicExch(status, 4); *failed = 1; ok = false; }
+            uint8_t* x_tile = smem + s * T::STAGE_BYTES + T::W_BYTES;
+            const float* gain_tile = reinterpret_cast<const float*>(x_tile + T::X_BYTES);
+            const int k_abs = (kb_begin + i) * BLOCK_K;
+            float4 gn = make_float4(0.f, 0.f, 0.f, 0.f);           // the gain beyond K is unset (and x is zero there)
+            if (ok && k_abs + k < before.K) gn = *reinterpret_cast<const float4*>(gain_tile + k);
+            uint2 packed[PASSES];
+#pragma unroll
+            for (int it = 0; it < PASSES; ++it) {
+                const int row = (c >> 4) + it * 8;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (ok) v = *reinterpret_cast<const float4*>(
+                    x_tile + (kq >> 3) * T::X_BOX_BYTES + row * 128 + (((kq & 7) ^ (row & 7)) << 4));
+                ss[it] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * gn.x, v.y * gn.y);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * gn.z, v.w * gn.w);
+                packed[it].x = *reinterpret_cast<uint32_t*>(&lo);
+                packed[it].y = *reinterpret_cast<uint32_t*>(&hi);
+            }
+            asm volatile("bar.sync 2, 128;" ::: "memory");        // every maker has read its share of the float32 tile
+#pragma unroll
+            for (int it = 0; it < PASSES; ++it) {
+                const int row = (c >> 4) + it * 8;
+                *reinterpret_cast<uint2*>(x_tile + row * 128 + (((k >> 3) ^ (row & 7)) << 4) + (k & 7) * 2) = packed[it];
+            }
+            // written through the generic proxy, read by the MMA through the async proxy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&made[s])) : "memory");
+        }
+        // a row's sum of x^2: over the sixteen threads that shared it
+#pragma unroll
+        for (int it = 0; it < PASSES; ++it) {
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) ss[it] += __shfl_xor_sync(0xffffffffu, ss[it], o);
+        }
+        if (kq == 0) {
+#pragma unroll
+            for (int it = 0; it < PASSES; ++it) {
+                const int row = (c >> 4) + it * 8;
+                if (whole_k) row_scale[row] = 1.0f / sqrtf(ss[it] / (float)before.K + before.eps);
+                else if (blockIdx.x == 0 && ok && row < tokens) atomicAdd(before.sumsq_out + row, ss[it]);
+            }
+        }
+        if (whole_k) asm volatile("bar.sync 1, 256;" ::: "memory");     // with the four epilogue warps
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        lp_grid_wait();
+        if (before.zero != nullptr) {              // all CTAs share the clearing
+            const int cta = blockIdx.z * gridDim.x + blockIdx.x, ctas = gridDim.x * gridDim.z;
+            for (int i = cta * 128 + threadIdx.x - 64; i < before.zero_count; i += ctas * 128) before.zero[i] = 0.f;
+        }
+        const int quarter = warp & 3;
+        const bool ready = mbar_wait(acc_ready, 0);
+        if (!ready && lane == 0) atomicExch(status, 3);
+        tcgen05_fence_after();
+        if (whole_k) asm volatile("bar.sync 1, 256;" ::: "memory");     // the makers have written the rows' factors
+        const bool go = __all_sync(0xffffffffu, ready && *failed == 0);
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        if (MODE != LP_GEMM_SWIGLU) {
+            if (go) {
+                const int f = feat0 + quarter * 32 + lane;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BLOCK_TOK; c0 += 32) {
+                    uint32_t g[32];
+                    tmem_ld32(lane_addr + c0, g);
+                    tmem_ld_wait();
+                    if (f < features) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int t = c0 + j;
+                            if (t >= tokens) break;
+                            float v = __uint_as_float(g[j]);
+                            if (whole_k) v *= row_scale[t];
+                            const size_t at = (size_t)t * ldc + f;
+                            if (ATOMIC) atomicAdd((float*)out + at, v);
+                            else if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                            else ((float*)out)[at] = v;
+                        }
+                    }
+                }
+            }
+        } else {
+            // rows 0..63 of the tile are gate, rows 64..127 up, of the same 64 output features; the ring's memory
+            // (every load has been consumed) carries the gate half across
+            float* cross = reinterpret_cast<float*>(smem);            // [64][BLOCK_TOK + 1]
+            constexpr int LD = BLOCK_TOK + 1;
+            const int local = (quarter & 1) * 32 + lane;
+            if (go && quarter < 2) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BLOCK_TOK; c0 += 32) {
+                    uint32_t g[32];
+                    tmem_ld32(lane_addr + c0, g);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) cross[local * LD + c0 + j] = __uint_as_float(g[j]);
+                }
+            }
+            asm volatile("bar.sync 3, 128;" ::: "memory");            // the four epilogue warps
+            if (go && quarter >= 2) {
+                const int f = blockIdx.x * (BLOCK_FEAT / 2) + local;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BLOCK_TOK; c0 += 32) {
+                    uint32_t u[32];
+                    tmem_ld32(lane_addr + c0, u);
+                    tmem_ld_wait();
+                    if (f < features) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const int t = c0 + j;
+                            if (t >= tokens) break;
+                            const float rs = row_scale[t];               // the gated product is never split along K
+                            const float gate = cross[local * LD + c0 + j] * rs;
+                            const float v = __fdividef(gate, 1.0f + __expf(-gate)) * (__uint_as_float(u[j]) * rs);
+                            const size_t at = (size_t)t * ldc + f;
+                            if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                            else ((float*)out)[at] = v;
+                        }
+                    }
+                }
+            }
+        }
+        tcgen05_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS));
+    }
+}
+
+template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
+int launch_normed(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
+                  int splits, int* status, const NormBefore& before, cudaStream_t stream) {
+    using T = NormedTile<BLOCK_TOK>;
+    auto kernel = gemm_tcgen05_normed_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC>;
+    static bool configured = false;
+    if (!configured) {
+        const int most = T::STAGES_ALONE * T::STAGE_BYTES + T::TAIL_BYTES;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+        if (e != cudaSuccess) LP_REFUSE("gemm: cannot reserve %d bytes of shared memory: %s", most, cudaGetErrorString(e));
+        configured = true;
+    }
+    const int per_split = (k_blocks + splits - 1) / splits;
+    const int grid_z = (k_blocks + per_split - 1) / per_split;
+    const int per_cta = MODE == LP_GEMM_SWIGLU ? BLOCK_FEAT / 2 : BLOCK_FEAT;
+    dim3 grid((features + per_cta - 1) / per_cta, 1, grid_z);
+    // a float32 tile of x beside each tile of weights shrinks what a ring of a given size keeps in flight: a grid
+    // of at most one CTA per SM takes up to lp_gemm_configure's ring_normed stages (0: never more than what lets
+    // two CTAs share an SM)
+    int stages = T::STAGES_SHARED;
+    const int wanted = few_settings().ring_normed;
+    if ((long long)grid.x * grid.z <= lp_sm_count() && wanted > stages) stages = wanted < T::STAGES_ALONE ? wanted : T::STAGES_ALONE;
+    if (stages > per_split) stages = per_split > T::STAGES_SHARED ? per_split : T::STAGES_SHARED;
+    const int smem = stages * T::STAGE_BYTES + T::TAIL_BYTES;
+    cudaError_t err = lp_launch(kernel, grid, NORMED_THREADS, smem, stream, mw, mx, out, tokens, features, ldc,
+                                k_blocks, per_split, stages, status, before);
+    if (err != cudaSuccess) {
+        snprintf(lp_error_text, sizeof(lp_error_text), "gemm_tcgen05_normed: %s", cudaGetErrorString(err));
+        return (int)err;
+    }
+    return lp_check_launch("gemm_tcgen05_normed");
+}
+
+template <int BLOCK_TOK>
+int dispatch_normed(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens,
+                    int features, int ldc, int k_blocks, int splits, int* status, const NormBefore& before,
+                    cudaStream_t stream) {
+#define LP_GO(MODE, BF, AT) \
+    return launch_normed<BLOCK_TOK, MODE, BF, AT>(mw, mx, out, tokens, features, ldc, k_blocks, splits, status, before, stream)
+    if (mode == LP_GEMM_SWIGLU) {
+        if (out_bf16) LP_GO(LP_GEMM_SWIGLU, true, false);
+        LP_GO(LP_GEMM_SWIGLU, false, false);
+    }
+    if (atomic) LP_GO(LP_GEMM_STORE, false, true);
+    if (out_bf16) LP_GO(LP_GEMM_STORE, true, false);
+    LP_GO(LP_GEMM_STORE, false, false);
+#undef LP_GO
+}
 
 // ------------------------------------------------------------------ persistent form for prompts
 // One CTA per SM walks over output tiles (tile = blockIdx.x, + gridDim.x, ...). Tensor memory holds two
@@ -1172,12 +1510,13 @@ extern "C" int lp_gemm_withhold_next(int kblock) {
 // that kernel's ring when two CTAs share an SM / when a CTA has an SM to itself (at least 2 each); ring_alone_tile:
 // the most stages the one-tile tcgen05 kernel takes when its grid has no more CTAs than there are SMs (0: never
 // more than what lets two CTAs share an SM).
-extern "C" int lp_gemm_configure(int fewtok, int ring_shared, int ring_alone, int ring_alone_tile) {
+extern "C" int lp_gemm_configure(int fewtok, int ring_shared, int ring_alone, int ring_alone_tile, int ring_normed) {
     FewSettings& st = few_settings();
     st.enabled = fewtok ? 1 : 0;
     st.ring_shared = ring_shared < 2 ? 2 : ring_shared;
     st.ring_alone = ring_alone < 2 ? 2 : ring_alone;
     st.ring_alone_tile = ring_alone_tile;
+    st.ring_normed = ring_normed;
     return 0;
 }
 
@@ -1299,7 +1638,8 @@ extern "C" int lp_gemm_tcgen05(const void* X, const void* W, void* out, int out_
     }
 }
 
-// A product for at most 64 tokens (the mma.sync kernel above) with what a decode step fuses around it.
+// A product for at most 64 tokens with what a decode step fuses around it: the mma.sync kernel above up to 16
+// tokens, the one-tile tcgen05 kernels (with the norm on the way in, or plain) beyond.
 // x_dtype LP_F32: X is the float32 residual stream and the product applies the RMS norm (gain, eps) on the
 // way in; with splits > 1 the output then still lacks the rows' factors and `sumsq_out` [tokens] (zero before
 // the call) receives sum x^2 per token for the reader to apply them. x_dtype LP_BF16: X as in lp_gemm_tcgen05.
@@ -1331,16 +1671,30 @@ extern "C" int lp_gemm_fewtok(const void* X, int x_dtype, const void* W, void* o
     CUtensorMap mw, mx;
     int rc = make_map(&mw, W, w_rows, K, ldw, BLOCK_FEAT);
     if (rc) return rc;
-    const int nt = tokens <= 8 ? 1 : tokens <= 16 ? 2 : tokens <= 32 ? 4 : 8;
-    const int x_rows = nt <= 2 ? 16 : 8 * nt;
-    rc = xnorm ? make_map_f32(&mx, X, tokens, K, ldx, x_rows) : make_map(&mx, X, tokens, K, ldx, x_rows);
-    if (rc) return rc;
     const NormAfter after{};
     const NormBefore before{gain, eps, K, sumsq_out, zero, zero ? zero_count : 0};
     const bool bf = out_dtype == LP_BF16;
     const int mmode = mode == LP_GEMM_SWIGLU ? LP_GEMM_SWIGLU : LP_GEMM_STORE;
+    if (tokens > 16) {
+        // beyond what the mma.sync consumers serve well: the tcgen05 kernels, with the norm on the way in or without
+        const int tile = tokens <= 32 ? 32 : 64;
+        if (xnorm) {
+            rc = make_map_f32(&mx, X, tokens, K, ldx, tile);
+            if (rc) return rc;
+            if (tile == 32) return dispatch_normed<32>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, status, before, stream);
+            return dispatch_normed<64>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, status, before, stream);
+        }
+        rc = make_map(&mx, X, tokens, K, ldx, tile);
+        if (rc) return rc;
+        const NormAfter side{nullptr, nullptr, 0.f, nullptr, zero, zero ? zero_count : 0};
+        if (tile == 32) return dispatch<32>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, side, stream);
+        return dispatch<64>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, features, status, side, stream);
+    }
+    // at most 16 tokens: the mma.sync consumers, one or two tiles of 8 tokens
+    rc = xnorm ? make_map_f32(&mx, X, tokens, K, ldx, 16) : make_map(&mx, X, tokens, K, ldx, 16);
+    if (rc) return rc;
 #define LP_FEW(NT, XN) dispatch_fewtok<NT, XN>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, status, after, before, stream)
-    if (xnorm) return nt == 1 ? LP_FEW(1, true) : nt == 2 ? LP_FEW(2, true) : nt == 4 ? LP_FEW(4, true) : LP_FEW(8, true);
-    return nt == 1 ? LP_FEW(1, false) : nt == 2 ? LP_FEW(2, false) : nt == 4 ? LP_FEW(4, false) : LP_FEW(8, false);
+    if (xnorm) return tokens <= 8 ? LP_FEW(1, true) : LP_FEW(2, true);
+    return tokens <= 8 ? LP_FEW(1, false) : LP_FEW(2, false);
 #undef LP_FEW
 }

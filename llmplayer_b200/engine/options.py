@@ -39,6 +39,7 @@ class EngineOptions:
     ring_shared: Optional[int] = None
     ring_alone: Optional[int] = None
     ring_alone_tile: Optional[int] = None
+    ring_normed: Optional[int] = None
 
     def __post_init__(self):
         if self.dtype not in ("bfloat16", "float32"):
@@ -54,7 +55,7 @@ class EngineOptions:
 
     def kernel_settings(self) -> dict:
         return {name: getattr(self, name) for name in ("pdl", "few_tokens", "fewtok_kernel", "ring_shared", "ring_alone",
-                                                          "ring_alone_tile")
+                                                          "ring_alone_tile", "ring_normed")
                 if getattr(self, name) is not None}
 
     def with_changes(self, **changes) -> "EngineOptions":

@@ -40,7 +40,7 @@ _SIGNATURES = {
                             ctypes.c_longlong, _P, _P],
         "lp_gemm_persistent": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P],
         "lp_gemm_fewtok": [_P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P, _P, _F, _P, _P, _I, _P],
-        "lp_gemm_configure": [_I, _I, _I, _I],
+        "lp_gemm_configure": [_I, _I, _I, _I, _I],
         "lp_gemm_qkv_rope": [_P, _P, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, _P],
     },
     "attention_mma": {
@@ -89,21 +89,25 @@ class KernelSettings:
     whether 16-token tiles of the general product go to the mma.sync few-token kernel. ``ring_shared`` /
     ``ring_alone``: stages of that kernel's ring when two CTAs share an SM / when a CTA has one to itself.
     ``ring_alone_tile``: the most stages the one-tile tcgen05 product takes when its grid has no more CTAs than SMs
-    (0, the default: never more than what lets two CTAs share an SM; a deeper ring measured slower)."""
+    (0, the default: never more than what lets two CTAs share an SM; a deeper ring measured slower).
+    ``ring_normed``: the same for the tcgen05 product with the norm on the way in (17 to 64 tokens), whose stages
+    also hold a float32 tile of x; there the deeper ring measured faster."""
     pdl: bool = True
-    few_tokens: int = 16
+    few_tokens: int = 32
     fewtok_kernel: bool = True
     ring_shared: int = 6
     ring_alone: int = 10
     ring_alone_tile: int = 0
+    ring_normed: int = 6
 
     @classmethod
     def from_env(cls) -> "KernelSettings":
-        return cls(pdl=_env_int("LLMPLAYER_B200_PDL", 1) != 0, few_tokens=_env_int("LLMPLAYER_B200_FEW_TOKENS", 16),
+        return cls(pdl=_env_int("LLMPLAYER_B200_PDL", 1) != 0, few_tokens=_env_int("LLMPLAYER_B200_FEW_TOKENS", 32),
                    fewtok_kernel=_env_int("LLMPLAYER_B200_FEWTOK", 1) != 0,
                    ring_shared=_env_int("LLMPLAYER_B200_RING_SHARED", 6),
                    ring_alone=_env_int("LLMPLAYER_B200_RING_ALONE", 10),
-                   ring_alone_tile=_env_int("LLMPLAYER_B200_RING_ALONE_TILE", 0))
+                   ring_alone_tile=_env_int("LLMPLAYER_B200_RING_ALONE_TILE", 0),
+                   ring_normed=_env_int("LLMPLAYER_B200_RING_NORMED", 6))
 
 
 settings = KernelSettings.from_env()
@@ -115,7 +119,7 @@ def _apply_settings(name: str, lib: ctypes.CDLL) -> None:
     lib.lp_set_pdl(1 if settings.pdl else 0)
     if name == "gemm_tcgen05":
         lib.lp_gemm_configure(1 if settings.fewtok_kernel else 0, int(settings.ring_shared), int(settings.ring_alone),
-                              int(settings.ring_alone_tile))
+                              int(settings.ring_alone_tile), int(settings.ring_normed))
 
 
 def configure(**changes) -> KernelSettings:
@@ -644,16 +648,18 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
     return out
 
 
-FEW_TOKENS_MAX = 64                  # what the few-token kernel takes
+FEW_TOKENS_MAX = 64                  # what the few-token entry takes
 # Up to where the parts choose it with the norm inside (``settings.few_tokens``). Measured at the 1B shape (ms per
 # step, norm inside against separate norm kernels): 8 tokens 0.70 / 0.76, 12 tokens 0.84 / 0.87, 16 tokens
-# 0.85 / 0.88; at 32 tokens the mma.sync kernel itself loses to the tcgen05 one (1.34 against 1.02).
+# 0.85 / 0.88 (the mma.sync kernel); 24 tokens 0.96 / 1.01, 32 tokens 0.99 / 1.03 (the tcgen05 kernel with operand
+# makers); 48 tokens 1.28 / 1.17 and 64 tokens 1.30 / 1.25: beyond 32 tokens the norm kernels stay.
 FEW_TOKENS = max(0, min(int(settings.few_tokens), FEW_TOKENS_MAX))
 
 
 def gemm_few(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, norm=None,
              sumsq: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None) -> bool:
-    """out (=|+=) f(x) @ w.T for at most ``FEW_TOKENS`` rows, with what a decode step fuses around it.
+    """out (=|+=) f(x) @ w.T for at most ``FEW_TOKENS_MAX`` rows, with what a decode step fuses around it
+    (up to 16 rows the mma.sync kernel, beyond that the one-tile tcgen05 kernels).
 
     ``norm = (gain, eps)``: ``x`` is the float32 residual stream and the product applies the RMS norm on
     the way in. If the K range is then shared out over CTAs (few output features), ``out`` still lacks each

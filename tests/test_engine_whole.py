@@ -99,11 +99,12 @@ def test_full_width_layers_bfloat16_against_float32(tmp_path):
     assert_close(logits["bfloat16"][1], ref_tail, "bfloat16", "1B widths, decoded", config="1B")
 
 
-@pytest.mark.parametrize("batch", [12, 20])
+@pytest.mark.parametrize("batch", [12, 20, 40])
 def test_full_width_decode_batches(tmp_path, batch):
     """Sequences of unequal lengths decoding together at the Llama-3.2-1B widths, against the float32 engine.
     Twelve: the few-token products with two tiles of 8 tokens, the norm inside them and the row factor left to
-    the attention kernel. Twenty: the tcgen05 products with a 32-token tile and norm kernels of their own."""
+    the attention kernel. Twenty: the tcgen05 products with a 32-token tile, the norm applied by operand makers
+    inside them. Forty: 64-token tiles and norm kernels of their own."""
     from llmplayer_b200 import Engine
     from llmplayer_b200.config import config_from_dict
     from llmplayer_b200.weights import write_random_model

@@ -149,7 +149,8 @@ FEW_SHAPES = [(1, 64, 64), (3, 200, 72), (8, 3072, 2048), (9, 130, 200), (16, 52
 @pytest.mark.parametrize("M,N,K", FEW_SHAPES)
 @pytest.mark.parametrize("mode", ["store", "accumulate", "swiglu"])
 def test_few_token_product(M, N, K, mode):
-    """The mma.sync kernel for at most 64 rows with bfloat16 activations, against a float64 product."""
+    """The products for at most 64 rows with bfloat16 activations (the mma.sync kernel up to 16 rows, the one-tile
+    tcgen05 kernel beyond), against a float64 product."""
     from llmplayer_b200.kernels import ops
     torch.manual_seed(M * 11 + N + K)
     dev = "cuda:0"
