@@ -52,7 +52,8 @@ constexpr int THREADS = 192;      // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5:
 // The weight tile(s) of one k-block. WIDE: gate rows of two neighbouring 64-feature blocks form the
 // first 128-row tile, their up rows the second (the tensor map's box is 64 rows then).
 template <int MODE>
-__device__ __forceinline__ void load_weights(uint8_t* stage, const CUtensorMap* map_w, int k, int cta, uint64_t* bar) {
+__device__ __forceinline__ void load_weights(uint8_t* stage, const CUtensorMap* map_w, int k, int cta, uint64_t* bar,
+                                             uint64_t read_once = 0) {
     if (MODE == LP_GEMM_SWIGLU_TOKM || MODE == LP_GEMM_QKV_TOKM) {
         tma_load_2d(stage, map_w, k, cta * 256, bar);            // one box of 256 rows (gated: gate | up | gate | up of 128 features)
     } else if (MODE == LP_GEMM_SWIGLU_WIDE) {
@@ -61,6 +62,8 @@ __device__ __forceinline__ void load_weights(uint8_t* stage, const CUtensorMap* 
         tma_load_2d(stage + 8192, map_w, k, row + 128, bar);     // gate, features 128 cta + 64 ..
         tma_load_2d(stage + 16384, map_w, k, row + 64, bar);     // up
         tma_load_2d(stage + 24576, map_w, k, row + 192, bar);    // up
+    } else if (read_once != 0) {
+        tma_load_2d_hint(stage, map_w, k, cta * BLOCK_FEAT, bar, read_once);
     } else {
         tma_load_2d(stage, map_w, k, cta * BLOCK_FEAT, bar);
     }
@@ -207,6 +210,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
+            // with one token tile each weight is read once: its lines need not stay in L2
+            const uint64_t read_once = gridDim.y == 1 ? l2_policy_evict_first() : 0;
             // Weights are written by no kernel of a step: the first ring of weight tiles is requested
             // before waiting for the previous kernel, the activation tiles only after it.
             const int early = min(nkb, num_stages);
@@ -215,7 +220,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint8_t* stage = smem + i * T::STAGE_BYTES;
                 mbar_expect_tx(&full[i], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BLOCK_K;
-                load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[i]);
+                load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[i], read_once);
             }
             lp_grid_wait();
             for (int i = 0; i < early; ++i) {
@@ -233,7 +238,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 uint8_t* stage = smem + s * T::STAGE_BYTES;
                 mbar_expect_tx(&full[s], T::STAGE_BYTES);
                 const int k = (kb_begin + i) * BLOCK_K;
-                load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[s]);
+                load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[s], read_once);
                 tma_load_2d(stage + T::W_TILES * T::W_BYTES, &map_x, k, tok0, &full[s]);
             }
             if (!ok || *failed) {
@@ -518,6 +523,7 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             // weights are written by no kernel of a step: the first ring is requested before waiting for
             // the previous kernel, the activation tiles only after it
             constexpr int TILE_BYTES = FEW_W_BYTES + FT::X_BYTES;
+            const uint64_t read_once = l2_policy_evict_first();      // a decode step reads each weight once
             // what nothing in the step writes (weights, the norm's gain) ...
             auto load_constants = [&](int i, int s) {
                 uint8_t* stage = smem + s * FEW_STAGE_BYTES;
@@ -525,7 +531,7 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 uint32_t gain_bytes = 0;
                 if (XNORM) gain_bytes = (uint32_t)min(BLOCK_K, before.K - k) * 4u;
                 mbar_expect_tx(&full[s], TILE_BYTES + gain_bytes);
-                tma_load_2d(stage, &map_w, k, blockIdx.x * BLOCK_FEAT, &full[s]);
+                tma_load_2d_hint(stage, &map_w, k, blockIdx.x * BLOCK_FEAT, &full[s], read_once);
                 if (XNORM) bulk_load(stage + TILE_BYTES, before.gain + k, gain_bytes, &full[s]);
             };
             // ... and the activations, which the previous kernel produced
@@ -815,12 +821,13 @@ gemm_tcgen05_normed_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         // ------------------------------------------------------------ producer
         if (lane == 0) {
             constexpr int TILE_BYTES = T::W_BYTES + T::X_BYTES;
+            const uint64_t read_once = l2_policy_evict_first();      // a decode step reads each weight once
             auto load_constants = [&](int i, int s) {            // what nothing in the step writes: weights, gain
                 uint8_t* stage = smem + s * T::STAGE_BYTES;
                 const int k = (kb_begin + i) * BLOCK_K;
                 const uint32_t gain_bytes = (uint32_t)min(BLOCK_K, before.K - k) * 4u;
                 mbar_expect_tx(&full[s], TILE_BYTES + gain_bytes);
-                tma_load_2d(stage, &map_w, k, blockIdx.x * BLOCK_FEAT, &full[s]);
+                tma_load_2d_hint(stage, &map_w, k, blockIdx.x * BLOCK_FEAT, &full[s], read_once);
                 bulk_load(stage + TILE_BYTES, before.gain + k, gain_bytes, &full[s]);
             };
             auto load_activations = [&](int i, int s) {          // what the previous kernel produced
