@@ -53,6 +53,15 @@ __device__ __forceinline__ int swz(int r, int c, int cpr) {
     return (cpr & 7) == 0 ? (c ^ (r & 7)) : (c + r) % cpr;
 }
 
+// The same for a tile written by TMA with its 128-byte swizzle (head sizes that are multiples of 64): panels of
+// 64 columns, each [64 rows x 128 bytes], chunk c % 8 of a row at (c % 8) xor (r % 8). PANELS = false: the layout
+// above (rows of hd elements). Returns the byte offset of chunk c of row r.
+template <bool PANELS>
+__device__ __forceinline__ uint32_t tile_offset(int r, int c, int hd, int cpr) {
+    if (PANELS) return (uint32_t)((c >> 3) * (PAGE * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+    return (uint32_t)(r * (hd * 2) + swz(r, c, cpr) * 16);
+}
+
 // Copy one page (64 keys and 64 values of one kv head) into a stage: K tile, then V tile.
 __device__ __forceinline__ void load_page(uint8_t* stage, const __nv_bfloat16* pages, int page, int G, int g, int hd,
                                           int tid, int nthreads) {
@@ -197,13 +206,19 @@ template <bool NAMED, int NT> __device__ __forceinline__ void unit_sync() {
 // from an earlier operation of the same kernel waits for that operation there, so that the page
 // copies (the cache holds nothing the step writes, except the new row this unit patches in itself)
 // are already in flight.
-template <int HD_MAX, bool FUSED, int HD_EXACT, bool NAMED, int STAGES, int NW, typename Before>
+// TMA: the pages come as bulk tensor copies (`kv_map`: the cache as a matrix of [pages x 2 x G x 64 rows, hd] with
+// boxes of 64 x 64 and the 128-byte swizzle) that one thread requests, two to four instructions per page, and
+// each warp awaits its own page at an mbarrier (bounded: `status` is set to 6 if a wait runs out and the page is
+// skipped); else every thread copies 16-byte pieces with cp.async, about 120 instructions per page and thread
+// at a head size of 64, which was most of what the kernel issued. TMA needs hd % 64 == 0 and `smem` aligned to 1024.
+template <int HD_MAX, bool FUSED, int HD_EXACT, bool NAMED, int STAGES, int NW, bool TMA = false, typename Before>
 __device__ __forceinline__ void attention_decode_unit(
     uint8_t* smem, const int tid, const int split, const int by, const int b, const __nv_bfloat16* __restrict__ q,
     const __nv_bfloat16* __restrict__ pages, const int* __restrict__ page_table, int pt_stride,
     const int* __restrict__ kv_len, float* __restrict__ part_o, float* __restrict__ part_ml,
     __nv_bfloat16* __restrict__ out, int H, int G, int hd_arg, float scale_log2, int window, int pages_per_split,
-    int num_splits, int min_share_pages, int head_groups, const FusedDecodeArgs& fused, Before&& before_inputs) {
+    int num_splits, int min_share_pages, int head_groups, const FusedDecodeArgs& fused, Before&& before_inputs,
+    const CUtensorMap* kv_map = nullptr, int* status = nullptr) {
     constexpr int KSTEPS = HD_MAX / 16;
     constexpr int NT = 32 * NW, PG = NW / 4, GROUPS = STAGES / PG;
     static_assert(NW % 4 == 0 && STAGES % PG == 0 && GROUPS >= 1, "whole groups of pages in the ring");
@@ -248,15 +263,37 @@ __device__ __forceinline__ void attention_decode_unit(
     const int stage_bytes = 2 * PAGE * hd * 2;
     const int npages = page_hi - page_lo + 1;      // may be <= 0: this share holds nothing of the sequence
 
-    // the ring is requested first; what follows overlaps with the copies
+    // TMA: one barrier per stage, behind the ring and (FUSED) the extras described below
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * stage_bytes + (HEAD_ROWS * hd + 2 * hd) * 2 + 256 * 4);
+    auto request_page = [&](int p) {               // by one thread: the share's page p into stage p % STAGES
+        uint8_t* st = smem + (p % STAGES) * stage_bytes;
+        uint64_t* bar = &full[p % STAGES];
+        mbar_expect_tx(bar, (uint32_t)stage_bytes);
+        const int page = table[page_lo + p];
 #pragma unroll
-    for (int gi = 0; gi < GROUPS; ++gi) {          // one group of copies per group of pages
-#pragma unroll
-        for (int j = 0; j < PG; ++j) {
-            const int p = gi * PG + j;
-            if (p < npages) load_page(smem + p * stage_bytes, pages, table[page_lo + p], G, g, hd, tid, NT);
+        for (int which = 0; which < 2; ++which) {
+            const int row = ((page * 2 + which) * G + g) * PAGE;
+            for (int x = 0; x < hd; x += 64)
+                tma_load_2d(st + which * (PAGE * hd * 2) + (x >> 6) * (PAGE * 128), kv_map, x, row, bar);
         }
-        cp_async_commit();
+    };
+    // the ring is requested first; what follows overlaps with the copies
+    if (TMA) {
+        if (tid == 0) {
+            for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            for (int p = 0; p < STAGES && p < npages; ++p) request_page(p);
+        }
+    } else {
+#pragma unroll
+        for (int gi = 0; gi < GROUPS; ++gi) {          // one group of copies per group of pages
+#pragma unroll
+            for (int j = 0; j < PG; ++j) {
+                const int p = gi * PG + j;
+                if (p < npages) load_page(smem + p * stage_bytes, pages, table[page_lo + p], G, g, hd, tid, NT);
+            }
+            cp_async_commit();
+        }
     }
 
     const int g8 = lane >> 2, t4 = lane & 3;       // the lane's place in a fragment: row / column group
@@ -348,21 +385,31 @@ __device__ __forceinline__ void attention_decode_unit(
     const int cpr = hd >> 3;
     const int frag_row = (lane & 7) + ((lane >> 3) & 1) * 8, frag_chunk = lane >> 4;      // ldmatrix.x4 for a 16 x 16 row operand
     for (int gi = 0; gi < ngroups; ++gi) {
-        cp_async_wait<GROUPS - 1>();                 // all but the newest groups of copies: this group's pages are there
-        unit_sync<NAMED, NT>();
-        if (FUSED && holds_new && new_at >= gi * PG && new_at < (gi + 1) * PG) {
+        const bool patch = FUSED && holds_new && new_at >= gi * PG && new_at < (gi + 1) * PG;
+        if (!TMA) {
+            cp_async_wait<GROUPS - 1>();             // all but the newest groups of copies: this group's pages are there
+            unit_sync<NAMED, NT>();
+        } else if (patch) {
+            mbar_wait(&full[new_at % STAGES], (uint32_t)(new_at / STAGES) & 1u);      // its owners check the outcome below
+        }
+        if (patch) {
             // the copy of this page predates the new token: put its key and value in place
             const int row = pos % PAGE;
             uint8_t* tile = smem + (new_at % STAGES) * stage_bytes;
             for (int c = tid; c < 2 * cpr; c += NT) {
                 const int which = c >= cpr, cc = which ? c - cpr : c;
                 const uint4 v = *reinterpret_cast<const uint4*>((which ? new_v : new_k) + cc * 8);
-                *reinterpret_cast<uint4*>(tile + which * (PAGE * hd * 2) + row * (hd * 2) + swz(row, cc, cpr) * 16) = v;
+                *reinterpret_cast<uint4*>(tile + which * (PAGE * hd * 2) + tile_offset<TMA>(row, cc, hd, cpr)) = v;
             }
             unit_sync<NAMED, NT>();
         }
         const int i = gi * PG + pg;                  // this warp's page
-        if (i < npages) {
+        bool arrived = true;
+        if (TMA && i < npages) {
+            arrived = mbar_wait(&full[i % STAGES], (uint32_t)(i / STAGES) & 1u);
+            if (!arrived && lane == 0) atomicExch(status, 6);
+        }
+        if (i < npages && arrived) {
             const int key_base = (page_lo + i) * PAGE;
             const uint32_t k_tile = smem_u32(smem + (i % STAGES) * stage_bytes);
             const uint32_t v_tile = k_tile + PAGE * hd * 2;
@@ -375,7 +422,7 @@ __device__ __forceinline__ void attention_decode_unit(
                 for (int kk = 0; kk < KSTEPS; ++kk) {
                     if (kk * 16 < hd) {
                         uint32_t a[4];
-                        ldmatrix_x4(k_tile + k_row * (hd * 2) + swz(k_row, kk * 2 + frag_chunk, cpr) * 16, a[0], a[1], a[2], a[3]);
+                        ldmatrix_x4(k_tile + tile_offset<TMA>(k_row, kk * 2 + frag_chunk, hd, cpr), a[0], a[1], a[2], a[3]);
                         mma_bf16(s, a, qf[kk][0], qf[kk][1]);
                     }
                 }
@@ -405,7 +452,7 @@ __device__ __forceinline__ void attention_decode_unit(
                     if (mt * 16 < hd) {
                         o[mt][0] *= a0; o[mt][1] *= a1; o[mt][2] *= a0; o[mt][3] *= a1;
                         uint32_t a[4];
-                        ldmatrix_x4_trans(v_tile + v_row * (hd * 2) + swz(v_row, mt * 2 + v_chunk, cpr) * 16, a[0], a[1], a[2], a[3]);
+                        ldmatrix_x4_trans(v_tile + tile_offset<TMA>(v_row, mt * 2 + v_chunk, hd, cpr), a[0], a[1], a[2], a[3]);
                         mma_bf16(o[mt], a, p0, p1);
                     }
                 }
@@ -413,16 +460,27 @@ __device__ __forceinline__ void attention_decode_unit(
         }
         unit_sync<NAMED, NT>();
         // the group's stages are free: the group that comes GROUPS later goes there
+        if (TMA) {
+            if (tid == 0) {
+                for (int j = 0; j < PG; ++j) {
+                    const int nxt = (gi + GROUPS) * PG + j;
+                    if (nxt < npages) request_page(nxt);
+                }
+            }
+        } else {
 #pragma unroll
-        for (int j = 0; j < PG; ++j) {
-            const int nxt = (gi + GROUPS) * PG + j;
-            if (nxt < npages)
-                load_page(smem + (nxt % STAGES) * stage_bytes, pages, table[page_lo + nxt], G, g, hd, tid, NT);
+            for (int j = 0; j < PG; ++j) {
+                const int nxt = (gi + GROUPS) * PG + j;
+                if (nxt < npages)
+                    load_page(smem + (nxt % STAGES) * stage_bytes, pages, table[page_lo + nxt], G, g, hd, tid, NT);
+            }
+            cp_async_commit();
         }
-        cp_async_commit();
     }
-    cp_async_wait<0>();
-    unit_sync<NAMED, NT>();
+    if (!TMA) {
+        cp_async_wait<0>();
+        unit_sync<NAMED, NT>();
+    }
 
     // merge the warps (each saw a quarter of some pages) through shared memory; a head's sum over the keys lies in
     // the lanes of equal t4

@@ -20,6 +20,7 @@
 // Reference: src/main/resources/kernels/cuda/attention.cu:10-108 (one block per head,
 // scores of one query in shared memory) and the online-softmax form of
 // inference/Attention.java:161-207; head mapping kvHead = h / (H/G) (inference/Attention.java:212).
+#include "tcgen05_utils.cuh"
 #include "attention_decode.cuh"
 
 namespace {
@@ -170,7 +171,6 @@ attention_prefill_exact_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat1
                                int pt_stride, const int* __restrict__ q_start, const int* __restrict__ kv_len, int H,
                                int G, float scale_log2, int window) {
     constexpr int KSTEPS = HD / 16;
-    constexpr int CPR = HD / 8;                       // 16-byte chunks per row: a multiple of 8
     constexpr int ROW = HD * 2;
     constexpr int TILE = PAGE * ROW;                  // bytes of a K (or V) tile
     constexpr int STAGE = 2 * TILE;
@@ -346,6 +346,25 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
         [early] { if (early) lp_grid_wait(); });
 }
 
+// The fused form with the pages brought by TMA (head sizes 64 and 128; see attention_decode.cuh).
+template <int HD, int STAGES, int NW>
+__global__ void __launch_bounds__(32 * NW)
+attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __nv_bfloat16* __restrict__ pages,
+                            const int* __restrict__ page_table, int pt_stride, const int* __restrict__ kv_len,
+                            float* __restrict__ part_o, float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out,
+                            int H, int G, float scale_log2, int window, int pages_per_split, int num_splits,
+                            int min_share_pages, int head_groups, FusedDecodeArgs fused, int* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // the swizzle's pattern repeats every 1024 bytes
+    lp_grid_release();
+    const bool early = fused.pages_rw != nullptr;
+    if (!early) lp_grid_wait();
+    attention_decode_unit<HD, true, HD, false, STAGES, NW, true>(
+        smem, threadIdx.x, blockIdx.x, blockIdx.y, blockIdx.z, nullptr, pages, page_table, pt_stride, kv_len, part_o,
+        part_ml, out, H, G, HD, scale_log2, window, pages_per_split, num_splits, min_share_pages, head_groups, fused,
+        [early] { if (early) lp_grid_wait(); }, &kv_map, status);
+}
+
 // out[b][head][:] = sum_s part_o * 2^(m_s - m*) / sum_s l_s * 2^(m_s - m*); grid: (H, B), hd threads (<= 256).
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        __nv_bfloat16* __restrict__ out, int H, int hd, int num_splits) {
@@ -515,7 +534,7 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
                                          const int* kv_len, float* scratch, int* counters, int B, int H, int G,
                                          int hd, int page_size, float scale, int window, int pages_per_split,
                                          int num_splits, int min_share_pages, const float* row_sumsq, float norm_eps,
-                                         int norm_width, cudaStream_t stream) {
+                                         int norm_width, long long num_pages, int* status, cudaStream_t stream) {
     if (B <= 0) return 0;
     int rc = check_geometry("attention_decode_fused", H, G, hd);
     if (row_sumsq && norm_width <= 0) LP_REFUSE("attention_decode_fused: a row factor over %d values", norm_width);
@@ -548,6 +567,28 @@ extern "C" int lp_attention_decode_fused(const float* qkv, int ld, const float* 
     const float scale_log2 = scale * 1.4426950408889634f;
     FusedDecodeArgs fused{qkv, ld, inv_freq, rd, interleaved, write_kv ? (__nv_bfloat16*)pages : nullptr, counters,
                           row_sumsq, norm_eps, norm_width};
+    // heads of 64 or 128: the pages come by TMA (num_pages and status given; LLMPLAYER_B200_DECODE_TMA=0 keeps cp.async)
+    static int use_tma = -1;
+    if (use_tma < 0) { const char* v = getenv("LLMPLAYER_B200_DECODE_TMA"); use_tma = (v && v[0] == '0') ? 0 : 1; }
+    if (use_tma && (hd == 64 || hd == 128) && num_pages > 0 && status) {
+        CUtensorMap kv_map;
+        rc = make_map(&kv_map, pages, num_pages * 2 * G * PAGE, hd, hd, PAGE);
+        if (rc) return rc;
+        const int smem_tma = smem + 1024 + 64;          // alignment slack and the stages' barriers
+#define LP_DECODE_TMA(HDX, ST, NWARPS)                                                                          \
+        do {                                                                                                    \
+            rc = set_smem(attention_decode_tma_kernel<HDX, ST, NWARPS>, smem_tma, "attention_decode_fused");    \
+            if (rc) return rc;                                                                                  \
+            lp_launch(attention_decode_tma_kernel<HDX, ST, NWARPS>, grid, 32 * NWARPS, smem_tma, stream, kv_map, \
+                      (const __nv_bfloat16*)pages, page_table, pt_stride, kv_len, part_o, part_ml,              \
+                      (__nv_bfloat16*)out, H, G, scale_log2, window, pages_per_split, num_splits,               \
+                      min_share_pages, head_groups, fused, status);                                             \
+        } while (0)
+        if (hd == 64) { if (wide) LP_DECODE_TMA(64, 8, 16); else if (mid) LP_DECODE_TMA(64, 6, 8); else LP_DECODE_TMA(64, 3, 4); }
+        else { if (wide128) LP_DECODE_TMA(128, 4, 8); else LP_DECODE_TMA(128, 3, 4); }
+#undef LP_DECODE_TMA
+        return lp_check_launch("attention_decode_fused");
+    }
 #define LP_DECODE_FUSED(HDM, EXACT, ST, NWARPS)                                                                  \
     do {                                                                                                         \
         rc = set_smem(attention_decode_kernel<HDM, true, EXACT, ST, NWARPS>, smem,  \

@@ -48,7 +48,7 @@ _SIGNATURES = {
         "lp_attention_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
         "lp_attention_decode_fitted": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
         "lp_attention_decode_fused": [_P, _I, _P, _I, _I, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I,
-                                      _I, _I, _I, _P, _F, _I, _P],
+                                      _I, _I, _I, _P, _F, _I, ctypes.c_longlong, _P, _P],
     },
     "attention_tcgen05": {
         "lp_attention_prefill_tc": [_P, _P, _P, ctypes.c_longlong, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I,
@@ -525,7 +525,7 @@ def check_kernel_status() -> None:
         _status.zero_()
         raise KernelError(f"a tensor-core kernel gave up waiting on a barrier (code {code}: "
                           "1 = loader, 2 = MMA issuer, 3 = epilogue, 4-5 = operand maker; 2x the same in the "
-                          "persistent product)")
+                          "persistent product; 6 = a page of the decode attention)")
 
 
 def _token_tile(tokens: int, gated: bool) -> int:
@@ -865,7 +865,7 @@ def attention_decode_fused(qkv: torch.Tensor, rotation: Rotation, out: torch.Ten
         out.data_ptr(), pages.data_ptr(), 1 if write_kv else 0, page_table.data_ptr(), page_table.shape[1],
         kv_len.data_ptr(), buf.data_ptr(), counters.data_ptr(), B, H, G, hd, pages.shape[3], float(scale),
         int(window) if window else 0, pages_per_split, num_splits, MIN_SHARE_PAGES if fitted else 0, _ptr(row_sumsq),
-        float(norm_eps), int(norm_width), _stream()))
+        float(norm_eps), int(norm_width), pages.shape[0], kernel_status().data_ptr(), _stream()))
     return out
 
 
