@@ -158,11 +158,16 @@ struct Tile {
     static constexpr int TAIL_BYTES = 1024 /* alignment slack */ + 256 /* barriers */;
     static constexpr int ACC_COLS = BLOCK_TOK * W_TILES;
     static constexpr int TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;       // power of two by construction
+    // Token tiles of 32 and 64 belong to decode steps, where the epilogue is not hidden under another tile's main
+    // loop: two warps per quarter of the tensor memory's lanes share its columns (measured at 64 tokens: the
+    // epilogue of four warps took 5 of the gated product's 21 us, 2 of the output projection's 6).
+    static constexpr int EPI_WARPS = (BLOCK_TOK == 32 || BLOCK_TOK == 64) ? 8 : 4;
+    static constexpr int NTHREADS = 64 + 32 * EPI_WARPS;
 };
 
 // out: [tokens, ldc]; OUT_BF16 selects the element type of a STORE / SWIGLU output.
 template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(Tile<BLOCK_TOK, MODE>::NTHREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
                     int withheld_kblock, int num_stages, int* __restrict__ status, NormAfter norm) {
@@ -229,17 +234,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                             &full[i]);
             }
             issued = early;
+            int s = early == num_stages ? 0 : early;          // stage and phase of k-block i, kept by counting (a
+            uint32_t phase = early == num_stages ? 1 : 0;     // division per k-block is felt in a one-thread loop)
             for (int i = early; i < nkb && ok; ++i) {
-                const int s = i % num_stages;
-                const uint32_t phase = (i / num_stages) & 1;
                 if (!mbar_wait(&empty[s], phase ^ 1, wait_limit)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
                 issued = i + 1;
-                if (kb_begin + i == withheld_kblock) continue;
-                uint8_t* stage = smem + s * T::STAGE_BYTES;
-                mbar_expect_tx(&full[s], T::STAGE_BYTES);
-                const int k = (kb_begin + i) * BLOCK_K;
-                load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[s], read_once);
-                tma_load_2d(stage + T::W_TILES * T::W_BYTES, &map_x, k, tok0, &full[s]);
+                if (kb_begin + i != withheld_kblock) {
+                    uint8_t* stage = smem + s * T::STAGE_BYTES;
+                    mbar_expect_tx(&full[s], T::STAGE_BYTES);
+                    const int k = (kb_begin + i) * BLOCK_K;
+                    load_weights<MODE>(stage, &map_w, k, blockIdx.x, &full[s], read_once);
+                    tma_load_2d(stage + T::W_TILES * T::W_BYTES, &map_x, k, tok0, &full[s]);
+                }
+                if (++s == num_stages) { s = 0; phase ^= 1; }
             }
             if (!ok || *failed) {
                 // consumers may be gone: await the copies still in flight before the CTA's memory is released
@@ -255,9 +262,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_TOK >> 3) << 17) |
                                        ((uint32_t)(BLOCK_FEAT >> 4) << 24);
             bool ok = true;
+            int s = 0;
+            uint32_t phase = 0;
             for (int i = 0; i < nkb; ++i) {
-                const int s = i % num_stages;
-                const uint32_t phase = (i / num_stages) & 1;
                 if (!mbar_wait(&full[s], phase, wait_limit)) { atomicExch(status, 2); *failed = 1; ok = false; break; }
                 tcgen05_fence_after();
                 const uint32_t w_addr = smem_u32(smem + s * T::STAGE_BYTES);
@@ -273,14 +280,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     }
                 }
                 tcgen05_commit(&empty[s]);        // the stage is free once these MMAs have read it
+                if (++s == num_stages) { s = 0; phase ^= 1; }
             }
             (void)ok;
             tcgen05_commit(acc_ready);            // arrives when every MMA issued so far is complete
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------ epilogue (warps 2 ..)
         const int quarter = warp & 3;             // TMEM lanes 32*quarter .. +31 belong to this warp
+        // with eight epilogue warps, warps 2-5 take the lower half of the columns (tokens) and warps 6-9 the upper
+        constexpr int EPI = T::EPI_WARPS, COLS = BLOCK_TOK / (EPI / 4);
+        const int col_lo = ((warp - 2) >> 2) * COLS;
         const bool ready = mbar_wait(acc_ready, 0, wait_limit);
         if (!ready && lane == 0) atomicExch(status, 3);
         tcgen05_fence_after();
@@ -290,15 +301,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             // so the kernel before this one, the buffer's last reader, has ended)
             const long long cta = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
             const long long ctas = (long long)gridDim.x * gridDim.y * gridDim.z;
-            for (long long i = cta * 128 + threadIdx.x - 64; i < norm.clear_count; i += ctas * 128) norm.clear[i] = 0.f;
+            for (long long i = cta * (32 * EPI) + threadIdx.x - 64; i < norm.clear_count; i += ctas * (32 * EPI)) norm.clear[i] = 0.f;
         }
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        constexpr int CHUNK = BLOCK_TOK >= 32 ? 32 : 16;
-        if (MODE != LP_GEMM_SWIGLU) {
+        constexpr int CHUNK = COLS >= 32 ? 32 : 16;
+        if constexpr (MODE != LP_GEMM_SWIGLU) {
             if (go) {
                 const int f = feat0 + quarter * 32 + lane;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
+                for (int c0 = col_lo; c0 < col_lo + COLS; c0 += CHUNK) {
                     uint32_t g[CHUNK], u[MODE == LP_GEMM_SWIGLU_WIDE ? CHUNK : 1];
                     if (CHUNK == 32) tmem_ld32(lane_addr + c0, g); else tmem_ld16(lane_addr + c0, g);
                     if (MODE == LP_GEMM_SWIGLU_WIDE) {
@@ -322,40 +333,43 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 }
             }
         } else {
-            // rows 0..63 of the tile are gate, rows 64..127 up, of the same 64 output features. Every load
-            // has been consumed by now, so the ring's memory carries the gate half across.
-            float* cross = reinterpret_cast<float*>(smem);            // [64][BLOCK_TOK + 1]
-            constexpr int LD = BLOCK_TOK + 1;
+            // Rows 0..63 of the tile are gate, rows 64..127 up, of the same 64 output features, and a warp reaches
+            // only its own quarter of the lanes: of its columns, a gate warp hands the upper half of its gates
+            // to the up warp of the same feature and takes that warp's lower half of the ups, so that all warps
+            // share the activation and the stores. Every load has been consumed by now: the ring's memory carries
+            // the halves across.
+            float* cross = reinterpret_cast<float*>(smem);            // [EPI / 4][2][64][COLS / 2 + 1]
+            constexpr int HALF = COLS / 2, LD = HALF + 1;
             const int local = (quarter & 1) * 32 + lane;              // feature within the 64
-            if (go && quarter < 2) {
-#pragma unroll 1
-                for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
-                    uint32_t g[CHUNK];
-                    if (CHUNK == 32) tmem_ld32(lane_addr + c0, g); else tmem_ld16(lane_addr + c0, g);
-                    tmem_ld_wait();
+            const bool is_gate = quarter < 2;
+            float* mine = cross + (((warp - 2) >> 2) * 2 + (is_gate ? 0 : 1)) * 64 * LD + local * LD;     // what this warp hands over
+            float* theirs = cross + (((warp - 2) >> 2) * 2 + (is_gate ? 1 : 0)) * 64 * LD + local * LD;
+            // the half this warp keeps: gate warps the lower half of their columns, up warps the upper
+            const int keep_lo = col_lo + (is_gate ? 0 : HALF), give_lo = col_lo + (is_gate ? HALF : 0);
+            uint32_t kept[HALF];
+            if (go) {
+                uint32_t given[HALF];
+                static_assert(HALF == 8 || HALF == 16, "the gated epilogue serves token tiles of 16, 32 and 64");
+                if constexpr (HALF == 16) { tmem_ld16(lane_addr + give_lo, given); tmem_ld16(lane_addr + keep_lo, kept); }
+                else { tmem_ld8(lane_addr + give_lo, given); tmem_ld8(lane_addr + keep_lo, kept); }
+                tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < CHUNK; ++j) cross[local * LD + c0 + j] = __uint_as_float(g[j]);
-                }
+                for (int j = 0; j < HALF; ++j) mine[j] = __uint_as_float(given[j]);
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps
-            if (go && quarter >= 2) {
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI) : "memory");            // the epilogue warps
+            if (go) {
                 const int f = blockIdx.x * (BLOCK_FEAT / 2) + local;
-#pragma unroll 1
-                for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
-                    uint32_t u[CHUNK];
-                    if (CHUNK == 32) tmem_ld32(lane_addr + c0, u); else tmem_ld16(lane_addr + c0, u);
-                    tmem_ld_wait();
-                    if (f < features) {
+                if (f < features) {
 #pragma unroll
-                        for (int j = 0; j < CHUNK; ++j) {
-                            const int t = tok0 + c0 + j;
-                            if (t >= tokens) break;
-                            const float gate = cross[local * LD + c0 + j];
-                            const float v = __fdividef(gate, 1.0f + __expf(-gate)) * __uint_as_float(u[j]);
-                            const size_t at = (size_t)t * ldc + f;
-                            if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
-                            else ((float*)out)[at] = v;
-                        }
+                    for (int j = 0; j < HALF; ++j) {
+                        const int t = tok0 + keep_lo + j;
+                        if (t >= tokens) break;
+                        const float gate = is_gate ? __uint_as_float(kept[j]) : theirs[j];
+                        const float up = is_gate ? theirs[j] : __uint_as_float(kept[j]);
+                        const float v = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+                        const size_t at = (size_t)t * ldc + f;
+                        if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                        else ((float*)out)[at] = v;
                     }
                 }
             }
@@ -368,7 +382,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS));
     }
-    if (ATOMIC) norm_after_tail<THREADS>(norm, out, tokens, features, ldc);
+    if (ATOMIC) norm_after_tail<T::NTHREADS>(norm, out, tokens, features, ldc);
 }
 
 // ------------------------------------------------------------------ a handful of tokens: mma.sync consumers
@@ -1473,7 +1487,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, 
         if (stages > per_split) stages = per_split > T::STAGES ? per_split : T::STAGES;
     }
     const int smem = stages * T::STAGE_BYTES + T::TAIL_BYTES;
-    cudaError_t err = lp_launch(kernel, grid, THREADS, smem, stream, mw, mx, out, tokens, features, ldc,
+    cudaError_t err = lp_launch(kernel, grid, T::NTHREADS, smem, stream, mw, mx, out, tokens, features, ldc,
                                 k_blocks, per_split, withheld, stages, status, norm);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_tcgen05: %s", cudaGetErrorString(err));
