@@ -762,13 +762,15 @@ static bool fewtok_enabled() { return few_settings().enabled != 0; }
 // CTAs of the first feature tile add their shares of the sums of squares to `sumsq_out` and the reader of the
 // output applies the factor. Saves the norm kernels in front of the q|k|v and the gated products of a layer.
 //
-// Measured at the 1B shape (ms per decode step, this kernel against norm kernels of their own): 24 tokens
-// 0.960 / 1.008, 32 tokens 0.992 / 1.027; with the 64-token tile 48 tokens 1.279 / 1.169 and 64 tokens
-// 1.303 / 1.248: there the float32 tile makes 80 KB of shared-memory traffic per k-block against 48 KB, and the
+// Once the last operand is made, the makers join the epilogue: eight warps share its columns.
+//
+// Measured at the 1B shape (ms per decode step, this kernel against norm kernels of their own): 20 tokens
+// 0.840 / 0.887, 32 tokens 0.858 / 0.939; with the 64-token tile 48 tokens 1.068 / 0.991 and 64 tokens
+// 1.138 / 1.059: there the float32 tile makes 80 KB of shared-memory traffic per k-block against 48 KB, and the
 // callers keep the norm kernels. A variant whose makers read x from L2 with plain loads, two k-blocks ahead
 // (no float32 tile in shared memory), was slower at every size (1.17 ms at 24 tokens): TMA keeps as many
 // k-blocks of x in flight as the ring has stages, the makers' registers cannot.
-constexpr int NORMED_THREADS = 320;       // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue, warps 6-9: operand makers
+constexpr int NORMED_THREADS = 320;       // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue, warps 6-9: operand makers, then epilogue
 
 template <int BLOCK_TOK> struct NormedTile {
     static constexpr int W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
@@ -856,12 +858,14 @@ gemm_tcgen05_normed_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             for (int i = 0; i < early; ++i) load_activations(i, i);
             int issued = early;
             bool ok = true;
+            int s = early == STAGES ? 0 : early;              // stage and phase of k-block i, kept by counting
+            uint32_t phase = early == STAGES ? 1 : 0;
             for (int i = early; i < nkb; ++i) {
-                const int s = i % STAGES;
-                if (!mbar_wait(&empty[s], ((i / STAGES) & 1) ^ 1)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
+                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(status, 1); *failed = 1; ok = false; break; }
                 load_constants(i, s);
                 load_activations(i, s);
                 issued = i + 1;
+                if (++s == STAGES) { s = 0; phase ^= 1; }
             }
             if (!ok) {
                 for (int i = max(0, issued - STAGES); i < issued; ++i) mbar_wait(&full[i % STAGES], (i / STAGES) & 1);
@@ -873,9 +877,10 @@ gemm_tcgen05_normed_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         if (lane == 0) {
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BLOCK_TOK >> 3) << 17) |
                                        ((uint32_t)(BLOCK_FEAT >> 4) << 24);
+            int s = 0;
+            uint32_t phase = 0;
             for (int i = 0; i < nkb; ++i) {
-                const int s = i % STAGES;
-                if (!mbar_wait(&made[s], (i / STAGES) & 1)) { atomicExch(status, 2); *failed = 1; break; }
+                if (!mbar_wait(&made[s], phase)) { atomicExch(status, 2); *failed = 1; break; }
                 tcgen05_fence_after();
                 const uint32_t w_addr = smem_u32(smem + s * T::STAGE_BYTES);
                 const uint64_t dw = smem_desc(w_addr), dx = smem_desc(w_addr + T::W_BYTES);
@@ -885,11 +890,13 @@ gemm_tcgen05_normed_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                     tcgen05_mma(tmem_base, dw + step, dx + step, idesc, (i > 0 || k > 0) ? 1u : 0u);
                 }
                 tcgen05_commit(&empty[s]);
+                if (++s == STAGES) { s = 0; phase ^= 1; }
             }
             tcgen05_commit(acc_ready);
         }
         __syncwarp();
-    } else if (warp >= 6) {
+    } else {
+      if (warp >= 6) {
         // ------------------------------------------------------------ operand makers (128 threads)
         // float4 q of the k-block: row q / 16, values 4 (q % 16) ..; thread c takes q = c, c + 128, ...: a fixed
         // place in the row, rows 8 apart, so sixteen neighbouring threads share a row
@@ -900,9 +907,10 @@ gemm_tcgen05_normed_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 #pragma unroll
         for (int it = 0; it < PASSES; ++it) ss[it] = 0.f;
         bool ok = true;
+        int s = 0;
+        uint32_t phase = 0;
         for (int i = 0; i < nkb && ok; ++i) {
-            const int s = i % STAGES;
-            if (!mbar_wait(&full[s], (i / STAGES) & 1)) { if (lane == 0) atomicExch(status, 4); *failed = 1; ok = false; }
+            if (!mbar_wait(&full[s], phase)) { if (lane == 0) atomicExch(status, 4); *failed = 1; ok = false; }
             uint8_t* x_tile = smem + s * T::STAGE_BYTES + T::W_BYTES;
             const float* gain_tile = reinterpret_cast<const float*>(x_tile + T::X_BYTES);
             const int k_abs = (kb_begin + i) * BLOCK_K;
@@ -931,6 +939,7 @@ gemm_tcgen05_normed_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&made[s])) : "memory");
+            if (++s == STAGES) { s = 0; phase ^= 1; }
         }
         // a row's sum of x^2: over the sixteen threads that shared it
 #pragma unroll
@@ -946,32 +955,36 @@ gemm_tcgen05_normed_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 else if (blockIdx.x == 0 && ok && row < tokens) atomicAdd(before.sumsq_out + row, ss[it]);
             }
         }
-        if (whole_k) asm volatile("bar.sync 1, 256;" ::: "memory");     // with the four epilogue warps
-    } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
+        lp_grid_wait();
+      } else {
         lp_grid_wait();
         if (before.zero != nullptr) {              // all CTAs share the clearing
             const int cta = blockIdx.z * gridDim.x + blockIdx.x, ctas = gridDim.x * gridDim.z;
             for (int i = cta * 128 + threadIdx.x - 64; i < before.zero_count; i += ctas * 128) before.zero[i] = 0.f;
         }
+      }
+        // ------------------------------------------------------------ epilogue (warps 2..9: the makers, their work done,
+        // take the upper half of the columns)
         const int quarter = warp & 3;
+        constexpr int COLS = BLOCK_TOK / 2, CHUNK = COLS >= 32 ? 32 : 16;
+        const int col_lo = ((warp - 2) >> 2) * COLS;
         const bool ready = mbar_wait(acc_ready, 0);
         if (!ready && lane == 0) atomicExch(status, 3);
         tcgen05_fence_after();
         if (whole_k) asm volatile("bar.sync 1, 256;" ::: "memory");     // the makers have written the rows' factors
         const bool go = __all_sync(0xffffffffu, ready && *failed == 0);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        if (MODE != LP_GEMM_SWIGLU) {
+        if constexpr (MODE != LP_GEMM_SWIGLU) {
             if (go) {
                 const int f = feat0 + quarter * 32 + lane;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BLOCK_TOK; c0 += 32) {
-                    uint32_t g[32];
-                    tmem_ld32(lane_addr + c0, g);
+                for (int c0 = col_lo; c0 < col_lo + COLS; c0 += CHUNK) {
+                    uint32_t g[CHUNK];
+                    if (CHUNK == 32) tmem_ld32(lane_addr + c0, g); else tmem_ld16(lane_addr + c0, g);
                     tmem_ld_wait();
                     if (f < features) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
+                        for (int j = 0; j < CHUNK; ++j) {
                             const int t = c0 + j;
                             if (t >= tokens) break;
                             float v = __uint_as_float(g[j]);
@@ -985,41 +998,42 @@ gemm_tcgen05_normed_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 }
             }
         } else {
-            // rows 0..63 of the tile are gate, rows 64..127 up, of the same 64 output features; the ring's memory
-            // (every load has been consumed) carries the gate half across
-            float* cross = reinterpret_cast<float*>(smem);            // [64][BLOCK_TOK + 1]
-            constexpr int LD = BLOCK_TOK + 1;
+            // rows 0..63 of the tile are gate, rows 64..127 up, of the same 64 output features, and a warp reaches
+            // only its own quarter of the lanes: of its columns, a gate warp hands the upper half of its gates to the
+            // up warp of the same feature and takes that warp's lower half of the ups (as in the kernel above); the
+            // ring's memory (every load has been consumed) carries the halves across
+            float* cross = reinterpret_cast<float*>(smem);            // [2][2][64][COLS / 2 + 1]
+            constexpr int HALF = COLS / 2, LD = HALF + 1;
+            static_assert(HALF == 8 || HALF == 16, "token tiles of 32 and 64");
             const int local = (quarter & 1) * 32 + lane;
-            if (go && quarter < 2) {
-#pragma unroll 1
-                for (int c0 = 0; c0 < BLOCK_TOK; c0 += 32) {
-                    uint32_t g[32];
-                    tmem_ld32(lane_addr + c0, g);
-                    tmem_ld_wait();
+            const bool is_gate = quarter < 2;
+            float* mine = cross + (((warp - 2) >> 2) * 2 + (is_gate ? 0 : 1)) * 64 * LD + local * LD;
+            float* theirs = cross + (((warp - 2) >> 2) * 2 + (is_gate ? 1 : 0)) * 64 * LD + local * LD;
+            const int keep_lo = col_lo + (is_gate ? 0 : HALF), give_lo = col_lo + (is_gate ? HALF : 0);
+            uint32_t kept[HALF];
+            if (go) {
+                uint32_t given[HALF];
+                if constexpr (HALF == 16) { tmem_ld16(lane_addr + give_lo, given); tmem_ld16(lane_addr + keep_lo, kept); }
+                else { tmem_ld8(lane_addr + give_lo, given); tmem_ld8(lane_addr + keep_lo, kept); }
+                tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) cross[local * LD + c0 + j] = __uint_as_float(g[j]);
-                }
+                for (int j = 0; j < HALF; ++j) mine[j] = __uint_as_float(given[j]);
             }
-            asm volatile("bar.sync 3, 128;" ::: "memory");            // the four epilogue warps
-            if (go && quarter >= 2) {
+            asm volatile("bar.sync 3, 256;" ::: "memory");            // the eight epilogue warps
+            if (go) {
                 const int f = blockIdx.x * (BLOCK_FEAT / 2) + local;
-#pragma unroll 1
-                for (int c0 = 0; c0 < BLOCK_TOK; c0 += 32) {
-                    uint32_t u[32];
-                    tmem_ld32(lane_addr + c0, u);
-                    tmem_ld_wait();
-                    if (f < features) {
+                if (f < features) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const int t = c0 + j;
-                            if (t >= tokens) break;
-                            const float rs = row_scale[t];               // the gated product is never split along K
-                            const float gate = cross[local * LD + c0 + j] * rs;
-                            const float v = __fdividef(gate, 1.0f + __expf(-gate)) * (__uint_as_float(u[j]) * rs);
-                            const size_t at = (size_t)t * ldc + f;
-                            if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
-                            else ((float*)out)[at] = v;
-                        }
+                    for (int j = 0; j < HALF; ++j) {
+                        const int t = keep_lo + j;
+                        if (t >= tokens) break;
+                        const float rs = row_scale[t];                   // the gated product is never split along K
+                        const float gate = (is_gate ? __uint_as_float(kept[j]) : theirs[j]) * rs;
+                        const float up = (is_gate ? theirs[j] : __uint_as_float(kept[j])) * rs;
+                        const float v = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+                        const size_t at = (size_t)t * ldc + f;
+                        if (OUT_BF16) ((__nv_bfloat16*)out)[at] = __float2bfloat16_rn(v);
+                        else ((float*)out)[at] = v;
                     }
                 }
             }

@@ -651,8 +651,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
 FEW_TOKENS_MAX = 64                  # what the few-token entry takes
 # Up to where the parts choose it with the norm inside (``settings.few_tokens``). Measured at the 1B shape (ms per
 # step, norm inside against separate norm kernels): 8 tokens 0.70 / 0.76, 12 tokens 0.84 / 0.87, 16 tokens
-# 0.85 / 0.88 (the mma.sync kernel); 24 tokens 0.96 / 1.01, 32 tokens 0.99 / 1.03 (the tcgen05 kernel with operand
-# makers); 48 tokens 1.28 / 1.17 and 64 tokens 1.30 / 1.25: beyond 32 tokens the norm kernels stay.
+# 0.85 / 0.88 (the mma.sync kernel); 20 tokens 0.84 / 0.89, 32 tokens 0.86 / 0.94 (the tcgen05 kernel with operand
+# makers); 48 tokens 1.07 / 0.99 and 64 tokens 1.14 / 1.06: beyond 32 tokens the norm kernels stay.
 FEW_TOKENS = max(0, min(int(settings.few_tokens), FEW_TOKENS_MAX))
 
 
