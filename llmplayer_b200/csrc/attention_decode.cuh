@@ -310,9 +310,27 @@ __device__ __forceinline__ void attention_decode_unit(
         for (int i = tid; i < half; i += NT) sincosf((float)pos * fused.inv_freq[i], &sn[i], &cs[i]);
         unit_sync<NAMED, NT>();
         before_inputs();
-        const float in_scale = fused.row_sumsq
-            ? 1.0f / sqrtf(__ldcg(fused.row_sumsq + b) / (float)fused.norm_width + fused.norm_eps) : 1.0f;
+        // everything the step itself produced is asked for before any of it is used: the row's sum of squares, the
+        // new key and value, the queries. One round trip to L2 instead of three (which was 2 of the 3 us between
+        // the end of the projection and the first page's product).
+        const float ssq = fused.row_sumsq ? __ldcg(fused.row_sumsq + b) : 0.f;
         const float* row = fused.qkv + (size_t)b * fused.ld;
+        constexpr int KV_PER = (HD_MAX + NT - 1) / NT;
+        float k_val[KV_PER], k_other[KV_PER], v_val[KV_PER];
+        if (holds_new) {
+            const float* k_head = row + (size_t)(H + g) * hd;
+            const float* v_head = row + (size_t)(H + G + g) * hd;
+#pragma unroll
+            for (int u = 0; u < KV_PER; ++u) {
+                const int e = tid + u * NT;
+                k_val[u] = k_other[u] = v_val[u] = 0.f;
+                if (e < hd) {
+                    k_val[u] = __ldcg(k_head + e);
+                    if (e < fused.rd) k_other[u] = __ldcg(k_head + rotation_partner(e, fused.rd, fused.interleaved));
+                    v_val[u] = __ldcg(v_head + e);
+                }
+            }
+        }
         // the queries (heads beyond the unit's own are zero): the loads of four elements (each with its partner of
         // the rotation) are in flight together
         for (int idx0 = tid; idx0 < HEAD_ROWS * hd; idx0 += 4 * NT) {
@@ -330,6 +348,7 @@ __device__ __forceinline__ void attention_decode_unit(
                     }
                 }
             }
+            const float in_scale = fused.row_sumsq ? 1.0f / sqrtf(ssq / (float)fused.norm_width + fused.norm_eps) : 1.0f;
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
                 const int idx = idx0 + u * NT;
@@ -340,9 +359,14 @@ __device__ __forceinline__ void attention_decode_unit(
             }
         }
         if (holds_new) {
-            for (int e = tid; e < hd; e += NT) {
-                new_k[e] = __float2bfloat16_rn(rotated(row + (size_t)(H + g) * hd, e, fused.rd, fused.interleaved, cs, sn) * in_scale);
-                new_v[e] = __float2bfloat16_rn(__ldcg(row + (size_t)(H + G + g) * hd + e) * in_scale);
+            const float in_scale = fused.row_sumsq ? 1.0f / sqrtf(ssq / (float)fused.norm_width + fused.norm_eps) : 1.0f;
+#pragma unroll
+            for (int u = 0; u < KV_PER; ++u) {
+                const int e = tid + u * NT;
+                if (e < hd) {
+                    new_k[e] = __float2bfloat16_rn(rotate_value(k_val[u], k_other[u], e, fused.rd, fused.interleaved, cs, sn) * in_scale);
+                    new_v[e] = __float2bfloat16_rn(v_val[u] * in_scale);
+                }
             }
         }
         unit_sync<NAMED, NT>();
