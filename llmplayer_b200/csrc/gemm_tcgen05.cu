@@ -397,14 +397,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 // features, so the gated activation needs no exchange.
 //
 // XNORM: the activations are the float32 residual stream and the product applies an RMS norm on the way in.
-// The tile of x comes as float32 (two boxes of rows x 32 values per k-block) with the gain's 64 values; the
-// a fifth warp turns it into the bfloat16 operand bfloat16(x * gain) a stage ahead of the consumers (a
-// half-warp per token row, which also sums x^2) and hands it over through a barrier of its own. The row's factor
+// The tile of x comes as float32 (two boxes of rows x 32 values per k-block) with the gain's 64 values, and every
+// consumer warp forms its own column operand bfloat16(x * gain) from it in registers (a pair of float2 and a pair
+// of gains per k-step and token tile; the first warp also sums x^2). A fifth warp that made one bfloat16 tile
+// for all four was measured first: at 8 tokens the gated product took 15.6 us with it against 12.2 without the
+// norm, at 16 tokens 20.3 against 12.5 (one warp's conversions and the hand-over were in the way). The row's factor
 // 1 / sqrt(mean x^2 + eps) is a scalar per token, so it is applied to the sums at the end: by this kernel when
 // a CTA sees the whole K range, else (K shared out over CTAs, partial sums meeting in atomics) the CTAs
 // with blockIdx.x == 0 add their share of the sum of squares to `sumsq_out` and the reader of the output
 // applies the factor. `zero` (optional) is cleared on the side, a slice by every CTA.
-constexpr int FEW_THREADS = 160;          // warp 0: TMA; warps 1-4: consumers; XNORM adds warp 5, which makes the operand
+constexpr int FEW_THREADS = 160;          // warp 0: TMA; warps 1-4: consumers
 constexpr int FEW_W_BYTES = BLOCK_FEAT * BLOCK_K * 2;
 // The ring has as many stages as the launch gives it (`stages`): what lets two CTAs share an SM (up to six,
 // LLMPLAYER_B200_RING_SHARED), or, for a grid of no more than one CTA per SM whose K range is longer than that,
@@ -444,7 +446,7 @@ __device__ __forceinline__ void mma_m16n8k16(float* c, const uint32_t* a, uint32
 
 // NT: n-tiles of 8 tokens (1, 2, 4 or 8). MODE: STORE or SWIGLU (interleaved rows). out as in the tcgen05 kernel.
 template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
-__global__ void __launch_bounds__(FEW_THREADS + (XNORM ? 32 : 0), 2)
+__global__ void __launch_bounds__(FEW_THREADS, 2)
 gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
                    int FEW_STAGES, int* __restrict__ status, NormAfter norm, NormBefore before) {
@@ -454,10 +456,9 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* full = (uint64_t*)(smem + FEW_STAGES * FEW_STAGE_BYTES);
     uint64_t* empty = full + FEW_STAGES;
-    uint64_t* made = empty + FEW_STAGES;              // XNORM: the bfloat16 operand of the stage is ready
-    volatile uint32_t* failed = (volatile uint32_t*)(made + FEW_STAGES);
+    volatile uint32_t* failed = (volatile uint32_t*)(empty + FEW_STAGES);
     float* row_scale = (float*)(failed + 1);          // [8 NT], XNORM
-    constexpr int NTHREADS = FEW_THREADS + (XNORM ? 32 : 0);
+    constexpr int NTHREADS = FEW_THREADS;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int kb_begin = blockIdx.z * k_blocks_per_split;
@@ -469,70 +470,12 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         *failed = 0;
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-        for (int s = 0; s < FEW_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); mbar_init(&made[s], 1); }
+        for (int s = 0; s < FEW_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    if (XNORM && warp == 5) {
-        // ------------------------------------------------------------ operand maker
-        // float32 tile: value k of the k-block lies in box k / 32, 16-byte chunk (k % 32) / 4 of its row; the gain
-        // beyond K is unset (and x is zero there). Per k-block, thread `lane` takes quads lane, lane + 32, ...:
-        // row = index / 16, so a half-warp shares a row and the warp covers two rows per pass.
-        constexpr int PASSES = 4 * NT;
-        float ss[PASSES];
-#pragma unroll
-        for (int it = 0; it < PASSES; ++it) ss[it] = 0.f;
-        bool ok = true;
-        int s = 0;
-        uint32_t phase = 0;
-        for (int i = 0; i < nkb && ok; ++i, s = (s + 1 == FEW_STAGES ? 0 : s + 1), phase ^= (s == 0)) {
-            if (!mbar_wait(&full[s], phase)) { if (lane == 0) atomicExch(status, 4); *failed = 1; ok = false; break; }
-            uint8_t* x_tile = smem + s * FEW_STAGE_BYTES + FEW_W_BYTES;
-            const float* gain_tile = reinterpret_cast<const float*>(x_tile + FT::X_BYTES);
-            const int k_abs = (kb_begin + i) * BLOCK_K;
-            // the bfloat16 operand takes the place of the first float32 box: everything is read first
-            uint2 packed[PASSES];
-#pragma unroll
-            for (int it = 0; it < PASSES; ++it) {
-                const int idx = lane + it * 32;
-                const int row = idx >> 4, k = (idx & 15) * 4;
-                const float4 v = *reinterpret_cast<const float4*>(
-                    x_tile + (k >> 5) * FT::X_BOX_BYTES + row * 128 + ((((k & 31) >> 2) ^ (row & 7)) << 4));
-                float4 gn = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (k_abs + k < before.K) gn = *reinterpret_cast<const float4*>(gain_tile + k);
-                ss[it] += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-                __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * gn.x, v.y * gn.y);
-                __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * gn.z, v.w * gn.w);
-                packed[it].x = *reinterpret_cast<uint32_t*>(&lo);
-                packed[it].y = *reinterpret_cast<uint32_t*>(&hi);
-            }
-            __syncwarp();                              // every lane has read its share of the float32 tile
-#pragma unroll
-            for (int it = 0; it < PASSES; ++it) {
-                const int idx = lane + it * 32;
-                const int row = idx >> 4, k = (idx & 15) * 4;
-                *reinterpret_cast<uint2*>(x_tile + row * 128 + (((k >> 3) ^ (row & 7)) << 4) + (k & 7) * 2) = packed[it];
-            }
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&made[s])) : "memory");
-        }
-        // sum x^2 of a token row: over the half-warp that converted it
-#pragma unroll
-        for (int it = 0; it < PASSES; ++it) {
-#pragma unroll
-            for (int o = 1; o < 16; o <<= 1) ss[it] += __shfl_xor_sync(0xffffffffu, ss[it], o);
-        }
-        if ((lane & 15) == 0) {
-#pragma unroll
-            for (int it = 0; it < PASSES; ++it) {
-                const int row = (lane >> 4) + 2 * it;
-                if (gridDim.z == 1) row_scale[row] = 1.0f / sqrtf(ss[it] / (float)before.K + before.eps);
-                else if (blockIdx.x == 0 && ok && row < tokens) atomicAdd(before.sumsq_out + row, ss[it]);
-            }
-        }
-        if (gridDim.z == 1) asm volatile("bar.sync 1, 160;" ::: "memory");   // with the four consumer warps
-    } else if (warp == 0) {
+    if (warp == 0) {
         if (lane == 0) {
             // weights are written by no kernel of a step: the first ring is requested before waiting for
             // the previous kernel, the activation tiles only after it
@@ -595,24 +538,48 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         bool ok = true;
         int s = 0;
         uint32_t phase = 0;
+        float ss[NT];                                  // XNORM, first consumer warp: sum x^2 of tokens g + 8 nt over this lane's k
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) ss[nt] = 0.f;
         for (int i = 0; i < nkb; ++i, s = (s + 1 == FEW_STAGES ? 0 : s + 1), phase ^= (s == 0)) {
             if (!mbar_wait(&full[s], phase)) { if (lane == 0) atomicExch(status, 2); *failed = 1; ok = false; }
             const uint32_t w_tile = smem_u32(smem + s * FEW_STAGE_BYTES);
             const uint8_t* x_tile = smem + s * FEW_STAGE_BYTES + FEW_W_BYTES;
-            if (XNORM) {
-                if (ok && !mbar_wait(&made[s], phase)) { if (lane == 0) atomicExch(status, 5); *failed = 1; ok = false; }
-                // the bfloat16 operand now lies where the first float32 box was
-            }
             if (!ok) break;
+            const float* gain_tile = reinterpret_cast<const float*>(x_tile + FT::X_BYTES);
+            const int k_abs = (kb_begin + i) * BLOCK_K;
 #pragma unroll
             for (int ks = 0; ks < BLOCK_K / 16; ++ks) {
                 uint32_t b[NT][2];
+                if (XNORM) {
+                    // float32 tile: value k of the k-block lies in box k / 32, 16-byte chunk (k % 32) / 4 of its row
+                    // (swizzled with the row). This lane's k: 16 ks + 2 t, + 1 and the same + 8. The gain beyond K
+                    // is unset (and x is zero there).
+                    const int k0 = ks * 16 + 2 * t;
+                    float2 g0 = make_float2(0.f, 0.f), g1 = g0;
+                    if (k_abs + k0 < before.K) g0 = *reinterpret_cast<const float2*>(gain_tile + k0);
+                    if (k_abs + k0 + 8 < before.K) g1 = *reinterpret_cast<const float2*>(gain_tile + k0 + 8);
+                    const int c0 = 4 * (ks & 1) + (t >> 1);
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const int row = g + 8 * nt;                    // token; row & 7 == g
-                    const uint8_t* xr = x_tile + row * 128 + t * 4;
-                    b[nt][0] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks) ^ g) << 4));
-                    b[nt][1] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks + 1) ^ g) << 4));
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const int row = g + 8 * nt;                // token; row & 7 == g
+                        const uint8_t* xr = x_tile + (ks >> 1) * FT::X_BOX_BYTES + row * 128 + (t & 1) * 8;
+                        const float2 v0 = *reinterpret_cast<const float2*>(xr + ((c0 ^ g) << 4));
+                        const float2 v1 = *reinterpret_cast<const float2*>(xr + (((c0 + 2) ^ g) << 4));
+                        if (w == 0) ss[nt] += v0.x * v0.x + v0.y * v0.y + v1.x * v1.x + v1.y * v1.y;
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(v0.x * g0.x, v0.y * g0.y);
+                        __nv_bfloat162 hi = __floats2bfloat162_rn(v1.x * g1.x, v1.y * g1.y);
+                        b[nt][0] = *reinterpret_cast<uint32_t*>(&lo);
+                        b[nt][1] = *reinterpret_cast<uint32_t*>(&hi);
+                    }
+                } else {
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const int row = g + 8 * nt;                    // token; row & 7 == g
+                        const uint8_t* xr = x_tile + row * 128 + t * 4;
+                        b[nt][0] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks) ^ g) << 4));
+                        b[nt][1] = *reinterpret_cast<const uint32_t*>(xr + (((2 * ks + 1) ^ g) << 4));
+                    }
                 }
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
@@ -627,8 +594,21 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty[s])) : "memory");
         }
         ok = ok && *failed == 0;
+        if (XNORM && w == 0) {
+            // a token's sum of x^2: over the four lanes that shared its row
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 1);
+                ss[nt] += __shfl_xor_sync(0xffffffffu, ss[nt], 2);
+                const int row = g + 8 * nt;
+                if (t == 0) {
+                    if (gridDim.z == 1) row_scale[row] = 1.0f / sqrtf(ss[nt] / (float)before.K + before.eps);
+                    else if (blockIdx.x == 0 && ok && row < tokens) atomicAdd(before.sumsq_out + row, ss[nt]);
+                }
+            }
+        }
         if (XNORM && gridDim.z == 1) {
-            asm volatile("bar.sync 1, 160;" ::: "memory");             // the operand maker has written the rows' factors
+            asm volatile("bar.sync 1, 128;" ::: "memory");             // the first consumer warp has written the rows' factors
 #pragma unroll
             for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -725,7 +705,7 @@ int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int t
     // with 6; giving the short products no more stages than they have k-blocks changed nothing; a q|k|v product
     // with more than the shared ring keeps the attention kernel's CTAs from starting beside it: 0.81 ms)
     const int smem = stages * FT::STAGE_BYTES + FT::TAIL_BYTES;
-    cudaError_t err = lp_launch(kernel, grid, FEW_THREADS + (XNORM ? 32 : 0), smem, stream, mw, mx, out, tokens, features,
+    cudaError_t err = lp_launch(kernel, grid, FEW_THREADS, smem, stream, mw, mx, out, tokens, features,
                                 ldc, k_blocks, per_split, stages, status, norm, before);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_fewtok: %s", cudaGetErrorString(err));
