@@ -732,7 +732,7 @@ int dispatch_fewtok(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw,
 
 static bool fewtok_enabled() { return few_settings().enabled != 0; }
 
-// ------------------------------------------------------------------ 17 to 64 tokens with the norm on the way in
+// ------------------------------------------------------------------ 9 to 64 tokens with the norm on the way in
 // The one-tile tcgen05 product for a decode batch beyond what the mma.sync kernel above serves, taking the
 // float32 residual stream and applying an RMS norm on the way in, as that kernel does: the tile of x comes as
 // float32 (two boxes of rows x 32 values per k-block) with the gain's 64 values; four "maker" warps turn it into
@@ -1654,7 +1654,7 @@ extern "C" int lp_gemm_tcgen05(const void* X, const void* W, void* out, int out_
 }
 
 // A product for at most 64 tokens with what a decode step fuses around it: the mma.sync kernel above up to 16
-// tokens, the one-tile tcgen05 kernels (with the norm on the way in, or plain) beyond.
+// tokens (8 with the norm on the way in), the one-tile tcgen05 kernels (with the norm on the way in, or plain) beyond.
 // x_dtype LP_F32: X is the float32 residual stream and the product applies the RMS norm (gain, eps) on the
 // way in; with splits > 1 the output then still lacks the rows' factors and `sumsq_out` [tokens] (zero before
 // the call) receives sum x^2 per token for the reader to apply them. x_dtype LP_BF16: X as in lp_gemm_tcgen05.
@@ -1690,8 +1690,11 @@ extern "C" int lp_gemm_fewtok(const void* X, int x_dtype, const void* W, void* o
     const NormBefore before{gain, eps, K, sumsq_out, zero, zero ? zero_count : 0};
     const bool bf = out_dtype == LP_BF16;
     const int mmode = mode == LP_GEMM_SWIGLU ? LP_GEMM_SWIGLU : LP_GEMM_STORE;
-    if (tokens > 16) {
-        // beyond what the mma.sync consumers serve well: the tcgen05 kernels, with the norm on the way in or without
+    // Beyond what the mma.sync consumers serve well: the tcgen05 kernels. With the norm on the way in that is beyond
+    // 8 tokens (two token tiles double what every consumer warp converts; measured at the 1B shape, ms per step
+    // with the mma.sync kernel against the tcgen05 kernel: 9 tokens 0.803 / 0.796, 12 tokens 0.840 / 0.790,
+    // 16 tokens 0.842 / 0.797), without it beyond 16 (12 tokens: 0.790 against 0.807 with the tcgen05 kernel).
+    if (tokens > (xnorm ? 8 : 16)) {
         const int tile = tokens <= 32 ? 32 : 64;
         if (xnorm) {
             rc = make_map_f32(&mx, X, tokens, K, ldx, tile);
@@ -1709,7 +1712,7 @@ extern "C" int lp_gemm_fewtok(const void* X, int x_dtype, const void* W, void* o
     rc = xnorm ? make_map_f32(&mx, X, tokens, K, ldx, 16) : make_map(&mx, X, tokens, K, ldx, 16);
     if (rc) return rc;
 #define LP_FEW(NT, XN) dispatch_fewtok<NT, XN>(mmode, bf, atomic, mw, mx, out, tokens, features, ldc, k_blocks, splits, status, after, before, stream)
-    if (xnorm) return tokens <= 8 ? LP_FEW(1, true) : LP_FEW(2, true);
+    if (xnorm) return LP_FEW(1, true);
     return tokens <= 8 ? LP_FEW(1, false) : LP_FEW(2, false);
 #undef LP_FEW
 }

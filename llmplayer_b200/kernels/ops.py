@@ -90,7 +90,7 @@ class KernelSettings:
     ``ring_alone``: stages of that kernel's ring when two CTAs share an SM / when a CTA has one to itself.
     ``ring_alone_tile``: the most stages the one-tile tcgen05 product takes when its grid has no more CTAs than SMs
     (0, the default: never more than what lets two CTAs share an SM; a deeper ring measured slower).
-    ``ring_normed``: the same for the tcgen05 product with the norm on the way in (17 to 64 tokens), whose stages
+    ``ring_normed``: the same for the tcgen05 product with the norm on the way in (9 to 64 tokens), whose stages
     also hold a float32 tile of x; there the deeper ring measured faster."""
     pdl: bool = True
     few_tokens: int = 32
@@ -650,8 +650,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE,
 
 FEW_TOKENS_MAX = 64                  # what the few-token entry takes
 # Up to where the parts choose it with the norm inside (``settings.few_tokens``). Measured at the 1B shape (ms per
-# step, norm inside against separate norm kernels): 8 tokens 0.70 / 0.76, 12 tokens 0.84 / 0.87, 16 tokens
-# 0.85 / 0.88 (the mma.sync kernel); 20 tokens 0.84 / 0.89, 32 tokens 0.86 / 0.94 (the tcgen05 kernel with operand
+# step, norm inside against separate norm kernels): 8 tokens 0.68 / 0.76 (the mma.sync kernel); 12 tokens
+# 0.79 / 0.87, 16 tokens 0.80 / 0.88, 20 tokens 0.84 / 0.89, 32 tokens 0.86 / 0.94 (the tcgen05 kernel with operand
 # makers); 48 tokens 1.07 / 0.99 and 64 tokens 1.14 / 1.06: beyond 32 tokens the norm kernels stay.
 FEW_TOKENS = max(0, min(int(settings.few_tokens), FEW_TOKENS_MAX))
 
@@ -659,7 +659,7 @@ FEW_TOKENS = max(0, min(int(settings.few_tokens), FEW_TOKENS_MAX))
 def gemm_few(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, mode: int = STORE, *, norm=None,
              sumsq: Optional[torch.Tensor] = None, zero: Optional[torch.Tensor] = None) -> bool:
     """out (=|+=) f(x) @ w.T for at most ``FEW_TOKENS_MAX`` rows, with what a decode step fuses around it
-    (up to 16 rows the mma.sync kernel, beyond that the one-tile tcgen05 kernels).
+    (up to 16 rows, 8 with a norm, the mma.sync kernel; beyond that the one-tile tcgen05 kernels).
 
     ``norm = (gain, eps)``: ``x`` is the float32 residual stream and the product applies the RMS norm on
     the way in. If the K range is then shared out over CTAs (few output features), ``out`` still lacks each
