@@ -265,11 +265,21 @@ __device__ __forceinline__ void attention_decode_unit(
 
     // TMA: one barrier per stage, behind the ring and (FUSED) the extras described below
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * stage_bytes + (HEAD_ROWS * hd + 2 * hd) * 2 + 256 * 4);
-    auto request_page = [&](int p) {               // by one thread: the share's page p into stage p % STAGES
+    // The first warp keeps 32 entries of the page table in its lanes (entry p of the share in lane p % 32, loaded
+    // 32 at a time), so that a request does not begin with a round trip to L2 for the page's number.
+    int table_lane = 0, table_base = 0;
+    if (TMA && warp == 0 && lane < npages) table_lane = table[page_lo + lane];
+    auto page_number = [&](int p) {                // called by the whole first warp
+        if (p >= table_base + 32) {
+            table_base = p & ~31;
+            table_lane = table_base + lane < npages ? table[page_lo + table_base + lane] : 0;
+        }
+        return __shfl_sync(0xffffffffu, table_lane, p & 31);
+    };
+    auto request_page = [&](int p, int page) {     // by one thread: the share's page p (number `page`) into stage p % STAGES
         uint8_t* st = smem + (p % STAGES) * stage_bytes;
         uint64_t* bar = &full[p % STAGES];
         mbar_expect_tx(bar, (uint32_t)stage_bytes);
-        const int page = table[page_lo + p];
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
             const int row = ((page * 2 + which) * G + g) * PAGE;
@@ -279,10 +289,15 @@ __device__ __forceinline__ void attention_decode_unit(
     };
     // the ring is requested first; what follows overlaps with the copies
     if (TMA) {
-        if (tid == 0) {
-            for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            for (int p = 0; p < STAGES && p < npages; ++p) request_page(p);
+        if (warp == 0) {
+            if (lane == 0) {
+                for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            }
+            for (int p = 0; p < STAGES && p < npages; ++p) {
+                const int page = page_number(p);
+                if (lane == 0) request_page(p, page);
+            }
         }
     } else {
 #pragma unroll
@@ -485,10 +500,13 @@ __device__ __forceinline__ void attention_decode_unit(
         unit_sync<NAMED, NT>();
         // the group's stages are free: the group that comes GROUPS later goes there
         if (TMA) {
-            if (tid == 0) {
+            if (warp == 0) {
                 for (int j = 0; j < PG; ++j) {
                     const int nxt = (gi + GROUPS) * PG + j;
-                    if (nxt < npages) request_page(nxt);
+                    if (nxt < npages) {
+                        const int page = page_number(nxt);
+                        if (lane == 0) request_page(nxt, page);
+                    }
                 }
             }
         } else {

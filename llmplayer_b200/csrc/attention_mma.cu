@@ -356,6 +356,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map, const __
                             int min_share_pages, int head_groups, FusedDecodeArgs fused, int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);     // the swizzle's pattern repeats every 1024 bytes
+    if (threadIdx.x == 32) asm volatile("prefetch.tensormap [%0];" ::"l"(&kv_map) : "memory");
     lp_grid_release();
     const bool early = fused.pages_rw != nullptr;
     if (!early) lp_grid_wait();
