@@ -166,7 +166,9 @@ struct Tile {
 };
 
 // out: [tokens, ldc]; OUT_BF16 selects the element type of a STORE / SWIGLU output.
-template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
+// TAIL: the product is followed by a norm that its last CTA writes (NormAfter); a kernel of its own, since the
+// tail's registers (116 against 48) would otherwise keep the next kernel's CTAs from starting beside this one.
+template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC, bool TAIL = false>
 __global__ void __launch_bounds__(Tile<BLOCK_TOK, MODE>::NTHREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
@@ -382,7 +384,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)T::TMEM_COLS));
     }
-    if (ATOMIC) norm_after_tail<T::NTHREADS>(norm, out, tokens, features, ldc);
+    if constexpr (ATOMIC && TAIL) norm_after_tail<T::NTHREADS>(norm, out, tokens, features, ldc);
 }
 
 // ------------------------------------------------------------------ a handful of tokens: mma.sync consumers
@@ -445,7 +447,7 @@ __device__ __forceinline__ void mma_m16n8k16(float* c, const uint32_t* a, uint32
 }
 
 // NT: n-tiles of 8 tokens (1, 2, 4 or 8). MODE: STORE or SWIGLU (interleaved rows). out as in the tcgen05 kernel.
-template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
+template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM, bool TAIL = false>
 __global__ void __launch_bounds__(FEW_THREADS, 2)
 gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                    void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int k_blocks_per_split,
@@ -655,7 +657,7 @@ gemm_fewtok_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         if (ATOMIC) __threadfence();
     }
     __syncthreads();
-    if (ATOMIC) norm_after_tail<NTHREADS>(norm, out, tokens, features, ldc);
+    if constexpr (ATOMIC && TAIL) norm_after_tail<NTHREADS>(norm, out, tokens, features, ldc);
 }
 
 // Settings of the few-token product (lp_gemm_configure; until that is called, the environment's
@@ -681,11 +683,11 @@ static FewSettings& few_settings() {
     return st;
 }
 
-template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM>
+template <int NT, int MODE, bool OUT_BF16, bool ATOMIC, bool XNORM, bool TAIL = false>
 int launch_fewtok(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
                   int splits, int* status, const NormAfter& norm, const NormBefore& before, cudaStream_t stream) {
     using FT = FewTile<XNORM, NT>;
-    auto kernel = gemm_fewtok_kernel<NT, MODE, OUT_BF16, ATOMIC, XNORM>;
+    auto kernel = gemm_fewtok_kernel<NT, MODE, OUT_BF16, ATOMIC, XNORM, TAIL>;
     static bool configured = false;
     if (!configured) {
         const int most = FT::MAX_ALONE * FT::STAGE_BYTES + FT::TAIL_BYTES;
@@ -724,6 +726,9 @@ int dispatch_fewtok(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw,
         if (out_bf16) LP_GO(LP_GEMM_SWIGLU, true, false);
         LP_GO(LP_GEMM_SWIGLU, false, false);
     }
+    if (atomic && norm.weight != nullptr)
+        return launch_fewtok<NT, LP_GEMM_STORE, false, true, XNORM, true>(mw, mx, out, tokens, features, ldc, k_blocks, splits,
+                                                                       status, norm, before, stream);
     if (atomic) LP_GO(LP_GEMM_STORE, false, true);
     if (out_bf16) LP_GO(LP_GEMM_STORE, true, false);
     LP_GO(LP_GEMM_STORE, false, false);
@@ -1451,14 +1456,14 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, i
 // For tests of the bounded waits: the next launch of the one-tile kernel gets this k-block withheld (then -1 again).
 static int withhold_next_kblock = -1;
 
-template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
+template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC, bool TAIL = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int tokens, int features, int ldc, int k_blocks,
            int splits, int up_offset, int* status, const NormAfter& norm, cudaStream_t stream) {
     (void)up_offset;
     const int withheld = withhold_next_kblock;
     withhold_next_kblock = -1;
     using T = Tile<BLOCK_TOK, MODE>;
-    auto kernel = gemm_tcgen05_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC>;
+    auto kernel = gemm_tcgen05_kernel<BLOCK_TOK, MODE, OUT_BF16, ATOMIC, TAIL>;
     static bool configured = false;
     if (!configured) {
         const int most = T::STAGES_ALONE * T::STAGE_BYTES + T::TAIL_BYTES;
@@ -1505,6 +1510,9 @@ int dispatch(int mode, bool out_bf16, bool atomic, const CUtensorMap& mw, const 
             LP_GO(LP_GEMM_SWIGLU, false, false);
         }
     }
+    if (atomic && norm.weight != nullptr)
+        return launch<BLOCK_TOK, LP_GEMM_STORE, false, true, true>(mw, mx, out, tokens, features, ldc, k_blocks, splits,
+                                                                  up_offset, status, norm, stream);
     if (atomic) LP_GO(LP_GEMM_STORE, false, true);
     if (out_bf16) LP_GO(LP_GEMM_STORE, true, false);
     LP_GO(LP_GEMM_STORE, false, false);
