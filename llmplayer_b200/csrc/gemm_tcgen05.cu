@@ -20,11 +20,11 @@
 //
 // Three forms live in this file, chosen by the number of tokens of a step:
 //   * gemm_tcgen05_kernel: one output tile per CTA, token tiles of 16..256 (what is described above);
-//     serves 17 to some hundred tokens.
-//   * gemm_fewtok_kernel: at most 64 tokens (chosen up to 16). The same TMA ring, but four warps of
-//     ldmatrix + mma.sync consume it: one tcgen05.mma takes about 142 cycles whatever its shape, and with
-//     weights as its 128-row operand that is too few weight bytes per instruction to keep up with HBM.
-//     Can apply the RMS norm of its input itself.
+//     serves 17 to some hundred tokens. gemm_tcgen05_normed_kernel: the same for 9 to 32 tokens with the RMS
+//     norm of its input applied on the way in.
+//   * gemm_fewtok_kernel: at most 16 tokens. The same TMA ring, but four warps of ldmatrix + mma.sync consume
+//     it: the sums stay in registers and the epilogue, which nothing hides in a one-tile kernel, is a few
+//     stores per thread. Can apply the RMS norm of its input itself (8 tokens at most).
 //   * gemm_persistent_kernel: prompts. One CTA per SM walks over the tiles with two accumulators in tensor
 //     memory; for the gated product the tokens are the MMA's M and 256 weight rows its N.
 //
@@ -388,9 +388,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 }
 
 // ------------------------------------------------------------------ a handful of tokens: mma.sync consumers
-// For up to 16 tokens the tcgen05 path is bound by its issue rate, not by memory: one tcgen05.mma takes
-// about 142 cycles whatever its shape (measured: M 64/128, N 16..256), and with the weights as the
-// 128-row operand it consumes only 4 KB of them, some 40-50 GB/s per SM, below an SM's share of HBM.
+// For up to 16 tokens the one-tile tcgen05 kernel measured slower (8 tokens: 0.80 against 0.69 ms per step at
+// the 1B shape): what it does after its last MMA (accumulator ready, tensor memory to registers, the exchange of
+// the gated halves, stores) is not hidden by anything, and the main loop gains nothing from the tensor memory at
+// these sizes. (A tcgen05.mma of 128 x N x 16 issues every 55 cycles for N <= 64; an earlier figure of 142
+// cycles for any shape came from a probe whose loop divided by a run-time number in the issuing thread.)
 // Here the same ring of TMA stages feeds four warps that read the swizzled tiles with ldmatrix and
 // multiply with mma.sync m16n8k16: the 8 tokens of an n-tile are exactly the instruction's N, nothing
 // is issued by a single thread, and the sums stay in registers (no tensor memory, no accumulator

@@ -102,9 +102,9 @@ def test_full_width_layers_bfloat16_against_float32(tmp_path):
 @pytest.mark.parametrize("batch", [12, 20, 40])
 def test_full_width_decode_batches(tmp_path, batch):
     """Sequences of unequal lengths decoding together at the Llama-3.2-1B widths, against the float32 engine.
-    Twelve: the few-token products with two tiles of 8 tokens, the norm inside them and the row factor left to
-    the attention kernel. Twenty: the tcgen05 products with a 32-token tile, the norm applied by operand makers
-    inside them. Forty: 64-token tiles and norm kernels of their own."""
+    Twelve: the tcgen05 products with operand makers for the two products behind a norm (the row factor of q|k|v
+    left to the attention kernel), the few-token products with two tiles of 8 tokens for the other two. Twenty:
+    tcgen05 products with a 32-token tile throughout. Forty: 64-token tiles and norm kernels of their own."""
     from llmplayer_b200 import Engine
     from llmplayer_b200.config import config_from_dict
     from llmplayer_b200.weights import write_random_model
