@@ -336,3 +336,45 @@ def test_fused_decode_equals_rotation_then_attention(H, G, hd, rd, pairing, wind
     torch.cuda.synchronize()
     assert torch.equal(pages_a, pages_b)                      # the same keys and values were stored
     assert float((got.float() - want.float()).abs().max()) <= 2e-2
+
+
+@pytest.mark.parametrize("H,G,hd", [(8, 2, 64), (4, 1, 128)])
+def test_fused_decode_over_more_than_32_pages_in_one_share(H, G, hd):
+    """One share per sequence holding 33 to 47 pages: the kernel that brings its pages by TMA keeps 32 entries
+    of the page table in the first warp's lanes and has to fetch the next 32 on the way. Against the separate
+    rotation and decode kernels (16-byte copies), on pages that are scattered over the cache."""
+    from llmplayer_b200.kernels import ops
+    dev = "cuda:0"
+    lengths = [2500, 2049, 3000, 70, 2113]
+    B = len(lengths)
+    _, pages, table = build_cache(lengths, G, hd, torch.bfloat16, seed=hd)
+    g = torch.Generator().manual_seed(8)
+    qkv = torch.randn(B, (H + 2 * G) * hd, generator=g).to(dev)
+    rd = hd
+    inv = (torch.rand(rd // 2, generator=g) * 0.01).to(dev)
+    table_d = table.to(dev)
+    kv_len = torch.tensor(lengths, dtype=torch.int32, device=dev)
+    positions = kv_len - 1
+    seq_ids = torch.arange(B, dtype=torch.int32, device=dev)
+    kw = dict(num_heads=H, num_kv_heads=G, head_dim=hd)
+    per = table.shape[1]
+
+    def scratch(name, shape, dt):
+        return torch.full(shape, float("nan"), dtype=dt, device=dev)
+
+    rotation = ops.Rotation(inv, rd, False)
+    pages_a = pages.to(dev).clone()
+    q = torch.empty(B, H * hd, dtype=torch.bfloat16, device=dev)
+    ops.rope_cache_write(qkv, rotation, positions, seq_ids, table_d, q, pages_a, **kw)
+    want = torch.zeros_like(q)
+    ops.attention_decode(q, want, pages_a, table_d, kv_len, scratch, scale=hd ** -0.5, window=None,
+                         pages_per_split=per, num_splits=1, **kw)
+    pages_b = pages.to(dev).clone()
+    got = torch.full_like(q, 3.0)
+    counters = torch.zeros(ops.decode_groups(B, H, G), dtype=torch.int32, device=dev)
+    ops.attention_decode_fused(qkv, rotation, got, pages_b, table_d, kv_len, scratch, counters, write_kv=True,
+                               scale=hd ** -0.5, window=None, pages_per_split=per, num_splits=1, **kw)
+    torch.cuda.synchronize()
+    ops.check_kernel_status()
+    assert torch.equal(pages_a, pages_b)
+    assert float((got.float() - want.float()).abs().max()) <= 2e-2
