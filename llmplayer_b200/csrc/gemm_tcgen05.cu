@@ -48,7 +48,6 @@ namespace {
 
 constexpr int BLOCK_FEAT = 128;   // weight rows per CTA = MMA M
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;      // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
 // The weight tile(s) of one k-block. WIDE: gate rows of two neighbouring 64-feature blocks form the
 // first 128-row tile, their up rows the second (the tensor map's box is 64 rows then).
 template <int MODE>
@@ -1132,8 +1131,12 @@ struct PersistentTile {
     static_assert(!TOKM || BLOCK_TOK == 128, "tokens are the MMA's M");
 };
 
+// Eight epilogue warps: two per quarter of the tensor memory's lanes, each with half of the accumulator's columns.
+// The products of a prompt with about one tile per CTA (output and down projection: 128 tiles, q|k|v: 192) have
+// no next tile under whose MMAs the epilogue could run.
+constexpr int PERSIST_THREADS = 64 + 32 * 8;
 template <int BLOCK_TOK, int MODE, bool OUT_BF16, bool ATOMIC>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(PERSIST_THREADS, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                        void* __restrict__ out, int tokens, int features, int ldc, int k_blocks, int feat_tiles,
                        int num_tiles, int group_tok, int* __restrict__ status, QkvEpilogue qkv) {
@@ -1165,7 +1168,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
         for (int s = 0; s < T::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int k = 0; k < 2; ++k) { mbar_init(&acc_full[k], 1); mbar_init(&acc_empty[k], 4); }
+        for (int k = 0; k < 2; ++k) { mbar_init(&acc_full[k], 1); mbar_init(&acc_empty[k], 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -1242,6 +1245,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     } else {
         // ------------------------------------------------------------ epilogue: drains one accumulator at a time
         const int quarter = warp & 3;
+        const int ehalf = (warp - 2) >> 2;                 // which half of the columns this warp drains
         constexpr int CHUNK = 32;
         int j = 0;
         bool ok = true;
@@ -1275,9 +1279,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 };
                 const int rotated_heads = ang == nullptr ? 0 : (qkv.pages ? qkv.H + qkv.G : qkv.H);     // heads below this index are rotated
                 const bool split_half = ang != nullptr && !qkv.interleaved;
+                // this warp's heads of the tile
+                const int hh_lo = ehalf ? (heads_per_tile + 1) / 2 : 0, hh_hi = ehalf ? heads_per_tile : (heads_per_tile + 1) / 2;
                 // heads that pass through (values; everything when there is no rotation) and interleaved pairs: chunk by chunk
 #pragma unroll 1
-                for (int hh = 0; hh < heads_per_tile; ++hh) {
+                for (int hh = hh_lo; hh < hh_hi; ++hh) {
                     const int head = ft * heads_per_tile + hh;
                     if (head >= total_heads) break;
                     const bool rotate = head < rotated_heads;
@@ -1315,7 +1321,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 #pragma unroll
                         for (int i = 0; i < 32; ++i) cs[i] = live ? ang[c * 32 + i] : make_float2(1.f, 0.f);
 #pragma unroll 1
-                        for (int hh = 0; hh < heads_per_tile; ++hh) {
+                        for (int hh = hh_lo; hh < hh_hi; ++hh) {
                             const int head = ft * heads_per_tile + hh;
                             if (head >= rotated_heads) break;
                             __nv_bfloat16* dst = dest(head);
@@ -1344,7 +1350,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 const uint32_t lane_addr = tmem_base + ab * T::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
                 const int t = tt * BLOCK_TOK + quarter * 32 + lane;
 #pragma unroll 1
-                for (int part = 0; part < 4; ++part) {
+                for (int part = 2 * ehalf; part < 2 * ehalf + 2; ++part) {
                     const int half = part >> 1, c0 = (part & 1) * 32;
                     uint32_t g[CHUNK], u[CHUNK];
                     tmem_ld32(lane_addr + half * 128 + c0, g);
@@ -1386,7 +1392,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 const int f = ft * BLOCK_FEAT + quarter * 32 + lane;
                 const int tok0 = tt * BLOCK_TOK;
 #pragma unroll 1
-                for (int c0 = 0; c0 < BLOCK_TOK; c0 += CHUNK) {
+                for (int c0 = ehalf * (BLOCK_TOK / 2); c0 < (ehalf + 1) * (BLOCK_TOK / 2); c0 += CHUNK) {
                     uint32_t g[CHUNK], u[MODE == LP_GEMM_SWIGLU_WIDE ? CHUNK : 1];
                     tmem_ld32(lane_addr + c0, g);
                     if (MODE == LP_GEMM_SWIGLU_WIDE) tmem_ld32(lane_addr + BLOCK_TOK + c0, u);
@@ -1446,7 +1452,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, i
         const long long cost = (long long)gt * BLOCK_TOK + (long long)(gf < feat_tiles ? gf : feat_tiles) * w_rows;
         if (best < 0 || cost <= best) { best = cost; group_tok = gt; }       // ties: the larger band
     }
-    cudaError_t err = lp_launch(kernel, dim3(grid), THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
+    cudaError_t err = lp_launch(kernel, dim3(grid), PERSIST_THREADS, T::SMEM_BYTES, stream, mw, mx, out, tokens, features, ldc,
                                 k_blocks, feat_tiles, num_tiles, group_tok, status, qkv);
     if (err != cudaSuccess) {
         snprintf(lp_error_text, sizeof(lp_error_text), "gemm_persistent: %s", cudaGetErrorString(err));
