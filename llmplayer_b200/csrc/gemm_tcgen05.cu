@@ -1102,10 +1102,10 @@ struct QkvEpilogue {
     int H, G, hd, page_size;
 };
 
-// 32 float32 values of a token -> 32 bfloat16 at dst (16-byte aligned)
-__device__ __forceinline__ void store_row32(__nv_bfloat16* dst, const float* v) {
+// 16 float32 values of a token -> 16 bfloat16 at dst (16-byte aligned)
+__device__ __forceinline__ void store_row16(__nv_bfloat16* dst, const float* v) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < 2; ++q) {
         uint4 packed;
         __nv_bfloat162 t0 = __floats2bfloat162_rn(v[q * 8], v[q * 8 + 1]), t1 = __floats2bfloat162_rn(v[q * 8 + 2], v[q * 8 + 3]);
         __nv_bfloat162 t2 = __floats2bfloat162_rn(v[q * 8 + 4], v[q * 8 + 5]), t3 = __floats2bfloat162_rn(v[q * 8 + 6], v[q * 8 + 7]);
@@ -1279,11 +1279,12 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 };
                 const int rotated_heads = ang == nullptr ? 0 : (qkv.pages ? qkv.H + qkv.G : qkv.H);     // heads below this index are rotated
                 const bool split_half = ang != nullptr && !qkv.interleaved;
-                // this warp's heads of the tile
-                const int hh_lo = ehalf ? (heads_per_tile + 1) / 2 : 0, hh_hi = ehalf ? heads_per_tile : (heads_per_tile + 1) / 2;
+                // Of every chunk of 32 columns this warp takes 16 (the two warps of a quarter of the lanes share
+                // each head, so that neither fetches the token's angles twice).
+                const int sub = ehalf * 16;
                 // heads that pass through (values; everything when there is no rotation) and interleaved pairs: chunk by chunk
 #pragma unroll 1
-                for (int hh = hh_lo; hh < hh_hi; ++hh) {
+                for (int hh = 0; hh < heads_per_tile; ++hh) {
                     const int head = ft * heads_per_tile + hh;
                     if (head >= total_heads) break;
                     const bool rotate = head < rotated_heads;
@@ -1292,23 +1293,23 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     const uint32_t col0 = lane_addr + hh * hd;
 #pragma unroll 1
                     for (int c = 0; c < chunks; ++c) {
-                        uint32_t g[32];
-                        float v[32];
-                        tmem_ld32(col0 + c * 32, g);
+                        uint32_t g[16];
+                        float v[16];
+                        tmem_ld16(col0 + c * 32 + sub, g);
                         tmem_ld_wait();
                         if (rotate) {
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                const float2 cs = live ? ang[c * 16 + i] : make_float2(1.f, 0.f);
+                            for (int i = 0; i < 8; ++i) {
+                                const float2 cs = live ? ang[c * 16 + ehalf * 8 + i] : make_float2(1.f, 0.f);
                                 const float xa = __uint_as_float(g[2 * i]), xb = __uint_as_float(g[2 * i + 1]);
                                 v[2 * i] = __fsub_rn(__fmul_rn(xa, cs.x), __fmul_rn(xb, cs.y));
                                 v[2 * i + 1] = __fadd_rn(__fmul_rn(xa, cs.y), __fmul_rn(xb, cs.x));
                             }
                         } else {
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(g[i]);
+                            for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(g[i]);
                         }
-                        if (live) store_row32(dst + c * 32, v);
+                        if (live) store_row16(dst + c * 32 + sub, v);
                     }
                 }
                 // pairs (i, i + hd / 2): chunk c of a head with its chunk c + half_chunks; the token's angles of a
@@ -1317,29 +1318,29 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                     const int half_chunks = chunks >> 1;
 #pragma unroll 1
                     for (int c = 0; c < half_chunks; ++c) {
-                        float2 cs[32];
+                        float2 cs[16];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) cs[i] = live ? ang[c * 32 + i] : make_float2(1.f, 0.f);
+                        for (int i = 0; i < 16; ++i) cs[i] = live ? ang[c * 32 + sub + i] : make_float2(1.f, 0.f);
 #pragma unroll 1
-                        for (int hh = hh_lo; hh < hh_hi; ++hh) {
+                        for (int hh = 0; hh < heads_per_tile; ++hh) {
                             const int head = ft * heads_per_tile + hh;
                             if (head >= rotated_heads) break;
                             __nv_bfloat16* dst = dest(head);
                             const uint32_t col0 = lane_addr + hh * hd;
-                            uint32_t g[32], u[32];
-                            float va[32], vb[32];
-                            tmem_ld32(col0 + c * 32, g);
-                            tmem_ld32(col0 + (c + half_chunks) * 32, u);
+                            uint32_t g[16], u[16];
+                            float va[16], vb[16];
+                            tmem_ld16(col0 + c * 32 + sub, g);
+                            tmem_ld16(col0 + (c + half_chunks) * 32 + sub, u);
                             tmem_ld_wait();
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) {
+                            for (int i = 0; i < 16; ++i) {
                                 const float xa = __uint_as_float(g[i]), xb = __uint_as_float(u[i]);
                                 va[i] = __fsub_rn(__fmul_rn(xa, cs[i].x), __fmul_rn(xb, cs[i].y));
                                 vb[i] = __fadd_rn(__fmul_rn(xa, cs[i].y), __fmul_rn(xb, cs[i].x));
                             }
                             if (live) {
-                                store_row32(dst + c * 32, va);
-                                store_row32(dst + (c + half_chunks) * 32, vb);
+                                store_row16(dst + c * 32 + sub, va);
+                                store_row16(dst + (c + half_chunks) * 32 + sub, vb);
                             }
                         }
                     }
