@@ -770,18 +770,23 @@ def attention_prefill(q: torch.Tensor, out: torch.Tensor, pages: torch.Tensor, p
 
 
 MIN_SHARE_PAGES = 8
+LONG_SHARE_PAGES = 14
 
 
 def decode_split(batch: int, num_kv_heads: int, num_heads: int, table_width: int):
     """How a decode step's pages are shared out over CTAs: (pages per share, shares) for page tables of
     ``table_width`` entries. A share and the merge of shares cost several dependent round trips to memory, so a
     sequence is cut only into shares of at least ``MIN_SHARE_PAGES`` pages, and into no more CTAs than there are SMs
-    (the kernel then gives each CTA 16 warps; measured at batch 8, context 1.9 k / 3.9 k: 0.82 / 0.96 ms per step
-    against 0.92 / 1.01 with twice the CTAs). This is the most shares a sequence can get; the kernels fit the
+    (the kernel then gives each CTA 16 warps), or twice that for shares of twice the pages. This is the most shares
+    a sequence can get; the kernels fit the
     number to each sequence's own length (at batch 8 and a context of 600 in a table of 16 pages: one share,
     0.69 ms per step, against 0.75 with two shares of 8 pages)."""
     groups = decode_groups(batch, num_heads, num_kv_heads)
     shares = max(1, min(table_width // MIN_SHARE_PAGES, num_sms() // groups))
+    # long sequences: up to two CTAs per SM (8 warps each) if every share still has LONG_SHARE_PAGES pages. Measured with the pages
+    # brought by TMA, ms per step at contexts of 3.5 k / 1 k: batch 4: 0.771 -> 0.756 / 0.716 -> 0.711, batch 8:
+    # 0.837 -> 0.818 / unchanged, batch 16: 1.080 -> 1.048 / 0.828 (0.856 with shares of 8 pages there)
+    shares = max(shares, min(table_width // LONG_SHARE_PAGES, 2 * num_sms() // groups))
     per = -(-table_width // shares)
     return per, -(-table_width // per)
 
