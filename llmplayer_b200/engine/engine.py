@@ -142,9 +142,13 @@ class Engine:
         width = 1
         if all(n == 1 for n in counts):
             # steps of one token each are replayed from captured graphs: keep the shape of the
-            # page tables stable while sequences grow (padding entries are never read)
+            # page tables stable while sequences grow (padding entries are never read). The width doubles
+            # when the longest table has come within a page of it, so that a batch is captured anew a
+            # handful of times in its life and not every 512 tokens.
             longest = max((len(t) for group in tables for t in group), default=1)
-            width = -(-longest // 8) * 8
+            width = 8
+            while width < longest + 1:
+                width *= 2
         return StepContext(self.workspace, sequences, tokens, tables, rows, min_table_width=width)
 
     def run(self, ctx: StepContext) -> torch.Tensor:
