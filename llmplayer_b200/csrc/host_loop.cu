@@ -33,11 +33,24 @@ extern "C" int lp_decode_loop(cudaGraphExec_t graph, cudaStream_t stream, int* m
     if (!graph || !meta || !sampled || !quiet || !stop_begin || !out) LP_REFUSE("decode_loop: a null argument");
     int fewest = quiet[0];
     for (int i = 1; i < B; ++i) fewest = quiet[i] < fewest ? quiet[i] : fewest;
-    volatile const int* fresh = sampled;
+    // The graph's last node copies the chosen tokens (all >= 0) into `sampled`. The loop marks the words with -1
+    // before each launch and watches them turn: that sees the end of a step a few microseconds before the stream's
+    // synchronisation wakes up. After a bounded number of looks it synchronises instead, and it always does so
+    // before it returns.
+    volatile int* fresh = const_cast<volatile int*>(sampled);
     for (int step = 0; step < max_steps; ++step) {
+        for (int i = 0; i < B; ++i) fresh[i] = -1;
         cudaError_t err = cudaGraphLaunch(graph, stream);
-        if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
+        if (err == cudaSuccess) {
+            bool seen = false;
+            for (long spin = 0; spin < 2000000 && !seen; ++spin) {
+                seen = true;
+                for (int i = 0; i < B; ++i) seen = seen && fresh[i] >= 0;
+            }
+            if (!seen) err = cudaStreamSynchronize(stream);     // after it every word is set
+        }
         if (err != cudaSuccess) {
+            cudaStreamSynchronize(stream);
             snprintf(lp_error_text, sizeof(lp_error_text), "decode_loop: step %d: %s", step, cudaGetErrorString(err));
             return (int)err;
         }
@@ -55,6 +68,11 @@ extern "C" int lp_decode_loop(cudaGraphExec_t graph, cudaStream_t stream, int* m
             meta[positions_at + i] += 1;
             meta[lengths_at + i] += 1;
         }
+    }
+    cudaError_t err = cudaStreamSynchronize(stream);
+    if (err != cudaSuccess) {
+        snprintf(lp_error_text, sizeof(lp_error_text), "decode_loop: %s", cudaGetErrorString(err));
+        return (int)err;
     }
     return 0;
 }
