@@ -903,3 +903,32 @@ extern "C" int lp_argmax(const float* logits, long long stride, int V, int B, vo
     lp_launch(argmax_final_kernel, B, 32, 0, stream, (const float*)part_val, (const int*)part_idx, out_token);
     return lp_check_launch("argmax");
 }
+
+// ---------------------------------------------------------------- the step's sampler block, fetched by a kernel
+// A captured decode step whose sampler block lies in page-locked host memory (see lp_decode_loop_sampled in
+// host_loop.cu): block i brings record i and as many of sequence i's edits as the record names, so that a step
+// moves what it uses and not the whole capacity. host: the page-locked block (device-readable); dev: the same
+// layout in device memory (records, then per sequence `cap` tokens, `cap` amounts, `cap` factors).
+__global__ void sample_fetch_kernel(const int* __restrict__ host, int* __restrict__ dev, int B, int cap, int record_words,
+                                    int field_count) {
+    lp_grid_release();
+    lp_grid_wait();
+    const int i = blockIdx.x;
+    for (int w = threadIdx.x; w < record_words; w += blockDim.x) dev[(size_t)i * record_words + w] = host[(size_t)i * record_words + w];
+    int count = host[(size_t)i * record_words + field_count];
+    count = count < 0 ? 0 : (count > cap ? cap : count);
+    const size_t edits = (size_t)B * record_words;
+    for (int part = 0; part < 3; ++part) {
+        const size_t base = edits + ((size_t)part * B + i) * cap;
+        for (int j = threadIdx.x; j < count; j += blockDim.x) dev[base + j] = host[base + j];
+    }
+}
+
+extern "C" int lp_sample_fetch(const int* host, int* dev, int B, int cap, int record_words, int field_count,
+                               cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (!host || !dev || cap <= 0 || record_words <= 0 || field_count < 0 || field_count >= record_words)
+        LP_REFUSE("sample_fetch: a block of %d records of %d words, %d edits each", B, record_words, cap);
+    lp_launch(sample_fetch_kernel, B, 128, 0, stream, host, dev, B, cap, record_words, field_count);
+    return lp_check_launch("sample_fetch");
+}

@@ -293,21 +293,27 @@ class Engine:
         that ran (at least one step), oldest first.
 
         ``quiet[i]``: how many of sequence i's next chosen tokens are certain to need no decision other than
-        "is it one of ``stops[i]``" (the generation loop knows: token budget, context). Given these, and
-        when every sampler is a plain greedy choice, the steps run from the native host loop: one captured
-        graph per step that holds the upload of the step's integers from page-locked memory, the model
-        walk, the argmax and the read-back of the chosen tokens (csrc/host_loop.cu), until a step is not
-        quiet. Otherwise one step runs through :meth:`step` and :meth:`sample`.
+        "is it one of ``stops[i]``" (the generation loop knows: token budget, context). Given these, the steps
+        run from the native host loop: one captured graph per step that holds the upload of the step's
+        integers from page-locked memory, the model walk, the choice of the tokens and their read-back
+        (csrc/host_loop.cu), until a step is not quiet. The choice is the argmax when every sampler is a plain
+        greedy one; with temperature, top-k, top-p, min-p and a repetition penalty it is the sampling kernels,
+        and the loop keeps each sequence's generator and window of recent tokens. Samplers with DRY or mirostat
+        (state that follows the drawn probabilities or searches the history) run one step at a time through
+        :meth:`step` and :meth:`sample`.
         """
+        # samplers whose state the native loop keeps: a generator and the window of recent tokens
+        native = all(s.plain_greedy or (s.config.mirostat == 0 and s.config.dry_multiplier <= 0) for s in samplers)
         if (quiet is not None and self.options.host_loop and self.use_graphs and self.runtime.fast
-                and self.model.capture_safe and all(s.plain_greedy for s in samplers)):
-            out = self._decode_fused(entries, quiet, stops, max_steps)
+                and self.model.capture_safe and native):
+            greedy = all(s.plain_greedy for s in samplers)
+            out = self._decode_fused(entries, quiet, stops, max_steps, None if greedy else list(samplers))
             if out is not None:
                 return out
         logits = self.step([(slot, [tok]) for slot, tok in entries], [[0]] * len(entries))
         return [self.sample(logits, list(range(len(entries))), samplers)]
 
-    def _decode_fused(self, entries, quiet, stops, max_steps) -> Optional[List[List[int]]]:
+    def _decode_fused(self, entries, quiet, stops, max_steps, samplers=None) -> Optional[List[List[int]]]:
         B = len(entries)
         want = [[0]] * B
         step_entries = [(slot, [tok]) for slot, tok in entries]
@@ -343,22 +349,39 @@ class Engine:
         key = ctx.fused_key
         if key is None:
             key = ctx.fused_key = (B, tuple(t.shape[1] for t in ctx.page_tables), ctx.meta.data_ptr(), ctx.host_pointer)
+        logits = self.workspace.get("logits", (B, self.vocab_size), torch.float32)
+        sampled = self.workspace.get("sampled", (B,), torch.int32)
+        landing, _ = self.workspace.pinned("sampled_host", B)
+        draw = None
+        if samplers is None:
+            work = self.workspace.get("argmax_work", (64 * B,), torch.float32)
+        else:
+            draw = self._sampler_block(samplers, B)
+            key = key + ("sampled", draw["sliced"], draw["host"].data_ptr(), draw["cap"])
         entry = self._fused.get(key)
         if entry is not None and entry["version"] != self.workspace.version:
             entry = None
-        logits = self.workspace.get("logits", (B, self.vocab_size), torch.float32)
-        sampled = self.workspace.get("sampled", (B,), torch.int32)
-        work = self.workspace.get("argmax_work", (64 * B,), torch.float32)
-        landing, _ = self.workspace.pinned("sampled_host", B)
 
         def one_step(upload: bool, captured: bool = False):
             if upload:
                 ctx.upload_moving(record=not captured)
             self.model.forward(ctx, self.cache, ctx.rows, logits)
-            ops.argmax(logits, work, sampled)
+            if draw is None:
+                ops.argmax(logits, work, sampled)
+            else:
+                d = draw
+                ops.sample_fetch(d["host"], d["dev"], B, d["cap"], d["record_words"], d["field_count"])
+                ops.sample(logits, d["work"], d["params"], d["edit_tok"], d["edit_sub"], d["edit_fac"], sampled,
+                           d["prob"], select=d["select"])
             landing[:B].copy_(sampled, non_blocking=True)
 
         try:
+            if entry is None and draw is not None:
+                # a shape's first step with a sampler: run once for nothing (it sizes every buffer; the step's keys
+                # and values are written again, the same, by the step that counts), then capture and go on below
+                one_step(upload=moved is not None)
+                torch.cuda.current_stream().synchronize()
+                entry = self._fused[key] = {"graph": None, "version": self.workspace.version}
             if entry is None:
                 # the first step of a shape runs directly (it sizes every buffer), the second is captured
                 one_step(upload=moved is not None)
@@ -378,7 +401,10 @@ class Engine:
                     entry = self._fused[key] = {"graph": graph, "version": entry["version"],
                                                 "exec": graph.raw_cuda_graph_exec(),
                                                 "launches": ops.launch_count() - before}
-                chosen = self._host_loop(ctx, entry, landing, B, steps, quiet, stops)
+                if draw is None:
+                    chosen = self._host_loop(ctx, entry, landing, B, steps, quiet, stops)
+                else:
+                    chosen = self._host_loop_sampled(ctx, entry, landing, B, steps, quiet, stops, samplers, draw)
                 ops.count_launches(entry["launches"] * len(chosen))
         except BaseException:
             self._last_ctx = None
@@ -390,12 +416,12 @@ class Engine:
         k = len(chosen)
         ctx.moved_on(k - 1)
         self.cache.commit(slots, [k] * B)
-        self.last_step_h2d_bytes = ctx.moving_bytes
+        self.last_step_h2d_bytes = ctx.moving_bytes + (0 if draw is None else 4 * B * draw["record_words"])
         self.last_step_d2h_bytes = 4 * B
         return chosen
 
-    def _host_loop(self, ctx, entry, landing, B, steps, quiet, stops) -> List[List[int]]:
-        lib = ops.library("host_loop")
+    @staticmethod
+    def _stop_arrays(B, quiet, stops):
         quiet_arr = np.asarray([int(q) for q in quiet], dtype=np.int32)
         begin = np.zeros(B + 1, dtype=np.int32)
         flat: List[int] = []
@@ -403,7 +429,81 @@ class Engine:
             if stops is not None:
                 flat.extend(int(t) for t in stops[i])
             begin[i + 1] = len(flat)
-        stop_arr = np.asarray(flat or [0], dtype=np.int32)
+        return quiet_arr, begin, np.asarray(flat or [0], dtype=np.int32)
+
+    def _sampler_block(self, samplers, B) -> dict:
+        """The buffers of a captured step that draws its tokens: the sampler block (one record per sequence and room
+        for the logit edits of a full window of recent tokens each) in page-locked and in device memory, and the
+        sampling kernels' scratch. The records' fixed fields are written here; the native loop fills in each step's
+        uniform number and edits."""
+        from ..sampling.sampler import PARAMS_DTYPE
+        lib = ops.library("sampling")
+        record = PARAMS_DTYPE.itemsize
+        if record != lib.lp_sample_params_size() or record % 4:
+            raise LLMPlayerError("the sampler's parameter record and the kernel's disagree")
+        words = record // 4
+        cap = max(s.max_recent for s in samplers)
+        total = B * (words + 3 * cap)
+        host, _ = self.workspace.pinned("sample_block_host", total)
+        host = host[:total]
+        dev = self.workspace.get("sample_block", (total,), torch.int32)
+        params = np.zeros(B, dtype=PARAMS_DTYPE)
+        for i, smp in enumerate(samplers):
+            c = smp.config
+            params[i] = (0.0 if c.is_greedy else 1.0 / np.float32(c.temperature), c.top_k, c.top_p, c.min_p,
+                         -1.0, 0.0, i * cap, 0, i)
+        host.numpy()[:B * words] = params.view(np.int32)
+        fields = {name: PARAMS_DTYPE.fields[name][1] // 4 for name in ("uniform", "edit_begin", "edit_count")}
+        capacity = ops.sample_slice_capacity(self.vocab_size)
+        sliced = any(not smp.config.is_greedy and 0 < smp.config.top_k <= capacity for smp in samplers)
+        head = B * words
+        return {
+            "host": host, "dev": dev, "cap": cap, "record_words": words, "field_count": fields["edit_count"],
+            "field_uniform": fields["uniform"], "field_begin": fields["edit_begin"], "sliced": sliced,
+            "params": dev[:head].view(torch.uint8), "edit_tok": dev[head:head + B * cap],
+            "edit_sub": dev[head + B * cap:head + 2 * B * cap].view(torch.float32),
+            "edit_fac": dev[head + 2 * B * cap:head + 3 * B * cap].view(torch.float32),
+            "work": self.workspace.get("sample_work", (B, self.vocab_size), torch.float32),
+            "prob": self.workspace.get("sample_prob", (B,), torch.float32),
+            "select": (self.workspace.get("sample_select", (B * ops.sample_select_words(),), torch.int32)
+                       if sliced else None),
+        }
+
+    def _host_loop_sampled(self, ctx, entry, landing, B, steps, quiet, stops, samplers, draw) -> List[List[int]]:
+        """The native loop with the samplers' state (csrc/host_loop.cu: lp_decode_loop_sampled); the samplers take
+        over the generators' states and the windows of recent tokens it leaves."""
+        lib = ops.library("host_loop")
+        quiet_arr, begin, stop_arr = self._stop_arrays(B, quiet, stops)
+        cap = draw["cap"]
+        rng = np.asarray([smp.rng._state for smp in samplers], dtype=np.uint64)
+        draws = np.asarray([0 if smp.config.is_greedy else 1 for smp in samplers], dtype=np.int32)
+        penalty = np.asarray([float(smp.config.repetition_penalty) for smp in samplers], dtype=np.float64)
+        recent = np.zeros((B, cap), dtype=np.int32)
+        recent_len = np.zeros(B, dtype=np.int32)
+        for i, smp in enumerate(samplers):
+            kept = smp.recent[-cap:]
+            recent[i, :len(kept)] = kept
+            recent_len[i] = len(kept)
+        scratch = np.zeros(2 * B * cap, dtype=np.int32)
+        out = np.empty((steps, B), dtype=np.int32)
+        ran = ctypes.c_int(0)
+        tokens_at, positions_at, lengths_at = ctx.moving_offsets
+        code = lib.lp_decode_loop_sampled(
+            entry["exec"], ops.current_stream(), ctx.host_pointer, tokens_at, positions_at, lengths_at,
+            draw["host"].data_ptr(), draw["record_words"], draw["field_uniform"], draw["field_begin"],
+            draw["field_count"], cap, landing.data_ptr(), B, steps, quiet_arr.ctypes.data, stop_arr.ctypes.data,
+            begin.ctypes.data, rng.ctypes.data, draws.ctypes.data, penalty.ctypes.data, recent.ctypes.data,
+            recent_len.ctypes.data, scratch.ctypes.data, out.ctypes.data, ctypes.byref(ran))
+        for i, smp in enumerate(samplers):                   # what ran, ran: the samplers go on from there
+            smp.rng._state = int(rng[i])
+            smp.recent = recent[i, :int(recent_len[i])].tolist()
+        if code != 0:
+            raise LLMPlayerError(lib.lp_last_error().decode("utf-8", "replace") or f"decode loop failed ({code})")
+        return out[:ran.value].tolist()
+
+    def _host_loop(self, ctx, entry, landing, B, steps, quiet, stops) -> List[List[int]]:
+        lib = ops.library("host_loop")
+        quiet_arr, begin, stop_arr = self._stop_arrays(B, quiet, stops)
         out = np.empty((steps, B), dtype=np.int32)
         ran = ctypes.c_int(0)
         tokens_at, positions_at, lengths_at = ctx.moving_offsets

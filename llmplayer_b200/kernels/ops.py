@@ -56,6 +56,8 @@ _SIGNATURES = {
     },
     "host_loop": {
         "lp_decode_loop": [_P, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P],
+        "lp_decode_loop_sampled": [_P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P,
+                                   _P, _P, _P, _P, _P],
     },
     "sampling": {
         "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P],
@@ -63,6 +65,7 @@ _SIGNATURES = {
         "lp_sample_select_words": [],
         "lp_sample_slice_capacity": [_I],
         "lp_argmax": [_P, ctypes.c_longlong, _I, _I, _P, _P, _P],
+        "lp_sample_fetch": [_P, _P, _I, _I, _I, _I, _P],
     },
 }
 
@@ -931,6 +934,21 @@ def sample(logits: torch.Tensor, work: torch.Tensor, params: torch.Tensor, edit_
     _check(lib, lib.lp_sample(logits.data_ptr(), V, work.data_ptr(), V, params.data_ptr(), B, edit_token.data_ptr(),
                               edit_subtract.data_ptr(), edit_factor.data_ptr(), select_ptr, out_token.data_ptr(),
                               out_prob.data_ptr(), _stream()))
+
+
+def sample_fetch(host_block: torch.Tensor, dev_block: torch.Tensor, batch: int, cap: int, record_words: int,
+                 field_count: int) -> None:
+    """Bring a step's sampler block (records, then ``cap`` edit tokens, amounts and factors per sequence) from
+    page-locked host memory: each record and as many edits as it names."""
+    _want(dev_block, "sample_fetch device block", torch.int32, 1)
+    if host_block.dtype != torch.int32 or not host_block.is_pinned() or host_block.numel() != dev_block.numel():
+        raise KernelError("sample_fetch: the host block must be page-locked int32 of the device block's size")
+    if dev_block.numel() != batch * (record_words + 3 * cap):
+        raise KernelError(f"sample_fetch: a block of {dev_block.numel()} words for {batch} records of {record_words} "
+                          f"words and {cap} edits each")
+    lib = library("sampling")
+    _check(lib, lib.lp_sample_fetch(host_block.data_ptr(), dev_block.data_ptr(), batch, cap, record_words, field_count,
+                                    _stream()))
 
 
 def advance(tokens: torch.Tensor, positions: torch.Tensor, kv_len: torch.Tensor, sampled: torch.Tensor) -> None:
