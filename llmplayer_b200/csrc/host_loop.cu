@@ -117,26 +117,29 @@ inline void window_drop(Window& w, int token) {
 }  // namespace
 
 // rng_state [B] (in/out), draws [B] (1: the sequence takes one float per token), penalty [B] (1.0: none),
-// recent [B, cap] with recent_len [B] (in/out, oldest first), scratch [2 * B * cap] ints for this loop's tables.
+// recent [B, cap] with recent_len [B] (in/out, oldest first) and window_len [B] (how many recent tokens sequence i
+// keeps, at most cap), scratch [2 * B * cap] ints for this loop's tables.
 // field_uniform / field_begin / field_count: word offsets of those fields in a record.
 extern "C" int lp_decode_loop_sampled(cudaGraphExec_t graph, cudaStream_t stream, int* meta, int tokens_at,
                                       int positions_at, int lengths_at, int* blob, int record_words, int field_uniform,
                                       int field_begin, int field_count, int cap, const int* sampled, int B,
                                       int max_steps, const int* quiet, const int* stop_ids, const int* stop_begin,
                                       unsigned long long* rng_state, const int* draws, const double* penalty,
-                                      int* recent, int* recent_len, int* scratch, int* out, int* steps_run) {
+                                      int* recent, int* recent_len, const int* window_len, int* scratch, int* out,
+                                      int* steps_run) {
     *steps_run = 0;
     if (B <= 0 || max_steps <= 0) return 0;
     if (!graph || !meta || !blob || !sampled || !quiet || !stop_begin || !out || !rng_state || !draws || !penalty ||
-        !recent || !recent_len || !scratch)
+        !recent || !recent_len || !window_len || !scratch)
         LP_REFUSE("decode_loop_sampled: a null argument");
     if (B > 4096) LP_REFUSE("decode_loop_sampled: %d sequences", B);
     static Window windows[4096];
     for (int i = 0; i < B; ++i) {
         Window& w = windows[i];
-        w.recent = recent + (size_t)i * cap; w.len = recent_len[i]; w.max_len = cap;
+        w.recent = recent + (size_t)i * cap; w.len = recent_len[i]; w.max_len = window_len[i];
+        if (w.max_len < 1 || w.max_len > cap) LP_REFUSE("decode_loop_sampled: a window of %d tokens (capacity %d)", w.max_len, cap);
         w.tok = scratch + (size_t)i * cap; w.cnt = scratch + (size_t)(B + i) * cap; w.distinct = 0;
-        if (w.len > cap) LP_REFUSE("decode_loop_sampled: %d recent tokens for a window of %d", w.len, cap);
+        if (w.len > w.max_len) LP_REFUSE("decode_loop_sampled: %d recent tokens for a window of %d", w.len, w.max_len);
         if (penalty[i] != 1.0) for (int j = 0; j < w.len; ++j) window_add(w, w.recent[j]);
     }
     int* edit_tok = blob + (size_t)B * record_words;

@@ -480,8 +480,9 @@ class Engine:
         penalty = np.asarray([float(smp.config.repetition_penalty) for smp in samplers], dtype=np.float64)
         recent = np.zeros((B, cap), dtype=np.int32)
         recent_len = np.zeros(B, dtype=np.int32)
+        window = np.asarray([smp.max_recent for smp in samplers], dtype=np.int32)
         for i, smp in enumerate(samplers):
-            kept = smp.recent[-cap:]
+            kept = smp.recent[-smp.max_recent:]
             recent[i, :len(kept)] = kept
             recent_len[i] = len(kept)
         scratch = np.zeros(2 * B * cap, dtype=np.int32)
@@ -493,7 +494,7 @@ class Engine:
             draw["host"].data_ptr(), draw["record_words"], draw["field_uniform"], draw["field_begin"],
             draw["field_count"], cap, landing.data_ptr(), B, steps, quiet_arr.ctypes.data, stop_arr.ctypes.data,
             begin.ctypes.data, rng.ctypes.data, draws.ctypes.data, penalty.ctypes.data, recent.ctypes.data,
-            recent_len.ctypes.data, scratch.ctypes.data, out.ctypes.data, ctypes.byref(ran))
+            recent_len.ctypes.data, window.ctypes.data, scratch.ctypes.data, out.ctypes.data, ctypes.byref(ran))
         for i, smp in enumerate(samplers):                   # what ran, ran: the samplers go on from there
             smp.rng._state = int(rng[i])
             smp.recent = recent[i, :int(recent_len[i])].tolist()

@@ -57,7 +57,7 @@ _SIGNATURES = {
     "host_loop": {
         "lp_decode_loop": [_P, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P],
         "lp_decode_loop_sampled": [_P, _P, _P, _I, _I, _I, _P, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P, _P, _P, _P, _P,
-                                   _P, _P, _P, _P, _P],
+                                   _P, _P, _P, _P, _P, _P],
     },
     "sampling": {
         "lp_sample": [_P, ctypes.c_longlong, _P, _I, _P, _I, _P, _P, _P, _P, _P, _P, _P],

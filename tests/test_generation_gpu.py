@@ -151,8 +151,8 @@ def test_native_loop_with_samplers_equals_stepping_from_python(tmp_path):
     generator and its window of recent tokens kept by csrc/host_loop.cu, the sampler block fetched inside the
     captured step) must give, token for token, what ``Engine.step`` + ``Engine.sample`` give from the interpreter:
     same seeds, unequal prompts and budgets, a greedy row with a penalty among them, a stop token on the way, and
-    a second call that continues with the samplers' state (seeds differ per request, so a generator that was
-    advanced wrongly shows)."""
+    and one sequence whose window of recent tokens is 64 long, so that its oldest tokens leave the window on the
+    way (seeds differ per request, so a generator that was advanced wrongly shows)."""
     from llmplayer_b200 import Engine, SamplerConfig
     from llmplayer_b200.engine.generate import GenerationRequest
     model_dir = make_model(tmp_path, "C", dtype="bfloat16")
@@ -160,7 +160,8 @@ def test_native_loop_with_samplers_equals_stepping_from_python(tmp_path):
     configs = [SamplerConfig(temperature=0.8, top_k=20, top_p=0.9, repetition_penalty=1.3, seed=11),
                SamplerConfig(temperature=1.1, top_k=0, top_p=1.0, repetition_penalty=1.0, seed=12),
                SamplerConfig(temperature=0.0, top_k=1, top_p=1.0, repetition_penalty=1.2, seed=13),
-               SamplerConfig(temperature=0.7, top_k=40, top_p=0.9, repetition_penalty=1.1, seed=14, min_p=0.02)]
+               SamplerConfig(temperature=0.7, top_k=40, top_p=0.9, repetition_penalty=1.5, seed=14, min_p=0.02,
+                             dry_range=64)]
     fast = Engine.load(model_dir, dtype="bfloat16", context_length=512, max_batch=4)
     slow = Engine.load(model_dir, dtype="bfloat16", context_length=512, max_batch=4, host_loop=False)
 
@@ -168,8 +169,8 @@ def test_native_loop_with_samplers_equals_stepping_from_python(tmp_path):
         return [GenerationRequest(p, max_tokens=m, sampler_config=c, stop_token_ids=stop)
                 for p, m, c in zip(prompts, budgets, configs)]
 
-    ref = slow.generate(requests((90, 91, 70, 40)))
-    got = fast.generate(requests((90, 91, 70, 40)))
+    ref = slow.generate(requests((90, 91, 70, 150)))
+    got = fast.generate(requests((90, 91, 70, 150)))
     assert any(e.get("graph") is not None for e in fast._fused.values()), "the captured step never ran"
     assert any(len(k) > 4 and k[4] == "sampled" for k in fast._fused), "the sampled form of the captured step never ran"
     for r, g in zip(ref, got):
